@@ -1,0 +1,416 @@
+// C ABI of the library: argument checks, then the launch sequence of one policy forward.
+//
+// The sequence restates NotePolicy._forward_stacked (python/policy.py:1198-1344) as a fixed
+// list of kernel launches on the caller's stream, with every intermediate in the caller's
+// workspace; nothing here allocates, frees or synchronises, so the whole call can be captured
+// in a CUDA graph next to the simulator's step kernel (python/rollout_graph.py:45-74).
+#include <string.h>
+
+#include "kernels.cuh"
+#include "layout.h"
+
+namespace bsrl {
+const char* last_error();
+
+namespace {
+
+inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+template <typename T>
+inline T* at(void* base, int64_t off) {
+  return reinterpret_cast<T*>(static_cast<uint8_t*>(base) + off);
+}
+template <typename T>
+inline const T* at(const void* base, int64_t off) {
+  return reinterpret_cast<const T*>(static_cast<const uint8_t*>(base) + off);
+}
+
+// engine choice for one linear layer: tcgen05 where the shape fits, warp-MMA otherwise
+int linear(const LinearArgs& p, cudaStream_t st) {
+  if (linear_tc5_ok(p)) return linear_tc5(p, st);
+  return linear_mma(p, st);
+}
+
+struct Ctx {
+  const bsrl_config* cfg;
+  Layout l;
+  Workspace w;
+  const void* arena;
+  void* ws;
+  int64_t B;
+  cudaStream_t st;
+  const __half* W(const Mat& m, int row0 = 0) const { return at<__half>(arena, m.w) + (int64_t)row0 * m.pitch; }
+  const float* Bv(const Mat& m, int row0 = 0) const { return at<float>(arena, m.b) + row0; }
+  const float* G(const Norm& n) const { return at<float>(arena, n.g); }
+  const float* Be(const Norm& n) const { return at<float>(arena, n.b); }
+};
+
+#define BSRL_TRY(expr)             \
+  do {                             \
+    int rc__ = (expr);             \
+    if (rc__ != BSRL_OK) return rc__; \
+  } while (0)
+
+// obs -> x (B*29, d) f32 + key bias
+int run_embed(const Ctx& c, const void* obs, int obs_dtype, float* x, float* key_bias) {
+  const Layout& l = c.l;
+  const Workspace& w = c.w;
+  const int d = l.d;
+  const int64_t B = c.B;
+  EmbedBuffers eb;
+  eb.saber = at<__half>(c.ws, w.f_saber);
+  eb.torso = at<__half>(c.ws, w.f_torso);
+  eb.leg = at<__half>(c.ws, w.f_leg);
+  eb.note = at<__half>(c.ws, w.f_note);
+  eb.key_bias = key_bias;
+  eb.ks = kSaberK; eb.kt = kTorsoK; eb.kl = kLegK; eb.kn = l.note_k;
+  BSRL_TRY(embed_gather(obs, obs_dtype, B, c.cfg->note_geo, c.cfg->z_asinh, eb, c.st));
+  __half* hid = at<__half>(c.ws, w.enc_hid);
+  struct Part { const Encoder* e; const __half* f; int kpad; int64_t rows; int64_t row0; int group; int first; };
+  const Part parts[4] = {
+      {&l.saber, eb.saber, kSaberK, 2 * B, 0, 2, 0},
+      {&l.torso, eb.torso, kTorsoK, B, 2 * B, 1, 2},
+      {&l.leg, eb.leg, kLegK, 2 * B, 3 * B, 2, 3},
+      {&l.note, eb.note, l.note_k, (int64_t)kSlots * B, 5 * B, kSlots, kLead},
+  };
+  for (const Part& p : parts) {
+    __half* hp = hid + p.row0 * d;
+    LinearArgs a0 = linear_args(p.f, p.kpad, c.W(p.e->l0), p.e->l0.pitch, c.Bv(p.e->l0), hp, d, 0, 1,
+                                p.rows, d, p.kpad);
+    BSRL_TRY(linear(a0, c.st));
+    LinearArgs a1 = linear_args(hp, d, c.W(p.e->l1), p.e->l1.pitch, c.Bv(p.e->l1), x, d, 1, 0, p.rows, d, d);
+    a1.cmap = RowMap{p.group, kT, p.first};
+    BSRL_TRY(linear(a1, c.st));
+  }
+  return BSRL_OK;
+}
+
+int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs& tail_in) {
+  const Layout& l = c.l;
+  const Workspace& w = c.w;
+  const int d = l.d, F = l.F, D = l.D;
+  const int64_t B = c.B, R = B * kT, Rl = B * kLead;
+  const float eps = c.cfg->eps;
+  float* x = at<float>(c.ws, w.x);
+  float* key_bias = at<float>(c.ws, w.key_bias);
+  __half* h = at<__half>(c.ws, w.h);
+  __half* qkv = at<__half>(c.ws, w.qkv);
+  __half* att = at<__half>(c.ws, w.att);
+  __half* hid = at<__half>(c.ws, w.hid);
+  const RowMap lead_rows{kLead, kT, 0};
+  const RowMap ident = identity_map();
+
+  BSRL_TRY(run_embed(c, obs, obs_dtype, x, key_bias));
+
+  for (int i = 0; i + 1 < l.L; ++i) {
+    const BlockW& b = l.blocks[i];
+    BSRL_TRY(layernorm_rows(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
+    BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, R, 3 * d, d), c.st));
+    BSRL_TRY(attention29(qkv, 3 * d, key_bias, B, d, l.H, 0, kT, att, d, c.st));
+    LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x, d, 1, 0, R, d, d);
+    po.R = x; po.ldr = d;
+    BSRL_TRY(linear(po, c.st));
+    BSRL_TRY(layernorm_rows(x, d, ident, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, R, d, h, d, c.st));
+    BSRL_TRY(linear(linear_args(h, d, c.W(b.up), d, c.Bv(b.up), hid, F, 0, 1, R, F, d), c.st));
+    LinearArgs pd = linear_args(hid, F, c.W(b.down), F, c.Bv(b.down), x, d, 1, 0, R, d, F);
+    pd.R = x; pd.ldr = d;
+    BSRL_TRY(linear(pd, c.st));
+  }
+
+  // final block: keys/values over all 29 rows, everything else on the 5 lead rows
+  float* x_lead = at<float>(c.ws, w.x_lead);
+  __half* h_lead = at<__half>(c.ws, w.h_lead);
+  __half* lead16 = at<__half>(c.ws, w.lead16);
+  {
+    const BlockW& b = l.blocks[l.L - 1];
+    BSRL_TRY(layernorm_rows(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
+    BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv, d), d, c.Bv(b.qkv, d), qkv + d, 3 * d, 0, 0, R, 2 * d, d), c.st));
+    LinearArgs pq = linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, Rl, d, d);
+    pq.amap = lead_rows;
+    pq.cmap = lead_rows;
+    BSRL_TRY(linear(pq, c.st));
+    BSRL_TRY(attention29(qkv, 3 * d, key_bias, B, d, l.H, 0, kLead, att, d, c.st));
+    LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x_lead, d, 1, 0, Rl, d, d);
+    po.R = x; po.ldr = d; po.rmap = lead_rows;
+    BSRL_TRY(linear(po, c.st));
+    BSRL_TRY(layernorm_rows(x_lead, d, ident, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, Rl, d, h_lead, d, c.st));
+    BSRL_TRY(linear(linear_args(h_lead, d, c.W(b.up), d, c.Bv(b.up), hid, F, 0, 1, Rl, F, d), c.st));
+    LinearArgs pd = linear_args(hid, F, c.W(b.down), F, c.Bv(b.down), lead16, d, 0, 0, Rl, d, F);
+    pd.R = x_lead; pd.ldr = d;
+    BSRL_TRY(linear(pd, c.st));
+  }
+
+  // SimBa trunk on the (B, 5d) readout; its output h lands in z[:, d:]
+  float* xt = at<float>(c.ws, w.xt);
+  __half* u = at<__half>(c.ws, w.u);
+  __half* r = at<__half>(c.ws, w.r);
+  __half* z = at<__half>(c.ws, w.z);
+  const int ldz = d + D;
+  BSRL_TRY(linear(linear_args(lead16, kLead * d, c.W(l.trunk_proj), kLead * d, c.Bv(l.trunk_proj), xt, D, 1, 0, B, D, kLead * d), c.st));
+  BSRL_TRY(layernorm_rows(xt, D, ident, c.G(l.trunk_ln1), c.Be(l.trunk_ln1), eps, B, D, u, D, c.st));
+  BSRL_TRY(linear(linear_args(u, D, c.W(l.trunk_fc1), D, c.Bv(l.trunk_fc1), r, l.Hh, 0, 1, B, l.Hh, D), c.st));
+  {
+    LinearArgs p2 = linear_args(r, l.Hh, c.W(l.trunk_fc2), l.Hh, c.Bv(l.trunk_fc2), xt, D, 1, 0, B, D, l.Hh);
+    p2.R = xt; p2.ldr = D;
+    BSRL_TRY(linear(p2, c.st));
+  }
+  BSRL_TRY(layernorm_rows(xt, D, ident, c.G(l.trunk_ln2), c.Be(l.trunk_ln2), eps, B, D, z + d, ldz, c.st));
+  float* raw = at<float>(c.ws, w.raw);
+  BSRL_TRY(linear(linear_args(z + d, ldz, c.W(l.heads), D, c.Bv(l.heads), raw, l.head_cols_pad, 1, 0, B, l.head_cols_pad, D), c.st));
+
+  // adapool critic over the resolved stream entering the final block (still in x)
+  __half* att_c = at<__half>(c.ws, w.att_c);
+  __half* m1 = at<__half>(c.ws, w.m1);
+  __half* m2 = at<__half>(c.ws, w.m2);
+  float* vraw = at<float>(c.ws, w.vraw);
+  {
+    const RowMap torso_rows{1, kT, 2};
+    BSRL_TRY(layernorm_rows(x, d, ident, c.G(l.critic_ln), c.Be(l.critic_ln), eps, R, d, h, d, c.st));
+    BSRL_TRY(linear(linear_args(h, d, c.W(l.critic_kv), d, c.Bv(l.critic_kv), qkv + d, 3 * d, 0, 0, R, 2 * d, d), c.st));
+    LinearArgs pq = linear_args(h, d, c.W(l.critic_q), d, c.Bv(l.critic_q), qkv, 3 * d, 0, 0, B, d, d);
+    pq.amap = torso_rows;
+    pq.cmap = torso_rows;
+    BSRL_TRY(linear(pq, c.st));
+    BSRL_TRY(attention29(qkv, 3 * d, key_bias, B, d, l.H, 2, 1, att_c, d, c.st));
+    BSRL_TRY(linear(linear_args(att_c, d, c.W(l.critic_out), d, c.Bv(l.critic_out), z, ldz, 0, 0, B, d, d), c.st));
+    BSRL_TRY(linear(linear_args(z, ldz, c.W(l.critic_m0), ldz, c.Bv(l.critic_m0), m1, D, 0, 1, B, D, ldz), c.st));
+    BSRL_TRY(linear(linear_args(m1, D, c.W(l.critic_m1), D, c.Bv(l.critic_m1), m2, D, 0, 1, B, D, D), c.st));
+    BSRL_TRY(linear(linear_args(m2, D, c.W(l.critic_m2), D, c.Bv(l.critic_m2), vraw, l.bins_pad, 1, 0, B, l.bins_pad, D), c.st));
+  }
+
+  HeadTailArgs t = tail_in;
+  t.raw = raw; t.ld_raw = l.head_cols_pad;
+  t.vraw = vraw; t.ld_v = l.bins_pad;
+  t.bins = l.bins; t.vmax = c.cfg->value_vmax; t.k_max = l.k_max;
+  for (int j = 0; j < kActHeads; ++j) {
+    t.gears[j] = c.cfg->head_gears[j];
+    t.first[j] = l.head_first[j];
+  }
+  t.n_envs = B;
+  return head_tail(t, c.st);
+}
+
+int make_ctx(Ctx& c, const bsrl_config* cfg, const void* arena, int64_t n_envs, void* ws,
+             int64_t ws_bytes, void* stream) {
+  BSRL_TRY(validate_config(cfg));
+  if (!arena || !ws) {
+    set_error("forward: NULL arena or workspace");
+    return BSRL_ERR_NULL;
+  }
+  if (n_envs < 0 || n_envs > (int64_t)1 << 26) {
+    set_error("forward: n_envs %lld out of range", (long long)n_envs);
+    return BSRL_ERR_SHAPE;
+  }
+  if ((reinterpret_cast<uintptr_t>(arena) & 255) || (reinterpret_cast<uintptr_t>(ws) & 255)) {
+    set_error("forward: arena and workspace must be 256-byte aligned");
+    return BSRL_ERR_ALIGN;
+  }
+  c.cfg = cfg;
+  c.l = make_layout(*cfg);
+  c.w = make_workspace(c.l, n_envs);
+  if (ws_bytes < c.w.bytes) {
+    set_error("forward: workspace %lld bytes < required %lld", (long long)ws_bytes, (long long)c.w.bytes);
+    return BSRL_ERR_WORKSPACE;
+  }
+  c.arena = arena;
+  c.ws = ws;
+  c.B = n_envs;
+  c.st = as_stream(stream);
+  return BSRL_OK;
+}
+
+}  // namespace
+}  // namespace bsrl
+
+using namespace bsrl;
+
+extern "C" {
+
+int bsrl_abi_version(void) { return BSRL_ABI_VERSION; }
+const char* bsrl_last_error(void) { return bsrl::last_error(); }
+int bsrl_config_validate(const bsrl_config* cfg) { return validate_config(cfg); }
+
+int64_t bsrl_mac_per_env(const bsrl_config* cfg) {
+  if (validate_config(cfg) != BSRL_OK) return -1;
+  Layout l = make_layout(*cfg);
+  const int64_t d = l.d, T = kT, ld = kLead, D = l.D, Hh = l.Hh, f = cfg->ffn_mult;
+  int64_t enc = d * (kSlots * l.note_in + 2 * (kSaberFeat + 2) + kTorsoFeat + 2 * (kLegFeat + 2)) + T * d * d;
+  int64_t blk = (4 + 2 * f) * T * d * d + 2 * T * T * d;
+  int64_t last = 2 * T * d * d + (2 + 2 * f) * ld * d * d + 2 * ld * T * d;
+  int64_t tr = ld * d * D + 2 * D * Hh;
+  int64_t heads = D * l.n_head_cols;
+  int64_t cr = 2 * T * d * d + 2 * d * d + 2 * T * d + (d + D) * D + D * D + l.bins * D;
+  return enc + (l.L - 1) * blk + last + tr + heads + cr;
+}
+
+int32_t bsrl_param_count(const bsrl_config* cfg) {
+  if (validate_config(cfg) != BSRL_OK) return -1;
+  Layout l = make_layout(*cfg);
+  return (int32_t)make_param_slots(*cfg, l).size();
+}
+
+int bsrl_param_desc(const bsrl_config* cfg, int32_t i, char* name, int32_t name_cap, int64_t* rows,
+                    int64_t* cols) {
+  BSRL_TRY(validate_config(cfg));
+  Layout l = make_layout(*cfg);
+  std::vector<ParamSlot> s = make_param_slots(*cfg, l);
+  if (i < 0 || i >= (int32_t)s.size()) {
+    set_error("param_desc: index %d out of range [0, %d)", i, (int)s.size());
+    return BSRL_ERR_SHAPE;
+  }
+  if (name && name_cap > 0) {
+    strncpy(name, s[i].name.c_str(), name_cap - 1);
+    name[name_cap - 1] = 0;
+  }
+  if (rows) *rows = s[i].rows;
+  if (cols) *cols = s[i].cols;
+  return BSRL_OK;
+}
+
+int64_t bsrl_weights_bytes(const bsrl_config* cfg) {
+  if (validate_config(cfg) != BSRL_OK) return -1;
+  return make_layout(*cfg).bytes;
+}
+
+int bsrl_pack_weights(const bsrl_config* cfg, const float* const* params, int32_t n_params, void* arena,
+                      int64_t arena_bytes, void* stream) {
+  BSRL_TRY(validate_config(cfg));
+  Layout l = make_layout(*cfg);
+  std::vector<ParamSlot> s = make_param_slots(*cfg, l);
+  if (!params || !arena) {
+    set_error("pack_weights: NULL argument");
+    return BSRL_ERR_NULL;
+  }
+  if (n_params != (int32_t)s.size()) {
+    set_error("pack_weights: %d parameters given, %d expected", n_params, (int)s.size());
+    return BSRL_ERR_SHAPE;
+  }
+  if (arena_bytes < l.bytes) {
+    set_error("pack_weights: arena %lld bytes < required %lld", (long long)arena_bytes, (long long)l.bytes);
+    return BSRL_ERR_WORKSPACE;
+  }
+  if (reinterpret_cast<uintptr_t>(arena) & 255) {
+    set_error("pack_weights: arena must be 256-byte aligned");
+    return BSRL_ERR_ALIGN;
+  }
+  for (int32_t i = 0; i < n_params; ++i)
+    if (!params[i]) {
+      set_error("pack_weights: parameter %d (%s) is NULL", i, s[i].name.c_str());
+      return BSRL_ERR_NULL;
+    }
+  cudaStream_t st = as_stream(stream);
+  // padding columns / rows of the stacked matrices must read as zero
+  BSRL_CUDA_OK(cudaMemsetAsync(arena, 0, l.bytes, st));
+  for (int32_t i = 0; i < n_params; ++i) {
+    const ParamSlot& p = s[i];
+    if (p.half)
+      BSRL_TRY(pack_cast(params[i], p.rows, p.cols, at<__half>(arena, p.dst), p.dst_pitch, st));
+    else
+      BSRL_TRY(pack_copy(params[i], p.rows, at<float>(arena, p.dst), st));
+  }
+  return BSRL_OK;
+}
+
+int64_t bsrl_workspace_bytes(const bsrl_config* cfg, int64_t n_envs) {
+  if (validate_config(cfg) != BSRL_OK) return -1;
+  if (n_envs < 0) return -1;
+  Layout l = make_layout(*cfg);
+  return make_workspace(l, n_envs).bytes;
+}
+
+int bsrl_forward(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
+                 int64_t n_envs, float* logits, float* value, float* value_logits, void* workspace,
+                 int64_t workspace_bytes, void* stream) {
+  Ctx c;
+  BSRL_TRY(make_ctx(c, cfg, arena, n_envs, workspace, workspace_bytes, stream));
+  if (!obs || !logits || !value) {
+    set_error("forward: NULL obs / logits / value");
+    return BSRL_ERR_NULL;
+  }
+  if (n_envs == 0) return BSRL_OK;
+  HeadTailArgs t;
+  memset(&t, 0, sizeof(t));
+  t.logits = logits;
+  t.value = value;
+  t.value_logits = value_logits;
+  return run_forward(c, obs, obs_dtype, t);
+}
+
+int bsrl_forward_act(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
+                     int64_t n_envs, const void* actions, int32_t act_dtype, float* logits,
+                     float* logprob, float* entropy, float* ent_head, float* value, float* value_logits,
+                     void* workspace, int64_t workspace_bytes, void* stream) {
+  Ctx c;
+  BSRL_TRY(make_ctx(c, cfg, arena, n_envs, workspace, workspace_bytes, stream));
+  if (!obs || !actions || !logprob || !value) {
+    set_error("forward_act: NULL obs / actions / logprob / value");
+    return BSRL_ERR_NULL;
+  }
+  if (act_dtype != BSRL_U8 && act_dtype != BSRL_I32 && act_dtype != BSRL_I64) {
+    set_error("forward_act: actions must be u8, i32 or i64");
+    return BSRL_ERR_UNSUPPORTED;
+  }
+  if (n_envs == 0) return BSRL_OK;
+  HeadTailArgs t;
+  memset(&t, 0, sizeof(t));
+  t.actions = actions;
+  t.act_dtype = act_dtype;
+  t.logits = logits;
+  t.logprob = logprob;
+  t.entropy = entropy;
+  t.ent_head = ent_head;
+  t.value = value;
+  t.value_logits = value_logits;
+  return run_forward(c, obs, obs_dtype, t);
+}
+
+int32_t bsrl_token_lane(int32_t tok, int32_t k) { return token_lane_host(tok, k); }
+
+int bsrl_embed(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
+               int64_t n_envs, float* x, float* key_bias, void* workspace, int64_t workspace_bytes,
+               void* stream) {
+  Ctx c;
+  BSRL_TRY(make_ctx(c, cfg, arena, n_envs, workspace, workspace_bytes, stream));
+  if (!obs || !x || !key_bias) {
+    set_error("embed: NULL obs / x / key_bias");
+    return BSRL_ERR_NULL;
+  }
+  if (!aligned16(x)) {
+    set_error("embed: x must be 16-byte aligned");
+    return BSRL_ERR_ALIGN;
+  }
+  if (n_envs == 0) return BSRL_OK;
+  return run_embed(c, obs, obs_dtype, x, key_bias);
+}
+
+int bsrl_layernorm(const float* x, const float* gamma, const float* beta, float eps, int64_t rows,
+                   int32_t d, void* y_f16, int64_t ldy, void* stream) {
+  return layernorm_rows(x, d, identity_map(), gamma, beta, eps, rows, d, static_cast<__half*>(y_f16), ldy,
+                        as_stream(stream));
+}
+
+int bsrl_linear(const void* a_f16, const void* w_f16, const float* bias, const float* residual, void* out,
+                int32_t out_f32, int32_t relu, int64_t m, int32_t n, int32_t k, int32_t engine,
+                void* stream) {
+  LinearArgs p = linear_args(static_cast<const __half*>(a_f16), k, static_cast<const __half*>(w_f16), k, bias,
+                             out, n, out_f32, relu, m, n, k);
+  p.R = residual;
+  p.ldr = n;
+  if (engine == 0) return linear_mma(p, as_stream(stream));
+  if (engine == 1) {
+    if (!linear_tc5_ok(p)) {
+      set_error("linear: shape m=%lld n=%d k=%d does not fit the tcgen05 engine", (long long)m, n, k);
+      return BSRL_ERR_UNSUPPORTED;
+    }
+    return linear_tc5(p, as_stream(stream));
+  }
+  set_error("linear: engine must be 0 (warp-MMA) or 1 (tcgen05)");
+  return BSRL_ERR_UNSUPPORTED;
+}
+
+int bsrl_attention(const void* qkv_f16, const float* key_bias, int64_t n_envs, int32_t d, int32_t n_heads,
+                   int32_t q_first, int32_t n_q, void* out_f16, void* stream) {
+  return attention29(static_cast<const __half*>(qkv_f16), 3 * d, key_bias, n_envs, d, n_heads, q_first, n_q,
+                     static_cast<__half*>(out_f16), d, as_stream(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,203 @@
+// Masked multi-head self-attention over the 29 tokens of one environment.
+//
+// One warp owns one (env, head) pair: it stages that head's q, k, v slices (29 x head_dim
+// fp16 each) in its private shared-memory tile, computes the 32 x 32 score tile with
+// m16n8k16 MMAs, runs the softmax in fp32 on the accumulator fragments (row statistics by
+// quad shuffles) and feeds the probabilities straight back as the A operand of the P V MMAs.
+// Scores never leave registers.  The additive key bias (0 or -16384) makes masked keys'
+// probabilities exactly 0; the three pad keys (29..31) are forced to -inf.
+//
+// Reference: attn29_fwd_kernel (python/beat_arena_env/csrc/small_attn.cu:228-332) and the
+// fp32 arithmetic it is checked against, softmax(q k^T / sqrt(dh) + bias) v
+// (python/policy.py:686-690).  The kernel is not tied to (T, d, H) = (29, 192, 4): head_dim
+// 32, 48 or 64, any head count.
+#include "kernels.cuh"
+
+namespace bsrl {
+namespace {
+constexpr int kWarps = 8;
+constexpr int kRows = 32;  // 29 tokens padded to two 16-row MMA tiles / four 8-key tiles
+
+template <int DH>
+__global__ void __launch_bounds__(kWarps * 32) attn29_kernel(const __half* __restrict__ qkv, int ld,
+                                                            const float* __restrict__ key_bias,
+                                                            int64_t n_pairs, int d, int n_heads,
+                                                            int q_first, int n_q,
+                                                            __half* __restrict__ out, int ldo) {
+  constexpr int LDS = DH + 8;          // padded row (halfs): ldmatrix rows land in distinct banks
+  constexpr int CH = DH / 8;           // 16-byte chunks per row
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __half* sq = reinterpret_cast<__half*>(smem) + (size_t)warp * 3 * kRows * LDS;
+  __half* sk = sq + kRows * LDS;
+  __half* sv = sk + kRows * LDS;
+  const uint32_t sq_u = smem_u32(sq), sk_u = smem_u32(sk), sv_u = smem_u32(sv);
+  const float scale = rsqrtf(static_cast<float>(DH));
+  const int g = lane >> 2, tig = lane & 3;
+  const int m_tiles = (n_q + 15) >> 4;
+
+  for (int64_t pair = (int64_t)blockIdx.x * kWarps + warp; pair < n_pairs;
+       pair += (int64_t)gridDim.x * kWarps) {
+    const int64_t env = pair / n_heads;
+    const int head = static_cast<int>(pair % n_heads);
+    const __half* base = qkv + env * kT * (int64_t)ld + head * DH;
+    __syncwarp();
+    // stage q (query rows), k, v; rows past the live range are zero
+    for (int c = lane; c < kRows * CH; c += 32) {
+      int row = c / CH, ch = c % CH;
+      uint4 zq = make_uint4(0, 0, 0, 0), zk = zq, zv = zq;
+      if (row < n_q)
+        zq = *reinterpret_cast<const uint4*>(base + (int64_t)(q_first + row) * ld + ch * 8);
+      if (row < kT) {
+        const __half* r = base + (int64_t)row * ld + ch * 8;
+        zk = *reinterpret_cast<const uint4*>(r + d);
+        zv = *reinterpret_cast<const uint4*>(r + 2 * d);
+      }
+      *reinterpret_cast<uint4*>(sq + row * LDS + ch * 8) = zq;
+      *reinterpret_cast<uint4*>(sk + row * LDS + ch * 8) = zk;
+      *reinterpret_cast<uint4*>(sv + row * LDS + ch * 8) = zv;
+    }
+    // key bias of the 8 key columns this lane sees: keys nt*8 + tig*2 + {0,1}
+    float kb[4][2];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        int key = nt * 8 + tig * 2 + e;
+        kb[nt][e] = key < kT ? key_bias[env * kT + key] : -INFINITY;
+      }
+    __syncwarp();
+
+    for (int mt = 0; mt < m_tiles; ++mt) {
+      float s[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < DH / 16; ++ks) {
+        uint32_t a[4];
+        ldmatrix_x4(a, sq_u + ((mt * 16 + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8) * 2);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          uint32_t b[4];
+          int row = j * 16 + (lane & 7) + ((lane >> 4) << 3);
+          ldmatrix_x4(b, sk_u + (row * LDS + ks * 16 + ((lane >> 3) & 1) * 8) * 2);
+          mma_f16(s[2 * j], a, b[0], b[1]);
+          mma_f16(s[2 * j + 1], a, b[2], b[3]);
+        }
+      }
+      // softmax over keys for rows g (e = 0,1) and g + 8 (e = 2,3)
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s[nt][e] = s[nt][e] * scale + kb[nt][e & 1];
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+        }
+      float sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      }
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s[nt][e] = expf(s[nt][e] - mx[e >> 1]);
+          sum[e >> 1] += s[nt][e];
+        }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+        sum[r] = 1.f / sum[r];
+      }
+      // P (normalised, fp16) as the A operand of P V
+      uint32_t pa[2][4];
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        pa[ks][0] = pack_half2(s[2 * ks][0] * sum[0], s[2 * ks][1] * sum[0]);
+        pa[ks][1] = pack_half2(s[2 * ks][2] * sum[1], s[2 * ks][3] * sum[1]);
+        pa[ks][2] = pack_half2(s[2 * ks + 1][0] * sum[0], s[2 * ks + 1][1] * sum[0]);
+        pa[ks][3] = pack_half2(s[2 * ks + 1][2] * sum[1], s[2 * ks + 1][3] * sum[1]);
+      }
+      float o[DH / 8][4];
+#pragma unroll
+      for (int nt = 0; nt < DH / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+        for (int j = 0; j < DH / 16; ++j) {
+          uint32_t b[4];
+          int row = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          ldmatrix_x4_trans(b, sv_u + (row * LDS + j * 16 + (lane >> 4) * 8) * 2);
+          mma_f16(o[2 * j], pa[ks], b[0], b[1]);
+          mma_f16(o[2 * j + 1], pa[ks], b[2], b[3]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        int qrow = mt * 16 + g + r * 8;
+        if (qrow < n_q) {
+          __half* orow = out + (env * n_q + qrow) * (int64_t)ldo + head * DH + tig * 2;
+#pragma unroll
+          for (int nt = 0; nt < DH / 8; ++nt)
+            *reinterpret_cast<uint32_t*>(orow + nt * 8) = pack_half2(o[nt][r * 2], o[nt][r * 2 + 1]);
+        }
+      }
+    }
+  }
+}
+
+template <int DH>
+int launch(const __half* qkv, int ld, const float* key_bias, int64_t n_envs, int d, int n_heads,
+           int q_first, int n_q, __half* out, int ldo, cudaStream_t stream) {
+  constexpr int smem = kWarps * 3 * kRows * (DH + 8) * 2;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  BSRL_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    BSRL_CUDA_OK(cudaFuncSetAttribute(attn29_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set[dev] = true;
+  }
+  int64_t pairs = n_envs * n_heads;
+  int64_t blocks = (pairs + kWarps - 1) / kWarps;
+  int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  attn29_kernel<DH><<<static_cast<unsigned>(blocks), kWarps * 32, smem, stream>>>(
+      qkv, ld, key_bias, pairs, d, n_heads, q_first, n_q, out, ldo);
+  BSRL_LAUNCH_OK("attn29_kernel");
+  return BSRL_OK;
+}
+}  // namespace
+
+int attention29(const __half* qkv, int ld_qkv, const float* key_bias, int64_t n_envs, int d,
+                int n_heads, int q_first, int n_q, __half* out, int ldo, cudaStream_t stream) {
+  if (!qkv || !key_bias || !out) {
+    set_error("attention: NULL operand");
+    return BSRL_ERR_NULL;
+  }
+  if (n_envs < 0 || n_heads <= 0 || d % n_heads != 0 || q_first < 0 || n_q < 1 ||
+      q_first + n_q > kT || ld_qkv < 3 * d || ldo < d) {
+    set_error("attention: bad shape d=%d heads=%d q=[%d,%d)", d, n_heads, q_first, q_first + n_q);
+    return BSRL_ERR_SHAPE;
+  }
+  if (!aligned16(qkv) || !aligned16(out) || (ld_qkv % 8) || (ldo % 8) || (d % 8)) {
+    set_error("attention: buffers must be 16-byte aligned, leading dimensions %% 8 == 0");
+    return BSRL_ERR_ALIGN;
+  }
+  if (n_envs == 0) return BSRL_OK;
+  const int dh = d / n_heads;
+  if (dh == 32) return launch<32>(qkv, ld_qkv, key_bias, n_envs, d, n_heads, q_first, n_q, out, ldo, stream);
+  if (dh == 48) return launch<48>(qkv, ld_qkv, key_bias, n_envs, d, n_heads, q_first, n_q, out, ldo, stream);
+  if (dh == 64) return launch<64>(qkv, ld_qkv, key_bias, n_envs, d, n_heads, q_first, n_q, out, ldo, stream);
+  set_error("attention: head_dim %d unsupported (32, 48 or 64)", dh);
+  return BSRL_ERR_UNSUPPORTED;
+}
+
+}  // namespace bsrl

@@ -1,0 +1,181 @@
+// Tokenizer: one obs row (630 lanes) -> fp16 input rows of the four token encoders + key bias.
+//
+// One warp per environment.  The obs row is staged in shared memory once (coalesced), then
+// scattered through a constant lane table into K-padded fp16 rows: 2 saber rows (47 lanes +
+// hand one-hot), 1 torso row (29), 2 leg rows (32 + side one-hot), 24 slot rows (18 lanes, plus
+// the 22 hand-relative geometry lanes when note_geo is on, computed here in fp32).  Pure
+// streaming: 2,520 B read per env, ~2-4 KB written.
+//
+// Reference: NotePolicy._split (python/policy.py:1099-1105), the one-hot / concat code at
+// :1226-1249, _note_geo (:329-404) and the key bias (:1257-1260).
+#include "kernels.cuh"
+#include "obs_layout.h"
+
+namespace bsrl {
+namespace {
+
+struct LaneTable {
+  int16_t v[5][64];  // >= 0 obs lane, -1 zero, -2 one
+};
+constexpr LaneTable make_lane_table() {
+  LaneTable t{};
+  for (int tok = 0; tok < 5; ++tok)
+    for (int k = 0; k < 64; ++k) {
+      int lane = token_lane(tok, k);
+      int v = lane;
+      if (lane < 0) {
+        int oh = k - kTokenFeat[tok];
+        v = (kTokenOneHot[tok] >= 0 && oh == kTokenOneHot[tok]) ? -2 : -1;
+      }
+      t.v[tok][k] = static_cast<int16_t>(v);
+    }
+  return t;
+}
+__constant__ LaneTable c_lanes = make_lane_table();
+constexpr LaneTable h_lanes = make_lane_table();
+
+constexpr int kWarps = 8;
+
+__device__ __forceinline__ float tab(const float* o, int tok, int k) {
+  int l = c_lanes.v[tok][k];
+  return l >= 0 ? o[l] : (l == -2 ? 1.f : 0.f);
+}
+
+// 22 geometry lanes of one slot (standard game): per hand 7, then per hand 4.
+__device__ void slot_geometry(const float* o, int slot, float z_asinh, float* out) {
+  const float XN = 1.0f, YN = 0.75f, ZS = 8.0f, VN = 6.0f, HANDLE = 0.16f;
+  const float* n = o + kOffNotes + slot * kNoteFeat;
+  const float z_m = sinhf(n[2]) * z_asinh;
+  const float px = n[0] * XN, py = n[1] * YN, pz = z_m;
+  const float cx = n[6], cy = n[7];
+  const float live = 1.0f - n[14];
+  const float speed = fmaxf(-n[3] * ZS, 1e-3f);
+  const float zrel = z_m - o[kObsHeadZ] * XN;
+  const float tpl = fminf(fmaxf(zrel / speed, -0.5f), 3.0f) / 3.0f;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float wx = tab(o, h, 15) * XN, wy = tab(o, h, 16) * YN, wz = tab(o, h, 17);
+    const float mx = px - wx, my = py - wy, mz = pz - wz;  // metres
+    const float dx = mx * 0.5f, dy = my * 0.5f, dz = mz * 0.5f;
+    const float dist = sqrtf(dx * dx + dy * dy + dz * dz);
+    const float vx = tab(o, h, 18) * VN, vy = tab(o, h, 19) * VN, vz = tab(o, h, 20) * VN;
+    const float vn = sqrtf(vx * vx + vy * vy + vz * vz) + 0.05f;
+    const float bx = tab(o, h, 21), by = tab(o, h, 22), bz = tab(o, h, 23);
+    float* f = out + h * 7;
+    f[0] = dx;
+    f[1] = dy;
+    f[2] = asinhf(dz * 2.0f / 8.0f);
+    f[3] = asinhf(dist * 2.0f / 8.0f);
+    f[4] = tpl;
+    f[5] = ((vx / vn) * cx + (vy / vn) * cy) * live;
+    f[6] = (bx * cx + by * cy) * live;
+    const float ab = mx * bx + my * by + mz * bz;
+    const float rx = mx - ab * bx, ry = my - ab * by, rz = mz - ab * bz;
+    const float tx = tab(o, h, 44), ty = tab(o, h, 45), tz = tab(o, h, 46);
+    const float ux = tx * VN, uy = ty * VN, uz = tz * VN;
+    const float nx = by * uz - bz * uy, ny = bz * ux - bx * uz, nz = bx * uy - by * ux;
+    const float nn = sqrtf(nx * nx + ny * ny + nz * nz) + 0.05f;
+    float* s = out + 14 + h * 4;
+    s[0] = asinhf((ab - HANDLE) * 0.5f);
+    s[1] = asinhf(sqrtf(rx * rx + ry * ry + rz * rz) * 0.5f);
+    s[2] = asinhf((mx * (nx / nn) + my * (ny / nn) + mz * (nz / nn)) * 0.5f);
+    s[3] = (tx * cx + ty * cy) * live;
+  }
+}
+
+template <bool OBS_F16>
+__global__ void __launch_bounds__(kWarps * 32) embed_gather_kernel(const void* __restrict__ obs_,
+                                                                  int64_t n_envs, int note_geo,
+                                                                  float z_asinh, EmbedBuffers out) {
+  __shared__ float s_obs[kWarps][kObs + 2];
+  __shared__ float s_geo[kWarps][kSlots * kGeoFeat];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* o = s_obs[warp];
+  float* geo = s_geo[warp];
+  for (int64_t env = (int64_t)blockIdx.x * kWarps + warp; env < n_envs;
+       env += (int64_t)gridDim.x * kWarps) {
+    __syncwarp();
+    if (OBS_F16) {
+      const __half* src = static_cast<const __half*>(obs_) + env * kObs;
+      for (int i = lane; i < kObs; i += 32) o[i] = __half2float(src[i]);
+    } else {
+      const float* src = static_cast<const float*>(obs_) + env * kObs;
+      for (int i = lane; i < kObs; i += 32) o[i] = src[i];
+    }
+    __syncwarp();
+    if (note_geo && lane < kSlots) slot_geometry(o, lane, z_asinh, geo + lane * kGeoFeat);
+    // lead tokens: lane writes features 2*lane, 2*lane + 1
+    {
+      const int k = lane * 2;
+      uint32_t* d;
+      d = reinterpret_cast<uint32_t*>(out.saber + (env * 2 + 0) * out.ks);
+      d[lane] = pack_half2(tab(o, 0, k), tab(o, 0, k + 1));
+      d = reinterpret_cast<uint32_t*>(out.saber + (env * 2 + 1) * out.ks);
+      d[lane] = pack_half2(tab(o, 1, k), tab(o, 1, k + 1));
+      d = reinterpret_cast<uint32_t*>(out.leg + (env * 2 + 0) * out.kl);
+      d[lane] = pack_half2(tab(o, 3, k), tab(o, 3, k + 1));
+      d = reinterpret_cast<uint32_t*>(out.leg + (env * 2 + 1) * out.kl);
+      d[lane] = pack_half2(tab(o, 4, k), tab(o, 4, k + 1));
+      if (lane < out.kt / 2) {
+        d = reinterpret_cast<uint32_t*>(out.torso + env * out.kt);
+        d[lane] = pack_half2(tab(o, 2, k), tab(o, 2, k + 1));
+      }
+    }
+    __syncwarp();
+    // slot rows
+    {
+      const int kn = out.kn, kn2 = kn >> 1;
+      uint32_t* d = reinterpret_cast<uint32_t*>(out.note + env * kSlots * kn);
+      for (int i = lane; i < kSlots * kn2; i += 32) {
+        int slot = i / kn2, k = (i % kn2) * 2;
+        float v[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          int kk = k + e;
+          v[e] = kk < kNoteFeat ? o[kOffNotes + slot * kNoteFeat + kk]
+                 : (note_geo && kk < kNoteFeat + kGeoFeat) ? geo[slot * kGeoFeat + kk - kNoteFeat]
+                                                            : 0.f;
+        }
+        d[i] = pack_half2(v[0], v[1]);
+      }
+    }
+    if (lane < kT)
+      out.key_bias[env * kT + lane] = lane < kLead ? 0.f : (o[kOffMask + lane - kLead] - 1.0f) * kMaskBias;
+  }
+}
+}  // namespace
+
+int token_lane_host(int tok, int k) {
+  if (tok < 0 || tok >= 5 || k < 0 || k >= kTokenFeat[tok]) return -1;
+  return h_lanes.v[tok][k];
+}
+
+int embed_gather(const void* obs, int obs_dtype, int64_t n_envs, int note_geo, float z_asinh,
+                 const EmbedBuffers& out, cudaStream_t stream) {
+  if (!obs || !out.saber || !out.torso || !out.leg || !out.note || !out.key_bias) {
+    set_error("embed: NULL operand");
+    return BSRL_ERR_NULL;
+  }
+  if (obs_dtype != BSRL_F32 && obs_dtype != BSRL_F16) {
+    set_error("embed: obs must be f32 or f16");
+    return BSRL_ERR_UNSUPPORTED;
+  }
+  if (out.ks != kSaberK || out.kl != kLegK || out.kt != kTorsoK || out.kn != note_k(note_geo != 0)) {
+    set_error("embed: feature pitches do not match the encoder layout");
+    return BSRL_ERR_SHAPE;
+  }
+  if (n_envs <= 0) return n_envs == 0 ? BSRL_OK : BSRL_ERR_SHAPE;
+  int64_t blocks = (n_envs + kWarps - 1) / kWarps;
+  int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (obs_dtype == BSRL_F16)
+    embed_gather_kernel<true><<<static_cast<unsigned>(blocks), kWarps * 32, 0, stream>>>(
+        obs, n_envs, note_geo, z_asinh, out);
+  else
+    embed_gather_kernel<false><<<static_cast<unsigned>(blocks), kWarps * 32, 0, stream>>>(
+        obs, n_envs, note_geo, z_asinh, out);
+  BSRL_LAUNCH_OK("embed_gather_kernel");
+  return BSRL_OK;
+}
+
+}  // namespace bsrl

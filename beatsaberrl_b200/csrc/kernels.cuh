@@ -1,0 +1,82 @@
+// Host-side launchers of every kernel in the library (one translation unit each).
+#pragma once
+#include "common.cuh"
+
+namespace bsrl {
+
+// C = act(A W^T + bias) (+ R).  A (M, K) f16 and W (N, K) f16, both K-contiguous.
+struct LinearArgs {
+  const __half* A;
+  int lda;
+  RowMap amap;
+  const __half* W;
+  int ldw;
+  const float* bias;   // (N) or nullptr
+  const float* R;      // residual f32 or nullptr
+  int ldr;
+  RowMap rmap;
+  void* C;             // f16 or f32
+  int ldc;
+  RowMap cmap;
+  int out_f32;
+  int relu;
+  int64_t M;
+  int N, K;
+};
+LinearArgs linear_args(const __half* A, int lda, const __half* W, int ldw, const float* bias,
+                       void* C, int ldc, int out_f32, int relu, int64_t M, int N, int K);
+
+int linear_mma(const LinearArgs& p, cudaStream_t stream);   // warp-MMA engine
+int linear_tc5(const LinearArgs& p, cudaStream_t stream);   // tcgen05 / TMEM engine
+bool linear_tc5_ok(const LinearArgs& p);                     // shape fits the tcgen05 engine
+
+// y(f16, ldy) = LayerNorm(x(f32, ldx)) per row, fp32 statistics.
+int layernorm_rows(const float* x, int64_t ldx, RowMap xmap, const float* gamma, const float* beta,
+                   float eps, int64_t rows, int d, __half* y, int64_t ldy, cudaStream_t stream);
+
+// Tokenizer: obs -> per-encoder fp16 feature rows + additive key bias.
+struct EmbedBuffers {
+  __half* saber;  // (2B, ks)
+  __half* torso;  // (B, kt)
+  __half* leg;    // (2B, kl)
+  __half* note;   // (24B, kn)
+  float* key_bias;  // (B, 29)
+  int ks, kt, kl, kn;
+};
+int embed_gather(const void* obs, int obs_dtype, int64_t n_envs, int note_geo, float z_asinh,
+                 const EmbedBuffers& out, cudaStream_t stream);
+int token_lane_host(int tok, int k);
+
+// Masked MHA over the 29 keys of each env.
+int attention29(const __half* qkv, int ld_qkv, const float* key_bias, int64_t n_envs, int d,
+                int n_heads, int q_first, int n_q, __half* out, int ldo, cudaStream_t stream);
+
+// Head tail: masked-lane fill, log-softmax, log-prob of given actions, entropy; HL-Gauss value.
+struct HeadTailArgs {
+  const float* raw;      // (B, ld_raw) packed head outputs, bias included
+  int ld_raw;
+  const float* vraw;     // (B, ld_v) value-bin logits
+  int ld_v;
+  int bins;
+  float vmax;
+  int k_max;
+  int gears[kActHeads];
+  int first[kActHeads];  // first packed column of each head
+  const void* actions;   // (B, 29) or nullptr
+  int act_dtype;
+  float* logits;         // (B, 29, k_max) or nullptr
+  float* logprob;        // (B) or nullptr
+  float* entropy;        // (B) or nullptr
+  float* ent_head;       // (B, 29) or nullptr
+  float* value;          // (B)
+  float* value_logits;   // (B, bins) or nullptr
+  int64_t n_envs;
+};
+int head_tail(const HeadTailArgs& a, cudaStream_t stream);
+
+// f32 -> f16 cast with row pitch (weight packing), and plain f32 copy.
+int pack_cast(const float* src, int64_t rows, int64_t cols, __half* dst, int64_t dst_pitch,
+              cudaStream_t stream);
+int pack_copy(const float* src, int64_t n, float* dst, cudaStream_t stream);
+
+}  // namespace bsrl

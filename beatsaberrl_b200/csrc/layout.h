@@ -1,0 +1,65 @@
+// Byte layout of the packed weight arena and of the forward workspace (host only).
+//
+// The arena is this library's form of the reference's flat fp16 replica buffer
+// (flatten_fp16_replicas, python/fp16_linear.py:220-427): fp16 GEMM operands in nn.Linear's
+// (out, in) layout -- K-contiguous, which is what both MMA engines want for the B operand --
+// with q|k|v, the critic's k|v and the 29 heads stacked into single matrices, first-layer
+// encoder weights K-padded with zero columns, and fp32 biases / LayerNorm parameters.
+#pragma once
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "obs_layout.h"
+
+namespace bsrl {
+
+struct Mat {          // fp16 (rows, pitch) matrix + fp32 bias(rows) in the arena
+  int64_t w = 0, b = 0;
+  int rows = 0, cols = 0, pitch = 0;
+};
+struct Norm {         // fp32 gamma, beta
+  int64_t g = 0, b = 0;
+  int width = 0;
+};
+struct BlockW {
+  Norm ln_attn, ln_ffn;
+  Mat qkv, out, up, down;
+};
+struct Encoder {
+  Mat l0, l1;
+};
+
+struct Layout {
+  int d, H, L, F, D, Hh, bins, bins_pad, k_max, n_head_cols, head_cols_pad, note_in, note_k;
+  Encoder note, saber, torso, leg;
+  std::vector<BlockW> blocks;
+  Mat trunk_proj, trunk_fc1, trunk_fc2, heads;
+  Norm trunk_ln1, trunk_ln2, critic_ln;
+  Mat critic_q, critic_kv, critic_out, critic_m0, critic_m1, critic_m2;
+  int head_first[kActHeads];
+  int64_t bytes = 0;
+};
+
+// One fp32 master parameter and where it lands in the arena.
+struct ParamSlot {
+  std::string name;
+  int64_t rows, cols;      // master shape (cols = 1 for vectors)
+  int64_t dst;             // byte offset in the arena
+  int64_t dst_pitch;       // elements per destination row (fp16 matrices); 0 for fp32 vectors
+  bool half;
+};
+
+int validate_config(const bsrl_config* c);
+Layout make_layout(const bsrl_config& c);
+std::vector<ParamSlot> make_param_slots(const bsrl_config& c, const Layout& l);
+
+// Workspace carve-up for a batch of n_envs.
+struct Workspace {
+  int64_t key_bias, f_saber, f_torso, f_leg, f_note, enc_hid, x, h, qkv, att, hid;
+  int64_t x_lead, h_lead, lead16, xt, u, r, z, m1, m2, raw, vraw, att_c;
+  int64_t bytes;
+};
+Workspace make_workspace(const Layout& l, int64_t n_envs);
+
+}  // namespace bsrl

@@ -1,0 +1,306 @@
+"""``NotePolicy`` with the reference's surface, running the forward on the sm_100a kernels.
+
+Mirrors the part of the reference's ``python/policy.py`` that callers of the policy-forward
+path touch (``train_batch.py`` rollout and PPO recompute, ``rollout_graph.py``,
+``cuda_graphs.py`` style graph drivers, the forward benches):
+
+* constructor keywords and checks           -- ``NotePolicy.__init__``, python/policy.py:795-850
+* parameter names / ``state_dict`` layout    -- python/policy.py:940-1067 (a reference checkpoint's
+  ``state_dict`` loads with ``load_state_dict`` unchanged)
+* ``forward_stacked`` / ``forward`` / ``get_action_and_value`` -- python/policy.py:1179-1196,
+  :1463-1516
+* ``flatten_fp16`` / ``refresh_fp16_caches`` and the module-level ``bump_weights_version`` --
+  python/policy.py:1405-1461, python/fp16_linear.py:241-246: here they repack the fp32 masters
+  into the packed fp16 arena IN PLACE, so storages captured in a CUDA graph stay valid.
+
+The fp32 parameters are the masters (trainable by any optimizer); the forward itself is
+inference-only (no autograd graph is built).  There is no torch or CPU fallback: a CPU tensor,
+or a missing ``libbsrl.so``, raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+import torch.nn as nn
+
+from . import _native as nat
+
+OBS_DIM = 630
+N_NOTE_SLOTS = 24
+NOTE_FEAT = 18
+OFF_NOTES = 102
+OFF_NOTE_MASK = OFF_NOTES + N_NOTE_SLOTS * NOTE_FEAT
+SABER_FEAT, TORSO_FEAT, LEG_FEAT = 47, 29, 32
+NOTE_GEO_FEAT = 22
+N_ACTION_HEADS = 29
+MASK_BIAS = 16384.0
+MASKED_LOGIT = -1e9
+TRUNK_ARCHS = ("simba", "simbav2")
+ACCUM_MODES = ("off", "fwd", "all")
+FFN_MODES = ("off", "on", "up16", "up16dn16")
+
+_weights_version = 0
+
+
+def bump_weights_version() -> None:
+    """Tell every policy that the fp32 masters changed (call after ``optimizer.step()``); the
+    next forward, or ``refresh_fp16_caches()``, repacks the fp16 arena in place.
+    Same role as ``fp16_linear.bump_weights_version`` (python/fp16_linear.py:241-246)."""
+    global _weights_version
+    _weights_version += 1
+
+
+def _mlp(sizes):
+    layers = []
+    for i in range(len(sizes) - 1):
+        layers.append(nn.Linear(sizes[i], sizes[i + 1]))
+        if i < len(sizes) - 2:
+            layers.append(nn.ReLU())
+    return nn.Sequential(*layers)
+
+
+class _Block(nn.Module):
+    """Parameter holder of one pre-LN block (names as python/policy.py:498-507)."""
+
+    def __init__(self, d: int, ffn_mult: int):
+        super().__init__()
+        self.ln_attn = nn.LayerNorm(d)
+        self.q_proj = nn.Linear(d, d)
+        self.k_proj = nn.Linear(d, d)
+        self.v_proj = nn.Linear(d, d)
+        self.out_proj = nn.Linear(d, d)
+        self.ln_ffn = nn.LayerNorm(d)
+        self.ffn = _mlp([d, ffn_mult * d, d])
+
+
+_ACT_DTYPES = {torch.uint8: nat.U8, torch.int32: nat.I32, torch.int64: nat.I64}
+
+
+class NotePolicy(nn.Module):
+    def __init__(self, embed: int = 128, trunk_dim: int = 256, encoder: str = "transformer",
+                 n_blocks: int = 3, n_heads: int = 4, n_gears: int = 3, ffn_mult: int = 4,
+                 note_geo: bool = False, value_bins: int = 101, value_vmax: float = 6.0,
+                 value_sigma: float = 0.75, trunk_hidden: int | None = None, z_asinh: float = 8.0,
+                 game: str = "standard", fp16_accum: str = "off", fused_ffn: str = "off",
+                 emb_ln: bool = False, value_residual: bool = False, final_ln: bool = False,
+                 trunk_arch: str = "simba", head_gears: tuple | list | None = None):
+        super().__init__()
+        if trunk_arch not in TRUNK_ARCHS:
+            raise ValueError(f"trunk_arch must be one of {TRUNK_ARCHS}, got {trunk_arch!r}")
+        if game not in ("standard", "flux"):
+            raise ValueError(f"game must be 'standard' or 'flux', got {game!r}")
+        if not float(z_asinh) > 0:
+            raise ValueError(f"z_asinh must be > 0 (metres), got {z_asinh}")
+        if fp16_accum not in ACCUM_MODES:
+            raise ValueError(f"fp16_accum must be one of {ACCUM_MODES}, got {fp16_accum!r}")
+        if fused_ffn not in FFN_MODES:
+            raise ValueError(f"fused_ffn must be one of {FFN_MODES}, got {fused_ffn!r}")
+        assert encoder == "transformer", f"unknown encoder: {encoder}"
+        assert n_gears in (3, 5, 7), f"n_gears must be 3/5/7, got {n_gears}"
+        assert value_bins > 1, f"value_bins must be > 1, got {value_bins}"
+        # options of the reference that change the forward and are not built here
+        for flag, name in ((emb_ln, "emb_ln"), (value_residual, "value_residual"),
+                           (final_ln, "final_ln"), (trunk_arch != "simba", "trunk_arch='simbav2'"),
+                           (game != "standard", "game='flux'"),
+                           (fp16_accum != "off", "fp16_accum (accumulation is always fp32)")):
+            if flag:
+                raise NotImplementedError(f"NotePolicy option {name} is not built in this library")
+        if head_gears is None:
+            head_gears = (n_gears,) * N_ACTION_HEADS
+        head_gears = tuple(int(k) for k in head_gears)
+        assert len(head_gears) == N_ACTION_HEADS and all(3 <= k <= 7 for k in head_gears), (
+            f"head_gears must be {N_ACTION_HEADS} counts in [3, 7], got {head_gears}")
+        self.encoder, self.embed, self.n_heads, self.n_gears = encoder, embed, n_heads, n_gears
+        self.head_sizes = head_gears
+        self.k_max = max(head_gears)
+        H = int(trunk_hidden) if trunk_hidden else trunk_dim
+        self.arch = {"embed": embed, "trunk_dim": trunk_dim, "n_blocks": n_blocks, "n_heads": n_heads,
+                     "n_gears": n_gears, "obs_dim": OBS_DIM, "ffn_mult": ffn_mult,
+                     "critic": "adapool_v1", "n_action_heads": N_ACTION_HEADS, "body_token": True,
+                     "body_tokens": 3, "note_geo": bool(note_geo), "note_geo_norm": True,
+                     "blade_geo": 1, "z_asinh": float(z_asinh), "trunk_arch": trunk_arch,
+                     "trunk_hidden": H, "value_bins": int(value_bins),
+                     "value_vmax": float(value_vmax), "value_sigma": float(value_sigma),
+                     "game": game, "fp16_accum": fp16_accum, "fused_ffn": fused_ffn,
+                     "emb_ln": False, "value_residual": False, "final_ln": False}
+        if head_gears != (n_gears,) * N_ACTION_HEADS:
+            self.arch["head_gears"] = list(head_gears)
+        self.value_bins = int(value_bins)
+        self.value_sigma_bins = float(value_sigma)
+        centers = torch.linspace(-float(value_vmax), float(value_vmax), self.value_bins)
+        self.register_buffer("value_centers", centers, persistent=False)
+        self.value_sigma = float(value_sigma) * float(centers[1] - centers[0])
+        self.note_geo, self.z_asinh, self.game = bool(note_geo), float(z_asinh), game
+        self.body_tokens, self.n_lead = 3, 5
+        # fp32 masters, created in the reference's order so a seeded init draws the same stream
+        self.note_mlp = _mlp([NOTE_FEAT + (NOTE_GEO_FEAT if note_geo else 0), embed, embed])
+        self.saber_mlp = _mlp([SABER_FEAT + 2, embed, embed])
+        self.torso_mlp = _mlp([TORSO_FEAT, embed, embed])
+        self.leg_mlp = _mlp([LEG_FEAT + 2, embed, embed])
+        self.blocks = nn.ModuleList(_Block(embed, ffn_mult) for _ in range(n_blocks))
+        self.trunk_arch = trunk_arch
+        self.trunk_proj = nn.Linear(self.n_lead * embed, trunk_dim)
+        self.trunk_ln1 = nn.LayerNorm(trunk_dim)
+        self.trunk_fc1 = nn.Linear(trunk_dim, H)
+        self.trunk_fc2 = nn.Linear(H, trunk_dim)
+        self.trunk_ln2 = nn.LayerNorm(trunk_dim)
+        self.heads = nn.ModuleList(nn.Linear(trunk_dim, n) for n in self.head_sizes)
+        self.critic_ln = nn.LayerNorm(embed)
+        self.critic_q = nn.Linear(embed, embed)
+        self.critic_k = nn.Linear(embed, embed)
+        self.critic_v = nn.Linear(embed, embed)
+        self.critic_out = nn.Linear(embed, embed)
+        self.critic_mlp = _mlp([embed + trunk_dim, trunk_dim, trunk_dim, self.value_bins])
+        # runtime state (plain attributes, not in state_dict)
+        self.fp16 = True            # the stream is always fp16 operands / fp32 accumulate here
+        self.fp16_accum = fp16_accum
+        self.fused_ffn = fused_ffn
+        self.upgraded_from = None
+        self._diag_stash = False
+        self._diag_h = None
+        self._ent_h = None
+        self._value_logits = None
+        self.keep_value_logits = False   # set True to have forwards fill _value_logits
+        self._cfg = nat.make_config(embed, n_heads, n_blocks, ffn_mult, trunk_dim, H, self.value_bins,
+                                    note_geo, head_gears, float(z_asinh), float(value_vmax),
+                                    float(self.blocks[0].ln_attn.eps))
+        nat.check(nat.lib.bsrl_config_validate(C.byref(self._cfg)))
+        self._param_table = nat.param_table(self._cfg)
+        self._arena = None
+        self._arena_version = None
+        self._workspaces = {}
+
+    # ------------------------------------------------------------------ weights
+    def _pack(self, force: bool = False) -> None:
+        dev = self.trunk_proj.weight.device
+        if dev.type != "cuda":
+            raise RuntimeError("NotePolicy runs on a CUDA device only (no CPU path): call .cuda() first")
+        key = (_weights_version, dev)
+        if not force and self._arena is not None and self._arena_version == key:
+            return
+        n_bytes = nat.lib.bsrl_weights_bytes(C.byref(self._cfg))
+        if self._arena is None or self._arena.device != dev:
+            self._arena = torch.empty(n_bytes, dtype=torch.uint8, device=dev)
+        sd = dict(self.named_parameters())
+        ptrs = (C.c_void_p * len(self._param_table))()
+        keep = []
+        for i, (name, rows, cols) in enumerate(self._param_table):
+            p = sd[name].detach()
+            assert p.dtype is torch.float32 and p.numel() == rows * cols, name
+            p = p.contiguous()
+            keep.append(p)
+            ptrs[i] = p.data_ptr()
+        with torch.cuda.device(dev):
+            nat.check(nat.lib.bsrl_pack_weights(C.byref(self._cfg), ptrs, len(keep),
+                                                self._arena.data_ptr(), n_bytes,
+                                                torch.cuda.current_stream().cuda_stream))
+        self._arena_version = key
+
+    def flatten_fp16(self) -> None:
+        """Build the packed fp16 arena now (call once before CUDA-graph capture)."""
+        self._pack(force=True)
+
+    def refresh_fp16_caches(self) -> None:
+        """Repack the arena in place from the current fp32 masters (after optimizer steps;
+        a captured graph keeps reading the same storage)."""
+        self._pack(force=True)
+
+    def _workspace(self, B: int, dev):
+        ws = self._workspaces.get((B, dev))
+        if ws is None:
+            n = nat.lib.bsrl_workspace_bytes(C.byref(self._cfg), B)
+            ws = torch.empty(max(n, 256), dtype=torch.uint8, device=dev)
+            self._workspaces = {(B, dev): ws}      # keep one batch size resident
+        return ws
+
+    @staticmethod
+    def _obs_dtype(obs):
+        if obs.dtype is torch.float32:
+            return nat.F32
+        if obs.dtype is torch.float16:
+            return nat.F16
+        raise TypeError(f"obs must be float32 or float16, got {obs.dtype}")
+
+    def _check_obs(self, obs):
+        if not obs.is_cuda:
+            raise RuntimeError("obs must live on a CUDA device (this library has no CPU path)")
+        if obs.dim() != 2 or obs.shape[1] != OBS_DIM:
+            raise ValueError(f"obs must be (B, {OBS_DIM}), got {tuple(obs.shape)}")
+        return obs.contiguous()
+
+    # ------------------------------------------------------------------ forward
+    @torch.no_grad()
+    def forward_stacked(self, obs: torch.Tensor):
+        """obs (B, 630) -> stacked logits (B, 29, k_max) fp32 + the critic's value (B,) fp32."""
+        obs = self._check_obs(obs)
+        self._pack()
+        B, dev = obs.shape[0], obs.device
+        logits = torch.empty(B, N_ACTION_HEADS, self.k_max, dtype=torch.float32, device=dev)
+        value = torch.empty(B, dtype=torch.float32, device=dev)
+        vl = (torch.empty(B, self.value_bins, dtype=torch.float32, device=dev)
+              if self.keep_value_logits else None)
+        ws = self._workspace(B, dev)
+        with torch.cuda.device(dev):
+            nat.check(nat.lib.bsrl_forward(
+                C.byref(self._cfg), self._arena.data_ptr(), obs.data_ptr(), self._obs_dtype(obs), B,
+                logits.data_ptr(), value.data_ptr(), vl.data_ptr() if vl is not None else None,
+                ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream))
+        self._value_logits = vl
+        return logits, value
+
+    def forward(self, obs: torch.Tensor):
+        logits, value = self.forward_stacked(obs)
+        return list(logits.unbind(1)), value
+
+    @torch.no_grad()
+    def get_action_and_value(self, obs, action=None, need_entropy=True):
+        """With ``action`` given (the PPO recompute call) the log-softmax, the summed log-prob
+        and the entropy come out of the fused head kernel.  With ``action=None`` the action is
+        sampled by Gumbel-max on the log-softmax with torch's default generator, as the
+        reference does (python/policy.py:1475-1490)."""
+        if action is None:
+            logits, value = self.forward_stacked(obs)
+            logsm = torch.log_softmax(logits, dim=-1)
+            g = torch.empty_like(logsm).exponential_()
+            score = logsm - g.log()
+            if min(self.head_sizes) < self.k_max:
+                score = score.masked_fill(logits < -1e8, -math.inf)
+            action = score.argmax(-1)
+            logprob = logsm.gather(-1, action.unsqueeze(-1)).squeeze(-1).sum(-1)
+            entropy = None
+            if need_entropy:
+                ent_h = -(logsm.exp() * logsm).sum(-1)
+                self._ent_h = ent_h
+                entropy = ent_h.sum(-1)
+            return action, logprob, entropy, value
+        obs = self._check_obs(obs)
+        self._pack()
+        B, dev = obs.shape[0], obs.device
+        if action.dtype not in _ACT_DTYPES:
+            action = action.long()
+        action = action.contiguous()
+        if tuple(action.shape) != (B, N_ACTION_HEADS) or action.device != dev:
+            raise ValueError(f"action must be ({B}, {N_ACTION_HEADS}) on {dev}")
+        f32 = dict(dtype=torch.float32, device=dev)
+        logprob, value = torch.empty(B, **f32), torch.empty(B, **f32)
+        entropy = torch.empty(B, **f32) if need_entropy else None
+        ent_h = torch.empty(B, N_ACTION_HEADS, **f32) if need_entropy else None
+        vl = torch.empty(B, self.value_bins, **f32) if self.keep_value_logits else None
+        ws = self._workspace(B, dev)
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        with torch.cuda.device(dev):
+            nat.check(nat.lib.bsrl_forward_act(
+                C.byref(self._cfg), self._arena.data_ptr(), obs.data_ptr(), self._obs_dtype(obs), B,
+                action.data_ptr(), _ACT_DTYPES[action.dtype], None, logprob.data_ptr(), ptr(entropy),
+                ptr(ent_h), value.data_ptr(), ptr(vl), ws.data_ptr(), ws.numel(),
+                torch.cuda.current_stream().cuda_stream))
+        if need_entropy:
+            self._ent_h = ent_h
+        self._value_logits = vl
+        return action, logprob, entropy, value
+
+    # ------------------------------------------------------------------ introspection
+    def mac_per_env(self) -> int:
+        return int(nat.lib.bsrl_mac_per_env(C.byref(self._cfg)))

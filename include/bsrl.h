@@ -1,0 +1,149 @@
+/*
+ * bsrl.h -- C ABI of the B200 policy-forward library (libbsrl.so).
+ *
+ * Every entry point takes plain pointers and sizes.  Device buffers are owned by the
+ * caller; the library never allocates or frees device memory and never synchronises
+ * the host with the device: work is enqueued on the stream passed in (a cudaStream_t
+ * passed as void*; NULL = the legacy default stream).  Return value: 0 on success, a
+ * negative bsrl_status otherwise, with a thread-local message behind bsrl_last_error().
+ * All argument checks happen on the host before the first launch.
+ *
+ * The entry points replace, for the policy-forward path, what the reference binds through
+ * its two pybind11 torch extensions and the torch library calls around them:
+ *   layer_norm_cuda {ln_fwd, ln_fwd_add}   python/beat_arena_env/csrc/layer_norm.cu:733-749
+ *   fp16_gemm {attn29_fwd, ffn_fused, linear_relu_aux, bias_relu_}
+ *                                          python/beat_arena_env/csrc/fp16_gemm.cu:535-566
+ *   torch.addmm / F.linear / SDPA on the fp16 stream      python/fp16_linear.py:134-181, :866-909
+ */
+#ifndef BSRL_H_
+#define BSRL_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BSRL_ABI_VERSION 1
+#define BSRL_OBS_DIM 630
+#define BSRL_N_TOKENS 29
+#define BSRL_N_LEAD 5
+#define BSRL_N_SLOTS 24
+#define BSRL_N_ACT_HEADS 29
+
+typedef enum bsrl_status {
+  BSRL_OK = 0,
+  BSRL_ERR_NULL = -1,        /* a required pointer is NULL */
+  BSRL_ERR_SHAPE = -2,       /* a size is out of range for the configuration */
+  BSRL_ERR_ALIGN = -3,       /* a pointer is not aligned as required (16 bytes) */
+  BSRL_ERR_WORKSPACE = -4,   /* workspace or arena smaller than the *_bytes() figure */
+  BSRL_ERR_UNSUPPORTED = -5, /* valid in the reference, not built here */
+  BSRL_ERR_CUDA = -6,        /* a CUDA call or launch failed */
+  BSRL_ERR_TIMEOUT = -7      /* a bounded device-side wait ran out */
+} bsrl_status;
+
+typedef enum bsrl_dtype {
+  BSRL_F32 = 0, BSRL_F16 = 1, BSRL_U8 = 2, BSRL_I32 = 3, BSRL_I64 = 4
+} bsrl_dtype;
+
+/* Shape of the network: the keyword arguments of the reference constructor that change
+ * the forward (NotePolicy.__init__, python/policy.py:795-806). */
+typedef struct bsrl_config {
+  int32_t embed;         /* d */
+  int32_t n_heads;       /* attention heads, head_dim = embed / n_heads in {32, 48, 64} */
+  int32_t n_blocks;      /* transformer blocks (>= 1); the last runs on the lead rows */
+  int32_t ffn_mult;      /* FFN hidden = ffn_mult * embed */
+  int32_t trunk_dim;     /* D */
+  int32_t trunk_hidden;  /* SimBa trunk hidden width */
+  int32_t value_bins;    /* HL-Gauss bins */
+  int32_t note_geo;      /* 1 = append the 22 hand-relative geometry lanes to each slot */
+  int32_t head_gears[BSRL_N_ACT_HEADS]; /* action ids per head, each in [3, 7] */
+  float z_asinh;         /* obs z encoding constant (metres) */
+  float value_vmax;      /* bin centres = linspace(-vmax, vmax, bins) */
+  float eps;             /* LayerNorm epsilon */
+} bsrl_config;
+
+/* --- library -------------------------------------------------------------------- */
+int bsrl_abi_version(void);
+const char* bsrl_last_error(void);
+
+/* Checks a configuration against what the kernels are built for.
+ * Mirrors the constructor checks at python/policy.py:808-850. */
+int bsrl_config_validate(const bsrl_config* cfg);
+
+/* Multiply-accumulates of one env-forward (dense over all 29 keys). */
+int64_t bsrl_mac_per_env(const bsrl_config* cfg);
+
+/* --- weights -------------------------------------------------------------------- *
+ * The packed arena plays the role of the reference's flat fp16 replica buffer
+ * (flatten_fp16_replicas / flat_refresh, python/fp16_linear.py:220-427;
+ * NotePolicy.flatten_fp16 / refresh_fp16_caches, python/policy.py:1405-1461):
+ * fp16 GEMM operands with q|k|v, critic k|v and the 29 heads stacked, fp32 biases and
+ * LayerNorm parameters.  Re-running bsrl_pack_weights refreshes it in place. */
+int32_t bsrl_param_count(const bsrl_config* cfg);
+/* i-th fp32 master in reference state_dict naming ("blocks.0.q_proj.weight", ...);
+ * rows x cols of the master (cols = 1 for vectors). */
+int bsrl_param_desc(const bsrl_config* cfg, int32_t i, char* name, int32_t name_cap,
+                    int64_t* rows, int64_t* cols);
+int64_t bsrl_weights_bytes(const bsrl_config* cfg);
+int bsrl_pack_weights(const bsrl_config* cfg, const float* const* params, int32_t n_params,
+                      void* arena, int64_t arena_bytes, void* stream);
+
+/* --- forward -------------------------------------------------------------------- */
+int64_t bsrl_workspace_bytes(const bsrl_config* cfg, int64_t n_envs);
+
+/* NotePolicy.forward_stacked (python/policy.py:1179-1344): obs (n_envs, 630) f32 or f16
+ * -> logits (n_envs, 29, k_max) f32 with -1e9 on lanes past a head's gear count, value
+ * (n_envs) f32.  value_logits (n_envs, value_bins) f32 is optional (NULL to skip): the
+ * reference keeps it as NotePolicy._value_logits (python/policy.py:1402). */
+int bsrl_forward(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
+                 int64_t n_envs, float* logits, float* value, float* value_logits,
+                 void* workspace, int64_t workspace_bytes, void* stream);
+
+/* NotePolicy.get_action_and_value with given actions (python/policy.py:1467-1516), the PPO
+ * recompute call: same forward, then log-softmax, summed log-prob of the given actions and
+ * entropy fused into the head kernel.  actions (n_envs, 29) u8 / i32 / i64.
+ * logits, entropy, ent_head (n_envs, 29) and value_logits may be NULL. */
+int bsrl_forward_act(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
+                     int64_t n_envs, const void* actions, int32_t act_dtype,
+                     float* logits, float* logprob, float* entropy, float* ent_head,
+                     float* value, float* value_logits,
+                     void* workspace, int64_t workspace_bytes, void* stream);
+
+/* --- single stages (unit tests and profiling) -------------------------------------- */
+
+/* Obs lane of feature k of lead token tok (0..4), or -1 past the token's width
+ * (index tables at python/policy.py:211-266). */
+int32_t bsrl_token_lane(int32_t tok, int32_t k);
+
+/* Tokenizer + four encoders: obs -> resolved token stream x (n_envs*29, d) f32 and additive
+ * key bias (n_envs, 29) f32 (python/policy.py:1198-1260). */
+int bsrl_embed(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
+               int64_t n_envs, float* x, float* key_bias,
+               void* workspace, int64_t workspace_bytes, void* stream);
+
+/* LayerNorm rows of x (rows, d) f32 -> y (rows, d) f16, fp32 statistics
+ * (FusedLayerNorm.forward, python/fused_ln.py:126-138). */
+int bsrl_layernorm(const float* x, const float* gamma, const float* beta, float eps,
+                   int64_t rows, int32_t d, void* y_f16, int64_t ldy, void* stream);
+
+/* y = act(a @ w^T + bias) (+ residual): a (m, k) f16 row-major, w (n, k) f16 row-major,
+ * bias (n) f32 or NULL, residual (m, n) f32 or NULL; out f16 (out_f32 = 0) or f32.
+ * k % 32 == 0, n % 8 == 0.  (fp16_linear / fp16_linear_relu, python/fp16_linear.py:633-641,
+ * :794-805.)  engine 0 = warp-MMA kernel, 1 = tcgen05/TMEM kernel (k % 64 == 0). */
+int bsrl_linear(const void* a_f16, const void* w_f16, const float* bias, const float* residual,
+                void* out, int32_t out_f32, int32_t relu, int64_t m, int32_t n, int32_t k,
+                int32_t engine, void* stream);
+
+/* Masked multi-head attention over 29 keys: qkv (n_envs*29, 3d) f16 packed [q|k|v],
+ * key_bias (n_envs, 29) f32, queries = token rows [q_first, q_first + n_q) of each env
+ * -> out (n_envs*n_q, d) f16 (attn29_fwd, python/beat_arena_env/csrc/small_attn.cu:515-536;
+ * reference arithmetic python/policy.py:686-690). */
+int bsrl_attention(const void* qkv_f16, const float* key_bias, int64_t n_envs, int32_t d,
+                   int32_t n_heads, int32_t q_first, int32_t n_q, void* out_f16, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BSRL_H_ */

@@ -1,0 +1,43 @@
+import os
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+os.environ.setdefault("PYTHONDONTWRITEBYTECODE", "1")
+
+REFERENCE = Path(os.environ.get("BSRL_REFERENCE", "/root/reference"))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    import torch
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session")
+def golden():
+    import numpy as np
+    return np.load(ROOT / "tests" / "golden" / "policy_golden.npz")
+
+
+@pytest.fixture(scope="session")
+def native():
+    """The ctypes binding; builds the library first if it is missing."""
+    lib = ROOT / "beatsaberrl_b200" / "_lib" / "libbsrl.so"
+    if not lib.exists():
+        from beatsaberrl_b200.build import build_library
+        build_library()
+    from beatsaberrl_b200 import _native
+    return _native

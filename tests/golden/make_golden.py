@@ -1,0 +1,93 @@
+"""Generates tests/golden/policy_golden.npz from the REFERENCE implementation.
+
+Run in a container that has the reference checkout (default /root/reference):
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+For each case the reference ``NotePolicy`` (python/policy.py) is built on the CPU from a seed,
+run in fp32 on a stored obs batch, and its outputs are stored: stacked logits, value, the value
+bin logits, and log-prob / entropy / per-head entropy for stored actions, plus a float64
+checksum of every parameter so a test can prove it rebuilt the same weights from the seed.
+The reference cannot travel to the GPU box; these vectors can.
+"""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+sys.path.insert(0, str(ROOT))
+from oracle import policy_oracle as po  # noqa: E402
+
+CASES = [
+    # name, config, note_geo, head_gears, xavier, weight seed, ln_jitter, B, padded, obs seed
+    ("tiny_plain", "tiny", False, None, False, 11, 0.0, 16, True, 21),
+    ("tiny_geo_mixed", "tiny", True, (5,) * 8 + (7,) + (5,) * 6 + (7,) + (5,) * 13, True, 12, 0.1, 16, True, 22),
+    ("cfg1", "cfg1", False, None, False, 0, 0.0, 8, False, 0),
+]
+
+
+def case_config(cfg_name, geo, hg):
+    cfg = po.named_config(cfg_name)
+    cfg.note_geo = geo
+    cfg.head_gears = hg
+    cfg.__post_init__()
+    return cfg
+
+
+def main():
+    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    sys.dont_write_bytecode = True
+    sys.path.insert(0, os.path.join(ref, "python"))
+    import policy as rp  # the reference module
+
+    out = {}
+    for name, cfg_name, geo, hg, xav, seed, jit, B, padded, oseed in CASES:
+        cfg = case_config(cfg_name, geo, hg)
+        torch.manual_seed(seed)
+        m = rp.NotePolicy(**cfg.ref_kwargs()).eval()
+        if xav:
+            for mod in m.modules():
+                if isinstance(mod, torch.nn.Linear):
+                    torch.nn.init.xavier_uniform_(mod.weight)
+                    torch.nn.init.zeros_(mod.bias)
+        if jit > 0:   # same LayerNorm perturbation the oracle's build_state_dict applies
+            sd = po.build_state_dict(cfg, seed, xavier=xav, ln_jitter=jit)
+            m.load_state_dict({k: sd[k] for k in m.state_dict()})
+        obs = po.make_obs(B, oseed, padded=padded)
+        act = po.make_actions(B, cfg, oseed + 1)
+        with torch.no_grad():
+            logits, value = m.forward_stacked(obs)
+            _, lp, ent, _ = m.get_action_and_value(obs, act)
+            ent_h = m._ent_h
+        with torch.enable_grad():
+            m.forward_stacked(obs)
+            vlogits = m._value_logits.detach()
+        out[f"{name}/obs"] = obs.numpy()
+        out[f"{name}/actions"] = act.numpy()
+        out[f"{name}/logits"] = logits.numpy()
+        out[f"{name}/value"] = value.numpy()
+        out[f"{name}/value_logits"] = vlogits.numpy()
+        out[f"{name}/logprob"] = lp.numpy()
+        out[f"{name}/entropy"] = ent.numpy()
+        out[f"{name}/ent_head"] = ent_h.numpy()
+        names = sorted(m.state_dict())
+        out[f"{name}/param_sums"] = np.array(
+            [[float(m.state_dict()[k].double().sum()), float(m.state_dict()[k].double().abs().sum())]
+             for k in names])
+        out[f"{name}/param_names"] = np.array(names)
+    # lane tables straight from the reference module
+    out["lanes/saber_l"] = np.array(rp._SABER_L_IDX)
+    out["lanes/saber_r"] = np.array(rp._SABER_R_IDX)
+    out["lanes/torso"] = np.array(rp._TORSO_IDX)
+    out["lanes/leg_l"] = np.array(rp._LEG_L_IDX)
+    out["lanes/leg_r"] = np.array(rp._LEG_R_IDX)
+    np.savez_compressed(HERE / "policy_golden.npz", **out)
+    print("wrote", HERE / "policy_golden.npz", sum(v.nbytes for v in out.values()), "bytes raw")
+
+
+if __name__ == "__main__":
+    main()
