@@ -71,6 +71,11 @@ _sig = {
     "bsrl_forward_act": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, C.c_int32, _P, _P, _P, _P, _P, _P,
                                    _P, C.c_int64, _P]),
     "bsrl_token_lane": (C.c_int32, [C.c_int32, C.c_int32]),
+    "bsrl_profile_enable": (C.c_int, [C.c_int32]),
+    "bsrl_profile_stage_count": (C.c_int32, []),
+    "bsrl_profile_stage_name": (C.c_char_p, [C.c_int32]),
+    "bsrl_profile_stage": (C.c_int, [C.c_int32, C.POINTER(C.c_double), C.POINTER(C.c_int64),
+                                     C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "bsrl_embed": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, _P, _P, C.c_int64, _P]),
     "bsrl_layernorm": (C.c_int, [_P, _P, _P, C.c_float, C.c_int64, C.c_int32, _P, C.c_int64, _P]),
     "bsrl_linear": (C.c_int, [_P, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
@@ -103,4 +108,17 @@ def param_table(cfg: Config):
     for i in range(n):
         check(lib.bsrl_param_desc(C.byref(cfg), i, buf, 128, C.byref(r), C.byref(c)))
         out.append((buf.value.decode(), r.value, c.value))
+    return out
+
+
+def profile_read():
+    """{stage: dict(ms, launches, flops, bytes)} accumulated since bsrl_profile_enable(1);
+    the caller synchronises the stream first."""
+    out = {}
+    for i in range(lib.bsrl_profile_stage_count()):
+        ms, n, fl, by = C.c_double(), C.c_int64(), C.c_double(), C.c_double()
+        check(lib.bsrl_profile_stage(i, C.byref(ms), C.byref(n), C.byref(fl), C.byref(by)))
+        if n.value:
+            out[lib.bsrl_profile_stage_name(i).decode()] = dict(ms=ms.value, launches=n.value,
+                                                                flops=fl.value, bytes=by.value)
     return out

@@ -6,6 +6,8 @@
 // in a CUDA graph next to the simulator's step kernel (python/rollout_graph.py:45-74).
 #include <string.h>
 
+#include <vector>
+
 #include "kernels.cuh"
 #include "layout.h"
 
@@ -24,10 +26,76 @@ inline const T* at(const void* base, int64_t off) {
   return reinterpret_cast<const T*>(static_cast<const uint8_t*>(base) + off);
 }
 
+// ---------------------------------------------------------------- stage profiler
+// Optional CUDA-event timing of every launch of a forward, grouped by stage.  Off by default
+// (a captured graph must not contain it); the benchmark switches it on to time the dominant
+// kernel live, on the stream the kernels run on.
+enum Stage { kStGather = 0, kStEncoder, kStLayerNorm, kStQkv, kStAttention, kStOutProj, kStFfnUp,
+             kStFfnDown, kStTrunk, kStCritic, kStHeadTail, kStCount };
+const char* const kStageNames[kStCount] = {"embed_gather", "encoder_gemm", "layernorm", "qkv_gemm",
+                                           "attention", "out_proj_gemm", "ffn_up_gemm", "ffn_down_gemm",
+                                           "trunk", "critic", "head_tail"};
+struct Profiler {
+  bool on = false;
+  struct Rec { int stage; cudaEvent_t e0, e1; double flops, bytes; };
+  std::vector<Rec> recs;
+  std::vector<cudaEvent_t> pool;
+  size_t used = 0;
+  cudaEvent_t get() {
+    if (used == pool.size()) {
+      cudaEvent_t e;
+      if (cudaEventCreate(&e) != cudaSuccess) return nullptr;
+      pool.push_back(e);
+    }
+    return pool[used++];
+  }
+  void reset() { recs.clear(); used = 0; }
+};
+Profiler g_prof;
+int g_stage = kStGather;   // stage label of the launches that follow
+
+double linear_bytes(const LinearArgs& p) {
+  double b = (double)p.M * p.K * 2 + (double)p.N * p.K * 2 + (double)p.M * p.N * (p.out_f32 ? 4 : 2);
+  if (p.R) b += (double)p.M * p.N * 4;
+  return b;
+}
+
+template <typename Fn>
+int timed(cudaStream_t st, double flops, double bytes, Fn&& fn) {
+  if (!g_prof.on) return fn();
+  cudaEvent_t e0 = g_prof.get(), e1 = g_prof.get();
+  if (!e0 || !e1) return fn();
+  cudaEventRecord(e0, st);
+  int rc = fn();
+  cudaEventRecord(e1, st);
+  g_prof.recs.push_back({g_stage, e0, e1, flops, bytes});
+  return rc;
+}
+
 // engine choice for one linear layer: tcgen05 where the shape fits, warp-MMA otherwise
 int linear(const LinearArgs& p, cudaStream_t st) {
-  if (linear_tc5_ok(p)) return linear_tc5(p, st);
-  return linear_mma(p, st);
+  return timed(st, 2.0 * p.M * p.N * p.K, linear_bytes(p), [&] {
+    if (linear_tc5_ok(p)) return linear_tc5(p, st);
+    return linear_mma(p, st);
+  });
+}
+int layernorm(const float* x, int64_t ldx, RowMap xmap, const float* g, const float* b, float eps,
+              int64_t rows, int d, __half* y, int64_t ldy, cudaStream_t st) {
+  int keep = g_stage;
+  if (g_stage != kStTrunk && g_stage != kStCritic) g_stage = kStLayerNorm;
+  int rc = timed(st, 0.0, (double)rows * d * 6, [&] { return layernorm_rows(x, ldx, xmap, g, b, eps, rows, d, y, ldy, st); });
+  g_stage = keep;
+  return rc;
+}
+int attention(const __half* qkv, int ld, const float* kb, int64_t B, int d, int H, int q0, int nq,
+              __half* out, int ldo, cudaStream_t st) {
+  int keep = g_stage;
+  if (g_stage != kStCritic) g_stage = kStAttention;
+  double fl = 4.0 * B * nq * kT * d;
+  double by = (double)B * (kT * 2 * d + nq * d * 2) * 2 + (double)B * kT * 4;
+  int rc = timed(st, fl, by, [&] { return attention29(qkv, ld, kb, B, d, H, q0, nq, out, ldo, st); });
+  g_stage = keep;
+  return rc;
 }
 
 struct Ctx {
@@ -63,7 +131,10 @@ int run_embed(const Ctx& c, const void* obs, int obs_dtype, float* x, float* key
   eb.note = at<__half>(c.ws, w.f_note);
   eb.key_bias = key_bias;
   eb.ks = kSaberK; eb.kt = kTorsoK; eb.kl = kLegK; eb.kn = l.note_k;
-  BSRL_TRY(embed_gather(obs, obs_dtype, B, c.cfg->note_geo, c.cfg->z_asinh, eb, c.st));
+  g_stage = kStGather;
+  BSRL_TRY(timed(c.st, 0.0, (double)B * (kObs * 4 + (2 * kSaberK + kTorsoK + 2 * kLegK + kSlots * l.note_k) * 2 + kT * 4),
+                 [&] { return embed_gather(obs, obs_dtype, B, c.cfg->note_geo, c.cfg->z_asinh, eb, c.st); }));
+  g_stage = kStEncoder;
   __half* hid = at<__half>(c.ws, w.enc_hid);
   struct Part { const Encoder* e; const __half* f; int kpad; int64_t rows; int64_t row0; int group; int first; };
   const Part parts[4] = {
@@ -103,16 +174,20 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
 
   for (int i = 0; i + 1 < l.L; ++i) {
     const BlockW& b = l.blocks[i];
-    BSRL_TRY(layernorm_rows(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
+    BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
+    g_stage = kStQkv;
     BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, R, 3 * d, d), c.st));
-    BSRL_TRY(attention29(qkv, 3 * d, key_bias, B, d, l.H, 0, kT, att, d, c.st));
+    BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 0, kT, att, d, c.st));
     LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x, d, 1, 0, R, d, d);
     po.R = x; po.ldr = d;
+    g_stage = kStOutProj;
     BSRL_TRY(linear(po, c.st));
-    BSRL_TRY(layernorm_rows(x, d, ident, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, R, d, h, d, c.st));
+    BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, R, d, h, d, c.st));
+    g_stage = kStFfnUp;
     BSRL_TRY(linear(linear_args(h, d, c.W(b.up), d, c.Bv(b.up), hid, F, 0, 1, R, F, d), c.st));
     LinearArgs pd = linear_args(hid, F, c.W(b.down), F, c.Bv(b.down), x, d, 1, 0, R, d, F);
     pd.R = x; pd.ldr = d;
+    g_stage = kStFfnDown;
     BSRL_TRY(linear(pd, c.st));
   }
 
@@ -122,20 +197,24 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   __half* lead16 = at<__half>(c.ws, w.lead16);
   {
     const BlockW& b = l.blocks[l.L - 1];
-    BSRL_TRY(layernorm_rows(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
+    BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
+    g_stage = kStQkv;
     BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv, d), d, c.Bv(b.qkv, d), qkv + d, 3 * d, 0, 0, R, 2 * d, d), c.st));
     LinearArgs pq = linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, Rl, d, d);
     pq.amap = lead_rows;
     pq.cmap = lead_rows;
     BSRL_TRY(linear(pq, c.st));
-    BSRL_TRY(attention29(qkv, 3 * d, key_bias, B, d, l.H, 0, kLead, att, d, c.st));
+    BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 0, kLead, att, d, c.st));
     LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x_lead, d, 1, 0, Rl, d, d);
     po.R = x; po.ldr = d; po.rmap = lead_rows;
+    g_stage = kStOutProj;
     BSRL_TRY(linear(po, c.st));
-    BSRL_TRY(layernorm_rows(x_lead, d, ident, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, Rl, d, h_lead, d, c.st));
+    BSRL_TRY(layernorm(x_lead, d, ident, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, Rl, d, h_lead, d, c.st));
+    g_stage = kStFfnUp;
     BSRL_TRY(linear(linear_args(h_lead, d, c.W(b.up), d, c.Bv(b.up), hid, F, 0, 1, Rl, F, d), c.st));
     LinearArgs pd = linear_args(hid, F, c.W(b.down), F, c.Bv(b.down), lead16, d, 0, 0, Rl, d, F);
     pd.R = x_lead; pd.ldr = d;
+    g_stage = kStFfnDown;
     BSRL_TRY(linear(pd, c.st));
   }
 
@@ -145,15 +224,16 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   __half* r = at<__half>(c.ws, w.r);
   __half* z = at<__half>(c.ws, w.z);
   const int ldz = d + D;
+  g_stage = kStTrunk;
   BSRL_TRY(linear(linear_args(lead16, kLead * d, c.W(l.trunk_proj), kLead * d, c.Bv(l.trunk_proj), xt, D, 1, 0, B, D, kLead * d), c.st));
-  BSRL_TRY(layernorm_rows(xt, D, ident, c.G(l.trunk_ln1), c.Be(l.trunk_ln1), eps, B, D, u, D, c.st));
+  BSRL_TRY(layernorm(xt, D, ident, c.G(l.trunk_ln1), c.Be(l.trunk_ln1), eps, B, D, u, D, c.st));
   BSRL_TRY(linear(linear_args(u, D, c.W(l.trunk_fc1), D, c.Bv(l.trunk_fc1), r, l.Hh, 0, 1, B, l.Hh, D), c.st));
   {
     LinearArgs p2 = linear_args(r, l.Hh, c.W(l.trunk_fc2), l.Hh, c.Bv(l.trunk_fc2), xt, D, 1, 0, B, D, l.Hh);
     p2.R = xt; p2.ldr = D;
     BSRL_TRY(linear(p2, c.st));
   }
-  BSRL_TRY(layernorm_rows(xt, D, ident, c.G(l.trunk_ln2), c.Be(l.trunk_ln2), eps, B, D, z + d, ldz, c.st));
+  BSRL_TRY(layernorm(xt, D, ident, c.G(l.trunk_ln2), c.Be(l.trunk_ln2), eps, B, D, z + d, ldz, c.st));
   float* raw = at<float>(c.ws, w.raw);
   BSRL_TRY(linear(linear_args(z + d, ldz, c.W(l.heads), D, c.Bv(l.heads), raw, l.head_cols_pad, 1, 0, B, l.head_cols_pad, D), c.st));
 
@@ -164,13 +244,14 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   float* vraw = at<float>(c.ws, w.vraw);
   {
     const RowMap torso_rows{1, kT, 2};
-    BSRL_TRY(layernorm_rows(x, d, ident, c.G(l.critic_ln), c.Be(l.critic_ln), eps, R, d, h, d, c.st));
+    g_stage = kStCritic;
+    BSRL_TRY(layernorm(x, d, ident, c.G(l.critic_ln), c.Be(l.critic_ln), eps, R, d, h, d, c.st));
     BSRL_TRY(linear(linear_args(h, d, c.W(l.critic_kv), d, c.Bv(l.critic_kv), qkv + d, 3 * d, 0, 0, R, 2 * d, d), c.st));
     LinearArgs pq = linear_args(h, d, c.W(l.critic_q), d, c.Bv(l.critic_q), qkv, 3 * d, 0, 0, B, d, d);
     pq.amap = torso_rows;
     pq.cmap = torso_rows;
     BSRL_TRY(linear(pq, c.st));
-    BSRL_TRY(attention29(qkv, 3 * d, key_bias, B, d, l.H, 2, 1, att_c, d, c.st));
+    BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 2, 1, att_c, d, c.st));
     BSRL_TRY(linear(linear_args(att_c, d, c.W(l.critic_out), d, c.Bv(l.critic_out), z, ldz, 0, 0, B, d, d), c.st));
     BSRL_TRY(linear(linear_args(z, ldz, c.W(l.critic_m0), ldz, c.Bv(l.critic_m0), m1, D, 0, 1, B, D, ldz), c.st));
     BSRL_TRY(linear(linear_args(m1, D, c.W(l.critic_m1), D, c.Bv(l.critic_m1), m2, D, 0, 1, B, D, D), c.st));
@@ -186,7 +267,9 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     t.first[j] = l.head_first[j];
   }
   t.n_envs = B;
-  return head_tail(t, c.st);
+  g_stage = kStHeadTail;
+  return timed(c.st, 0.0, (double)B * 4 * (l.head_cols_pad + l.bins_pad + kActHeads * l.k_max + 1),
+               [&] { return head_tail(t, c.st); });
 }
 
 int make_ctx(Ctx& c, const bsrl_config* cfg, const void* arena, int64_t n_envs, void* ws,
@@ -364,6 +447,35 @@ int bsrl_forward_act(const bsrl_config* cfg, const void* arena, const void* obs,
 }
 
 int32_t bsrl_token_lane(int32_t tok, int32_t k) { return token_lane_host(tok, k); }
+
+int bsrl_profile_enable(int32_t on) {
+  g_prof.reset();
+  g_prof.on = on != 0;
+  return BSRL_OK;
+}
+int32_t bsrl_profile_stage_count(void) { return kStCount; }
+const char* bsrl_profile_stage_name(int32_t i) { return (i >= 0 && i < kStCount) ? kStageNames[i] : ""; }
+int bsrl_profile_stage(int32_t i, double* ms_total, int64_t* launches, double* flops_total,
+                       double* bytes_total) {
+  if (i < 0 || i >= kStCount) {
+    set_error("profile_stage: index %d out of range", i);
+    return BSRL_ERR_SHAPE;
+  }
+  double ms = 0, fl = 0, by = 0;
+  int64_t n = 0;
+  for (const Profiler::Rec& r : g_prof.recs) {
+    if (r.stage != i) continue;
+    float t = 0.f;
+    cudaError_t e = cudaEventElapsedTime(&t, r.e0, r.e1);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaEventElapsedTime (synchronise the stream before reading the profile)");
+    ms += t; fl += r.flops; by += r.bytes; ++n;
+  }
+  if (ms_total) *ms_total = ms;
+  if (launches) *launches = n;
+  if (flops_total) *flops_total = fl;
+  if (bytes_total) *bytes_total = by;
+  return BSRL_OK;
+}
 
 int bsrl_embed(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
                int64_t n_envs, float* x, float* key_bias, void* workspace, int64_t workspace_bytes,

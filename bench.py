@@ -1,0 +1,307 @@
+"""Benchmark of the policy forward: env-forwards/s on N B200s, with roofline and CPU baseline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
+
+One step = one ``forward_stacked`` over one batch of synthetic observations (65,536 envs per GPU
+for the default ``cfg2`` workload: d=256, 4 blocks, 8 heads, Xavier init seed 1).  Under torchrun
+every rank runs the same per-GPU batch (weak scaling, no collective on the path); timing is
+CUDA events bracketed by barrier + synchronize, max over ranks.  Rank 0 prints ONE JSON line.
+
+``--impl reference`` times the reference algorithm's CPU implementation (the oracle port of
+python/policy.py) on the host cores over a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "policy env-forwards/sec"
+UNIT = "env-forwards/s"
+WORKLOADS = {
+    # name: (oracle config name, envs per GPU, weight seed, xavier, padded obs, obs seed)
+    "cfg1": ("cfg1", 1024, 0, False, False, 0),
+    "cfg2": ("cfg2", 65536, 1, True, False, 1),
+    "cfg3": ("cfg3", 131072, 1, True, True, 2),
+    "cfg4": ("cfg4", 32768, 3, False, False, 3),
+    "cfg5": ("cfg5", 131072, 1, True, False, 1),
+}
+
+
+def read_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        j = json.loads(p.read_text())
+        return dict(source="measured", hbm_gbs=j["hbm_gbs"], tflops_burst=j["bf16_tflops"],
+                    tflops_sustained=j.get("bf16_tflops_sustained", j["bf16_tflops"]))
+    return dict(source="fallback", hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        top = [s for s in sm if s >= 0.5 * max(sm)] or sm     # samples under load
+        return {"sm_mhz": statistics.median(top), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_forward_rate(cfg, sd, sample_envs, obs_seed, padded, reps, warm):
+    """Oracle (port of the reference forward) on the host cores; best-of-reps env-forwards/s."""
+    from oracle import policy_oracle as po
+    torch.set_num_threads(os.cpu_count() or 1)
+    obs = po.make_obs(sample_envs, obs_seed, padded=padded)
+    for _ in range(warm):
+        po.forward_stacked(sd, cfg, obs)
+    best = float("inf")
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        po.forward_stacked(sd, cfg, obs)
+        dt = time.perf_counter() - t0
+        times.append(dt)
+        best = min(best, dt)
+    return sample_envs / best, times
+
+
+def run_reference(args, rank, world):
+    """The reference's CPU implementation of the path, rank 0 only."""
+    if rank != 0:
+        return
+    from oracle import policy_oracle as po
+    name, envs, wseed, xavier, padded, oseed = WORKLOADS[args.workload]
+    cfg = po.named_config(name)
+    sd = po.build_state_dict(cfg, wseed, xavier=xavier)
+    sample = args.cpu_sample or max(64, min(envs, int(2.0e11 / (2 * po.mac_per_env(cfg)))))
+    torch.set_num_threads(os.cpu_count() or 1)
+    obs = po.make_obs(sample, oseed, padded=padded)
+    for _ in range(args.warmup):
+        po.forward_stacked(sd, cfg, obs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        po.forward_stacked(sd, cfg, obs)
+    dt = time.perf_counter() - t0
+    rate = sample * args.steps / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {describe(cfg)}, sample of {sample} envs per step"},
+        "cpu_baseline": {"value": rate, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{sample} envs per step, torch fp32, all host threads"},
+        "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def describe(cfg):
+    return (f"d={cfg.embed} L={cfg.n_blocks} H={cfg.n_heads} ffn={cfg.ffn_mult * cfg.embed} "
+            f"trunk={cfg.trunk_dim} T=29 lead=5 gears={cfg.n_gears}")
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from beatsaberrl_b200 import _native as nat
+    from beatsaberrl_b200.policy import NotePolicy
+    from oracle import policy_oracle as po   # weights / synthetic inputs / CPU baseline only
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    name, envs, wseed, xavier, padded, oseed = WORKLOADS[args.workload]
+    if args.envs:
+        envs = args.envs
+    cfg = po.named_config(name)
+    sd = po.build_state_dict(cfg, wseed, xavier=xavier)
+    policy = NotePolicy(**cfg.ref_kwargs())
+    policy.load_state_dict(sd)
+    policy = policy.to(dev)
+    policy.flatten_fp16()
+    # each rank owns its own contiguous env range: independent seeds, no exchange
+    obs_host = po.make_obs(envs, oseed + 1000 * rank, padded=padded).pin_memory()
+    obs = obs_host.to(dev, non_blocking=True)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident throughput (value) ------------------------------------------
+    for _ in range(args.warmup):
+        policy.forward_stacked(obs)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    nat.check(nat.lib.bsrl_profile_enable(1))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        policy.forward_stacked(obs)
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    stages = nat.profile_read()
+    nat.check(nat.lib.bsrl_profile_enable(0))
+    clocks = sampler.stop()
+    value = world * envs * args.steps / (ms * 1e-3)
+
+    # ---- end to end through the public API, host buffers (e2e) -----------------------
+    logits_host = torch.empty(envs, 29, cfg.k_max, dtype=torch.float32).pin_memory()
+    value_host = torch.empty(envs, dtype=torch.float32).pin_memory()
+    obs_dev = torch.empty_like(obs)
+
+    def e2e_step():
+        obs_dev.copy_(obs_host, non_blocking=True)
+        lg, vl = policy.forward_stacked(obs_dev)
+        logits_host.copy_(lg, non_blocking=True)
+        value_host.copy_(vl, non_blocking=True)
+
+    for _ in range(max(1, args.warmup // 2)):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+    e2e_value = world * envs * args.steps / (ms_e2e * 1e-3)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peaks = read_peaks()
+    mac = po.mac_per_env(cfg)
+    fwd_tflops = 2.0 * mac * (value / world) / 1e12          # per GPU
+    gemm = {k: v for k, v in stages.items() if v["flops"] > 0 and k != "attention"}
+    top_name = max(gemm, key=lambda k: gemm[k]["ms"]) if gemm else None
+    roofline = None
+    if top_name:
+        t = gemm[top_name]
+        achieved = t["flops"] / (t["ms"] * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": top_name, "achieved": achieved,
+                    "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["tflops_sustained"], "traffic": KNOWN_TRAFFIC.get(top_name),
+                    "peak_source": peaks["source"] + " (sustained bf16 GEMM; burst %.1f)" % peaks["tflops_burst"],
+                    "launches": t["launches"], "ms_per_launch": t["ms"] / t["launches"],
+                    "algorithmic_bytes_per_launch": t["bytes"] / t["launches"],
+                    "forward_tflops": fwd_tflops,
+                    "forward_frac_of_burst": fwd_tflops / peaks["tflops_burst"],
+                    "forward_frac_of_datasheet_2250": fwd_tflops / 2250.0,
+                    "stage_ms_per_step": {k: round(v["ms"] / args.steps, 4) for k, v in stages.items()}}
+    cpu_baseline = None
+    if world == 1:
+        sample = args.cpu_sample or max(64, min(envs, int(6.0e11 / (2 * mac))))
+        rate, times = cpu_forward_rate(cfg, sd, sample, oseed, padded, reps=3, warm=1)
+        cpu_baseline = {"value": rate, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                        "sample": f"{sample} envs, best of 3 after 1 warm-up, torch fp32 on all host threads"}
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {describe(cfg)}, {envs} envs per GPU, "
+                               f"{'Xavier' if xavier else 'default'} init seed {wseed}",
+                   "l2": "inputs and activations larger than L2 (obs %.0f MB, token stream %.1f GB)"
+                         % (envs * 630 * 4 / 1e6, envs * 29 * cfg.embed * 4 / 1e9),
+                   "mac_per_env": mac},
+        "roofline": roofline, "cpu_baseline": cpu_baseline,
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": obs_host.numel() * 4,
+                "d2h_bytes_per_step": (logits_host.numel() + value_host.numel()) * 4},
+        "gpu_launches": int(sum(v["launches"] for v in stages.values())),
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes per launch of a stage's kernel from the committed ncu captures (profiles/);
+# None until a capture of that kernel exists.
+KNOWN_TRAFFIC = {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--envs", type=int, default=0, help="envs per GPU (default: the workload's)")
+    ap.add_argument("--cpu-sample", type=int, default=0, help="envs in the CPU sample")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the policy forward has no CPU path)")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -143,6 +143,18 @@ int bsrl_linear(const void* a_f16, const void* w_f16, const float* bias, const f
 int bsrl_attention(const void* qkv_f16, const float* key_bias, int64_t n_envs, int32_t d,
                    int32_t n_heads, int32_t q_first, int32_t n_q, void* out_f16, void* stream);
 
+/* --- stage timing (benchmarks) ------------------------------------------------------- *
+ * When enabled, every launch of a forward is bracketed by CUDA events on the caller's stream
+ * and accounted to a stage ("ffn_down_gemm", "attention", ...).  Enabling clears earlier
+ * records.  Read the totals after synchronising the stream.  Leave it off while capturing a
+ * CUDA graph.  Counterpart in the reference: the per-tick CUDA-event timers of its --bench
+ * mode (python/train_batch.py:2120-2124, :2309-2352). */
+int bsrl_profile_enable(int32_t on);
+int32_t bsrl_profile_stage_count(void);
+const char* bsrl_profile_stage_name(int32_t i);
+int bsrl_profile_stage(int32_t i, double* ms_total, int64_t* launches, double* flops_total,
+                       double* bytes_total);
+
 #ifdef __cplusplus
 }
 #endif

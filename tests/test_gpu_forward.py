@@ -1,0 +1,135 @@
+"""Whole-forward parity of the CUDA path (through the NotePolicy facade -> C ABI) against the
+oracle and the reference-generated golden vectors."""
+import pytest
+import torch
+
+from helpers import GOLDEN_CASES, assert_parity, cuda_policy, golden_case, make_cfg, po
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", sorted(GOLDEN_CASES))
+def test_golden_vectors(golden, name):
+    cfg, sd = golden_case(name)
+    m = cuda_policy(cfg, sd)
+    obs = torch.from_numpy(golden[f"{name}/obs"]).cuda()
+    m.keep_value_logits = True
+    logits, value = m.forward_stacked(obs)
+    assert logits.shape == (obs.shape[0], 29, cfg.k_max) and logits.dtype is torch.float32
+    ref_l = torch.from_numpy(golden[f"{name}/logits"])
+    ref_v = torch.from_numpy(golden[f"{name}/value"])
+    assert_parity(logits, value, ref_l, ref_v, argmax_min=0.99)   # few heads: one near-tie may flip
+    dead = ref_l < -1e8
+    assert torch.equal(logits.cpu()[dead], ref_l[dead])            # masked lanes are exactly -1e9
+    torch.testing.assert_close(m._value_logits.cpu(), torch.from_numpy(golden[f"{name}/value_logits"]),
+                               atol=3e-2, rtol=1e-2)
+    act = torch.from_numpy(golden[f"{name}/actions"]).cuda()
+    for a in (act, act.to(torch.uint8), act.long()):
+        a2, lp, ent, v2 = m.get_action_and_value(obs, a)
+        # 29 summed log-probs: 29 x the per-logit tolerance is the bound, observed far smaller
+        torch.testing.assert_close(lp.cpu(), torch.from_numpy(golden[f"{name}/logprob"]), atol=5e-2, rtol=1e-2)
+        torch.testing.assert_close(ent.cpu(), torch.from_numpy(golden[f"{name}/entropy"]), atol=5e-2, rtol=1e-2)
+        torch.testing.assert_close(m._ent_h.cpu(), torch.from_numpy(golden[f"{name}/ent_head"]), atol=5e-3, rtol=1e-2)
+        torch.testing.assert_close(v2, value, atol=0, rtol=0)
+        torch.testing.assert_close(ent, m._ent_h.sum(-1), atol=1e-4, rtol=1e-5)
+
+
+@pytest.mark.parametrize("name,geo,xavier,seed,B,padded", [
+    ("cfg1", False, False, 0, 1024, False),      # the CPU-reference configuration, whole
+    ("cfg2", False, True, 1, 2048, False),       # single-GPU rollout model, Xavier seed 1
+    ("cfg2", False, True, 1, 1536, True),        # padded objects: masked attention path
+    ("recipe", True, False, 5, 512, True),       # the reference's production shape (head_dim 48, geo)
+    ("cfg4", False, False, 3, 256, False),       # wide policy, 7 gears
+])
+def test_parity_gates(name, geo, xavier, seed, B, padded):
+    cfg = make_cfg(name, geo)
+    sd = po.build_state_dict(cfg, seed, xavier=xavier)
+    m = cuda_policy(cfg, sd)
+    obs = po.make_obs(B, seed + (2 if padded else 0), padded=padded)
+    ref_l, ref_v = po.forward_stacked(sd, cfg, obs)
+    logits, value = m.forward_stacked(obs.cuda())
+    rep = assert_parity(logits, value, ref_l, ref_v)
+    print(name, rep)
+    act = po.make_actions(B, cfg, 4).cuda()
+    _, lp, ent, _ = m.get_action_and_value(obs.cuda(), act)
+    rlp, rent, _ = po.evaluate_actions(ref_l, act.cpu())
+    torch.testing.assert_close(lp.cpu(), rlp, atol=29 * 2e-2, rtol=1e-2)
+    torch.testing.assert_close(ent.cpu(), rent, atol=5e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("B", [1, 3, 127, 129, 1000])
+def test_ragged_batches_and_batch_invariance(B):
+    cfg, sd = golden_case("tiny_geo_mixed")
+    m = cuda_policy(cfg, sd)
+    obs = po.make_obs(1000, 31, padded=True)
+    full_l, full_v = m.forward_stacked(obs.cuda())
+    l, v = m.forward_stacked(obs[:B].cuda())
+    # an env's result does not depend on the batch around it (reference test_attn29.py:128-140)
+    assert torch.equal(l, full_l[:B]) and torch.equal(v, full_v[:B])
+    ref_l, ref_v = po.forward_stacked(sd, cfg, obs[:B])
+    assert_parity(l, v, ref_l, ref_v, argmax_min=0.99 if B < 100 else 0.998)
+
+
+def test_all_slots_masked_and_all_live():
+    cfg, sd = golden_case("tiny_plain")
+    m = cuda_policy(cfg, sd)
+    obs = po.make_obs(64, 8)
+    dead = obs.clone()
+    dead[:, po.OFF_MASK:po.OFF_MASK + 24] = 0.0
+    for o in (obs, dead):
+        l, v = m.forward_stacked(o.cuda())
+        assert torch.isfinite(l).all() and torch.isfinite(v).all()
+        ref_l, ref_v = po.forward_stacked(sd, cfg, o)
+        assert_parity(l, v, ref_l, ref_v, argmax_min=0.995)
+    # junk in masked slots cannot leak (reference test_policy.py:42-63)
+    junk = dead.clone()
+    junk[:, po.OFF_NOTES:po.OFF_MASK] = 55.0
+    l2, v2 = m.forward_stacked(junk.cuda())
+    l1, v1 = m.forward_stacked(dead.cuda())
+    torch.testing.assert_close(l1, l2, atol=1e-5, rtol=0)
+    torch.testing.assert_close(v1, v2, atol=1e-5, rtol=0)
+
+
+def test_weight_refresh_in_place_and_sampling():
+    from beatsaberrl_b200.policy import bump_weights_version
+    cfg, sd = golden_case("tiny_plain")
+    m = cuda_policy(cfg, sd)
+    obs = po.make_obs(256, 3).cuda()
+    l0, _ = m.forward_stacked(obs)
+    ptr = m._arena.data_ptr()
+    with torch.no_grad():
+        for p in m.heads.parameters():
+            p.mul_(2.0)
+    bump_weights_version()
+    l1, _ = m.forward_stacked(obs)
+    assert m._arena.data_ptr() == ptr                    # refreshed in place
+    torch.testing.assert_close(l1, 2 * l0, atol=1e-2, rtol=1e-2)
+    torch.manual_seed(0)
+    a, lp, ent, v = m.get_action_and_value(obs)          # sampled actions
+    assert a.shape == (256, 29) and a.dtype is torch.int64 and int(a.max()) < cfg.k_max
+    _, lp2, ent2, _ = m.get_action_and_value(obs, a)
+    torch.testing.assert_close(lp, lp2, atol=1e-4, rtol=1e-5)
+    torch.testing.assert_close(ent, ent2, atol=1e-4, rtol=1e-5)
+
+
+def test_cuda_graph_capture_replays():
+    """The forward allocates nothing between replays and never syncs, so it can be captured the
+    way the reference's graph drivers do (python/cuda_graphs.py:22-68)."""
+    cfg, sd = golden_case("tiny_plain")
+    m = cuda_policy(cfg, sd)
+    m.flatten_fp16()
+    static_obs = po.make_obs(128, 1).cuda()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(3):
+            m.forward_stacked(static_obs)
+    torch.cuda.current_stream().wait_stream(s)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        gl, gv = m.forward_stacked(static_obs)
+    new = po.make_obs(128, 2).cuda()
+    static_obs.copy_(new)
+    g.replay()
+    el, ev = m.forward_stacked(new)
+    assert torch.equal(gl, el) and torch.equal(gv, ev)

@@ -1,0 +1,112 @@
+"""Single kernels through the C ABI against torch fp32 arithmetic on the same inputs."""
+import ctypes as C
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from helpers import golden_case, make_cfg, po
+
+pytestmark = pytest.mark.gpu
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+@pytest.mark.parametrize("rows,d", [(1, 64), (37, 128), (1000, 256), (129, 512), (5, 1024)])
+def test_layernorm(native, rows, d):
+    g = torch.Generator().manual_seed(rows + d)
+    x = (torch.randn(rows, d, generator=g) * 3 + 0.5).cuda()
+    w = (1 + 0.1 * torch.randn(d, generator=g)).cuda()
+    b = (0.1 * torch.randn(d, generator=g)).cuda()
+    y = torch.empty(rows, d, dtype=torch.float16, device="cuda")
+    native.check(native.lib.bsrl_layernorm(x.data_ptr(), w.data_ptr(), b.data_ptr(), 1e-5, rows, d,
+                                           y.data_ptr(), d, _stream()))
+    ref = F.layer_norm(x, (d,), w, b, 1e-5)
+    # output is fp16: half an ulp of |ref| <= 8 is 4e-3
+    torch.testing.assert_close(y.float(), ref, atol=4e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("engine", [0, 1])
+@pytest.mark.parametrize("m,n,k,relu,resid,f32", [
+    (1, 8, 32, 0, 0, 1), (127, 152, 64, 0, 0, 1), (129, 104, 512, 0, 0, 1), (1000, 768, 256, 0, 0, 0),
+    (333, 1024, 256, 1, 0, 0), (260, 256, 1024, 0, 1, 1), (64, 512, 1280, 0, 0, 1), (4096, 256, 256, 0, 1, 1),
+])
+def test_linear(native, engine, m, n, k, relu, resid, f32):
+    if engine == 1 and (k % 64 != 0 or n % 16 != 0):
+        pytest.skip("shape outside the tcgen05 engine")
+    g = torch.Generator().manual_seed(m * 7 + n)
+    a = torch.randn(m, k, generator=g).half().cuda()
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).half().cuda()
+    bias = torch.randn(n, generator=g).cuda()
+    r = torch.randn(m, n, generator=g).cuda() if resid else None
+    out = torch.empty(m, n, dtype=torch.float32 if f32 else torch.float16, device="cuda")
+    rc = native.lib.bsrl_linear(a.data_ptr(), w.data_ptr(), bias.data_ptr(),
+                                r.data_ptr() if resid else None, out.data_ptr(), f32, relu, m, n, k,
+                                engine, _stream())
+    if engine == 1 and rc == -5:
+        pytest.skip("shape outside the tcgen05 engine: " + native.last_error())
+    native.check(rc)
+    ref = a.float() @ w.float().t() + bias
+    if relu:
+        ref = ref.relu()
+    if resid:
+        ref = ref + r
+    tol = dict(atol=2e-4, rtol=1e-4) if f32 else dict(atol=4e-3, rtol=1e-3)
+    torch.testing.assert_close(out.float(), ref, **tol)
+
+
+@pytest.mark.parametrize("B,d,H,q_first,n_q", [(1, 64, 2, 0, 29), (37, 256, 8, 0, 29), (50, 128, 4, 0, 5),
+                                               (33, 256, 8, 2, 1), (9, 512, 8, 0, 29), (11, 192, 4, 0, 29)])
+def test_attention(native, B, d, H, q_first, n_q):
+    g = torch.Generator().manual_seed(B + d)
+    qkv = torch.randn(B, 29, 3 * d, generator=g).half()
+    n_live = torch.randint(0, 25, (B,), generator=g)
+    n_live[0] = 0
+    bias = torch.zeros(B, 29)
+    bias[:, 5:] = ((torch.arange(24)[None, :] < n_live[:, None]).float() - 1.0) * 16384.0
+    out = torch.empty(B * n_q, d, dtype=torch.float16, device="cuda")
+    qkv_d, bias_d = qkv.cuda(), bias.cuda()
+    native.check(native.lib.bsrl_attention(qkv_d.data_ptr(), bias_d.data_ptr(), B, d, H, q_first, n_q,
+                                           out.data_ptr(), _stream()))
+    q, k, v = qkv.float().split(d, -1)
+    ref = po.attention(q[:, q_first:q_first + n_q], k, v, bias, H)
+    torch.testing.assert_close(out.float().cpu().view(B, n_q, d), ref, atol=4e-3, rtol=2e-3)
+    # masked keys carry exactly zero weight: junk in their k/v rows changes nothing
+    junk = qkv.clone()
+    dead = torch.cat([torch.zeros(B, 5, dtype=torch.bool), bias[:, 5:] < 0], 1)
+    junk[..., d:][dead] = 77.0
+    if q_first == 0 and n_q == 29:
+        junk[..., :d][dead] = 0.5          # query rows of dead tokens may change their own output only
+    out2 = torch.empty_like(out)
+    junk_d = junk.cuda()
+    native.check(native.lib.bsrl_attention(junk_d.data_ptr(), bias_d.data_ptr(), B, d, H, q_first, n_q,
+                                           out2.data_ptr(), _stream()))
+    o1 = out.view(B, n_q, d).cpu()
+    o2 = out2.view(B, n_q, d).cpu()
+    live_q = ~dead[:, q_first:q_first + n_q]
+    assert torch.equal(o1[live_q], o2[live_q])
+
+
+@pytest.mark.parametrize("case", ["tiny_plain", "tiny_geo_mixed"])
+@pytest.mark.parametrize("obs_f16", [False, True])
+def test_embed(native, case, obs_f16):
+    cfg, sd = golden_case(case)
+    from helpers import cuda_policy
+    m = cuda_policy(cfg, sd)
+    m.flatten_fp16()
+    B = 19
+    obs = po.make_obs(B, 77, padded=True)
+    if obs_f16:
+        obs = obs.half()
+    obs_d = obs.cuda()
+    x = torch.empty(B * 29, cfg.embed, device="cuda")
+    kb = torch.empty(B, 29, device="cuda")
+    ws = m._workspace(B, obs_d.device)
+    native.check(native.lib.bsrl_embed(C.byref(m._cfg), m._arena.data_ptr(), obs_d.data_ptr(),
+                                       1 if obs_f16 else 0, B, x.data_ptr(), kb.data_ptr(),
+                                       ws.data_ptr(), ws.numel(), _stream()))
+    tokens, bias = po.embed_tokens(sd, cfg, obs.float())
+    torch.testing.assert_close(kb.cpu(), bias, atol=0, rtol=0)
+    torch.testing.assert_close(x.cpu().view(B, 29, -1), tokens, atol=6e-3, rtol=5e-3)
