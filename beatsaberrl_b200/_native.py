@@ -71,6 +71,8 @@ _sig = {
     "bsrl_forward_act": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, C.c_int32, _P, _P, _P, _P, _P, _P,
                                    _P, C.c_int64, _P]),
     "bsrl_token_lane": (C.c_int32, [C.c_int32, C.c_int32]),
+    "bsrl_device_status": (C.c_int, []),
+    "bsrl_set_engine": (C.c_int, [C.c_int32]),
     "bsrl_profile_enable": (C.c_int, [C.c_int32]),
     "bsrl_profile_stage_count": (C.c_int32, []),
     "bsrl_profile_stage_name": (C.c_char_p, [C.c_int32]),
@@ -86,6 +88,10 @@ for _name, (_res, _args) in _sig.items():
     _fn = getattr(lib, _name)
     _fn.restype = _res
     _fn.argtypes = _args
+
+import os as _os
+if _os.environ.get("BSRL_ENGINE", "") == "mma":      # cross-check runs: warp-MMA kernels only
+    lib.bsrl_set_engine(1)
 
 
 def last_error() -> str:

@@ -54,7 +54,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
             if log:
                 print(log, file=sys.stderr)
     if force or not LIB.exists() or any(os.path.getmtime(o) > LIB.stat().st_mtime for o in objs):
-        cmd = [_nvcc(), "-shared", "-o", str(LIB), *objs, "-lcuda"]
+        cmd = [_nvcc(), "-shared", "-o", str(LIB), *objs]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

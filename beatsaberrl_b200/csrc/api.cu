@@ -10,6 +10,7 @@
 
 #include "kernels.cuh"
 #include "layout.h"
+#include "tc5.cuh"
 
 namespace bsrl {
 const char* last_error();
@@ -73,9 +74,10 @@ int timed(cudaStream_t st, double flops, double bytes, Fn&& fn) {
 }
 
 // engine choice for one linear layer: tcgen05 where the shape fits, warp-MMA otherwise
+int g_engine = 0;   // 0 = automatic, 1 = warp-MMA kernel only (cross-check runs)
 int linear(const LinearArgs& p, cudaStream_t st) {
   return timed(st, 2.0 * p.M * p.N * p.K, linear_bytes(p), [&] {
-    if (linear_tc5_ok(p)) return linear_tc5(p, st);
+    if (g_engine == 0 && p.M >= 128 && linear_tc5_ok(p)) return linear_tc5(p, st);
     return linear_mma(p, st);
   });
 }
@@ -447,6 +449,28 @@ int bsrl_forward_act(const bsrl_config* cfg, const void* arena, const void* obs,
 }
 
 int32_t bsrl_token_lane(int32_t tok, int32_t k) { return token_lane_host(tok, k); }
+
+int bsrl_set_engine(int32_t engine) {
+  if (engine != 0 && engine != 1) {
+    set_error("set_engine: 0 (automatic) or 1 (warp-MMA only)");
+    return BSRL_ERR_UNSUPPORTED;
+  }
+  g_engine = engine;
+  return BSRL_OK;
+}
+
+int bsrl_device_status(void) {
+  int v = device_status_take();
+  if (v < 0) {
+    set_error("device_status: could not read the status word");
+    return BSRL_ERR_CUDA;
+  }
+  if (v != 0) {
+    set_error("a bounded device-side wait ran out (kernel %d, role %d)", v / 16, v % 16);
+    return BSRL_ERR_TIMEOUT;
+  }
+  return BSRL_OK;
+}
 
 int bsrl_profile_enable(int32_t on) {
   g_prof.reset();

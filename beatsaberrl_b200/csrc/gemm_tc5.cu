@@ -1,9 +1,339 @@
-// placeholder until the tcgen05 engine lands
+// tcgen05 linear layer: C = act(A W^T + bias) (+ residual) on the 5th-generation tensor cores.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer: streams (128 x 64) A tiles and (BN x 64) W tiles, both K-major
+//               with the 128-byte swizzle, through a 4-stage shared-memory ring;
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M = 128, N <= 256, K = 16) on the
+//               shared-memory descriptors, accumulating in TMEM; two accumulator buffers of BN
+//               fp32 columns let tile t+1's MMAs overlap tile t's epilogue;
+//   warps 2..9  epilogue: tcgen05.ld the accumulator (thread = output row), add bias, ReLU,
+//               residual, convert and store (rows may be remapped on the way out).
+// All waits are bounded: a wait that runs out sets the library's device status word, raises
+// the CTA-wide abort flag, and every role falls through to the common teardown that frees TMEM.
+//
+// Stands in for the reference's cuBLAS / cuBLASLt calls on the fp16 stream (torch.addmm and the
+// RELU_BIAS epilogue, python/fp16_linear.py:134-181; linear_relu_aux,
+// python/beat_arena_env/csrc/fp16_gemm.cu:402-497).
 #include "kernels.cuh"
+#include "tc5.cuh"
+
 namespace bsrl {
-bool linear_tc5_ok(const LinearArgs&) { return false; }
-int linear_tc5(const LinearArgs&, cudaStream_t) {
-  set_error("tcgen05 engine not built");
-  return BSRL_ERR_UNSUPPORTED;
+
+namespace {
+__device__ int g_device_status = 0;
+
+using namespace tc5;
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;            // 16 KB
+constexpr int W_BYTES = BN * BK * 2;            // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + W_BYTES;  // 48 KB
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = (2 + EPI_WARPS) * 32;
+constexpr int TMEM_COLS = 2 * BN;               // two accumulator buffers = all 512 columns
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct Shared {
+  uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], mma_done;
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ void give_up(Shared* sh, int* status, int role) {
+  atomicCAS(status, 0, 1 * 16 + role);
+  sh->abort = 1;
 }
+
+__global__ void __launch_bounds__(THREADS, 1)
+linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+                  LinearArgs p, int m_tiles, int n_tiles, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_base = (raw + 1023u) & ~1023u;
+  Shared* sh = reinterpret_cast<Shared*>(smem_raw + (tiles_base - raw) + STAGES * STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k_blocks = p.K / BK;
+  const int64_t n_work = (int64_t)m_tiles * n_tiles;
+  volatile int* abort = &sh->abort;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&sh->full[s]), 1);
+      mbar_init(smem_u32(&sh->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh->tmem_full[b]), 1);
+      mbar_init(smem_u32(&sh->tmem_empty[b]), EPI_WARPS);
+    }
+    mbar_init(smem_u32(&sh->mma_done), 1);
+    sh->abort = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&sh->tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < n_work && ok; t += gridDim.x) {
+        const int m0 = (int)(t / n_tiles) * BM, n0 = (int)(t % n_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(smem_u32(&sh->empty[s]), ph ^ 1, abort)) { give_up(sh, status, 1); ok = false; break; }
+          const uint32_t bar = smem_u32(&sh->full[s]);
+          mbar_expect_tx(bar, STAGE_BYTES);
+          const uint32_t dst = tiles_base + s * STAGE_BYTES;
+          tma_load_2d(dst, &tm_a, kb * BK, m0, bar);
+          tma_load_2d(dst + A_BYTES, &tm_w, kb * BK, n0, bar);
+        }
+      }
+      // the loads still in flight must land before this CTA may exit (also when a wait above
+      // gave up): poll the full barriers of the last stages issued, bounded, ignoring abort
+      const uint32_t issued = it;
+      for (uint32_t j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
+        const uint32_t bar = smem_u32(&sh->full[j % STAGES]);
+        const uint32_t ph = (j / STAGES) & 1;
+        uint32_t spins = 0;
+        while (!mbar_try_wait(bar, ph) && ++spins < kSpinLimit) {}
+        if (spins >= kSpinLimit) give_up(sh, status, 2);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tile_i = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < n_work && ok; t += gridDim.x, ++tile_i) {
+        const int n0 = (int)(t % n_tiles) * BN;
+        int n_cols = p.N - n0;
+        if (n_cols > BN) n_cols = BN;
+        const uint32_t idesc = idesc_f16(BM, n_cols);
+        const int buf = tile_i & 1;
+        const uint32_t acc_ph = (tile_i >> 1) & 1;
+        if (!mbar_wait(smem_u32(&sh->tmem_empty[buf]), acc_ph ^ 1, abort)) { give_up(sh, status, 3); ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(smem_u32(&sh->full[s]), ph, abort)) { give_up(sh, status, 4); ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = tiles_base + s * STAGE_BYTES;
+          const uint64_t a_desc = smem_desc_sw128(a_addr);
+          const uint64_t w_desc = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)   // +32 bytes (2 x 16-byte units) per K step of 16
+            mma_f16_ss(d_tmem, a_desc + 2 * k, w_desc + 2 * k, idesc, (kb | k) != 0);
+          tc_commit(smem_u32(&sh->empty[s]));
+        }
+        if (ok) tc_commit(smem_u32(&sh->tmem_full[buf]));
+      }
+      // every MMA issued must have retired before TMEM is freed (bounded, ignoring abort)
+      tc_commit(smem_u32(&sh->mma_done));
+      uint32_t spins = 0;
+      while (!mbar_try_wait(smem_u32(&sh->mma_done), 0) && ++spins < kSpinLimit) {}
+      if (spins >= kSpinLimit) give_up(sh, status, 6);
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue warps
+    const int q = warp & 3;                    // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;          // which half of the tile's columns
+    uint32_t tile_i = 0;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; t < n_work && ok; t += gridDim.x, ++tile_i) {
+      const int64_t m0 = (t / n_tiles) * BM;
+      const int n0 = (int)(t % n_tiles) * BN;
+      const int buf = tile_i & 1;
+      const uint32_t acc_ph = (tile_i >> 1) & 1;
+      if (!mbar_wait(smem_u32(&sh->tmem_full[buf]), acc_ph, abort)) {
+        if (lane == 0) give_up(sh, status, 5);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int64_t row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const int64_t crow = row_ok ? p.cmap(row) * (int64_t)p.ldc : 0;
+      const float* rrow = (p.R && row_ok) ? p.R + p.rmap(row) * (int64_t)p.ldr : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BN / 2; c += 32) {
+        const int col = n0 + half * (BN / 2) + c;     // first of 32 columns
+        if (col >= p.N) break;                         // warp-uniform
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * (BN / 2) + c, r);
+        tmem_wait_ld();
+        if (!row_ok) continue;
+#pragma unroll
+        for (int h16 = 0; h16 < 2; ++h16) {
+          const int cc = col + h16 * 16;
+          if (cc >= p.N) break;
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[h16 * 16 + j]);
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+              float4 b = *reinterpret_cast<const float4*>(p.bias + cc + j);
+              v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+            }
+          }
+          if (p.relu) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
+          }
+          if (rrow) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+              float4 b = *reinterpret_cast<const float4*>(rrow + cc + j);
+              v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+            }
+          }
+          if (p.out_f32) {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.C) + crow + cc);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(p.C) + crow + cc);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              dst[j] = make_uint4(pack_half2(v[8 * j], v[8 * j + 1]), pack_half2(v[8 * j + 2], v[8 * j + 3]),
+                                  pack_half2(v[8 * j + 4], v[8 * j + 5]), pack_half2(v[8 * j + 6], v[8 * j + 7]));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+}  // namespace
+
+// ---------------------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+bool make_tmap_f16(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld_elems,
+                   int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return false;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld_elems * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed (%d) for a (%lld x %lld) fp16 matrix, ld %lld", (int)r,
+              (long long)rows, (long long)cols, (long long)ld_elems);
+    return false;
+  }
+  return true;
+}
+
+bool linear_tc5_ok(const LinearArgs& p) {
+  if (!p.A || !p.W || !p.C || p.M < 1) return false;
+  if (p.K % BK != 0 || p.N % 16 != 0 || p.N < 16) return false;
+  if (p.amap.group != 0x7fffffff || p.amap.first != 0) return false;      // TMA reads A rows in order
+  if (!aligned16(p.A) || !aligned16(p.W) || !aligned16(p.C) || (p.lda % 8) || (p.ldw % 8)) return false;
+  if (p.ldc % (p.out_f32 ? 4 : 8)) return false;
+  if (p.bias && !aligned16(p.bias)) return false;
+  if (p.R && (!aligned16(p.R) || (p.ldr % 4))) return false;
+  return true;
+}
+
+int linear_tc5(const LinearArgs& p, cudaStream_t stream) {
+  if (!linear_tc5_ok(p)) {
+    set_error("linear: shape m=%lld n=%d k=%d does not fit the tcgen05 engine", (long long)p.M, p.N, p.K);
+    return BSRL_ERR_UNSUPPORTED;
+  }
+  int* status = device_status_ptr();
+  if (!status) return BSRL_ERR_CUDA;
+  CUtensorMap tm_a, tm_w;
+  if (!make_tmap_f16(&tm_a, p.A, p.M, p.K, p.lda, BM)) return BSRL_ERR_CUDA;
+  if (!make_tmap_f16(&tm_w, p.W, p.N, p.K, p.ldw, BN)) return BSRL_ERR_CUDA;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  BSRL_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    BSRL_CUDA_OK(cudaFuncSetAttribute(linear_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr_set[dev] = true;
+  }
+  const int64_t m_tiles = (p.M + BM - 1) / BM;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  if (m_tiles > 0x7fffffff / n_tiles) {
+    set_error("linear: too many tiles");
+    return BSRL_ERR_SHAPE;
+  }
+  int64_t grid = m_tiles * n_tiles;
+  if (grid > sm_count()) grid = sm_count();
+  linear_tc5_kernel<<<(unsigned)grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_w, p, (int)m_tiles, n_tiles, status);
+  BSRL_LAUNCH_OK("linear_tc5_kernel");
+  return BSRL_OK;
+}
+
+int* device_status_ptr() {
+  static int* cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("device_status_ptr: no current device");
+    return nullptr;
+  }
+  if (!cached[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_device_status);
+    if (e != cudaSuccess) {
+      cuda_fail(e, "cudaGetSymbolAddress(g_device_status)");
+      return nullptr;
+    }
+    cached[dev] = static_cast<int*>(p);
+  }
+  return cached[dev];
+}
+
+int device_status_take() {
+  int* p = device_status_ptr();
+  int v = 0, zero = 0;
+  if (!p || cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  return v;
+}
+
 }  // namespace bsrl

@@ -143,6 +143,18 @@ int bsrl_linear(const void* a_f16, const void* w_f16, const float* bias, const f
 int bsrl_attention(const void* qkv_f16, const float* key_bias, int64_t n_envs, int32_t d,
                    int32_t n_heads, int32_t q_first, int32_t n_q, void* out_f16, void* stream);
 
+/* Which GEMM kernel the forward's linear layers use: 0 (default) = the tcgen05/TMEM kernel
+ * wherever the shape fits it, the warp-MMA kernel elsewhere; 1 = the warp-MMA kernel everywhere.
+ * Both are CUDA kernels of this library; 1 exists so tests can cross-check one against the
+ * other.  No counterpart in the reference. */
+int bsrl_set_engine(int32_t engine);
+
+/* Synchronises the current device, then reads and clears its status word: BSRL_OK, or
+ * BSRL_ERR_TIMEOUT when a bounded wait inside a tcgen05 kernel (on an mbarrier fed by TMA or by
+ * the tensor core) ran out since the last call -- the results of that launch are then invalid.
+ * The kernels never spin without a limit and never trap.  No counterpart in the reference. */
+int bsrl_device_status(void);
+
 /* --- stage timing (benchmarks) ------------------------------------------------------- *
  * When enabled, every launch of a forward is bracketed by CUDA events on the caller's stream
  * and accounted to a stage ("ffn_down_gemm", "attention", ...).  Enabling clears earlier

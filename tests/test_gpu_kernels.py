@@ -48,6 +48,7 @@ def test_linear(native, engine, m, n, k, relu, resid, f32):
     if engine == 1 and rc == -5:
         pytest.skip("shape outside the tcgen05 engine: " + native.last_error())
     native.check(rc)
+    native.check(native.lib.bsrl_device_status())     # no bounded wait ran out
     ref = a.float() @ w.float().t() + bias
     if relu:
         ref = ref.relu()
