@@ -82,6 +82,8 @@ _sig = {
     "bsrl_layernorm": (C.c_int, [_P, _P, _P, C.c_float, C.c_int64, C.c_int32, _P, C.c_int64, _P]),
     "bsrl_linear": (C.c_int, [_P, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
                               C.c_int32, _P]),
+    "bsrl_block_tail": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, C.c_float, C.c_int64, C.c_int32,
+                                  C.c_int32, _P, _P, _P, _P, _P]),
     "bsrl_attention": (C.c_int, [_P, _P, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
 }
 for _name, (_res, _args) in _sig.items():

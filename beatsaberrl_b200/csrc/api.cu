@@ -32,9 +32,9 @@ inline const T* at(const void* base, int64_t off) {
 // (a captured graph must not contain it); the benchmark switches it on to time the dominant
 // kernel live, on the stream the kernels run on.
 enum Stage { kStGather = 0, kStEncoder, kStLayerNorm, kStQkv, kStAttention, kStOutProj, kStFfnUp,
-             kStFfnDown, kStTrunk, kStCritic, kStHeadTail, kStCount };
+             kStFfnDown, kStBlockTail, kStTrunk, kStCritic, kStHeadTail, kStCount };
 const char* const kStageNames[kStCount] = {"embed_gather", "encoder_gemm", "layernorm", "qkv_gemm",
-                                           "attention", "out_proj_gemm", "ffn_up_gemm", "ffn_down_gemm",
+                                           "attention", "out_proj_gemm", "ffn_up_gemm", "ffn_down_gemm", "block_tail",
                                            "trunk", "critic", "head_tail"};
 struct Profiler {
   bool on = false;
@@ -96,6 +96,16 @@ int attention(const __half* qkv, int ld, const float* kb, int64_t B, int d, int 
   double fl = 4.0 * B * nq * kT * d;
   double by = (double)B * (kT * 2 * d + nq * d * 2) * 2 + (double)B * kT * 4;
   int rc = timed(st, fl, by, [&] { return attention29(qkv, ld, kb, B, d, H, q0, nq, out, ldo, st); });
+  g_stage = keep;
+  return rc;
+}
+
+int fused_tail(const BlockTailArgs& a, cudaStream_t st) {
+  int keep = g_stage;
+  g_stage = kStBlockTail;
+  double fl = 2.0 * a.M * ((double)a.d * a.d + 2.0 * a.d * a.F);
+  double by = (double)a.M * a.d * (2 + 4 + (a.x_out ? 4 : 0) + (a.out16[0] ? 2 : 0) + (a.out16[1] ? 2 : 0));
+  int rc = timed(st, fl, by, [&] { return block_tail(a, st); });
   g_stage = keep;
   return rc;
 }
@@ -174,12 +184,49 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
 
   BSRL_TRY(run_embed(c, obs, obs_dtype, x, key_bias));
 
+  // Fused block tail (out-projection + LayerNorm + FFN in one tcgen05 kernel) where the widths fit;
+  // it also emits the next block's LayerNorm rows (and the critic's), so the standalone LayerNorm
+  // kernel only runs ahead of block 0.
+  auto tail_args = [&](const BlockW& b, int64_t M) {
+    BlockTailArgs a;
+    memset(&a, 0, sizeof(a));
+    a.d = d; a.F = F; a.M = M;
+    a.att = att; a.ld_att = d;
+    a.x = x; a.ldx = d; a.xmap = ident;
+    a.wo = c.W(b.out); a.bo = c.Bv(b.out);
+    a.ln_g = c.G(b.ln_ffn); a.ln_b = c.Be(b.ln_ffn);
+    a.w0 = c.W(b.up); a.b0 = c.Bv(b.up);
+    a.w2 = c.W(b.down); a.b2 = c.Bv(b.down);
+    a.eps = eps;
+    return a;
+  };
+  bool fused = false;
+  {
+    BlockTailArgs probe = tail_args(l.blocks[0], R);
+    fused = g_engine == 0 && block_tail_ok(probe);
+  }
+  __half* hv = at<__half>(c.ws, w.enc_hid);   // critic LayerNorm rows (encoder scratch is free by now)
+  bool have_h = false, have_hv = false;
+
   for (int i = 0; i + 1 < l.L; ++i) {
     const BlockW& b = l.blocks[i];
-    BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
+    if (!have_h) BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
     g_stage = kStQkv;
     BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, R, 3 * d, d), c.st));
     BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 0, kT, att, d, c.st));
+    if (fused) {
+      const BlockW& nb = l.blocks[i + 1];
+      BlockTailArgs a = tail_args(b, R);
+      a.x_out = x;
+      a.out16[0] = h; a.ld16[0] = d; a.g16[0] = c.G(nb.ln_attn); a.b16[0] = c.Be(nb.ln_attn);
+      if (i + 2 == l.L) {
+        a.out16[1] = hv; a.ld16[1] = d; a.g16[1] = c.G(l.critic_ln); a.b16[1] = c.Be(l.critic_ln);
+        have_hv = true;
+      }
+      BSRL_TRY(fused_tail(a, c.st));
+      have_h = true;
+      continue;
+    }
     LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x, d, 1, 0, R, d, d);
     po.R = x; po.ldr = d;
     g_stage = kStOutProj;
@@ -199,7 +246,7 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   __half* lead16 = at<__half>(c.ws, w.lead16);
   {
     const BlockW& b = l.blocks[l.L - 1];
-    BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
+    if (!have_h) BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
     g_stage = kStQkv;
     BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv, d), d, c.Bv(b.qkv, d), qkv + d, 3 * d, 0, 0, R, 2 * d, d), c.st));
     LinearArgs pq = linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, Rl, d, d);
@@ -207,17 +254,24 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     pq.cmap = lead_rows;
     BSRL_TRY(linear(pq, c.st));
     BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 0, kLead, att, d, c.st));
-    LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x_lead, d, 1, 0, Rl, d, d);
-    po.R = x; po.ldr = d; po.rmap = lead_rows;
-    g_stage = kStOutProj;
-    BSRL_TRY(linear(po, c.st));
-    BSRL_TRY(layernorm(x_lead, d, ident, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, Rl, d, h_lead, d, c.st));
-    g_stage = kStFfnUp;
-    BSRL_TRY(linear(linear_args(h_lead, d, c.W(b.up), d, c.Bv(b.up), hid, F, 0, 1, Rl, F, d), c.st));
-    LinearArgs pd = linear_args(hid, F, c.W(b.down), F, c.Bv(b.down), lead16, d, 0, 0, Rl, d, F);
-    pd.R = x_lead; pd.ldr = d;
-    g_stage = kStFfnDown;
-    BSRL_TRY(linear(pd, c.st));
+    if (fused) {
+      BlockTailArgs a = tail_args(b, Rl);
+      a.xmap = lead_rows;
+      a.out16[0] = lead16; a.ld16[0] = d;     // plain fp16 rows: the trunk's GEMM operand
+      BSRL_TRY(fused_tail(a, c.st));
+    } else {
+      LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x_lead, d, 1, 0, Rl, d, d);
+      po.R = x; po.ldr = d; po.rmap = lead_rows;
+      g_stage = kStOutProj;
+      BSRL_TRY(linear(po, c.st));
+      BSRL_TRY(layernorm(x_lead, d, ident, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, Rl, d, h_lead, d, c.st));
+      g_stage = kStFfnUp;
+      BSRL_TRY(linear(linear_args(h_lead, d, c.W(b.up), d, c.Bv(b.up), hid, F, 0, 1, Rl, F, d), c.st));
+      LinearArgs pd = linear_args(hid, F, c.W(b.down), F, c.Bv(b.down), lead16, d, 0, 0, Rl, d, F);
+      pd.R = x_lead; pd.ldr = d;
+      g_stage = kStFfnDown;
+      BSRL_TRY(linear(pd, c.st));
+    }
   }
 
   // SimBa trunk on the (B, 5d) readout; its output h lands in z[:, d:]
@@ -247,9 +301,10 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   {
     const RowMap torso_rows{1, kT, 2};
     g_stage = kStCritic;
-    BSRL_TRY(layernorm(x, d, ident, c.G(l.critic_ln), c.Be(l.critic_ln), eps, R, d, h, d, c.st));
-    BSRL_TRY(linear(linear_args(h, d, c.W(l.critic_kv), d, c.Bv(l.critic_kv), qkv + d, 3 * d, 0, 0, R, 2 * d, d), c.st));
-    LinearArgs pq = linear_args(h, d, c.W(l.critic_q), d, c.Bv(l.critic_q), qkv, 3 * d, 0, 0, B, d, d);
+    const __half* hc = have_hv ? hv : h;
+    if (!have_hv) BSRL_TRY(layernorm(x, d, ident, c.G(l.critic_ln), c.Be(l.critic_ln), eps, R, d, h, d, c.st));
+    BSRL_TRY(linear(linear_args(hc, d, c.W(l.critic_kv), d, c.Bv(l.critic_kv), qkv + d, 3 * d, 0, 0, R, 2 * d, d), c.st));
+    LinearArgs pq = linear_args(hc, d, c.W(l.critic_q), d, c.Bv(l.critic_q), qkv, 3 * d, 0, 0, B, d, d);
     pq.amap = torso_rows;
     pq.cmap = torso_rows;
     BSRL_TRY(linear(pq, c.st));
@@ -541,6 +596,24 @@ int bsrl_linear(const void* a_f16, const void* w_f16, const float* bias, const f
   }
   set_error("linear: engine must be 0 (warp-MMA) or 1 (tcgen05)");
   return BSRL_ERR_UNSUPPORTED;
+}
+
+int bsrl_block_tail(const void* att_f16, const float* x, const void* wo_f16, const float* bo,
+                    const float* ln_g, const float* ln_b, const void* w0_f16, const float* b0,
+                    const void* w2_f16, const float* b2, float eps, int64_t m, int32_t d, int32_t f,
+                    float* x_out, void* ln_out_f16, const float* out_g, const float* out_b, void* stream) {
+  BlockTailArgs a;
+  memset(&a, 0, sizeof(a));
+  a.d = d; a.F = f; a.M = m;
+  a.att = static_cast<const __half*>(att_f16); a.ld_att = d;
+  a.x = x; a.ldx = d; a.xmap = identity_map();
+  a.wo = static_cast<const __half*>(wo_f16); a.bo = bo; a.ln_g = ln_g; a.ln_b = ln_b;
+  a.w0 = static_cast<const __half*>(w0_f16); a.b0 = b0;
+  a.w2 = static_cast<const __half*>(w2_f16); a.b2 = b2;
+  a.eps = eps;
+  a.x_out = x_out;
+  a.out16[0] = static_cast<__half*>(ln_out_f16); a.ld16[0] = d; a.g16[0] = out_g; a.b16[0] = out_b;
+  return block_tail(a, as_stream(stream));
 }
 
 int bsrl_attention(const void* qkv_f16, const float* key_bias, int64_t n_envs, int32_t d, int32_t n_heads,

@@ -1,0 +1,532 @@
+// Fused tail of one transformer block on tcgen05 / TMEM, one 128-row token tile at a time:
+//
+//   x1   = x + att Wo^T + bo                      (attention out-projection + residual)
+//   h2   = LN_ffn(x1)                             (fp32 statistics, fp16 operand)
+//   xo   = x1 + relu(h2 W0^T + b0) W2^T + b2      (FFN; the 4d-wide hidden never leaves the SM)
+//   out  : xo (fp32, optional), and up to two fp16 rows  LN_a(xo), LN_b(xo)  or plain fp16(xo)
+//
+// This is the reference's out_proj + ln_ffn.forward_add + fused_ffn(+ next LayerNorm) chain
+// (python/policy.py:655-715; ffn_fused_kernel, python/beat_arena_env/csrc/fused_ffn.cu:242-485)
+// as ONE kernel.  HBM traffic per token: read att (2d B) + x (4d B), write xo (4d B) + LN rows
+// (2d B each) -- against 18 d^2 FLOP, i.e. tensor-bound.
+//
+// Layout of one CTA (persistent, one per SM, 224 threads):
+//   warp 0       TMA producer: att tile -> sA (d/64 chunks of [128 x 64], 128B swizzle);
+//                weight tiles -> a 3-stage ring of 32 KB stages, in the MMA's consumption order
+//   warp 6       TMA producer of the attention tiles (sA is freed before the tile ends)
+//   warp 1       MMA issuer (one thread): tcgen05.mma, M = 128, K = 16
+//   warps 2..5   epilogue, thread = row: LayerNorm on TMEM rows -> h2 into sA; bias + ReLU of
+//                each 128-wide hidden chunk -> sH; final drain and LayerNorm outputs
+// TMEM (512 columns): region X (d columns) accumulates x1 and then xo in place -- x is
+// pre-stored there by the epilogue warps, so the out-projection and the FFN-down MMAs simply
+// accumulate onto it; the other 256 columns are two 128-column buffers for hidden chunks.  The
+// two regions swap roles every tile, so the next tile's x can be pre-stored and its
+// out-projection issued while this tile drains.
+//
+// Every wait is bounded (see tc5.cuh); on expiry the status word is set and all roles fall
+// through to the teardown.
+#include "kernels.cuh"
+#include "tc5.cuh"
+
+namespace bsrl {
+namespace {
+using namespace tc5;
+
+constexpr int BM = 128;          // rows per tile
+constexpr int HC = 128;          // hidden chunk width
+constexpr int STAGES = 3;
+constexpr int STAGE_BYTES = 32768;
+constexpr int CHUNK_BYTES = BM * 64 * 2;   // one [128 x 64] fp16 swizzled chunk
+constexpr int SA_BYTES = 4 * CHUNK_BYTES;  // d <= 256
+constexpr int SH_BYTES = 2 * CHUNK_BYTES;  // one 128 x 128 hidden chunk
+constexpr int THREADS = 7 * 32;
+constexpr int SMEM_BYTES = SA_BYTES + 2 * SH_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int KERNEL_ID = 2;
+
+struct Shared {
+  uint64_t w_full[STAGES], w_empty[STAGES];
+  uint64_t a_full, a_free, x_ready, o_done, h2_ready, x_done, mma_done;
+  uint64_t acc1_full[2], hid_ready[2], hid_free[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+struct TailParams {
+  int d, F;                 // embed, FFN hidden
+  int64_t M;                // rows
+  const float* x;           // residual in (fp32), rows mapped by xmap
+  int64_t ldx;
+  RowMap xmap;
+  const float* bo;          // (d)
+  const float* ln_g;        // ln_ffn gamma / beta (d)
+  const float* ln_b;
+  const float* b0;          // (F)
+  const float* b2;          // (d)
+  float eps;
+  float* x_out;             // (M, d) fp32 or nullptr
+  // up to two fp16 outputs: LayerNorm(xo) with (g, b), or plain fp16(xo) when g == nullptr
+  __half* out16[2];
+  int64_t ld16[2];
+  const float* g16[2];
+  const float* b16[2];
+  int n_tiles;
+  int* status;
+};
+
+__device__ __forceinline__ void give_up(Shared* sh, int* status, int role) {
+  atomicCAS(status, 0, KERNEL_ID * 16 + role);
+  sh->abort = 1;
+}
+
+#define TAIL_WAIT(bar, parity, role)                               \
+  if (!mbar_wait(smem_u32(bar), (parity), abort)) {                \
+    give_up(sh, p.status, role);                                   \
+    ok = false;                                                    \
+    break;                                                         \
+  }
+
+// four MMAs (K = 64) of one k-block: A chunk and B tile both [rows x 64] swizzled
+__device__ __forceinline__ void mma_kblock(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc,
+                                           bool acc_first) {
+  const uint64_t ad = smem_desc_sw128(a_addr), bd = smem_desc_sw128(b_addr);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) mma_f16_ss(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (acc_first || k) ? 1u : 0u);
+}
+
+__device__ __forceinline__ void load_f32x32(const float* src, uint32_t (&r)[32]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float4 v = reinterpret_cast<const float4*>(src)[j];
+    r[4 * j] = __float_as_uint(v.x); r[4 * j + 1] = __float_as_uint(v.y);
+    r[4 * j + 2] = __float_as_uint(v.z); r[4 * j + 3] = __float_as_uint(v.w);
+  }
+}
+
+// 32 fp32 values of row `row`, columns [col, col + 32) -> fp16 into a swizzled [128 x 64] chunk set
+__device__ __forceinline__ void store_h32(uint8_t* chunks, int row, int col, const float (&v)[32]) {
+  uint8_t* base = chunks + (col >> 6) * CHUNK_BYTES + (row >> 3) * 1024 + (row & 7) * 128;
+  const int p0 = (col & 63) >> 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 w = make_uint4(pack_half2(v[8 * i], v[8 * i + 1]), pack_half2(v[8 * i + 2], v[8 * i + 3]),
+                         pack_half2(v[8 * i + 4], v[8 * i + 5]), pack_half2(v[8 * i + 6], v[8 * i + 7]));
+    *reinterpret_cast<uint4*>(base + (((p0 + i) ^ (row & 7)) << 4)) = w;
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_constant__ CUtensorMap tm_wo,
+                  const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w2,
+                  TailParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - raw);
+  const uint32_t sA = base, sH = base + SA_BYTES, ring = sH + 2 * SH_BYTES;
+  uint8_t* sA_g = gen;
+  uint8_t* sH_g = gen + SA_BYTES;
+  Shared* sh = reinterpret_cast<Shared*>(gen + SA_BYTES + 2 * SH_BYTES + STAGES * STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int d = p.d, KB = d >> 6, NC = p.F / HC, S1 = (KB + 1) >> 1;
+  volatile int* abort = &sh->abort;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&sh->w_full[s]), 1);
+      mbar_init(smem_u32(&sh->w_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&sh->a_full), 1);
+    mbar_init(smem_u32(&sh->a_free), 1);
+    mbar_init(smem_u32(&sh->x_ready), 4);
+    mbar_init(smem_u32(&sh->o_done), 1);
+    mbar_init(smem_u32(&sh->h2_ready), 4);
+    mbar_init(smem_u32(&sh->x_done), 1);
+    mbar_init(smem_u32(&sh->mma_done), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh->acc1_full[b]), 1);
+      mbar_init(smem_u32(&sh->hid_ready[b]), 4);
+      mbar_init(smem_u32(&sh->hid_free[b]), 1);
+    }
+    sh->abort = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_att);
+    tma_prefetch_desc(&tm_wo);
+    tma_prefetch_desc(&tm_w0);
+    tma_prefetch_desc(&tm_w2);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&sh->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ weight producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      // one ring stage: wait for it to be free, arm the barrier, issue the loads
+      auto stage = [&](const CUtensorMap* map, int x0, int y0, int n_loads, uint32_t bytes_each) -> bool {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(smem_u32(&sh->w_empty[s]), ph ^ 1, abort)) { give_up(sh, p.status, 1); return false; }
+        const uint32_t bar = smem_u32(&sh->w_full[s]);
+        mbar_expect_tx(bar, bytes_each * n_loads);
+        for (int i = 0; i < n_loads; ++i)
+          tma_load_2d(ring + s * STAGE_BYTES + i * bytes_each, map, x0 + i * 64, y0, bar);
+        ++it;
+        return true;
+      };
+      auto g1 = [&](int j) -> bool {   // W0 rows [128 j, +128), two k-blocks per stage
+        for (int i = 0; i < S1; ++i) {
+          const int n = (2 * i + 1 < KB) ? 2 : 1;
+          if (!stage(&tm_w0, 128 * i, HC * j, n, HC * 128)) return false;
+        }
+        return true;
+      };
+      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+        for (int kb = 0; kb < KB && ok; ++kb) ok = stage(&tm_wo, 64 * kb, 0, 1, d * 128);
+        ok = ok && g1(0) && g1(1);
+        for (int j = 0; j < NC && ok; ++j) {
+          for (int kc = 0; kc < 2 && ok; ++kc) ok = stage(&tm_w2, HC * j + 64 * kc, 0, 1, d * 128);
+          if (ok && j + 2 < NC) ok = g1(j + 2);
+        }
+      }
+      // loads in flight must land before the CTA exits (bounded, ignoring abort)
+      for (uint32_t j = it > STAGES ? it - STAGES : 0; j < it; ++j) {
+        uint32_t spins = 0;
+        while (!mbar_try_wait(smem_u32(&sh->w_full[j % STAGES]), (j / STAGES) & 1) && ++spins < kSpinLimit) {}
+        if (spins >= kSpinLimit) give_up(sh, p.status, 2);
+      }
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------ attention-tile producer
+    if (lane == 0) {
+      uint32_t tile_i = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_i) {
+        if (!mbar_wait(smem_u32(&sh->a_free), (tile_i & 1) ^ 1, abort)) { give_up(sh, p.status, 3); ok = false; break; }
+        const uint32_t bar = smem_u32(&sh->a_full);
+        mbar_expect_tx(bar, KB * CHUNK_BYTES);
+        for (int c = 0; c < KB; ++c) tma_load_2d(sA + c * CHUNK_BYTES, &tm_att, 64 * c, t * BM, bar);
+      }
+      if (tile_i > 0) {
+        uint32_t spins = 0;
+        while (!mbar_try_wait(smem_u32(&sh->a_full), (tile_i - 1) & 1) && ++spins < kSpinLimit) {}
+        if (spins >= kSpinLimit) give_up(sh, p.status, 4);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tile_i = 0, n_hid[2] = {0, 0};
+      bool ok = true;
+      const uint32_t idesc_d = idesc_f16(BM, d), idesc_h = idesc_f16(BM, HC);
+      // consume one ring stage: wait, run `body(stage address)`, release the stage
+      auto with_stage = [&](auto&& body) -> bool {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(smem_u32(&sh->w_full[s]), ph, abort)) { give_up(sh, p.status, 5); return false; }
+        tc_fence_after();
+        body(ring + s * STAGE_BYTES);
+        tc_commit(smem_u32(&sh->w_empty[s]));
+        ++it;
+        return true;
+      };
+      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_i) {
+        const uint32_t par = tile_i & 1;
+        const uint32_t xcol = tmem_base + (par ? 256u : 0u);     // region X of this tile
+        const uint32_t acol = tmem_base + (par ? 0u : 256u);     // two hidden-chunk buffers
+        auto g1 = [&](int j) -> bool {                           // hidden chunk j = h2 W0[j]^T
+          const uint32_t dst = acol + (j & 1) * HC;
+          for (int i = 0; i < S1; ++i) {
+            if (!with_stage([&](uint32_t st) {
+                  mma_kblock(dst, sA + (2 * i) * CHUNK_BYTES, st, idesc_h, i != 0);
+                  if (2 * i + 1 < KB) mma_kblock(dst, sA + (2 * i + 1) * CHUNK_BYTES, st + HC * 128, idesc_h, true);
+                }))
+              return false;
+          }
+          tc_commit(smem_u32(&sh->acc1_full[j & 1]));
+          return true;
+        };
+        TAIL_WAIT(&sh->a_full, par, 6);
+        TAIL_WAIT(&sh->x_ready, par, 7);
+        tc_fence_after();
+        for (int kb = 0; kb < KB && ok; ++kb)       // x1 = x (pre-stored) + att Wo^T
+          ok = with_stage([&](uint32_t st) { mma_kblock(xcol, sA + kb * CHUNK_BYTES, st, idesc_d, true); });
+        if (!ok) break;
+        tc_commit(smem_u32(&sh->o_done));
+        TAIL_WAIT(&sh->h2_ready, par, 8);
+        tc_fence_after();
+        ok = g1(0) && g1(1);
+        if (NC == 2 && ok) tc_commit(smem_u32(&sh->a_free));
+        for (int j = 0; j < NC && ok; ++j) {
+          const int b = j & 1;
+          if (!mbar_wait(smem_u32(&sh->hid_ready[b]), n_hid[b] & 1, abort)) { give_up(sh, p.status, 9); ok = false; break; }
+          ++n_hid[b];
+          tc_fence_after();
+          for (int kc = 0; kc < 2 && ok; ++kc)      // xo += hidden chunk j * W2[:, chunk j]^T
+            ok = with_stage([&](uint32_t st) { mma_kblock(xcol, sH + b * SH_BYTES + kc * CHUNK_BYTES, st, idesc_d, true); });
+          if (ok && j + 2 < NC) {
+            ok = g1(j + 2);
+            if (ok && j + 3 == NC) tc_commit(smem_u32(&sh->a_free));   // last reader of h2 issued
+          }
+        }
+        if (ok) tc_commit(smem_u32(&sh->x_done));
+      }
+      tc_commit(smem_u32(&sh->mma_done));
+      uint32_t spins = 0;
+      while (!mbar_try_wait(smem_u32(&sh->mma_done), 0) && ++spins < kSpinLimit) {}
+      if (spins >= kSpinLimit) give_up(sh, p.status, 10);
+    }
+  } else if (warp >= 2 && warp <= 5) {
+    // ------------------------------------------------------------ epilogue warps, thread = row
+    const int q = warp & 3;
+    const int trow = q * 32 + lane;                         // row inside the tile
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    uint32_t tile_i = 0, n_acc[2] = {0, 0};
+    bool ok = true;
+    const float inv_d = 1.0f / (float)d;
+
+    // pre-store x rows of tile t, column block cb (128 wide), into TMEM region `col0`
+    auto prestore = [&](int t, int cb, uint32_t col0) {
+      const int64_t row = (int64_t)t * BM + trow;
+      const bool rok = row < p.M;
+      const float* xr = rok ? p.x + p.xmap(row) * p.ldx : nullptr;
+      const int c1 = min(d, cb * 128 + 128);
+      for (int c = cb * 128; c < c1; c += 32) {
+        uint32_t r[32];
+        if (rok) {
+          load_f32x32(xr + c, r);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        tmem_st32(lane_base + col0 + c, r);
+      }
+      tmem_wait_st();
+    };
+    auto signal = [&](uint64_t* bar) {   // one arrival per warp, after everyone's writes
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(bar));
+    };
+
+    if ((int)blockIdx.x < p.n_tiles) {
+      for (int cb = 0; cb * 128 < d; ++cb) prestore(blockIdx.x, cb, 0u);
+      signal(&sh->x_ready);
+    }
+    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_i) {
+      const uint32_t par = tile_i & 1;
+      const uint32_t xcol = par ? 256u : 0u, acol = par ? 0u : 256u;
+      const int t_next = t + gridDim.x;
+      // ---- E1: h2 = LN_ffn(x1 + bo) -> sA
+      TAIL_WAIT(&sh->o_done, par, 11);
+      tc_fence_after();
+      {
+        float sum = 0.f;
+        for (int c = 0; c < d; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(lane_base + xcol + c, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum += __uint_as_float(r[j]) + p.bo[c + j];
+        }
+        const float mean = sum * inv_d;
+        float sq = 0.f;
+        for (int c = 0; c < d; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(lane_base + xcol + c, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float dv = __uint_as_float(r[j]) + p.bo[c + j] - mean;
+            sq += dv * dv;
+          }
+        }
+        const float rstd = rsqrtf(sq * inv_d + p.eps);
+        for (int c = 0; c < d; c += 32) {
+          uint32_t r[32];
+          float v[32];
+          tmem_ld32(lane_base + xcol + c, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            v[j] = (__uint_as_float(r[j]) + p.bo[c + j] - mean) * rstd * p.ln_g[c + j] + p.ln_b[c + j];
+          store_h32(sA_g, trow, c, v);
+        }
+      }
+      fence_proxy_async_smem();
+      signal(&sh->h2_ready);
+      // ---- hidden chunks: relu(acc + b0) -> sH
+      for (int j = 0; j < NC && ok; ++j) {
+        const int b = j & 1;
+        if (!mbar_wait(smem_u32(&sh->acc1_full[b]), n_acc[b] & 1, abort)) {
+          if (lane == 0) give_up(sh, p.status, 12);
+          ok = false;
+          break;
+        }
+        ++n_acc[b];
+        tc_fence_after();
+        for (int c = 0; c < HC; c += 32) {
+          uint32_t r[32];
+          float v[32];
+          tmem_ld32(lane_base + acol + b * HC + c, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) v[jj] = fmaxf(__uint_as_float(r[jj]) + p.b0[j * HC + c + jj], 0.f);
+          store_h32(sH_g + b * SH_BYTES, trow, c, v);
+        }
+        fence_proxy_async_smem();
+        signal(&sh->hid_ready[b]);
+        // the buffers of the last two chunks are free now: pre-store the next tile's x there
+        if (t_next < p.n_tiles && j + 2 >= NC) {
+          const int cb = j + 2 - NC;               // NC-2 -> block 0, NC-1 -> block 1
+          if (cb * 128 < d) prestore(t_next, cb, acol);
+          if (j + 1 == NC) signal(&sh->x_ready);
+        }
+      }
+      if (!ok) break;
+      // ---- final: xo = X + bo + b2 -> fp32 out, LayerNorm / fp16 outputs
+      TAIL_WAIT(&sh->x_done, par, 13);
+      tc_fence_after();
+      {
+        const int64_t row = (int64_t)t * BM + trow;
+        const bool rok = row < p.M;
+        const bool need_stats = (p.out16[0] && p.g16[0]) || (p.out16[1] && p.g16[1]);
+        float sum = 0.f;
+        if (p.x_out || need_stats) {
+          for (int c = 0; c < d; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(lane_base + xcol + c, r);
+            tmem_wait_ld();
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              v[j] = __uint_as_float(r[j]) + p.bo[c + j] + p.b2[c + j];
+              sum += v[j];
+            }
+            if (p.x_out && rok) {
+              float4* dst = reinterpret_cast<float4*>(p.x_out + row * d + c);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+          }
+        }
+        const float mean = sum * inv_d;
+        float rstd = 1.f;
+        if (need_stats) {
+          float sq = 0.f;
+          for (int c = 0; c < d; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(lane_base + xcol + c, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float dv = __uint_as_float(r[j]) + p.bo[c + j] + p.b2[c + j] - mean;
+              sq += dv * dv;
+            }
+          }
+          rstd = rsqrtf(sq * inv_d + p.eps);
+        }
+        if (p.out16[0] || p.out16[1]) {
+          for (int c = 0; c < d; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(lane_base + xcol + c, r);
+            tmem_wait_ld();
+            if (!rok) continue;
+#pragma unroll
+            for (int o = 0; o < 2; ++o) {
+              if (!p.out16[o]) continue;
+              uint32_t h[16];
+              if (p.g16[o]) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const int c0 = c + 2 * j;
+                  float a0 = (__uint_as_float(r[2 * j]) + p.bo[c0] + p.b2[c0] - mean) * rstd * p.g16[o][c0] + p.b16[o][c0];
+                  float a1 = (__uint_as_float(r[2 * j + 1]) + p.bo[c0 + 1] + p.b2[c0 + 1] - mean) * rstd * p.g16[o][c0 + 1] + p.b16[o][c0 + 1];
+                  h[j] = pack_half2(a0, a1);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const int c0 = c + 2 * j;
+                  h[j] = pack_half2(__uint_as_float(r[2 * j]) + p.bo[c0] + p.b2[c0],
+                                    __uint_as_float(r[2 * j + 1]) + p.bo[c0 + 1] + p.b2[c0 + 1]);
+                }
+              }
+              uint4* dst = reinterpret_cast<uint4*>(p.out16[o] + row * p.ld16[o] + c);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) dst[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+}  // namespace
+
+bool block_tail_ok(const BlockTailArgs& a) {
+  if (a.d % 64 != 0 || a.d < 64 || a.d > 256) return false;
+  if (a.F % 256 != 0 || a.F < 256) return false;
+  if (a.M < 1 || a.M > (int64_t)0x7fffffff * 64) return false;
+  if (!aligned16(a.att) || !aligned16(a.x) || (a.ldx % 4) || (a.ld_att % 8)) return false;
+  if (a.x_out && !aligned16(a.x_out)) return false;
+  for (int o = 0; o < 2; ++o)
+    if (a.out16[o] && (!aligned16(a.out16[o]) || (a.ld16[o] % 8))) return false;
+  return true;
+}
+
+int block_tail(const BlockTailArgs& a, cudaStream_t stream) {
+  if (!block_tail_ok(a)) {
+    set_error("block_tail: shape d=%d F=%d m=%lld does not fit the fused kernel", a.d, a.F, (long long)a.M);
+    return BSRL_ERR_UNSUPPORTED;
+  }
+  if (!a.att || !a.x || !a.wo || !a.w0 || !a.w2 || !a.bo || !a.b0 || !a.b2 || !a.ln_g || !a.ln_b) {
+    set_error("block_tail: NULL operand");
+    return BSRL_ERR_NULL;
+  }
+  int* status = device_status_ptr();
+  if (!status) return BSRL_ERR_CUDA;
+  CUtensorMap tm_att, tm_wo, tm_w0, tm_w2;
+  if (!make_tmap_f16(&tm_att, a.att, a.M, a.d, a.ld_att, BM)) return BSRL_ERR_CUDA;
+  if (!make_tmap_f16(&tm_wo, a.wo, a.d, a.d, a.d, a.d)) return BSRL_ERR_CUDA;
+  if (!make_tmap_f16(&tm_w0, a.w0, a.F, a.d, a.d, HC)) return BSRL_ERR_CUDA;
+  if (!make_tmap_f16(&tm_w2, a.w2, a.d, a.F, a.F, a.d)) return BSRL_ERR_CUDA;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  BSRL_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    BSRL_CUDA_OK(cudaFuncSetAttribute(block_tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr_set[dev] = true;
+  }
+  TailParams p;
+  p.d = a.d; p.F = a.F; p.M = a.M;
+  p.x = a.x; p.ldx = a.ldx; p.xmap = a.xmap;
+  p.bo = a.bo; p.ln_g = a.ln_g; p.ln_b = a.ln_b; p.b0 = a.b0; p.b2 = a.b2; p.eps = a.eps;
+  p.x_out = a.x_out;
+  for (int o = 0; o < 2; ++o) {
+    p.out16[o] = a.out16[o]; p.ld16[o] = a.ld16[o]; p.g16[o] = a.g16[o]; p.b16[o] = a.b16[o];
+  }
+  p.n_tiles = (int)((a.M + BM - 1) / BM);
+  p.status = status;
+  int grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
+  block_tail_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_att, tm_wo, tm_w0, tm_w2, p);
+  BSRL_LAUNCH_OK("block_tail_kernel");
+  return BSRL_OK;
+}
+
+}  // namespace bsrl

@@ -30,6 +30,33 @@ int linear_mma(const LinearArgs& p, cudaStream_t stream);   // warp-MMA engine
 int linear_tc5(const LinearArgs& p, cudaStream_t stream);   // tcgen05 / TMEM engine
 bool linear_tc5_ok(const LinearArgs& p);                     // shape fits the tcgen05 engine
 
+// Fused block tail (out-projection + residual + LayerNorm + FFN + residual + output LayerNorms).
+struct BlockTailArgs {
+  int d, F;
+  int64_t M;
+  const __half* att;   // (M, d) f16
+  int ld_att;
+  const float* x;      // residual stream in, f32, rows mapped by xmap
+  int64_t ldx;
+  RowMap xmap;
+  const __half* wo;    // (d, d)
+  const float* bo;
+  const float* ln_g;   // ln_ffn
+  const float* ln_b;
+  const __half* w0;    // (F, d)
+  const float* b0;
+  const __half* w2;    // (d, F)
+  const float* b2;
+  float eps;
+  float* x_out;        // (M, d) f32 or nullptr
+  __half* out16[2];    // fp16 outputs: LayerNorm(xo) with (g16, b16), or plain cast when g16 is null
+  int64_t ld16[2];
+  const float* g16[2];
+  const float* b16[2];
+};
+bool block_tail_ok(const BlockTailArgs& a);
+int block_tail(const BlockTailArgs& a, cudaStream_t stream);
+
 // y(f16, ldy) = LayerNorm(x(f32, ldx)) per row, fp32 statistics.
 int layernorm_rows(const float* x, int64_t ldx, RowMap xmap, const float* gamma, const float* beta,
                    float eps, int64_t rows, int d, __half* y, int64_t ldy, cudaStream_t stream);

@@ -143,8 +143,21 @@ int bsrl_linear(const void* a_f16, const void* w_f16, const float* bias, const f
 int bsrl_attention(const void* qkv_f16, const float* key_bias, int64_t n_envs, int32_t d,
                    int32_t n_heads, int32_t q_first, int32_t n_q, void* out_f16, void* stream);
 
+/* Fused tail of one transformer block on a (m, d) token stream, one tcgen05 kernel:
+ *   x1 = x + att Wo^T + bo;  xo = x1 + relu(LN(x1; ln_g, ln_b) W0^T + b0) W2^T + b2
+ * att (m, d) f16, x (m, d) f32, Wo (d, d), W0 (f, d), W2 (d, f) f16 row-major.  Outputs (either
+ * may be NULL): x_out (m, d) f32 (may alias x), ln_out (m, d) f16 = LayerNorm(xo; out_g, out_b),
+ * or fp16(xo) when out_g is NULL.  d in {64, 128, 192, 256}, f % 256 == 0.
+ * Replaces out_proj + ln_ffn.forward_add + fused_ffn (python/policy.py:655-715; ffn_fused,
+ * python/beat_arena_env/csrc/fused_ffn.cu:551-619). */
+int bsrl_block_tail(const void* att_f16, const float* x, const void* wo_f16, const float* bo,
+                    const float* ln_g, const float* ln_b, const void* w0_f16, const float* b0,
+                    const void* w2_f16, const float* b2, float eps, int64_t m, int32_t d, int32_t f,
+                    float* x_out, void* ln_out_f16, const float* out_g, const float* out_b, void* stream);
+
 /* Which GEMM kernel the forward's linear layers use: 0 (default) = the tcgen05/TMEM kernel
- * wherever the shape fits it, the warp-MMA kernel elsewhere; 1 = the warp-MMA kernel everywhere.
+ * wherever the shape fits it (and the fused block-tail kernel), the warp-MMA kernel elsewhere;
+ * 1 = the warp-MMA kernel and separate LayerNorm kernels everywhere.
  * Both are CUDA kernels of this library; 1 exists so tests can cross-check one against the
  * other.  No counterpart in the reference. */
 int bsrl_set_engine(int32_t engine);

@@ -111,3 +111,42 @@ def test_embed(native, case, obs_f16):
     tokens, bias = po.embed_tokens(sd, cfg, obs.float())
     torch.testing.assert_close(kb.cpu(), bias, atol=0, rtol=0)
     torch.testing.assert_close(x.cpu().view(B, 29, -1), tokens, atol=6e-3, rtol=5e-3)
+
+
+@pytest.mark.parametrize("m,d,f,ln_out", [(128, 256, 1024, True), (1000, 256, 1024, True), (37, 128, 512, True),
+                                          (5 * 77, 256, 1024, False), (20000, 192, 768, True), (40000, 256, 1024, True)])
+def test_block_tail(native, m, d, f, ln_out):
+    """Fused out-projection + LayerNorm + FFN kernel against the same chain in torch fp32 on the
+    same fp16-rounded operands."""
+    g = torch.Generator().manual_seed(m + d)
+    att = torch.randn(m, d, generator=g).half().cuda()
+    x = (torch.randn(m, d, generator=g) * 2).cuda()
+    wo = (torch.randn(d, d, generator=g) / d ** 0.5).half().cuda()
+    w0 = (torch.randn(f, d, generator=g) / d ** 0.5).half().cuda()
+    w2 = (torch.randn(d, f, generator=g) / f ** 0.5).half().cuda()
+    bo, b2 = torch.randn(d, generator=g).cuda() * 0.1, torch.randn(d, generator=g).cuda() * 0.1
+    b0 = torch.randn(f, generator=g).cuda() * 0.1
+    lg, lb = (1 + 0.1 * torch.randn(d, generator=g)).cuda(), (0.1 * torch.randn(d, generator=g)).cuda()
+    og, ob = (1 + 0.1 * torch.randn(d, generator=g)).cuda(), (0.1 * torch.randn(d, generator=g)).cuda()
+    x_out = torch.empty_like(x)
+    out16 = torch.empty(m, d, dtype=torch.float16, device="cuda")
+    native.check(native.lib.bsrl_block_tail(
+        att.data_ptr(), x.data_ptr(), wo.data_ptr(), bo.data_ptr(), lg.data_ptr(), lb.data_ptr(),
+        w0.data_ptr(), b0.data_ptr(), w2.data_ptr(), b2.data_ptr(), 1e-5, m, d, f, x_out.data_ptr(),
+        out16.data_ptr(), og.data_ptr() if ln_out else None, ob.data_ptr() if ln_out else None, _stream()))
+    native.check(native.lib.bsrl_device_status())
+    x1 = x + att.float() @ wo.float().t() + bo
+    h2 = F.layer_norm(x1, (d,), lg, lb, 1e-5).half().float()
+    hid = (h2 @ w0.float().t() + b0).relu().half().float()
+    xo = x1 + hid @ w2.float().t() + b2
+    torch.testing.assert_close(x_out, xo, atol=3e-3, rtol=1e-3)
+    ref16 = F.layer_norm(xo, (d,), og, ob, 1e-5) if ln_out else xo
+    torch.testing.assert_close(out16.float(), ref16, atol=8e-3, rtol=2e-3)
+    # in place on the residual stream, as the forward runs it
+    x_in = x.clone()
+    native.check(native.lib.bsrl_block_tail(
+        att.data_ptr(), x_in.data_ptr(), wo.data_ptr(), bo.data_ptr(), lg.data_ptr(), lb.data_ptr(),
+        w0.data_ptr(), b0.data_ptr(), w2.data_ptr(), b2.data_ptr(), 1e-5, m, d, f, x_in.data_ptr(),
+        None, None, None, _stream()))
+    native.check(native.lib.bsrl_device_status())
+    assert torch.equal(x_in, x_out)
