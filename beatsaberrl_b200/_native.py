@@ -10,7 +10,7 @@ import re
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
-LIB_PATH = PKG / "_lib" / "libbsrl.so"
+LIB_PATH = Path(__import__("os").environ.get("BSRL_LIB") or PKG / "_lib" / "libbsrl.so")   # BSRL_LIB: alternative build
 HEADER = PKG.parent / "include" / "bsrl.h"
 
 N_ACT_HEADS = 29

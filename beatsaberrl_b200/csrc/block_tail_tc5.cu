@@ -16,7 +16,9 @@
 //   warp 6       TMA producer of the attention tiles (sA is freed before the tile ends)
 //   warp 1       MMA issuer (one thread): tcgen05.mma, M = 128, K = 16
 //   warps 2..5   epilogue, thread = row: LayerNorm on TMEM rows -> h2 into sA; bias + ReLU of
-//                each 128-wide hidden chunk -> sH; final drain and LayerNorm outputs
+//                each 128-wide hidden chunk -> sH; final drain and LayerNorm outputs; all global
+//                traffic goes through a per-warp transposition buffer so that it is coalesced;
+//                the per-column parameters live in shared memory
 // TMEM (512 columns): region X (d columns) accumulates x1 and then xo in place -- x is
 // pre-stored there by the epilogue warps, so the out-projection and the FFN-down MMAs simply
 // accumulate onto it; the other 256 columns are two 128-column buffers for hidden chunks.  The
@@ -40,13 +42,15 @@ constexpr int CHUNK_BYTES = BM * 64 * 2;   // one [128 x 64] fp16 swizzled chunk
 constexpr int SA_BYTES = 4 * CHUNK_BYTES;  // d <= 256
 constexpr int SH_BYTES = 2 * CHUNK_BYTES;  // one 128 x 128 hidden chunk
 constexpr int THREADS = 7 * 32;
-constexpr int SMEM_BYTES = SA_BYTES + 2 * SH_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int STG_BYTES = 32 * 128;              // per-warp transposition buffer (32 rows x 128 B)
+constexpr int PARAM_FLOATS = 8 * 256 + 1024;     // bo, ln_g, ln_b, b2, g16[2], b16[2] (d each) + b0 (F)
+constexpr int SMEM_BYTES = SA_BYTES + SH_BYTES + STAGES * STAGE_BYTES + 4 * STG_BYTES + PARAM_FLOATS * 4 + 1024 + 256;
 constexpr int KERNEL_ID = 2;
 
 struct Shared {
   uint64_t w_full[STAGES], w_empty[STAGES];
   uint64_t a_full, a_free, x_ready, o_done, h2_ready, x_done, mma_done;
-  uint64_t acc1_full[2], hid_ready[2], hid_free[2];
+  uint64_t acc1_full[2], hid_ready, hid_free;
   uint32_t tmem_base;
   int abort;
 };
@@ -73,6 +77,19 @@ struct TailParams {
   int* status;
 };
 
+#ifdef BSRL_TRACE
+__device__ long long g_trace[2 * 8192];
+__device__ int g_trace_n = 0;
+__device__ __forceinline__ void trace(int tag, long long val = -1) {
+  if (blockIdx.x != 0) return;
+  int i = atomicAdd(&g_trace_n, 1);
+  if (i < 8192) { g_trace[2 * i] = tag; g_trace[2 * i + 1] = val >= 0 ? val : clock64(); }
+}
+#define TRACE(...) trace(__VA_ARGS__)
+#else
+#define TRACE(...)
+#endif
+
 __device__ __forceinline__ void give_up(Shared* sh, int* status, int role) {
   atomicCAS(status, 0, KERNEL_ID * 16 + role);
   sh->abort = 1;
@@ -91,15 +108,6 @@ __device__ __forceinline__ void mma_kblock(uint32_t d_tmem, uint32_t a_addr, uin
   const uint64_t ad = smem_desc_sw128(a_addr), bd = smem_desc_sw128(b_addr);
 #pragma unroll
   for (int k = 0; k < 4; ++k) mma_f16_ss(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (acc_first || k) ? 1u : 0u);
-}
-
-__device__ __forceinline__ void load_f32x32(const float* src, uint32_t (&r)[32]) {
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    float4 v = reinterpret_cast<const float4*>(src)[j];
-    r[4 * j] = __float_as_uint(v.x); r[4 * j + 1] = __float_as_uint(v.y);
-    r[4 * j + 2] = __float_as_uint(v.z); r[4 * j + 3] = __float_as_uint(v.w);
-  }
 }
 
 // 32 fp32 values of row `row`, columns [col, col + 32) -> fp16 into a swizzled [128 x 64] chunk set
@@ -122,10 +130,12 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw);
-  const uint32_t sA = base, sH = base + SA_BYTES, ring = sH + 2 * SH_BYTES;
+  const uint32_t sA = base, sH = base + SA_BYTES, ring = sH + SH_BYTES;
   uint8_t* sA_g = gen;
   uint8_t* sH_g = gen + SA_BYTES;
-  Shared* sh = reinterpret_cast<Shared*>(gen + SA_BYTES + 2 * SH_BYTES + STAGES * STAGE_BYTES);
+  uint8_t* stg_all = gen + SA_BYTES + SH_BYTES + STAGES * STAGE_BYTES;
+  float* prm = reinterpret_cast<float*>(stg_all + 4 * STG_BYTES);
+  Shared* sh = reinterpret_cast<Shared*>(stg_all + 4 * STG_BYTES + PARAM_FLOATS * 4);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int d = p.d, KB = d >> 6, NC = p.F / HC, S1 = (KB + 1) >> 1;
   volatile int* abort = &sh->abort;
@@ -142,11 +152,9 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     mbar_init(smem_u32(&sh->h2_ready), 4);
     mbar_init(smem_u32(&sh->x_done), 1);
     mbar_init(smem_u32(&sh->mma_done), 1);
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&sh->acc1_full[b]), 1);
-      mbar_init(smem_u32(&sh->hid_ready[b]), 4);
-      mbar_init(smem_u32(&sh->hid_free[b]), 1);
-    }
+    for (int b = 0; b < 2; ++b) mbar_init(smem_u32(&sh->acc1_full[b]), 1);
+    mbar_init(smem_u32(&sh->hid_ready), 4);
+    mbar_init(smem_u32(&sh->hid_free), 1);
     sh->abort = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_att);
@@ -158,6 +166,19 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     tmem_alloc(smem_u32(&sh->tmem_base), 512);
     tmem_relinquish();
   }
+  // per-column parameters into shared memory: [bo | ln_g | ln_b | b2 | g16_0 | b16_0 | g16_1 | b16_1] (256
+  // floats each) then b0 (F floats); absent vectors read as gamma = 1, beta = 0
+  for (int i = threadIdx.x; i < 8 * 256; i += THREADS) {
+    const int which = i >> 8, c = i & 255;
+    float v = (which == 4 || which == 6) ? 1.f : 0.f;
+    if (c < d) {
+      const float* src = which == 0 ? p.bo : which == 1 ? p.ln_g : which == 2 ? p.ln_b : which == 3 ? p.b2
+                       : which == 4 ? p.g16[0] : which == 5 ? p.b16[0] : which == 6 ? p.g16[1] : p.b16[1];
+      if (src) v = src[c];
+    }
+    prm[i] = v;
+  }
+  for (int i = threadIdx.x; i < p.F; i += THREADS) prm[8 * 256 + i] = p.b0[i];
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -222,14 +243,20 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      uint32_t it = 0, tile_i = 0, n_hid[2] = {0, 0};
+      uint32_t it = 0, tile_i = 0, n_hid = 0;
       bool ok = true;
       const uint32_t idesc_d = idesc_f16(BM, d), idesc_h = idesc_f16(BM, HC);
       // consume one ring stage: wait, run `body(stage address)`, release the stage
       auto with_stage = [&](auto&& body) -> bool {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
+#ifdef BSRL_TRACE
+        long long t0 = clock64();
+#endif
         if (!mbar_wait(smem_u32(&sh->w_full[s]), ph, abort)) { give_up(sh, p.status, 5); return false; }
+#ifdef BSRL_TRACE
+        TRACE(160, clock64() - t0);
+#endif
         tc_fence_after();
         body(ring + s * STAGE_BYTES);
         tc_commit(smem_u32(&sh->w_empty[s]));
@@ -255,27 +282,33 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         TAIL_WAIT(&sh->a_full, par, 6);
         TAIL_WAIT(&sh->x_ready, par, 7);
         tc_fence_after();
+        TRACE(100);
         for (int kb = 0; kb < KB && ok; ++kb)       // x1 = x (pre-stored) + att Wo^T
           ok = with_stage([&](uint32_t st) { mma_kblock(xcol, sA + kb * CHUNK_BYTES, st, idesc_d, true); });
         if (!ok) break;
         tc_commit(smem_u32(&sh->o_done));
+        TRACE(101);
         TAIL_WAIT(&sh->h2_ready, par, 8);
         tc_fence_after();
+        TRACE(102);
         ok = g1(0) && g1(1);
         if (NC == 2 && ok) tc_commit(smem_u32(&sh->a_free));
         for (int j = 0; j < NC && ok; ++j) {
-          const int b = j & 1;
-          if (!mbar_wait(smem_u32(&sh->hid_ready[b]), n_hid[b] & 1, abort)) { give_up(sh, p.status, 9); ok = false; break; }
-          ++n_hid[b];
+          if (!mbar_wait(smem_u32(&sh->hid_ready), n_hid & 1, abort)) { give_up(sh, p.status, 9); ok = false; break; }
+          ++n_hid;
           tc_fence_after();
+          TRACE(110 + j);
           for (int kc = 0; kc < 2 && ok; ++kc)      // xo += hidden chunk j * W2[:, chunk j]^T
-            ok = with_stage([&](uint32_t st) { mma_kblock(xcol, sH + b * SH_BYTES + kc * CHUNK_BYTES, st, idesc_d, true); });
+            ok = with_stage([&](uint32_t st) { mma_kblock(xcol, sH + kc * CHUNK_BYTES, st, idesc_d, true); });
+          if (ok) tc_commit(smem_u32(&sh->hid_free));   // sH may be overwritten once these MMAs retire
+          TRACE(130 + j);
           if (ok && j + 2 < NC) {
             ok = g1(j + 2);
             if (ok && j + 3 == NC) tc_commit(smem_u32(&sh->a_free));   // last reader of h2 issued
           }
         }
         if (ok) tc_commit(smem_u32(&sh->x_done));
+        TRACE(150);
       }
       tc_commit(smem_u32(&sh->mma_done));
       uint32_t spins = 0;
@@ -284,28 +317,52 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     }
   } else if (warp >= 2 && warp <= 5) {
     // ------------------------------------------------------------ epilogue warps, thread = row
+    // TMEM gives every thread one row.  Global memory is touched only in "transposed" form:
+    // a 32-row x 128-byte block goes through the warp's staging buffer so that 8 lanes cover one
+    // full 128-byte line (lane = (row sub + 4 i, 16-byte piece)).
     const int q = warp & 3;
     const int trow = q * 32 + lane;                         // row inside the tile
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-    uint32_t tile_i = 0, n_acc[2] = {0, 0};
+    uint8_t* stg = stg_all + (warp - 2) * STG_BYTES;
+    const int sub = lane >> 3, piece = lane & 7;
+    const float4* prm4 = reinterpret_cast<const float4*>(prm);
+    // parameter vectors (float4 index = column / 4)
+    const float4 *P_bo = prm4, *P_g = prm4 + 64, *P_b = prm4 + 128, *P_b2 = prm4 + 192, *P_b0 = prm4 + 512;
+    uint32_t tile_i = 0, n_acc[2] = {0, 0}, n_free = 0;
     bool ok = true;
     const float inv_d = 1.0f / (float)d;
 
-    // pre-store x rows of tile t, column block cb (128 wide), into TMEM region `col0`
+    auto stg_write = [&](int row, int pc, uint4 v) {       // piece pc of row -> staging
+      *reinterpret_cast<uint4*>(stg + row * 128 + ((pc ^ (row & 7)) << 4)) = v;
+    };
+    auto stg_read = [&](int row, int pc) -> uint4 {
+      return *reinterpret_cast<const uint4*>(stg + row * 128 + ((pc ^ (row & 7)) << 4));
+    };
+    // pre-store (x + bo) rows of tile t, column block cb (128 wide), into TMEM columns col0 + ...
     auto prestore = [&](int t, int cb, uint32_t col0) {
-      const int64_t row = (int64_t)t * BM + trow;
-      const bool rok = row < p.M;
-      const float* xr = rok ? p.x + p.xmap(row) * p.ldx : nullptr;
       const int c1 = min(d, cb * 128 + 128);
       for (int c = cb * 128; c < c1; c += 32) {
-        uint32_t r[32];
-        if (rok) {
-          load_f32x32(xr + c, r);
-        } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        for (int i = 0; i < 8; ++i) {                       // coalesced: 4 rows x 128 B per instruction
+          const int rr = i * 4 + sub;
+          const int64_t row = (int64_t)t * BM + q * 32 + rr;
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (row < p.M) v = *reinterpret_cast<const uint4*>(p.x + p.xmap(row) * p.ldx + c + piece * 4);
+          stg_write(rr, piece, v);
+        }
+        __syncwarp();
+        uint32_t r[32];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 v = stg_read(lane, j);
+          const float4 bo = P_bo[(c >> 2) + j];
+          r[4 * j] = __float_as_uint(__uint_as_float(v.x) + bo.x);
+          r[4 * j + 1] = __float_as_uint(__uint_as_float(v.y) + bo.y);
+          r[4 * j + 2] = __float_as_uint(__uint_as_float(v.z) + bo.z);
+          r[4 * j + 3] = __float_as_uint(__uint_as_float(v.w) + bo.w);
         }
         tmem_st32(lane_base + col0 + c, r);
+        __syncwarp();
       }
       tmem_wait_st();
     };
@@ -323,45 +380,46 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       const uint32_t par = tile_i & 1;
       const uint32_t xcol = par ? 256u : 0u, acol = par ? 0u : 256u;
       const int t_next = t + gridDim.x;
-      // ---- E1: h2 = LN_ffn(x1 + bo) -> sA
+      // ---- E1: h2 = LN_ffn(x1) -> sA   (X already holds x + bo + att Wo^T)
       TAIL_WAIT(&sh->o_done, par, 11);
       tc_fence_after();
+      if (warp == 2 && lane == 0) TRACE(200);
       {
-        float sum = 0.f;
-        for (int c = 0; c < d; c += 32) {
-          uint32_t r[32];
-          tmem_ld32(lane_base + xcol + c, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) sum += __uint_as_float(r[j]) + p.bo[c + j];
-        }
-        const float mean = sum * inv_d;
-        float sq = 0.f;
+        float sum = 0.f, sq = 0.f;
         for (int c = 0; c < d; c += 32) {
           uint32_t r[32];
           tmem_ld32(lane_base + xcol + c, r);
           tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            float dv = __uint_as_float(r[j]) + p.bo[c + j] - mean;
-            sq += dv * dv;
+            const float v = __uint_as_float(r[j]);
+            sum += v;
+            sq = fmaf(v, v, sq);
           }
         }
-        const float rstd = rsqrtf(sq * inv_d + p.eps);
+        const float mean = sum * inv_d;
+        const float rstd = rsqrtf(fmaxf(sq * inv_d - mean * mean, 0.f) + p.eps);
+        const float shift = -mean * rstd;
         for (int c = 0; c < d; c += 32) {
           uint32_t r[32];
           float v[32];
           tmem_ld32(lane_base + xcol + c, r);
           tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            v[j] = (__uint_as_float(r[j]) + p.bo[c + j] - mean) * rstd * p.ln_g[c + j] + p.ln_b[c + j];
+          for (int j = 0; j < 8; ++j) {
+            const float4 g = P_g[(c >> 2) + j], bb = P_b[(c >> 2) + j];
+            v[4 * j] = fmaf(fmaf(__uint_as_float(r[4 * j]), rstd, shift), g.x, bb.x);
+            v[4 * j + 1] = fmaf(fmaf(__uint_as_float(r[4 * j + 1]), rstd, shift), g.y, bb.y);
+            v[4 * j + 2] = fmaf(fmaf(__uint_as_float(r[4 * j + 2]), rstd, shift), g.z, bb.z);
+            v[4 * j + 3] = fmaf(fmaf(__uint_as_float(r[4 * j + 3]), rstd, shift), g.w, bb.w);
+          }
           store_h32(sA_g, trow, c, v);
         }
       }
       fence_proxy_async_smem();
       signal(&sh->h2_ready);
-      // ---- hidden chunks: relu(acc + b0) -> sH
+      if (warp == 2 && lane == 0) TRACE(201);
+      // ---- hidden chunks: relu(acc + b0) -> sH (one buffer: wait until the previous chunk's MMAs retired)
       for (int j = 0; j < NC && ok; ++j) {
         const int b = j & 1;
         if (!mbar_wait(smem_u32(&sh->acc1_full[b]), n_acc[b] & 1, abort)) {
@@ -371,17 +429,40 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         }
         ++n_acc[b];
         tc_fence_after();
+        if (warp == 2 && lane == 0) TRACE(210 + j);
+        uint32_t hp[64];                                    // 128 fp16 values of this row
+#pragma unroll
         for (int c = 0; c < HC; c += 32) {
           uint32_t r[32];
-          float v[32];
           tmem_ld32(lane_base + acol + b * HC + c, r);
           tmem_wait_ld();
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) v[jj] = fmaxf(__uint_as_float(r[jj]) + p.b0[j * HC + c + jj], 0.f);
-          store_h32(sH_g + b * SH_BYTES, trow, c, v);
+          for (int jj = 0; jj < 8; ++jj) {
+            const float4 b0 = P_b0[((j * HC + c) >> 2) + jj];
+            hp[(c >> 1) + 2 * jj] = pack_half2(fmaxf(__uint_as_float(r[4 * jj]) + b0.x, 0.f),
+                                               fmaxf(__uint_as_float(r[4 * jj + 1]) + b0.y, 0.f));
+            hp[(c >> 1) + 2 * jj + 1] = pack_half2(fmaxf(__uint_as_float(r[4 * jj + 2]) + b0.z, 0.f),
+                                                   fmaxf(__uint_as_float(r[4 * jj + 3]) + b0.w, 0.f));
+          }
+        }
+        // sH is free once the previous chunk's FFN-down MMAs have retired
+        if (!mbar_wait(smem_u32(&sh->hid_free), (n_free & 1) ^ 1, abort)) {
+          if (lane == 0) give_up(sh, p.status, 14);
+          ok = false;
+          break;
+        }
+        ++n_free;
+        if (warp == 2 && lane == 0) TRACE(220 + j);
+        {
+          uint8_t* rowp = sH_g + (trow >> 3) * 1024 + (trow & 7) * 128;
+#pragma unroll
+          for (int pc = 0; pc < 16; ++pc)                   // 16 pieces of 8 halfs: chunk pc / 8, piece pc % 8
+            *reinterpret_cast<uint4*>(rowp + (pc >> 3) * CHUNK_BYTES + (((pc & 7) ^ (trow & 7)) << 4)) =
+                make_uint4(hp[4 * pc], hp[4 * pc + 1], hp[4 * pc + 2], hp[4 * pc + 3]);
         }
         fence_proxy_async_smem();
-        signal(&sh->hid_ready[b]);
+        signal(&sh->hid_ready);
+        if (warp == 2 && lane == 0) TRACE(230 + j);
         // the buffers of the last two chunks are free now: pre-store the next tile's x there
         if (t_next < p.n_tiles && j + 2 >= NC) {
           const int cb = j + 2 - NC;               // NC-2 -> block 0, NC-1 -> block 1
@@ -390,82 +471,84 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         }
       }
       if (!ok) break;
-      // ---- final: xo = X + bo + b2 -> fp32 out, LayerNorm / fp16 outputs
+      // ---- final: xo = X + b2 -> fp32 out (coalesced), then LayerNorm / fp16 outputs
       TAIL_WAIT(&sh->x_done, par, 13);
       tc_fence_after();
+      if (warp == 2 && lane == 0) TRACE(250);
       {
-        const int64_t row = (int64_t)t * BM + trow;
-        const bool rok = row < p.M;
-        const bool need_stats = (p.out16[0] && p.g16[0]) || (p.out16[1] && p.g16[1]);
-        float sum = 0.f;
-        if (p.x_out || need_stats) {
+        const int64_t row0 = (int64_t)t * BM + q * 32;      // first row of this warp
+        float sum = 0.f, sq = 0.f;
+        if (p.x_out || p.g16[0] || p.g16[1]) {
           for (int c = 0; c < d; c += 32) {
             uint32_t r[32];
             tmem_ld32(lane_base + xcol + c, r);
             tmem_wait_ld();
-            float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              v[j] = __uint_as_float(r[j]) + p.bo[c + j] + p.b2[c + j];
-              sum += v[j];
+            for (int j = 0; j < 8; ++j) {
+              const float4 b2 = P_b2[(c >> 2) + j];
+              float4 v = make_float4(__uint_as_float(r[4 * j]) + b2.x, __uint_as_float(r[4 * j + 1]) + b2.y,
+                                     __uint_as_float(r[4 * j + 2]) + b2.z, __uint_as_float(r[4 * j + 3]) + b2.w);
+              sum += (v.x + v.y) + (v.z + v.w);
+              sq = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, sq))));
+              if (p.x_out)
+                stg_write(lane, j, make_uint4(__float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z),
+                                              __float_as_uint(v.w)));
             }
-            if (p.x_out && rok) {
-              float4* dst = reinterpret_cast<float4*>(p.x_out + row * d + c);
+            if (p.x_out) {
+              __syncwarp();
 #pragma unroll
-              for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              for (int i = 0; i < 8; ++i) {
+                const int rr = i * 4 + sub;
+                if (row0 + rr < p.M)
+                  *reinterpret_cast<uint4*>(p.x_out + (row0 + rr) * d + c + piece * 4) = stg_read(rr, piece);
+              }
+              __syncwarp();
             }
           }
         }
         const float mean = sum * inv_d;
-        float rstd = 1.f;
-        if (need_stats) {
-          float sq = 0.f;
-          for (int c = 0; c < d; c += 32) {
-            uint32_t r[32];
-            tmem_ld32(lane_base + xcol + c, r);
-            tmem_wait_ld();
+        const float rstd = rsqrtf(fmaxf(sq * inv_d - mean * mean, 0.f) + p.eps);
+#pragma unroll 1
+        for (int o = 0; o < 2; ++o) {
+          if (!p.out16[o]) continue;
+          const bool ln = p.g16[o] != nullptr;
+          const float sc = ln ? rstd : 1.f, sh0 = ln ? -mean * rstd : 0.f;
+          const float4 *P_go = prm4 + 256 + 128 * o, *P_bo16 = prm4 + 320 + 128 * o;
+          for (int c = 0; c < d; c += 64) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float dv = __uint_as_float(r[j]) + p.bo[c + j] + p.b2[c + j] - mean;
-              sq += dv * dv;
-            }
-          }
-          rstd = rsqrtf(sq * inv_d + p.eps);
-        }
-        if (p.out16[0] || p.out16[1]) {
-          for (int c = 0; c < d; c += 32) {
-            uint32_t r[32];
-            tmem_ld32(lane_base + xcol + c, r);
-            tmem_wait_ld();
-            if (!rok) continue;
+            for (int hh = 0; hh < 2; ++hh) {
+              uint32_t r[32];
+              tmem_ld32(lane_base + xcol + c + 32 * hh, r);
+              tmem_wait_ld();
 #pragma unroll
-            for (int o = 0; o < 2; ++o) {
-              if (!p.out16[o]) continue;
-              uint32_t h[16];
-              if (p.g16[o]) {
+              for (int j = 0; j < 4; ++j) {                 // 8 columns -> one 16-byte fp16 piece
+                float y[8];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  const int c0 = c + 2 * j;
-                  float a0 = (__uint_as_float(r[2 * j]) + p.bo[c0] + p.b2[c0] - mean) * rstd * p.g16[o][c0] + p.b16[o][c0];
-                  float a1 = (__uint_as_float(r[2 * j + 1]) + p.bo[c0 + 1] + p.b2[c0 + 1] - mean) * rstd * p.g16[o][c0 + 1] + p.b16[o][c0 + 1];
-                  h[j] = pack_half2(a0, a1);
+                for (int e = 0; e < 2; ++e) {
+                  const int f4 = ((c + 32 * hh) >> 2) + 2 * j + e;
+                  const float4 b2 = P_b2[f4], g = P_go[f4], bb = P_bo16[f4];
+                  y[4 * e] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e]) + b2.x, sc, sh0), g.x, bb.x);
+                  y[4 * e + 1] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 1]) + b2.y, sc, sh0), g.y, bb.y);
+                  y[4 * e + 2] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 2]) + b2.z, sc, sh0), g.z, bb.z);
+                  y[4 * e + 3] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 3]) + b2.w, sc, sh0), g.w, bb.w);
                 }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  const int c0 = c + 2 * j;
-                  h[j] = pack_half2(__uint_as_float(r[2 * j]) + p.bo[c0] + p.b2[c0],
-                                    __uint_as_float(r[2 * j + 1]) + p.bo[c0 + 1] + p.b2[c0 + 1]);
-                }
+                stg_write(lane, 4 * hh + j, make_uint4(pack_half2(y[0], y[1]), pack_half2(y[2], y[3]),
+                                                        pack_half2(y[4], y[5]), pack_half2(y[6], y[7])));
               }
-              uint4* dst = reinterpret_cast<uint4*>(p.out16[o] + row * p.ld16[o] + c);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) dst[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
             }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + sub;
+              if (row0 + rr < p.M)
+                *reinterpret_cast<uint4*>(p.out16[o] + (row0 + rr) * p.ld16[o] + c + piece * 8) = stg_read(rr, piece);
+            }
+            __syncwarp();
           }
         }
       }
       tc_fence_before();
+      if (warp == 2 && lane == 0) TRACE(251);
     }
   }
 
@@ -481,7 +564,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
 
 bool block_tail_ok(const BlockTailArgs& a) {
   if (a.d % 64 != 0 || a.d < 64 || a.d > 256) return false;
-  if (a.F % 256 != 0 || a.F < 256) return false;
+  if (a.F % 256 != 0 || a.F < 256 || a.F > 1024) return false;
   if (a.M < 1 || a.M > (int64_t)0x7fffffff * 64) return false;
   if (!aligned16(a.att) || !aligned16(a.x) || (a.ldx % 4) || (a.ld_att % 8)) return false;
   if (a.x_out && !aligned16(a.x_out)) return false;
@@ -528,5 +611,18 @@ int block_tail(const BlockTailArgs& a, cudaStream_t stream) {
   BSRL_LAUNCH_OK("block_tail_kernel");
   return BSRL_OK;
 }
+
+#ifdef BSRL_TRACE
+extern "C" int bsrl_trace_read(long long* out, int cap) {
+  int n = 0;
+  cudaMemcpyFromSymbol(&n, g_trace_n, sizeof(int));
+  if (n > 8192) n = 8192;
+  if (n > cap) n = cap;
+  cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 2 * n);
+  int zero = 0;
+  cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(int));
+  return n;
+}
+#endif
 
 }  // namespace bsrl

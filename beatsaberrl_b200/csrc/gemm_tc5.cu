@@ -7,7 +7,8 @@
 //               shared-memory descriptors, accumulating in TMEM; two accumulator buffers of BN
 //               fp32 columns let tile t+1's MMAs overlap tile t's epilogue;
 //   warps 2..9  epilogue: tcgen05.ld the accumulator (thread = output row), add bias, ReLU,
-//               residual, convert and store (rows may be remapped on the way out).
+//               transpose through shared memory so stores (and the residual read) cover full
+//               128-byte lines; rows may be remapped on the way out.
 // All waits are bounded: a wait that runs out sets the library's device status word, raises
 // the CTA-wide abort flag, and every role falls through to the common teardown that frees TMEM.
 //
@@ -31,7 +32,8 @@ constexpr int STAGE_BYTES = A_BYTES + W_BYTES;  // 48 KB
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = (2 + EPI_WARPS) * 32;
 constexpr int TMEM_COLS = 2 * BN;               // two accumulator buffers = all 512 columns
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int STG_BYTES = 32 * 128;             // per-warp transposition buffer: 32 rows x 128 bytes
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * STG_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 struct Shared {
   uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], mma_done;
@@ -50,7 +52,8 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;
-  Shared* sh = reinterpret_cast<Shared*>(smem_raw + (tiles_base - raw) + STAGES * STAGE_BYTES);
+  uint8_t* staging = smem_raw + (tiles_base - raw) + STAGES * STAGE_BYTES;
+  Shared* sh = reinterpret_cast<Shared*>(staging + EPI_WARPS * STG_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_blocks = p.K / BK;
   const int64_t n_work = (int64_t)m_tiles * n_tiles;
@@ -147,8 +150,17 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
   } else {
     // ---------------------------------------------------------------- epilogue warps
+    // Each warp drains a 32-row x 128-column slab of the tile in blocks of 128 bytes per row
+    // (64 fp16 or 32 fp32 columns).  TMEM hands every thread one ROW; writing rows straight to
+    // HBM would touch 32 different 128-byte lines per store instruction, so the block is first
+    // transposed through a per-warp 4 KB staging buffer (16-byte pieces, XOR-swizzled) and then
+    // written -- and the residual read -- with 8 lanes covering one full 128-byte line.
     const int q = warp & 3;                    // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;          // which half of the tile's columns
+    uint8_t* stg = staging + (warp - 2) * STG_BYTES;
+    const bool wide = p.out_f32 || p.R;        // stage fp32 (32 columns per block) instead of fp16 (64)
+    const int cw = wide ? 32 : 64;
+    const int sub = lane >> 3, piece = lane & 7;   // transposed phase: row sub + 4 i, 16-byte piece
     uint32_t tile_i = 0;
     bool ok = true;
     for (int64_t t = blockIdx.x; t < n_work && ok; t += gridDim.x, ++tile_i) {
@@ -156,61 +168,87 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const int n0 = (int)(t % n_tiles) * BN;
       const int buf = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
+      // output / residual row offsets of the 8 rows this lane writes in the transposed phase
+      int64_t crow[8], rrow[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int64_t row = m0 + q * 32 + i * 4 + sub;
+        crow[i] = row < p.M ? p.cmap(row) * (int64_t)p.ldc : -1;
+        rrow[i] = (p.R && row < p.M) ? p.rmap(row) * (int64_t)p.ldr : 0;
+      }
       if (!mbar_wait(smem_u32(&sh->tmem_full[buf]), acc_ph, abort)) {
         if (lane == 0) give_up(sh, status, 5);
         ok = false;
         break;
       }
       tc_fence_after();
-      const int64_t row = m0 + q * 32 + lane;
-      const bool row_ok = row < p.M;
-      const int64_t crow = row_ok ? p.cmap(row) * (int64_t)p.ldc : 0;
-      const float* rrow = (p.R && row_ok) ? p.R + p.rmap(row) * (int64_t)p.ldr : nullptr;
+      const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * (BN / 2);
 #pragma unroll 1
-      for (int c = 0; c < BN / 2; c += 32) {
-        const int col = n0 + half * (BN / 2) + c;     // first of 32 columns
+      for (int c = 0; c < BN / 2; c += cw) {
+        const int col = n0 + half * (BN / 2) + c;     // first column of this block
         if (col >= p.N) break;                         // warp-uniform
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * (BN / 2) + c, r);
-        tmem_wait_ld();
-        if (!row_ok) continue;
+        // ---- phase 1: own row, 32 columns at a time -> bias / ReLU -> staging
+        for (int s32 = 0; s32 < cw; s32 += 32) {
+          if (col + s32 >= p.N) break;
+          tmem_ld32(tbase + c + s32, r);
+          tmem_wait_ld();
+          float v[32];
 #pragma unroll
-        for (int h16 = 0; h16 < 2; ++h16) {
-          const int cc = col + h16 * 16;
-          if (cc >= p.N) break;
-          float v[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[h16 * 16 + j]);
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           if (p.bias) {
 #pragma unroll
-            for (int j = 0; j < 16; j += 4) {
-              float4 b = *reinterpret_cast<const float4*>(p.bias + cc + j);
-              v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+            for (int j = 0; j < 32; j += 4) {
+              // columns past N read the zero padding of the accumulator; clamp the bias index
+              const int cb = min(col + s32 + j, p.N - 4);
+              float4 bv = *reinterpret_cast<const float4*>(p.bias + cb);
+              v[j] += bv.x; v[j + 1] += bv.y; v[j + 2] += bv.z; v[j + 3] += bv.w;
             }
           }
           if (p.relu) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
+            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
           }
-          if (rrow) {
+          if (wide) {
 #pragma unroll
-            for (int j = 0; j < 16; j += 4) {
-              float4 b = *reinterpret_cast<const float4*>(rrow + cc + j);
-              v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
-            }
-          }
-          if (p.out_f32) {
-            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.C) + crow + cc);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<float4*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                  make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
           } else {
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(p.C) + crow + cc);
 #pragma unroll
-            for (int j = 0; j < 2; ++j)
-              dst[j] = make_uint4(pack_half2(v[8 * j], v[8 * j + 1]), pack_half2(v[8 * j + 2], v[8 * j + 3]),
-                                  pack_half2(v[8 * j + 4], v[8 * j + 5]), pack_half2(v[8 * j + 6], v[8 * j + 7]));
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(stg + lane * 128 + ((((s32 >> 3) + j) ^ (lane & 7)) << 4)) =
+                  make_uint4(pack_half2(v[8 * j], v[8 * j + 1]), pack_half2(v[8 * j + 2], v[8 * j + 3]),
+                             pack_half2(v[8 * j + 4], v[8 * j + 5]), pack_half2(v[8 * j + 6], v[8 * j + 7]));
           }
         }
+        __syncwarp();
+        // ---- phase 2: 8 lanes per row, one 16-byte piece each
+        const int pcol = col + piece * (wide ? 4 : 8);   // first column of this lane's piece
+        if (pcol < p.N) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (crow[i] < 0) continue;
+            const int rr = i * 4 + sub;
+            const uint4 raw16 = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((piece ^ (rr & 7)) << 4));
+            if (!wide) {
+              *reinterpret_cast<uint4*>(static_cast<__half*>(p.C) + crow[i] + pcol) = raw16;
+            } else {
+              float4 f = make_float4(__uint_as_float(raw16.x), __uint_as_float(raw16.y),
+                                     __uint_as_float(raw16.z), __uint_as_float(raw16.w));
+              if (p.R) {
+                const float4 rv = *reinterpret_cast<const float4*>(p.R + rrow[i] + pcol);
+                f.x += rv.x; f.y += rv.y; f.z += rv.z; f.w += rv.w;
+              }
+              if (p.out_f32)
+                *reinterpret_cast<float4*>(static_cast<float*>(p.C) + crow[i] + pcol) = f;
+              else
+                *reinterpret_cast<uint2*>(static_cast<__half*>(p.C) + crow[i] + pcol) =
+                    make_uint2(pack_half2(f.x, f.y), pack_half2(f.z, f.w));
+            }
+          }
+        }
+        __syncwarp();
       }
       tc_fence_before();
       __syncwarp();
