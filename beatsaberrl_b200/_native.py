@@ -68,6 +68,8 @@ _sig = {
     "bsrl_pack_weights": (C.c_int, [_CFG, C.POINTER(_P), C.c_int32, _P, C.c_int64, _P]),
     "bsrl_workspace_bytes": (C.c_int64, [_CFG, C.c_int64]),
     "bsrl_forward": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, _P, _P, _P, C.c_int64, _P]),
+    "bsrl_fixed_scratch_bytes": (C.c_int64, []),
+    "bsrl_forward_fixed": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, _P, _P]),
     "bsrl_forward_act": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, C.c_int32, _P, _P, _P, _P, _P, _P,
                                    _P, C.c_int64, _P]),
     "bsrl_token_lane": (C.c_int32, [C.c_int32, C.c_int32]),

@@ -505,6 +505,55 @@ int bsrl_forward_act(const bsrl_config* cfg, const void* arena, const void* obs,
 
 int32_t bsrl_token_lane(int32_t tok, int32_t k) { return token_lane_host(tok, k); }
 
+// ---- forward on the library's own fixed scratch (no caller workspace, nothing allocated) ----
+// The scratch is a file-scope device array, so every GPU that loads the library holds these
+// 32 MiB until the process exits.  g_fixed_scratch names the array for DEVICE code only; on the
+// host the same name is just a handle, so the real device address is looked up once per device
+// with cudaGetSymbolAddress and that pointer is what the kernels get.
+#define BSRL_FIXED_SCRATCH_BYTES (32ll << 20)
+static __device__ __align__(256) unsigned char g_fixed_scratch[BSRL_FIXED_SCRATCH_BYTES];
+
+static int fixed_scratch_ptr(void** out) {
+  static void* cached[64] = {};
+  int dev = 0;
+  BSRL_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    set_error("forward_fixed: device ordinal %d not supported", dev);
+    return BSRL_ERR_UNSUPPORTED;
+  }
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    BSRL_CUDA_OK(cudaGetSymbolAddress(&ptr, g_fixed_scratch));   // address on the CURRENT device
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return BSRL_OK;
+}
+
+int64_t bsrl_fixed_scratch_bytes(void) { return BSRL_FIXED_SCRATCH_BYTES; }
+
+int bsrl_forward_fixed(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
+                       int64_t n_envs, float* logits, float* value, void* stream) {
+  BSRL_TRY(validate_config(cfg));
+  if (n_envs < 0) {
+    set_error("forward_fixed: n_envs %lld is negative", (long long)n_envs);
+    return BSRL_ERR_SHAPE;
+  }
+  const int64_t need = make_workspace(make_layout(*cfg), n_envs).bytes;
+  if (need > BSRL_FIXED_SCRATCH_BYTES) {
+    set_error("forward_fixed: %lld envs need %lld bytes of scratch, the built-in scratch holds %lld; "
+              "use bsrl_forward with a caller workspace for larger batches",
+              (long long)n_envs, (long long)need, (long long)BSRL_FIXED_SCRATCH_BYTES);
+    return BSRL_ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  BSRL_TRY(fixed_scratch_ptr(&scratch));
+  // Nothing in the scratch has to start at zero: every region a kernel reads was written earlier
+  // in the same call, so the previous call's contents are simply overwritten.
+  return bsrl_forward(cfg, arena, obs, obs_dtype, n_envs, logits, value, nullptr, scratch,
+                      BSRL_FIXED_SCRATCH_BYTES, stream);
+}
+
 int bsrl_set_engine(int32_t engine) {
   if (engine != 0 && engine != 1) {
     set_error("set_engine: 0 (automatic) or 1 (warp-MMA only)");

@@ -101,6 +101,28 @@ int bsrl_forward(const bsrl_config* cfg, const void* arena, const void* obs, int
                  int64_t n_envs, float* logits, float* value, float* value_logits,
                  void* workspace, int64_t workspace_bytes, void* stream);
 
+/* bsrl_forward for callers that cannot hand over a workspace.  Same inputs, outputs and
+ * arithmetic as bsrl_forward, but the intermediates live in a 32 MiB scratch array built into
+ * the library (bsrl_fixed_scratch_bytes()), so this call needs no workspace argument and
+ * allocates nothing -- no cudaMalloc, no cudaFree, no allocating library routine.  It is meant
+ * for hosts that own no device allocator of their own or may not allocate where they call from:
+ * a simulator-side C/C++ thread or a replay/evaluation tool that wants a handful of policy
+ * forwards without linking torch, or code running under a fixed device-memory budget in which
+ * any late cudaMalloc could fail or stall the other streams.
+ *   - Batches whose bsrl_workspace_bytes() exceeds the built-in scratch are refused with
+ *     BSRL_ERR_WORKSPACE (about 190 envs at embed 256, about 390 at embed 128).
+ *   - The first call on each device looks up the scratch's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call before any stream
+ *     capture begins.
+ *   - All calls on a device share the one scratch and it keeps the last call's contents.  Nothing
+ *     in it needs clearing between calls, but two calls whose kernels overlap on the GPU (two
+ *     streams, two host threads) race on it: serialise them, or use bsrl_forward.
+ *   - Every GPU that loads the library holds the 32 MiB until the process exits.
+ * This entry point has no counterpart in the reference (its extensions allocate through torch). */
+int64_t bsrl_fixed_scratch_bytes(void);
+int bsrl_forward_fixed(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
+                       int64_t n_envs, float* logits, float* value, void* stream);
+
 /* NotePolicy.get_action_and_value with given actions (python/policy.py:1467-1516), the PPO
  * recompute call: same forward, then log-softmax, summed log-prob of the given actions and
  * entropy fused into the head kernel.  actions (n_envs, 29) u8 / i32 / i64.
