@@ -95,6 +95,13 @@ __device__ __forceinline__ void give_up(Shared* sh, int* status, int role) {
   sh->abort = 1;
 }
 
+#define TAIL_WAIT_WARP(bar, parity, role)                          \
+  if (!mbar_wait_warp(smem_u32(bar), (parity), abort)) {           \
+    if ((threadIdx.x & 31) == 0) give_up(sh, p.status, role);      \
+    ok = false;                                                    \
+    break;                                                         \
+  }
+
 #define TAIL_WAIT(bar, parity, role)                               \
   if (!mbar_wait(smem_u32(bar), (parity), abort)) {                \
     give_up(sh, p.status, role);                                   \
@@ -225,20 +232,37 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     }
   } else if (warp == 6) {
     // ------------------------------------------------------------ attention-tile producer
-    if (lane == 0) {
-      uint32_t tile_i = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_i) {
-        if (!mbar_wait(smem_u32(&sh->a_free), (tile_i & 1) ^ 1, abort)) { give_up(sh, p.status, 3); ok = false; break; }
+    // lane 0 loads the attention tile into sA as soon as the previous tile's last reader is done;
+    // the whole warp then pulls the NEXT tile's residual rows into L2, so that the epilogue's
+    // pre-store of x finds them there.
+    uint32_t tile_i = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_i) {
+      if (!mbar_wait_warp(smem_u32(&sh->a_free), (tile_i & 1) ^ 1, abort)) {
+        if (lane == 0) give_up(sh, p.status, 3);
+        ok = false;
+        break;
+      }
+      if (lane == 0) {
         const uint32_t bar = smem_u32(&sh->a_full);
         mbar_expect_tx(bar, KB * CHUNK_BYTES);
         for (int c = 0; c < KB; ++c) tma_load_2d(sA + c * CHUNK_BYTES, &tm_att, 64 * c, t * BM, bar);
       }
-      if (tile_i > 0) {
-        uint32_t spins = 0;
-        while (!mbar_try_wait(smem_u32(&sh->a_full), (tile_i - 1) & 1) && ++spins < kSpinLimit) {}
-        if (spins >= kSpinLimit) give_up(sh, p.status, 4);
+      const int tn = t + gridDim.x;
+      if (tn < p.n_tiles) {
+        for (int r = lane; r < BM; r += 32) {
+          const int64_t row = (int64_t)tn * BM + r;
+          if (row < p.M) {
+            const float* xr = p.x + p.xmap(row) * p.ldx;
+            for (int c = 0; c < d; c += 32) prefetch_l2(xr + c);
+          }
+        }
       }
+    }
+    if (lane == 0 && tile_i > 0) {
+      uint32_t spins = 0;
+      while (!mbar_try_wait(smem_u32(&sh->a_full), (tile_i - 1) & 1) && ++spins < kSpinLimit) {}
+      if (spins >= kSpinLimit) give_up(sh, p.status, 4);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -340,15 +364,24 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     };
     // pre-store (x + bo) rows of tile t, column block cb (128 wide), into TMEM columns col0 + ...
     auto prestore = [&](int t, int cb, uint32_t col0) {
-      const int c1 = min(d, cb * 128 + 128);
-      for (int c = cb * 128; c < c1; c += 32) {
+      const int c0 = cb * 128, c1 = min(d, cb * 128 + 128);
+      const float* src[8];                                  // this lane's 8 rows in the transposed phase
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {                       // coalesced: 4 rows x 128 B per instruction
-          const int rr = i * 4 + sub;
-          const int64_t row = (int64_t)t * BM + q * 32 + rr;
-          uint4 v = make_uint4(0, 0, 0, 0);
-          if (row < p.M) v = *reinterpret_cast<const uint4*>(p.x + p.xmap(row) * p.ldx + c + piece * 4);
-          stg_write(rr, piece, v);
+      for (int i = 0; i < 8; ++i) {
+        const int64_t row = (int64_t)t * BM + q * 32 + i * 4 + sub;
+        src[i] = row < p.M ? p.x + p.xmap(row) * p.ldx + piece * 4 : nullptr;
+      }
+      uint4 nxt[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        nxt[i] = src[i] ? *reinterpret_cast<const uint4*>(src[i] + c0) : make_uint4(0, 0, 0, 0);
+      for (int c = c0; c < c1; c += 32) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) stg_write(i * 4 + sub, piece, nxt[i]);
+        if (c + 32 < c1) {                                  // next block's loads fly during this one
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            nxt[i] = src[i] ? *reinterpret_cast<const uint4*>(src[i] + c + 32) : make_uint4(0, 0, 0, 0);
         }
         __syncwarp();
         uint32_t r[32];
@@ -381,7 +414,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       const uint32_t xcol = par ? 256u : 0u, acol = par ? 0u : 256u;
       const int t_next = t + gridDim.x;
       // ---- E1: h2 = LN_ffn(x1) -> sA   (X already holds x + bo + att Wo^T)
-      TAIL_WAIT(&sh->o_done, par, 11);
+      TAIL_WAIT_WARP(&sh->o_done, par, 11);
       tc_fence_after();
       if (warp == 2 && lane == 0) TRACE(200);
       {
@@ -422,7 +455,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       // ---- hidden chunks: relu(acc + b0) -> sH (one buffer: wait until the previous chunk's MMAs retired)
       for (int j = 0; j < NC && ok; ++j) {
         const int b = j & 1;
-        if (!mbar_wait(smem_u32(&sh->acc1_full[b]), n_acc[b] & 1, abort)) {
+        if (!mbar_wait_warp(smem_u32(&sh->acc1_full[b]), n_acc[b] & 1, abort)) {
           if (lane == 0) give_up(sh, p.status, 12);
           ok = false;
           break;
@@ -446,7 +479,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
           }
         }
         // sH is free once the previous chunk's FFN-down MMAs have retired
-        if (!mbar_wait(smem_u32(&sh->hid_free), (n_free & 1) ^ 1, abort)) {
+        if (!mbar_wait_warp(smem_u32(&sh->hid_free), (n_free & 1) ^ 1, abort)) {
           if (lane == 0) give_up(sh, p.status, 14);
           ok = false;
           break;
@@ -472,7 +505,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       }
       if (!ok) break;
       // ---- final: xo = X + b2 -> fp32 out (coalesced), then LayerNorm / fp16 outputs
-      TAIL_WAIT(&sh->x_done, par, 13);
+      TAIL_WAIT_WARP(&sh->x_done, par, 13);
       tc_fence_after();
       if (warp == 2 && lane == 0) TRACE(250);
       {

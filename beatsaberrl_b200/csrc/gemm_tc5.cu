@@ -176,7 +176,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         crow[i] = row < p.M ? p.cmap(row) * (int64_t)p.ldc : -1;
         rrow[i] = (p.R && row < p.M) ? p.rmap(row) * (int64_t)p.ldr : 0;
       }
-      if (!mbar_wait(smem_u32(&sh->tmem_full[buf]), acc_ph, abort)) {
+      if (!mbar_wait_warp(smem_u32(&sh->tmem_full[buf]), acc_ph, abort)) {
         if (lane == 0) give_up(sh, status, 5);
         ok = false;
         break;
