@@ -32,9 +32,9 @@ inline const T* at(const void* base, int64_t off) {
 // (a captured graph must not contain it); the benchmark switches it on to time the dominant
 // kernel live, on the stream the kernels run on.
 enum Stage { kStGather = 0, kStEncoder, kStLayerNorm, kStQkv, kStAttention, kStOutProj, kStFfnUp,
-             kStFfnDown, kStBlockTail, kStTrunk, kStCritic, kStHeadTail, kStCount };
+             kStFfnDown, kStBlockTail, kStAttnBlock, kStTrunk, kStCritic, kStHeadTail, kStCount };
 const char* const kStageNames[kStCount] = {"embed_gather", "encoder_gemm", "layernorm", "qkv_gemm",
-                                           "attention", "out_proj_gemm", "ffn_up_gemm", "ffn_down_gemm", "block_tail",
+                                           "attention", "out_proj_gemm", "ffn_up_gemm", "ffn_down_gemm", "block_tail", "attn_block",
                                            "trunk", "critic", "head_tail"};
 struct Profiler {
   bool on = false;
@@ -106,6 +106,17 @@ int fused_tail(const BlockTailArgs& a, cudaStream_t st) {
   double fl = 2.0 * a.M * ((double)a.d * a.d + 2.0 * a.d * a.F);
   double by = (double)a.M * a.d * (2 + 4 + (a.x_out ? 4 : 0) + (a.out16[0] ? 2 : 0) + (a.out16[1] ? 2 : 0));
   int rc = timed(st, fl, by, [&] { return block_tail(a, st); });
+  g_stage = keep;
+  return rc;
+}
+
+int fused_attn(const AttnBlockArgs& a, cudaStream_t st) {
+  int keep = g_stage;
+  g_stage = kStAttnBlock;
+  const double rows = (double)a.n_envs * kT;
+  double fl = 2.0 * rows * 3.0 * a.d * a.d + 4.0 * a.n_envs * a.n_q * kT * a.d;
+  double by = rows * a.d * 2 + (double)a.n_envs * a.n_q * a.d * 2 + (double)a.n_envs * kT * 4;
+  int rc = timed(st, fl, by, [&] { return attn_block(a, st); });
   g_stage = keep;
   return rc;
 }
@@ -205,15 +216,30 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     BlockTailArgs probe = tail_args(l.blocks[0], R);
     fused = g_engine == 0 && block_tail_ok(probe);
   }
+  // Fused q|k|v projection + attention where head_dim is 32 (weights regrouped per head pair).
+  auto attn_args = [&](const __half* rows, const Mat& wg, int q_first, int n_q, __half* out) {
+    AttnBlockArgs a;
+    a.d = d; a.n_heads = l.H; a.n_envs = B;
+    a.h = rows; a.ldh = d;
+    a.wg = c.W(wg); a.bg = c.Bv(wg);
+    a.key_bias = key_bias; a.q_first = q_first; a.n_q = n_q;
+    a.out = out; a.ldo = d;
+    return a;
+  };
+  const bool fused_qkv = g_engine == 0 && l.attn_G == 2 && attn_block_ok(attn_args(h, l.blocks[0].qkv_g, 0, kT, att));
   __half* hv = at<__half>(c.ws, w.enc_hid);   // critic LayerNorm rows (encoder scratch is free by now)
   bool have_h = false, have_hv = false;
 
   for (int i = 0; i + 1 < l.L; ++i) {
     const BlockW& b = l.blocks[i];
     if (!have_h) BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
-    g_stage = kStQkv;
-    BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, R, 3 * d, d), c.st));
-    BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 0, kT, att, d, c.st));
+    if (fused_qkv) {
+      BSRL_TRY(fused_attn(attn_args(h, b.qkv_g, 0, kT, att), c.st));
+    } else {
+      g_stage = kStQkv;
+      BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, R, 3 * d, d), c.st));
+      BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 0, kT, att, d, c.st));
+    }
     if (fused) {
       const BlockW& nb = l.blocks[i + 1];
       BlockTailArgs a = tail_args(b, R);
@@ -247,13 +273,19 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   {
     const BlockW& b = l.blocks[l.L - 1];
     if (!have_h) BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
-    g_stage = kStQkv;
-    BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv, d), d, c.Bv(b.qkv, d), qkv + d, 3 * d, 0, 0, R, 2 * d, d), c.st));
-    LinearArgs pq = linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, Rl, d, d);
-    pq.amap = lead_rows;
-    pq.cmap = lead_rows;
-    BSRL_TRY(linear(pq, c.st));
-    BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 0, kLead, att, d, c.st));
+    if (fused_qkv) {
+      // q is projected for all 29 rows (a third of this kernel's MMAs, no extra HBM traffic);
+      // only the 5 lead rows are attended and written
+      BSRL_TRY(fused_attn(attn_args(h, b.qkv_g, 0, kLead, att), c.st));
+    } else {
+      g_stage = kStQkv;
+      BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv, d), d, c.Bv(b.qkv, d), qkv + d, 3 * d, 0, 0, R, 2 * d, d), c.st));
+      LinearArgs pq = linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, Rl, d, d);
+      pq.amap = lead_rows;
+      pq.cmap = lead_rows;
+      BSRL_TRY(linear(pq, c.st));
+      BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 0, kLead, att, d, c.st));
+    }
     if (fused) {
       BlockTailArgs a = tail_args(b, Rl);
       a.xmap = lead_rows;
@@ -303,12 +335,16 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     g_stage = kStCritic;
     const __half* hc = have_hv ? hv : h;
     if (!have_hv) BSRL_TRY(layernorm(x, d, ident, c.G(l.critic_ln), c.Be(l.critic_ln), eps, R, d, h, d, c.st));
-    BSRL_TRY(linear(linear_args(hc, d, c.W(l.critic_kv), d, c.Bv(l.critic_kv), qkv + d, 3 * d, 0, 0, R, 2 * d, d), c.st));
-    LinearArgs pq = linear_args(hc, d, c.W(l.critic_q), d, c.Bv(l.critic_q), qkv, 3 * d, 0, 0, B, d, d);
-    pq.amap = torso_rows;
-    pq.cmap = torso_rows;
-    BSRL_TRY(linear(pq, c.st));
-    BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 2, 1, att_c, d, c.st));
+    if (fused_qkv) {
+      BSRL_TRY(fused_attn(attn_args(hc, l.critic_qkv_g, 2, 1, att_c), c.st));
+    } else {
+      BSRL_TRY(linear(linear_args(hc, d, c.W(l.critic_kv), d, c.Bv(l.critic_kv), qkv + d, 3 * d, 0, 0, R, 2 * d, d), c.st));
+      LinearArgs pq = linear_args(hc, d, c.W(l.critic_q), d, c.Bv(l.critic_q), qkv, 3 * d, 0, 0, B, d, d);
+      pq.amap = torso_rows;
+      pq.cmap = torso_rows;
+      BSRL_TRY(linear(pq, c.st));
+      BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 2, 1, att_c, d, c.st));
+    }
     BSRL_TRY(linear(linear_args(att_c, d, c.W(l.critic_out), d, c.Bv(l.critic_out), z, ldz, 0, 0, B, d, d), c.st));
     BSRL_TRY(linear(linear_args(z, ldz, c.W(l.critic_m0), ldz, c.Bv(l.critic_m0), m1, D, 0, 1, B, D, ldz), c.st));
     BSRL_TRY(linear(linear_args(m1, D, c.W(l.critic_m1), D, c.Bv(l.critic_m1), m2, D, 0, 1, B, D, D), c.st));
@@ -446,6 +482,13 @@ int bsrl_pack_weights(const bsrl_config* cfg, const float* const* params, int32_
       BSRL_TRY(pack_cast(params[i], p.rows, p.cols, at<__half>(arena, p.dst), p.dst_pitch, st));
     else
       BSRL_TRY(pack_copy(params[i], p.rows, at<float>(arena, p.dst), st));
+  }
+  for (const CopySlot& cs : make_copy_slots(*cfg, l, s)) {
+    const float* src = params[cs.param] + cs.src_row0 * cs.cols;
+    if (cs.half)
+      BSRL_TRY(pack_cast(src, cs.n_rows, cs.cols, at<__half>(arena, cs.dst), cs.dst_pitch, st));
+    else
+      BSRL_TRY(pack_copy(src, cs.n_rows, at<float>(arena, cs.dst), st));
   }
   return BSRL_OK;
 }
@@ -663,6 +706,18 @@ int bsrl_block_tail(const void* att_f16, const float* x, const void* wo_f16, con
   a.x_out = x_out;
   a.out16[0] = static_cast<__half*>(ln_out_f16); a.ld16[0] = d; a.g16[0] = out_g; a.b16[0] = out_b;
   return block_tail(a, as_stream(stream));
+}
+
+int bsrl_qkv_attention(const void* h_f16, const void* w_grouped_f16, const float* b_grouped,
+                       const float* key_bias, int64_t n_envs, int32_t d, int32_t n_heads, int32_t q_first,
+                       int32_t n_q, void* out_f16, void* stream) {
+  AttnBlockArgs a;
+  a.d = d; a.n_heads = n_heads; a.n_envs = n_envs;
+  a.h = static_cast<const __half*>(h_f16); a.ldh = d;
+  a.wg = static_cast<const __half*>(w_grouped_f16); a.bg = b_grouped;
+  a.key_bias = key_bias; a.q_first = q_first; a.n_q = n_q;
+  a.out = static_cast<__half*>(out_f16); a.ldo = d;
+  return attn_block(a, as_stream(stream));
 }
 
 int bsrl_attention(const void* qkv_f16, const float* key_bias, int64_t n_envs, int32_t d, int32_t n_heads,

@@ -1,0 +1,377 @@
+// Fused head of one transformer block: packed q|k|v projection on tcgen05 / TMEM and the masked
+// 29-key multi-head attention on the projected rows, without the (rows, 3d) round trip through HBM.
+//
+//   qkv = h [Wq;Wk;Wv]^T + b          (h = LayerNorm rows, fp16)
+//   att = softmax(q k^T / sqrt(dh) + key_bias) v, heads concatenated
+//
+// One tile = 4 environments = 116 token rows (padded to the 128-row MMA).  The projection runs per
+// HEAD GROUP (two heads: 64 q + 64 k + 64 v = 192 output columns, the weight rows regrouped at
+// pack time), so that a group's q, k, v fit in one 50 KB shared-memory tile; the attention of the
+// group's 8 (env, head) pairs then runs on 8 warps from that tile (m16n8k16 MMAs, fp32 softmax in
+// registers) while the tensor core already projects the next group into the other TMEM buffer.
+//
+//   warp 0      TMA producer: the h tile (d/64 swizzled chunks, loaded once per tile) and the
+//               regrouped weight tiles (192 x 64 per stage, 4-stage ring)
+//   warp 1      MMA issuer: tcgen05.mma M = 128, N = 192, K = 16
+//   warps 2..9  drain the accumulator (+ bias, fp16) into the q|k|v tile, then attend
+//
+// HBM traffic per token: read h (2d B), write att (2d B).  Replaces fp16_packed_linear + attn29 /
+// packed_sdpa (python/policy.py:586-600, :645-692; python/beat_arena_env/csrc/small_attn.cu).
+// All waits are bounded (tc5.cuh); head_dim 32 only.
+#include "kernels.cuh"
+#include "tc5.cuh"
+
+namespace bsrl {
+namespace {
+using namespace tc5;
+
+constexpr int EPT = 4;                  // envs per tile
+constexpr int ROWS = EPT * kT;          // 116 live rows
+constexpr int BM = 128;
+constexpr int DH = 32, G = 2, GD = G * DH, NG = 3 * GD;   // 192 columns per head group
+constexpr int STAGES = 4;
+constexpr int STAGE_BYTES = NG * 128;   // 24 KB: 192 weight rows x 64 k-columns
+constexpr int CHUNK_BYTES = BM * 128;   // 16 KB: 128 rows x 64 k-columns
+constexpr int LDQ = NG * 2 + 16;        // 400-byte rows of the q|k|v tile (ldmatrix conflict-free)
+constexpr int SQ_BYTES = BM * LDQ;
+constexpr int WORKERS = 8;
+constexpr int THREADS = (2 + WORKERS) * 32;
+constexpr int SMEM_BYTES = 4 * CHUNK_BYTES + STAGES * STAGE_BYTES + SQ_BYTES + 768 * 4 + 1024 + 256;
+constexpr int KERNEL_ID = 3;
+
+struct Shared {
+  uint64_t w_full[STAGES], w_empty[STAGES], a_full[4], a_free[4], acc_full[2], acc_empty[2], mma_done;
+  uint32_t tmem_base;
+  int abort;
+};
+
+struct Params {
+  int d, n_heads, q_first, n_q;
+  int64_t n_envs;
+  int n_tiles;
+  const float* bias;       // regrouped q|k|v bias (3d)
+  const float* key_bias;   // (n_envs, 29)
+  __half* out;             // (n_envs * n_q, ldo)
+  int ldo;
+  int* status;
+};
+
+__device__ __forceinline__ void give_up(Shared* sh, int* status, int role) {
+  atomicCAS(status, 0, KERNEL_ID * 16 + role);
+  sh->abort = 1;
+}
+
+// Attention of one (env, head) pair from the shared q|k|v tile; one warp.  q, k, v are byte
+// addresses (shared window) of the pair's first row / first column; rows are LDQ bytes apart.
+__device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t sv, const float* key_bias_env,
+                                            int n_q, __half* out_env, int ldo, int lane) {
+  const int g = lane >> 2, tig = lane & 3;
+  const float scale = rsqrtf((float)DH);
+  float kb[4][2];
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int key = nt * 8 + tig * 2 + e;
+      kb[nt][e] = key < kT ? key_bias_env[key] : -INFINITY;
+    }
+  const int m_tiles = (n_q + 15) >> 4;
+  for (int mt = 0; mt < m_tiles; ++mt) {
+    float s[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < DH / 16; ++ks) {
+      uint32_t a[4];
+      ldmatrix_x4(a, sq + (mt * 16 + (lane & 15)) * LDQ + (ks * 16 + (lane >> 4) * 8) * 2);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        uint32_t b[4];
+        const int row = j * 16 + (lane & 7) + ((lane >> 4) << 3);
+        ldmatrix_x4(b, sk + row * LDQ + (ks * 16 + ((lane >> 3) & 1) * 8) * 2);
+        mma_f16(s[2 * j], a, b[0], b[1]);
+        mma_f16(s[2 * j + 1], a, b[2], b[3]);
+      }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        s[nt][e] = s[nt][e] * scale + kb[nt][e & 1];
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+      }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        s[nt][e] = expf(s[nt][e] - mx[e >> 1]);
+        sum[e >> 1] += s[nt][e];
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+      sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+      sum[r] = 1.f / sum[r];
+    }
+    uint32_t pa[2][4];
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      pa[ks][0] = pack_half2(s[2 * ks][0] * sum[0], s[2 * ks][1] * sum[0]);
+      pa[ks][1] = pack_half2(s[2 * ks][2] * sum[1], s[2 * ks][3] * sum[1]);
+      pa[ks][2] = pack_half2(s[2 * ks + 1][0] * sum[0], s[2 * ks + 1][1] * sum[0]);
+      pa[ks][3] = pack_half2(s[2 * ks + 1][2] * sum[1], s[2 * ks + 1][3] * sum[1]);
+    }
+    float o[DH / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < DH / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+      for (int j = 0; j < DH / 16; ++j) {
+        uint32_t b[4];
+        const int row = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4_trans(b, sv + row * LDQ + (j * 16 + (lane >> 4) * 8) * 2);
+        mma_f16(o[2 * j], pa[ks], b[0], b[1]);
+        mma_f16(o[2 * j + 1], pa[ks], b[2], b[3]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int qrow = mt * 16 + g + r * 8;
+      if (qrow < n_q) {
+        __half* orow = out_env + (int64_t)qrow * ldo + tig * 2;
+#pragma unroll
+        for (int nt = 0; nt < DH / 8; ++nt)
+          *reinterpret_cast<uint32_t*>(orow + nt * 8) = pack_half2(o[nt][r * 2], o[nt][r * 2 + 1]);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_w, Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - raw);
+  const uint32_t sA = base, ring = base + 4 * CHUNK_BYTES, sQ = ring + STAGES * STAGE_BYTES;
+  uint8_t* sQ_g = gen + 4 * CHUNK_BYTES + STAGES * STAGE_BYTES;
+  float* s_bias = reinterpret_cast<float*>(sQ_g + SQ_BYTES);
+  Shared* sh = reinterpret_cast<Shared*>(sQ_g + SQ_BYTES + 768 * 4);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int d = p.d, KB = d >> 6, n_groups = d / GD;
+  volatile int* abort = &sh->abort;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&sh->w_full[s]), 1);
+      mbar_init(smem_u32(&sh->w_empty[s]), 1);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(smem_u32(&sh->a_full[i]), 1);
+      mbar_init(smem_u32(&sh->a_free[i]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh->acc_full[b]), 1);
+      mbar_init(smem_u32(&sh->acc_empty[b]), WORKERS);
+    }
+    mbar_init(smem_u32(&sh->mma_done), 1);
+    sh->abort = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_h);
+    tma_prefetch_desc(&tm_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&sh->tmem_base), 512);
+    tmem_relinquish();
+  }
+  for (int i = threadIdx.x; i < 3 * d; i += THREADS) s_bias[i] = p.bias[i];
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0, tile_i = 0;
+      bool ok = true;
+      auto w_stage = [&](int g, int kb) -> bool {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(smem_u32(&sh->w_empty[s]), ph ^ 1, abort)) { give_up(sh, p.status, 1); return false; }
+        const uint32_t bar = smem_u32(&sh->w_full[s]);
+        mbar_expect_tx(bar, STAGE_BYTES);
+        tma_load_2d(ring + s * STAGE_BYTES, &tm_w, 64 * kb, NG * g, bar);
+        ++it;
+        return true;
+      };
+      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_i) {
+        for (int kb = 0; kb < KB && ok; ++kb) {
+          // chunk kb of the h tile is free once the previous tile's last group has used it
+          if (!mbar_wait(smem_u32(&sh->a_free[kb]), (tile_i & 1) ^ 1, abort)) { give_up(sh, p.status, 2); ok = false; break; }
+          const uint32_t bar = smem_u32(&sh->a_full[kb]);
+          mbar_expect_tx(bar, CHUNK_BYTES);
+          tma_load_2d(sA + kb * CHUNK_BYTES, &tm_h, 64 * kb, t * ROWS, bar);
+          ok = w_stage(0, kb);
+        }
+        for (int g = 1; g < n_groups && ok; ++g)
+          for (int kb = 0; kb < KB && ok; ++kb) ok = w_stage(g, kb);
+      }
+      // loads in flight must land before the CTA exits (bounded, ignoring abort)
+      for (uint32_t j = it > STAGES ? it - STAGES : 0; j < it; ++j) {
+        uint32_t spins = 0;
+        while (!mbar_try_wait(smem_u32(&sh->w_full[j % STAGES]), (j / STAGES) & 1) && ++spins < kSpinLimit) {}
+        if (spins >= kSpinLimit) give_up(sh, p.status, 3);
+      }
+      if (tile_i > 0)
+        for (int kb = 0; kb < KB; ++kb) {
+          uint32_t spins = 0;
+          while (!mbar_try_wait(smem_u32(&sh->a_full[kb]), (tile_i - 1) & 1) && ++spins < kSpinLimit) {}
+          if (spins >= kSpinLimit) give_up(sh, p.status, 4);
+        }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tile_i = 0, gi = 0;
+      bool ok = true;
+      const uint32_t idesc = idesc_f16(BM, NG);
+      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_i) {
+        for (int g = 0; g < n_groups && ok; ++g, ++gi) {
+          const int buf = gi & 1;
+          if (!mbar_wait(smem_u32(&sh->acc_empty[buf]), ((gi >> 1) & 1) ^ 1, abort)) { give_up(sh, p.status, 5); ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * 256;
+          for (int kb = 0; kb < KB; ++kb, ++it) {
+            if (g == 0 && !mbar_wait(smem_u32(&sh->a_full[kb]), tile_i & 1, abort)) { give_up(sh, p.status, 6); ok = false; break; }
+            const int s = it % STAGES;
+            if (!mbar_wait(smem_u32(&sh->w_full[s]), (it / STAGES) & 1, abort)) { give_up(sh, p.status, 7); ok = false; break; }
+            tc_fence_after();
+            const uint64_t ad = smem_desc_sw128(sA + kb * CHUNK_BYTES), wd = smem_desc_sw128(ring + s * STAGE_BYTES);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mma_f16_ss(d_tmem, ad + 2 * k, wd + 2 * k, idesc, (kb | k) != 0);
+            tc_commit(smem_u32(&sh->w_empty[s]));
+            if (g == n_groups - 1) tc_commit(smem_u32(&sh->a_free[kb]));
+          }
+          if (ok) tc_commit(smem_u32(&sh->acc_full[buf]));
+        }
+      }
+      tc_commit(smem_u32(&sh->mma_done));
+      uint32_t spins = 0;
+      while (!mbar_try_wait(smem_u32(&sh->mma_done), 0) && ++spins < kSpinLimit) {}
+      if (spins >= kSpinLimit) give_up(sh, p.status, 8);
+    }
+  } else {
+    // ------------------------------------------------------------ workers: drain, then attend
+    const int wi = warp - 2;
+    const int q = warp & 3, half = wi >> 2;           // TMEM lane quadrant, column half (96 columns)
+    const int trow = q * 32 + lane;
+    const int env_l = wi >> 1, hh = wi & 1;           // this warp's (env, head) pair inside a group
+    uint32_t gi = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+      const int64_t env = (int64_t)t * EPT + env_l;
+      for (int g = 0; g < n_groups && ok; ++g, ++gi) {
+        const int buf = gi & 1;
+        if (!mbar_wait_warp(smem_u32(&sh->acc_full[buf]), (gi >> 1) & 1, abort)) {
+          if (lane == 0) give_up(sh, p.status, 9);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 96; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + half * 96 + c, r);
+          tmem_wait_ld();
+          const float4* b4 = reinterpret_cast<const float4*>(s_bias + g * NG + half * 96 + c);
+          uint8_t* dst = sQ_g + trow * LDQ + (half * 96 + c) * 2;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 b0 = b4[2 * j], b1 = b4[2 * j + 1];
+            *reinterpret_cast<uint4*>(dst + 16 * j) = make_uint4(
+                pack_half2(__uint_as_float(r[8 * j]) + b0.x, __uint_as_float(r[8 * j + 1]) + b0.y),
+                pack_half2(__uint_as_float(r[8 * j + 2]) + b0.z, __uint_as_float(r[8 * j + 3]) + b0.w),
+                pack_half2(__uint_as_float(r[8 * j + 4]) + b1.x, __uint_as_float(r[8 * j + 5]) + b1.y),
+                pack_half2(__uint_as_float(r[8 * j + 6]) + b1.z, __uint_as_float(r[8 * j + 7]) + b1.w));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[buf]));     // the TMEM buffer may be refilled
+        asm volatile("bar.sync 1, %0;" ::"n"(WORKERS * 32) : "memory");  // q|k|v tile complete
+        if (env < p.n_envs) {
+          const uint32_t rows = sQ + (env_l * kT) * LDQ;
+          attend_pair(rows + p.q_first * LDQ + (hh * DH) * 2, rows + (GD + hh * DH) * 2,
+                      rows + (2 * GD + hh * DH) * 2, p.key_bias + env * kT, p.n_q,
+                      p.out + env * p.n_q * (int64_t)p.ldo + (g * G + hh) * DH, p.ldo, lane);
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(WORKERS * 32) : "memory");  // tile may be overwritten
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+}  // namespace
+
+bool attn_block_ok(const AttnBlockArgs& a) {
+  if (a.d % 64 != 0 || a.d < 64 || a.d > 256 || a.n_heads * DH != a.d || a.n_heads % G != 0) return false;
+  if (a.n_envs < 1 || a.n_envs > 0x7fffffffLL / (ROWS * 2)) return false;
+  if (a.q_first < 0 || a.n_q < 1 || a.q_first + a.n_q > kT) return false;
+  if (!aligned16(a.h) || !aligned16(a.wg) || !aligned16(a.bg) || !aligned16(a.out) || (a.ldh % 8) || (a.ldo % 8)) return false;
+  return true;
+}
+
+int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
+  if (!a.h || !a.wg || !a.bg || !a.key_bias || !a.out) {
+    set_error("attn_block: NULL operand");
+    return BSRL_ERR_NULL;
+  }
+  if (!attn_block_ok(a)) {
+    set_error("attn_block: shape d=%d heads=%d does not fit the fused kernel (head_dim 32, d <= 256)", a.d, a.n_heads);
+    return BSRL_ERR_UNSUPPORTED;
+  }
+  int* status = device_status_ptr();
+  if (!status) return BSRL_ERR_CUDA;
+  CUtensorMap tm_h, tm_w;
+  if (!make_tmap_f16(&tm_h, a.h, a.n_envs * kT, a.d, a.ldh, BM)) return BSRL_ERR_CUDA;
+  if (!make_tmap_f16(&tm_w, a.wg, 3 * a.d, a.d, a.d, NG)) return BSRL_ERR_CUDA;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  BSRL_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr_set[dev] = true;
+  }
+  Params p;
+  p.d = a.d; p.n_heads = a.n_heads; p.q_first = a.q_first; p.n_q = a.n_q;
+  p.n_envs = a.n_envs;
+  p.n_tiles = (int)((a.n_envs + EPT - 1) / EPT);
+  p.bias = a.bg; p.key_bias = a.key_bias; p.out = a.out; p.ldo = a.ldo;
+  p.status = status;
+  const int grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
+  attn_block_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_h, tm_w, p);
+  BSRL_LAUNCH_OK("attn_block_kernel");
+  return BSRL_OK;
+}
+
+}  // namespace bsrl

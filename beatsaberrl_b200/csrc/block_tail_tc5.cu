@@ -10,12 +10,13 @@
 // as ONE kernel.  HBM traffic per token: read att (2d B) + x (4d B), write xo (4d B) + LN rows
 // (2d B each) -- against 18 d^2 FLOP, i.e. tensor-bound.
 //
-// Layout of one CTA (persistent, one per SM, 224 threads):
+// Layout of one CTA (persistent, one per SM, 352 threads):
 //   warp 0       TMA producer: att tile -> sA (d/64 chunks of [128 x 64], 128B swizzle);
 //                weight tiles -> a 3-stage ring of 32 KB stages, in the MMA's consumption order
-//   warp 6       TMA producer of the attention tiles (sA is freed before the tile ends)
+//   warp 10      TMA producer of the attention tiles (sA is freed before the tile ends); pulls the
+//                next tile's residual rows into L2
 //   warp 1       MMA issuer (one thread): tcgen05.mma, M = 128, K = 16
-//   warps 2..5   epilogue, thread = row: LayerNorm on TMEM rows -> h2 into sA; bias + ReLU of
+//   warps 2..9   epilogue (two groups of four warps, each group owns half of the columns), thread = row: LayerNorm on TMEM rows -> h2 into sA; bias + ReLU of
 //                each 128-wide hidden chunk -> sH; final drain and LayerNorm outputs; all global
 //                traffic goes through a per-warp transposition buffer so that it is coalesced;
 //                the per-column parameters live in shared memory
@@ -41,16 +42,20 @@ constexpr int STAGE_BYTES = 32768;
 constexpr int CHUNK_BYTES = BM * 64 * 2;   // one [128 x 64] fp16 swizzled chunk
 constexpr int SA_BYTES = 4 * CHUNK_BYTES;  // d <= 256
 constexpr int SH_BYTES = 2 * CHUNK_BYTES;  // one 128 x 128 hidden chunk
-constexpr int THREADS = 7 * 32;
-constexpr int STG_BYTES = 32 * 128;              // per-warp transposition buffer (32 rows x 128 B)
+constexpr int EPI_WARPS = 8;                     // two groups of four: each group owns half of the columns
+constexpr int PROD_WARP = 2 + EPI_WARPS;         // attention-tile producer / L2 prefetcher
+constexpr int THREADS = (3 + EPI_WARPS) * 32;
+constexpr int STG_BYTES = 32 * 64;               // per-warp transposition buffer (32 rows x 64 B)
 constexpr int PARAM_FLOATS = 8 * 256 + 1024;     // bo, ln_g, ln_b, b2, g16[2], b16[2] (d each) + b0 (F)
-constexpr int SMEM_BYTES = SA_BYTES + SH_BYTES + STAGES * STAGE_BYTES + 4 * STG_BYTES + PARAM_FLOATS * 4 + 1024 + 256;
+constexpr int PART_BYTES = 2 * 2 * BM * 8;       // LayerNorm partial sums exchanged between the two groups
+constexpr int SMEM_BYTES = SA_BYTES + SH_BYTES + STAGES * STAGE_BYTES + EPI_WARPS * STG_BYTES + PARAM_FLOATS * 4 +
+                           PART_BYTES + 1024 + 256;
 constexpr int KERNEL_ID = 2;
 
 struct Shared {
   uint64_t w_full[STAGES], w_empty[STAGES];
   uint64_t a_full, a_free, x_ready, o_done, h2_ready, x_done, mma_done;
-  uint64_t acc1_full[2], hid_ready, hid_free;
+  uint64_t acc1_full[2], hid_ready[2], hid_free[2];   // hid_*: per 64-column half of the hidden chunk
   uint32_t tmem_base;
   int abort;
 };
@@ -141,8 +146,9 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
   uint8_t* sA_g = gen;
   uint8_t* sH_g = gen + SA_BYTES;
   uint8_t* stg_all = gen + SA_BYTES + SH_BYTES + STAGES * STAGE_BYTES;
-  float* prm = reinterpret_cast<float*>(stg_all + 4 * STG_BYTES);
-  Shared* sh = reinterpret_cast<Shared*>(stg_all + 4 * STG_BYTES + PARAM_FLOATS * 4);
+  float* prm = reinterpret_cast<float*>(stg_all + EPI_WARPS * STG_BYTES);
+  float2* part = reinterpret_cast<float2*>(stg_all + EPI_WARPS * STG_BYTES + PARAM_FLOATS * 4);
+  Shared* sh = reinterpret_cast<Shared*>(stg_all + EPI_WARPS * STG_BYTES + PARAM_FLOATS * 4 + PART_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int d = p.d, KB = d >> 6, NC = p.F / HC, S1 = (KB + 1) >> 1;
   volatile int* abort = &sh->abort;
@@ -154,14 +160,16 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     }
     mbar_init(smem_u32(&sh->a_full), 1);
     mbar_init(smem_u32(&sh->a_free), 1);
-    mbar_init(smem_u32(&sh->x_ready), 4);
+    mbar_init(smem_u32(&sh->x_ready), EPI_WARPS);
     mbar_init(smem_u32(&sh->o_done), 1);
-    mbar_init(smem_u32(&sh->h2_ready), 4);
+    mbar_init(smem_u32(&sh->h2_ready), EPI_WARPS);
     mbar_init(smem_u32(&sh->x_done), 1);
     mbar_init(smem_u32(&sh->mma_done), 1);
     for (int b = 0; b < 2; ++b) mbar_init(smem_u32(&sh->acc1_full[b]), 1);
-    mbar_init(smem_u32(&sh->hid_ready), 4);
-    mbar_init(smem_u32(&sh->hid_free), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh->hid_ready[b]), 4);
+      mbar_init(smem_u32(&sh->hid_free[b]), 1);
+    }
     sh->abort = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_att);
@@ -230,7 +238,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         if (spins >= kSpinLimit) give_up(sh, p.status, 2);
       }
     }
-  } else if (warp == 6) {
+  } else if (warp == PROD_WARP) {
     // ------------------------------------------------------------ attention-tile producer
     // lane 0 loads the attention tile into sA as soon as the previous tile's last reader is done;
     // the whole warp then pulls the NEXT tile's residual rows into L2, so that the epilogue's
@@ -318,13 +326,13 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         ok = g1(0) && g1(1);
         if (NC == 2 && ok) tc_commit(smem_u32(&sh->a_free));
         for (int j = 0; j < NC && ok; ++j) {
-          if (!mbar_wait(smem_u32(&sh->hid_ready), n_hid & 1, abort)) { give_up(sh, p.status, 9); ok = false; break; }
-          ++n_hid;
-          tc_fence_after();
-          TRACE(110 + j);
-          for (int kc = 0; kc < 2 && ok; ++kc)      // xo += hidden chunk j * W2[:, chunk j]^T
+          for (int kc = 0; kc < 2 && ok; ++kc) {    // xo += hidden chunk j * W2[:, chunk j]^T, one 64-column half at a time
+            if (!mbar_wait(smem_u32(&sh->hid_ready[kc]), n_hid & 1, abort)) { give_up(sh, p.status, 9); ok = false; break; }
+            tc_fence_after();
             ok = with_stage([&](uint32_t st) { mma_kblock(xcol, sH + kc * CHUNK_BYTES, st, idesc_d, true); });
-          if (ok) tc_commit(smem_u32(&sh->hid_free));   // sH may be overwritten once these MMAs retire
+            if (ok) tc_commit(smem_u32(&sh->hid_free[kc]));   // this half of sH may be overwritten once retired
+          }
+          ++n_hid;
           TRACE(130 + j);
           if (ok && j + 2 < NC) {
             ok = g1(j + 2);
@@ -339,74 +347,88 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       while (!mbar_try_wait(smem_u32(&sh->mma_done), 0) && ++spins < kSpinLimit) {}
       if (spins >= kSpinLimit) give_up(sh, p.status, 10);
     }
-  } else if (warp >= 2 && warp <= 5) {
+  } else if (warp >= 2 && warp < PROD_WARP) {
     // ------------------------------------------------------------ epilogue warps, thread = row
-    // TMEM gives every thread one row.  Global memory is touched only in "transposed" form:
-    // a 32-row x 128-byte block goes through the warp's staging buffer so that 8 lanes cover one
-    // full 128-byte line (lane = (row sub + 4 i, 16-byte piece)).
+    // Two groups of four warps; both cover all 128 rows (warp & 3 = TMEM lane quadrant), group 0
+    // owns the low half of the columns, group 1 the high half.  Global memory is touched only in
+    // "transposed" form: a 32-row x 64-byte block goes through the warp's staging buffer so that
+    // 4 lanes cover 64 contiguous bytes of one row (lane = (row sub8 + 8 i, 16-byte piece)).
+    const int grp = (warp - 2) >> 2;
     const int q = warp & 3;
     const int trow = q * 32 + lane;                         // row inside the tile
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     uint8_t* stg = stg_all + (warp - 2) * STG_BYTES;
-    const int sub = lane >> 3, piece = lane & 7;
+    const int sub8 = lane >> 2, piece = lane & 3;
+    const int dh2 = d >> 1, c_lo = grp * dh2;               // this group's columns of the d-wide row
     const float4* prm4 = reinterpret_cast<const float4*>(prm);
-    // parameter vectors (float4 index = column / 4)
     const float4 *P_bo = prm4, *P_g = prm4 + 64, *P_b = prm4 + 128, *P_b2 = prm4 + 192, *P_b0 = prm4 + 512;
     uint32_t tile_i = 0, n_acc[2] = {0, 0}, n_free = 0;
     bool ok = true;
     const float inv_d = 1.0f / (float)d;
 
-    auto stg_write = [&](int row, int pc, uint4 v) {       // piece pc of row -> staging
-      *reinterpret_cast<uint4*>(stg + row * 128 + ((pc ^ (row & 7)) << 4)) = v;
+    auto stg_write = [&](int row, int pc, uint4 v) {        // 16-byte piece pc (0..3) of row -> staging
+      *reinterpret_cast<uint4*>(stg + row * 64 + ((pc ^ ((row >> 1) & 3)) << 4)) = v;
     };
     auto stg_read = [&](int row, int pc) -> uint4 {
-      return *reinterpret_cast<const uint4*>(stg + row * 128 + ((pc ^ (row & 7)) << 4));
+      return *reinterpret_cast<const uint4*>(stg + row * 64 + ((pc ^ ((row >> 1) & 3)) << 4));
     };
-    // pre-store (x + bo) rows of tile t, column block cb (128 wide), into TMEM columns col0 + ...
-    auto prestore = [&](int t, int cb, uint32_t col0) {
-      const int c0 = cb * 128, c1 = min(d, cb * 128 + 128);
-      const float* src[8];                                  // this lane's 8 rows in the transposed phase
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int64_t row = (int64_t)t * BM + q * 32 + i * 4 + sub;
-        src[i] = row < p.M ? p.x + p.xmap(row) * p.ldx + piece * 4 : nullptr;
-      }
-      uint4 nxt[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        nxt[i] = src[i] ? *reinterpret_cast<const uint4*>(src[i] + c0) : make_uint4(0, 0, 0, 0);
-      for (int c = c0; c < c1; c += 32) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) stg_write(i * 4 + sub, piece, nxt[i]);
-        if (c + 32 < c1) {                                  // next block's loads fly during this one
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            nxt[i] = src[i] ? *reinterpret_cast<const uint4*>(src[i] + c + 32) : make_uint4(0, 0, 0, 0);
-        }
-        __syncwarp();
-        uint32_t r[32];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint4 v = stg_read(lane, j);
-          const float4 bo = P_bo[(c >> 2) + j];
-          r[4 * j] = __float_as_uint(__uint_as_float(v.x) + bo.x);
-          r[4 * j + 1] = __float_as_uint(__uint_as_float(v.y) + bo.y);
-          r[4 * j + 2] = __float_as_uint(__uint_as_float(v.z) + bo.z);
-          r[4 * j + 3] = __float_as_uint(__uint_as_float(v.w) + bo.w);
-        }
-        tmem_st32(lane_base + col0 + c, r);
-        __syncwarp();
-      }
-      tmem_wait_st();
-    };
+    auto group_sync = [&]() { asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory"); };
     auto signal = [&](uint64_t* bar) {   // one arrival per warp, after everyone's writes
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bar));
     };
+    // row statistics of the whole row from this group's partial sums and the other group's
+    auto row_stats = [&](int phase, float sum, float sq, float& mean, float& rstd) {
+      part[(phase * 2 + grp) * BM + trow] = make_float2(sum, sq);
+      group_sync();
+      const float2 o = part[(phase * 2 + (grp ^ 1)) * BM + trow];
+      mean = (sum + o.x) * inv_d;
+      rstd = rsqrtf(fmaxf((sq + o.y) * inv_d - mean * mean, 0.f) + p.eps);
+    };
+    // pre-store (x + bo) of tile t, this group's columns, into TMEM columns col0 + ...
+    auto prestore = [&](int t, uint32_t col0) {
+      const float* src[4];                                  // this lane's 4 rows in the transposed phase
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int64_t row = (int64_t)t * BM + q * 32 + i * 8 + sub8;
+        src[i] = row < p.M ? p.x + p.xmap(row) * p.ldx + piece * 4 : nullptr;
+      }
+      uint4 nxt[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        nxt[i] = src[i] ? *reinterpret_cast<const uint4*>(src[i] + c_lo) : make_uint4(0, 0, 0, 0);
+      for (int c = c_lo; c < c_lo + dh2; c += 32) {
+        uint32_t r[32];
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {                    // two 16-column blocks per 32 TMEM columns
+          const int cc = c + 16 * hb;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) stg_write(i * 8 + sub8, piece, nxt[i]);
+          if (cc + 16 < c_lo + dh2) {                       // next block's loads fly during this one
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              nxt[i] = src[i] ? *reinterpret_cast<const uint4*>(src[i] + cc + 16) : make_uint4(0, 0, 0, 0);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 v = stg_read(lane, j);
+            const float4 bo = P_bo[(cc >> 2) + j];
+            r[16 * hb + 4 * j] = __float_as_uint(__uint_as_float(v.x) + bo.x);
+            r[16 * hb + 4 * j + 1] = __float_as_uint(__uint_as_float(v.y) + bo.y);
+            r[16 * hb + 4 * j + 2] = __float_as_uint(__uint_as_float(v.z) + bo.z);
+            r[16 * hb + 4 * j + 3] = __float_as_uint(__uint_as_float(v.w) + bo.w);
+          }
+          __syncwarp();
+        }
+        tmem_st32(lane_base + col0 + c, r);
+      }
+      tmem_wait_st();
+    };
 
     if ((int)blockIdx.x < p.n_tiles) {
-      for (int cb = 0; cb * 128 < d; ++cb) prestore(blockIdx.x, cb, 0u);
+      prestore(blockIdx.x, 0u);
       signal(&sh->x_ready);
     }
     for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_i) {
@@ -419,7 +441,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       if (warp == 2 && lane == 0) TRACE(200);
       {
         float sum = 0.f, sq = 0.f;
-        for (int c = 0; c < d; c += 32) {
+        for (int c = c_lo; c < c_lo + dh2; c += 32) {
           uint32_t r[32];
           tmem_ld32(lane_base + xcol + c, r);
           tmem_wait_ld();
@@ -430,10 +452,10 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
             sq = fmaf(v, v, sq);
           }
         }
-        const float mean = sum * inv_d;
-        const float rstd = rsqrtf(fmaxf(sq * inv_d - mean * mean, 0.f) + p.eps);
+        float mean, rstd;
+        row_stats(0, sum, sq, mean, rstd);
         const float shift = -mean * rstd;
-        for (int c = 0; c < d; c += 32) {
+        for (int c = c_lo; c < c_lo + dh2; c += 32) {
           uint32_t r[32];
           float v[32];
           tmem_ld32(lane_base + xcol + c, r);
@@ -452,7 +474,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       fence_proxy_async_smem();
       signal(&sh->h2_ready);
       if (warp == 2 && lane == 0) TRACE(201);
-      // ---- hidden chunks: relu(acc + b0) -> sH (one buffer: wait until the previous chunk's MMAs retired)
+      // ---- hidden chunks: relu(acc + b0) -> sH; this group handles 64 of the chunk's 128 columns
       for (int j = 0; j < NC && ok; ++j) {
         const int b = j & 1;
         if (!mbar_wait_warp(smem_u32(&sh->acc1_full[b]), n_acc[b] & 1, abort)) {
@@ -463,23 +485,23 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         ++n_acc[b];
         tc_fence_after();
         if (warp == 2 && lane == 0) TRACE(210 + j);
-        uint32_t hp[64];                                    // 128 fp16 values of this row
+        uint32_t hp[32];                                    // 64 fp16 values of this row
 #pragma unroll
-        for (int c = 0; c < HC; c += 32) {
+        for (int c = 0; c < 64; c += 32) {
           uint32_t r[32];
-          tmem_ld32(lane_base + acol + b * HC + c, r);
+          tmem_ld32(lane_base + acol + b * HC + grp * 64 + c, r);
           tmem_wait_ld();
 #pragma unroll
           for (int jj = 0; jj < 8; ++jj) {
-            const float4 b0 = P_b0[((j * HC + c) >> 2) + jj];
+            const float4 b0 = P_b0[((j * HC + grp * 64 + c) >> 2) + jj];
             hp[(c >> 1) + 2 * jj] = pack_half2(fmaxf(__uint_as_float(r[4 * jj]) + b0.x, 0.f),
                                                fmaxf(__uint_as_float(r[4 * jj + 1]) + b0.y, 0.f));
             hp[(c >> 1) + 2 * jj + 1] = pack_half2(fmaxf(__uint_as_float(r[4 * jj + 2]) + b0.z, 0.f),
                                                    fmaxf(__uint_as_float(r[4 * jj + 3]) + b0.w, 0.f));
           }
         }
-        // sH is free once the previous chunk's FFN-down MMAs have retired
-        if (!mbar_wait_warp(smem_u32(&sh->hid_free), (n_free & 1) ^ 1, abort)) {
+        // this half of sH is free once the previous chunk's FFN-down MMAs on it have retired
+        if (!mbar_wait_warp(smem_u32(&sh->hid_free[grp]), (n_free & 1) ^ 1, abort)) {
           if (lane == 0) give_up(sh, p.status, 14);
           ok = false;
           break;
@@ -487,92 +509,93 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         ++n_free;
         if (warp == 2 && lane == 0) TRACE(220 + j);
         {
-          uint8_t* rowp = sH_g + (trow >> 3) * 1024 + (trow & 7) * 128;
+          uint8_t* rowp = sH_g + grp * CHUNK_BYTES + (trow >> 3) * 1024 + (trow & 7) * 128;
 #pragma unroll
-          for (int pc = 0; pc < 16; ++pc)                   // 16 pieces of 8 halfs: chunk pc / 8, piece pc % 8
-            *reinterpret_cast<uint4*>(rowp + (pc >> 3) * CHUNK_BYTES + (((pc & 7) ^ (trow & 7)) << 4)) =
+          for (int pc = 0; pc < 8; ++pc)
+            *reinterpret_cast<uint4*>(rowp + ((pc ^ (trow & 7)) << 4)) =
                 make_uint4(hp[4 * pc], hp[4 * pc + 1], hp[4 * pc + 2], hp[4 * pc + 3]);
         }
         fence_proxy_async_smem();
-        signal(&sh->hid_ready);
+        signal(&sh->hid_ready[grp]);
         if (warp == 2 && lane == 0) TRACE(230 + j);
-        // the buffers of the last two chunks are free now: pre-store the next tile's x there
-        if (t_next < p.n_tiles && j + 2 >= NC) {
-          const int cb = j + 2 - NC;               // NC-2 -> block 0, NC-1 -> block 1
-          if (cb * 128 < d) prestore(t_next, cb, acol);
-          if (j + 1 == NC) signal(&sh->x_ready);
-        }
       }
       if (!ok) break;
+      // both hidden-chunk buffers are consumed by both groups: pre-store the next tile's x there
+      if (t_next < p.n_tiles) {
+        group_sync();
+        prestore(t_next, acol);
+        signal(&sh->x_ready);
+      }
       // ---- final: xo = X + b2 -> fp32 out (coalesced), then LayerNorm / fp16 outputs
       TAIL_WAIT_WARP(&sh->x_done, par, 13);
       tc_fence_after();
       if (warp == 2 && lane == 0) TRACE(250);
       {
         const int64_t row0 = (int64_t)t * BM + q * 32;      // first row of this warp
+        const bool want_stats = p.g16[0] || p.g16[1];
         float sum = 0.f, sq = 0.f;
-        if (p.x_out || p.g16[0] || p.g16[1]) {
-          for (int c = 0; c < d; c += 32) {
+        if (p.x_out || want_stats) {
+          for (int c = c_lo; c < c_lo + dh2; c += 32) {
             uint32_t r[32];
             tmem_ld32(lane_base + xcol + c, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 b2 = P_b2[(c >> 2) + j];
-              float4 v = make_float4(__uint_as_float(r[4 * j]) + b2.x, __uint_as_float(r[4 * j + 1]) + b2.y,
-                                     __uint_as_float(r[4 * j + 2]) + b2.z, __uint_as_float(r[4 * j + 3]) + b2.w);
-              sum += (v.x + v.y) + (v.z + v.w);
-              sq = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, sq))));
-              if (p.x_out)
-                stg_write(lane, j, make_uint4(__float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z),
-                                              __float_as_uint(v.w)));
-            }
-            if (p.x_out) {
-              __syncwarp();
+            for (int hb = 0; hb < 2; ++hb) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const int rr = i * 4 + sub;
-                if (row0 + rr < p.M)
-                  *reinterpret_cast<uint4*>(p.x_out + (row0 + rr) * d + c + piece * 4) = stg_read(rr, piece);
+              for (int j = 0; j < 4; ++j) {
+                const float4 b2 = P_b2[((c + 16 * hb) >> 2) + j];
+                float4 v = make_float4(__uint_as_float(r[16 * hb + 4 * j]) + b2.x, __uint_as_float(r[16 * hb + 4 * j + 1]) + b2.y,
+                                       __uint_as_float(r[16 * hb + 4 * j + 2]) + b2.z, __uint_as_float(r[16 * hb + 4 * j + 3]) + b2.w);
+                sum += (v.x + v.y) + (v.z + v.w);
+                sq = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, sq))));
+                if (p.x_out)
+                  stg_write(lane, j, make_uint4(__float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z),
+                                                __float_as_uint(v.w)));
               }
-              __syncwarp();
+              if (p.x_out) {
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int rr = i * 8 + sub8;
+                  if (row0 + rr < p.M)
+                    *reinterpret_cast<uint4*>(p.x_out + (row0 + rr) * d + c + 16 * hb + piece * 4) = stg_read(rr, piece);
+                }
+                __syncwarp();
+              }
             }
           }
         }
-        const float mean = sum * inv_d;
-        const float rstd = rsqrtf(fmaxf(sq * inv_d - mean * mean, 0.f) + p.eps);
+        float mean = 0.f, rstd = 1.f;
+        if (want_stats) row_stats(1, sum, sq, mean, rstd);
 #pragma unroll 1
         for (int o = 0; o < 2; ++o) {
           if (!p.out16[o]) continue;
           const bool ln = p.g16[o] != nullptr;
           const float sc = ln ? rstd : 1.f, sh0 = ln ? -mean * rstd : 0.f;
           const float4 *P_go = prm4 + 256 + 128 * o, *P_bo16 = prm4 + 320 + 128 * o;
-          for (int c = 0; c < d; c += 64) {
+          for (int c = c_lo; c < c_lo + dh2; c += 32) {     // 32 columns = 64 bytes of fp16 per row
+            uint32_t r[32];
+            tmem_ld32(lane_base + xcol + c, r);
+            tmem_wait_ld();
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              uint32_t r[32];
-              tmem_ld32(lane_base + xcol + c + 32 * hh, r);
-              tmem_wait_ld();
+            for (int j = 0; j < 4; ++j) {                   // 8 columns -> one 16-byte fp16 piece
+              float y[8];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {                 // 8 columns -> one 16-byte fp16 piece
-                float y[8];
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                  const int f4 = ((c + 32 * hh) >> 2) + 2 * j + e;
-                  const float4 b2 = P_b2[f4], g = P_go[f4], bb = P_bo16[f4];
-                  y[4 * e] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e]) + b2.x, sc, sh0), g.x, bb.x);
-                  y[4 * e + 1] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 1]) + b2.y, sc, sh0), g.y, bb.y);
-                  y[4 * e + 2] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 2]) + b2.z, sc, sh0), g.z, bb.z);
-                  y[4 * e + 3] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 3]) + b2.w, sc, sh0), g.w, bb.w);
-                }
-                stg_write(lane, 4 * hh + j, make_uint4(pack_half2(y[0], y[1]), pack_half2(y[2], y[3]),
-                                                        pack_half2(y[4], y[5]), pack_half2(y[6], y[7])));
+              for (int e = 0; e < 2; ++e) {
+                const int f4 = (c >> 2) + 2 * j + e;
+                const float4 b2 = P_b2[f4], g = P_go[f4], bb = P_bo16[f4];
+                y[4 * e] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e]) + b2.x, sc, sh0), g.x, bb.x);
+                y[4 * e + 1] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 1]) + b2.y, sc, sh0), g.y, bb.y);
+                y[4 * e + 2] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 2]) + b2.z, sc, sh0), g.z, bb.z);
+                y[4 * e + 3] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 3]) + b2.w, sc, sh0), g.w, bb.w);
               }
+              stg_write(lane, j, make_uint4(pack_half2(y[0], y[1]), pack_half2(y[2], y[3]),
+                                            pack_half2(y[4], y[5]), pack_half2(y[6], y[7])));
             }
             __syncwarp();
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int rr = i * 4 + sub;
+            for (int i = 0; i < 4; ++i) {
+              const int rr = i * 8 + sub8;
               if (row0 + rr < p.M)
                 *reinterpret_cast<uint4*>(p.out16[o] + (row0 + rr) * p.ld16[o] + c + piece * 8) = stg_read(rr, piece);
             }

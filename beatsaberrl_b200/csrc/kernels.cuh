@@ -57,6 +57,22 @@ struct BlockTailArgs {
 bool block_tail_ok(const BlockTailArgs& a);
 int block_tail(const BlockTailArgs& a, cudaStream_t stream);
 
+// Fused q|k|v projection + masked attention (head_dim 32), weights regrouped per head group.
+struct AttnBlockArgs {
+  int d, n_heads;
+  int64_t n_envs;
+  const __half* h;       // (n_envs*29, d) LayerNorm rows
+  int ldh;
+  const __half* wg;      // regrouped [q|k|v] weight (3d, d)
+  const float* bg;       // regrouped bias (3d)
+  const float* key_bias; // (n_envs, 29)
+  int q_first, n_q;      // query rows of each env
+  __half* out;           // (n_envs*n_q, ldo)
+  int ldo;
+};
+bool attn_block_ok(const AttnBlockArgs& a);
+int attn_block(const AttnBlockArgs& a, cudaStream_t stream);
+
 // y(f16, ldy) = LayerNorm(x(f32, ldx)) per row, fp32 statistics.
 int layernorm_rows(const float* x, int64_t ldx, RowMap xmap, const float* gamma, const float* beta,
                    float eps, int64_t rows, int d, __half* y, int64_t ldy, cudaStream_t stream);

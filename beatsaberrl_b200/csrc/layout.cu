@@ -168,6 +168,7 @@ Layout make_layout(const bsrl_config& c) {
     b.ln_ffn = carve_norm(cv, d);
     b.up = carve_mat(cv, l.F, d);
     b.down = carve_mat(cv, d, l.F);
+    b.qkv_g = carve_mat(cv, 3 * d, d);
   }
   l.trunk_proj = carve_mat(cv, l.D, kLead * d);
   l.trunk_ln1 = carve_norm(cv, l.D);
@@ -182,6 +183,9 @@ Layout make_layout(const bsrl_config& c) {
   l.critic_m0 = carve_mat(cv, l.D, d + l.D);
   l.critic_m1 = carve_mat(cv, l.D, l.D);
   l.critic_m2 = carve_mat(cv, l.bins, l.D, 0, l.bins_pad);
+  l.critic_qkv_g = carve_mat(cv, 3 * d, d);
+  // fused QKV+attention kernel: head_dim 32, two heads per group (192 output columns per group)
+  l.attn_G = (d / l.H == 32 && l.H % 2 == 0 && d % 64 == 0 && d <= 256) ? 2 : 0;
   l.bytes = cv.off;
   return l;
 }
@@ -233,6 +237,36 @@ std::vector<ParamSlot> make_param_slots(const bsrl_config& c, const Layout& l) {
   lin("critic_mlp.2", l.critic_m1, l.D, l.D, 0);
   lin("critic_mlp.4", l.critic_m2, l.bins, l.D, 0);
   return s;
+}
+
+// Regrouped q|k|v: group g holds [q rows of its heads | k rows | v rows], 3*G*dh rows per group.
+std::vector<CopySlot> make_copy_slots(const bsrl_config& c, const Layout& l, const std::vector<ParamSlot>& params) {
+  std::vector<CopySlot> out;
+  if (l.attn_G == 0) return out;
+  auto find = [&](const std::string& name) {
+    for (size_t i = 0; i < params.size(); ++i)
+      if (params[i].name == name) return (int)i;
+    return -1;
+  };
+  const int d = l.d, gd = l.attn_G * (d / l.H), n_groups = d / gd;
+  auto regroup = [&](const Mat& m, const std::string names[3]) {
+    for (int sct = 0; sct < 3; ++sct) {
+      const int pw = find(names[sct] + ".weight"), pb = find(names[sct] + ".bias");
+      for (int g = 0; g < n_groups; ++g) {
+        const int64_t row = (int64_t)g * 3 * gd + sct * gd;
+        out.push_back({pw, (int64_t)g * gd, gd, d, m.w + row * m.pitch * 2, m.pitch, true});
+        out.push_back({pb, (int64_t)g * gd, gd, 1, m.b + row * 4, 0, false});
+      }
+    }
+  };
+  for (int i = 0; i < l.L; ++i) {
+    const std::string p = "blocks." + std::to_string(i);
+    const std::string names[3] = {p + ".q_proj", p + ".k_proj", p + ".v_proj"};
+    regroup(l.blocks[i].qkv_g, names);
+  }
+  const std::string cn[3] = {"critic_q", "critic_k", "critic_v"};
+  regroup(l.critic_qkv_g, cn);
+  return out;
 }
 
 // ------------------------------------------------------------------ workspace

@@ -25,6 +25,7 @@ struct Norm {         // fp32 gamma, beta
 struct BlockW {
   Norm ln_attn, ln_ffn;
   Mat qkv, out, up, down;
+  Mat qkv_g;   // q|k|v rows regrouped per head group for the fused attention kernel (see attn_G)
 };
 struct Encoder {
   Mat l0, l1;
@@ -37,6 +38,8 @@ struct Layout {
   Mat trunk_proj, trunk_fc1, trunk_fc2, heads;
   Norm trunk_ln1, trunk_ln2, critic_ln;
   Mat critic_q, critic_kv, critic_out, critic_m0, critic_m1, critic_m2;
+  Mat critic_qkv_g;   // critic q|k|v regrouped like BlockW::qkv_g
+  int attn_G = 0;     // heads per group of the fused QKV+attention kernel; 0 = shape not supported
   int head_first[kActHeads];
   int64_t bytes = 0;
 };
@@ -50,9 +53,18 @@ struct ParamSlot {
   bool half;
 };
 
+// A second destination for (a row range of) a master parameter: the regrouped q|k|v copies.
+struct CopySlot {
+  int param;               // index into make_param_slots()
+  int64_t src_row0, n_rows, cols;
+  int64_t dst, dst_pitch;
+  bool half;
+};
+
 int validate_config(const bsrl_config* c);
 Layout make_layout(const bsrl_config& c);
 std::vector<ParamSlot> make_param_slots(const bsrl_config& c, const Layout& l);
+std::vector<CopySlot> make_copy_slots(const bsrl_config& c, const Layout& l, const std::vector<ParamSlot>& params);
 
 // Workspace carve-up for a batch of n_envs.
 struct Workspace {

@@ -150,3 +150,32 @@ def test_block_tail(native, m, d, f, ln_out):
         None, None, None, _stream()))
     native.check(native.lib.bsrl_device_status())
     assert torch.equal(x_in, x_out)
+
+
+@pytest.mark.parametrize("B,d,H,q_first,n_q", [(1, 64, 2, 0, 29), (4, 256, 8, 0, 29), (37, 256, 8, 0, 29),
+                                               (50, 128, 4, 0, 5), (33, 256, 8, 2, 1), (3000, 256, 8, 0, 29)])
+def test_qkv_attention(native, B, d, H, q_first, n_q):
+    """Fused projection + attention kernel against torch fp32 on the same fp16 operands."""
+    g = torch.Generator().manual_seed(B + d + n_q)
+    h = torch.randn(B * 29, d, generator=g).half()
+    w = (torch.randn(3 * d, d, generator=g) / d ** 0.5).half()
+    bias = torch.randn(3 * d, generator=g) * 0.2
+    n_live = torch.randint(0, 25, (B,), generator=g)
+    kb = torch.zeros(B, 29)
+    kb[:, 5:] = ((torch.arange(24)[None, :] < n_live[:, None]).float() - 1.0) * 16384.0
+    # regroup per pair of heads: [q rows | k rows | v rows] of heads 2g, 2g+1
+    idx = []
+    for grp in range(d // 64):
+        for sct in range(3):
+            idx += list(range(sct * d + grp * 64, sct * d + grp * 64 + 64))
+    idx = torch.tensor(idx)
+    wg, bg = w[idx].contiguous().cuda(), bias[idx].contiguous().cuda()
+    out = torch.empty(B * n_q, d, dtype=torch.float16, device="cuda")
+    h_d, kb_d = h.cuda(), kb.cuda()
+    native.check(native.lib.bsrl_qkv_attention(h_d.data_ptr(), wg.data_ptr(), bg.data_ptr(), kb_d.data_ptr(),
+                                               B, d, H, q_first, n_q, out.data_ptr(), _stream()))
+    native.check(native.lib.bsrl_device_status())
+    qkv = (h.float() @ w.float().t() + bias).half().float().view(B, 29, 3 * d)
+    q, k, v = qkv.split(d, -1)
+    ref = po.attention(q[:, q_first:q_first + n_q], k, v, kb, H)
+    torch.testing.assert_close(out.float().cpu().view(B, n_q, d), ref, atol=5e-3, rtol=3e-3)
