@@ -43,6 +43,7 @@ struct Shared {
   uint64_t w_full[STAGES], w_empty[STAGES], a_full[4], a_free[4], acc_full[2], acc_empty[2], mma_done;
   uint32_t tmem_base;
   int abort;
+  int quit;   // abort flag as sampled by one thread before a CTA-level barrier, so all workers leave together
 };
 
 struct Params {
@@ -188,6 +189,7 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
     }
     mbar_init(smem_u32(&sh->mma_done), 1);
     sh->abort = 0;
+    sh->quit = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_h);
     tma_prefetch_desc(&tm_w);
@@ -285,11 +287,10 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
       const int64_t env = (int64_t)t * EPT + env_l;
       for (int g = 0; g < n_groups && ok; ++g, ++gi) {
         const int buf = gi & 1;
-        if (!mbar_wait_warp(smem_u32(&sh->acc_full[buf]), (gi >> 1) & 1, abort)) {
-          if (lane == 0) give_up(sh, p.status, 9);
-          ok = false;
-          break;
-        }
+        // A failed wait must not leave other workers stuck at the CTA-level barriers below: the
+        // warp keeps going (on garbage) and everyone leaves together once one thread has sampled
+        // the abort flag ahead of a barrier.
+        if (!mbar_wait_warp(smem_u32(&sh->acc_full[buf]), (gi >> 1) & 1, abort) && lane == 0) give_up(sh, p.status, 9);
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < 96; c += 32) {
@@ -311,7 +312,12 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[buf]));     // the TMEM buffer may be refilled
+        if (wi == 0 && lane == 0) sh->quit = *abort;
         asm volatile("bar.sync 1, %0;" ::"n"(WORKERS * 32) : "memory");  // q|k|v tile complete
+        if (*reinterpret_cast<volatile int*>(&sh->quit)) {
+          ok = false;
+          break;
+        }
         if (env < p.n_envs) {
           const uint32_t rows = sQ + (env_l * kT) * LDQ;
           attend_pair(rows + p.q_first * LDQ + (hh * DH) * 2, rows + (GD + hh * DH) * 2,

@@ -263,7 +263,9 @@ def run_ours(args, rank, world, local_rank):
         achieved = t["flops"] / (t["ms"] * 1e-3) / 1e12
         roofline = {"bound": "tensor", "kernel": top_name, "achieved": achieved,
                     "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
-                    "frac": achieved / peaks["tflops_sustained"], "traffic": KNOWN_TRAFFIC.get(top_name),
+                    "frac": achieved / peaks["tflops_sustained"],
+                    "traffic": (TRAFFIC_RATIO[top_name] * t["bytes"] / t["launches"] if top_name in TRAFFIC_RATIO else None),
+                    "traffic_source": "ncu dram bytes of a 237,568-row launch scaled by rows (profiles/)",
                     "peak_source": peaks["source"] + " (sustained bf16 GEMM; burst %.1f)" % peaks["tflops_burst"],
                     "launches": t["launches"], "ms_per_launch": t["ms"] / t["launches"],
                     "algorithmic_bytes_per_launch": t["bytes"] / t["launches"],
@@ -299,9 +301,65 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-# DRAM bytes per launch of a stage's kernel from the committed ncu captures (profiles/);
-# None until a capture of that kernel exists.
-KNOWN_TRAFFIC = {}
+def run_kernel(args):
+    """Single-kernel microbenchmark through the C ABI (the small cases the ncu captures under
+    profiles/ were taken on): block_tail, attn_block or linear on --rows token rows, d = --embed."""
+    from beatsaberrl_b200 import _native as nat
+    torch.cuda.set_device(0)
+    d, rows = args.embed, args.rows
+    f = 4 * d
+    g = torch.Generator().manual_seed(1)
+    rnd = lambda *shape, scale=1.0: (torch.randn(*shape, generator=g) * scale).cuda()
+    st = torch.cuda.current_stream().cuda_stream
+    if args.kernel == "block_tail":
+        att, x = rnd(rows, d).half(), rnd(rows, d)
+        wo, w0, w2 = rnd(d, d, scale=d ** -0.5).half(), rnd(f, d, scale=d ** -0.5).half(), rnd(d, f, scale=f ** -0.5).half()
+        bo, b2, b0 = rnd(d, scale=0.1), rnd(d, scale=0.1), rnd(f, scale=0.1)
+        lg, lb = torch.ones(d).cuda(), torch.zeros(d).cuda()
+        out16 = torch.empty(rows, d, dtype=torch.float16, device="cuda")
+        flops = 2.0 * rows * (d * d + 2 * d * f)
+        nbytes = rows * d * (2 + 4 + 4 + 2)
+        run = lambda: nat.check(nat.lib.bsrl_block_tail(
+            att.data_ptr(), x.data_ptr(), wo.data_ptr(), bo.data_ptr(), lg.data_ptr(), lb.data_ptr(), w0.data_ptr(),
+            b0.data_ptr(), w2.data_ptr(), b2.data_ptr(), 1e-5, rows, d, f, x.data_ptr(), out16.data_ptr(),
+            lg.data_ptr(), lb.data_ptr(), st))
+    elif args.kernel == "attn_block":
+        envs = rows // 29
+        h = rnd(envs * 29, d).half()
+        w, bias = rnd(3 * d, d, scale=d ** -0.5).half(), rnd(3 * d, scale=0.1)
+        kb = torch.zeros(envs, 29).cuda()
+        out = torch.empty(envs * 29, d, dtype=torch.float16, device="cuda")
+        flops = 2.0 * envs * 29 * 3 * d * d + 4.0 * envs * 29 * 29 * d
+        nbytes = envs * 29 * d * 4
+        run = lambda: nat.check(nat.lib.bsrl_qkv_attention(h.data_ptr(), w.data_ptr(), bias.data_ptr(), kb.data_ptr(),
+                                                           envs, d, d // 32, 0, 29, out.data_ptr(), st))
+    else:
+        n, k = args.cols or 3 * d, d
+        a, w, bias = rnd(rows, k).half(), rnd(n, k, scale=k ** -0.5).half(), rnd(n)
+        out = torch.empty(rows, n, dtype=torch.float16, device="cuda")
+        flops = 2.0 * rows * n * k
+        nbytes = rows * k * 2 + n * k * 2 + rows * n * 2
+        run = lambda: nat.check(nat.lib.bsrl_linear(a.data_ptr(), w.data_ptr(), bias.data_ptr(), None, out.data_ptr(),
+                                                    0, 0, rows, n, k, 1, st))
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    nat.check(nat.lib.bsrl_device_status())
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"kernel": args.kernel, "rows": rows, "embed": d, "ms_per_launch": ms,
+                      "tflops": flops / ms / 1e9, "algorithmic_gbs": nbytes / ms / 1e6}), flush=True)
+
+
+# Measured DRAM traffic / algorithmic bytes of each stage's kernel, from the committed ncu captures
+# (profiles/*_rows237568_d256.md, taken on 237,568-row cases; traffic grows in proportion to the
+# rows, so a full-size launch's traffic is this ratio times its algorithmic bytes).
+TRAFFIC_RATIO = {"block_tail": 1.00, "attn_block": 0.82}
 
 
 def main():
@@ -313,6 +371,11 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--envs", type=int, default=0, help="envs per GPU (default: the workload's)")
     ap.add_argument("--cpu-sample", type=int, default=0, help="envs in the CPU sample")
+    ap.add_argument("--kernel", default="", choices=("", "block_tail", "attn_block", "linear"),
+                    help="time one kernel alone on --rows token rows instead of the whole forward")
+    ap.add_argument("--rows", type=int, default=237568)
+    ap.add_argument("--embed", type=int, default=256)
+    ap.add_argument("--cols", type=int, default=0, help="output columns of --kernel linear (default 3 * embed)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -322,6 +385,9 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the policy forward has no CPU path)")
+    if args.kernel:
+        run_kernel(args)
+        return
     run_ours(args, rank, world, local_rank)
 
 
