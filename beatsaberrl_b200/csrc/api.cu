@@ -209,7 +209,6 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     a.w0 = c.W(b.up); a.b0 = c.Bv(b.up);
     a.w2 = c.W(b.down); a.b2 = c.Bv(b.down);
     a.eps = eps;
-    a.packed_params = at<float>(c.arena, b.tail_prm);
     return a;
   };
   bool fused = false;

@@ -67,14 +67,14 @@ __device__ __forceinline__ void give_up(Shared* sh, int* status, int role) {
 __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t sv, const float* key_bias_env,
                                             int n_q, __half* out_env, int ldo, int lane) {
   const int g = lane >> 2, tig = lane & 3;
-  const float scale = rsqrtf((float)DH);
+  const float scale = rsqrtf((float)DH) * 1.4426950408889634f;   // 1/sqrt(dh) * log2(e)
   float kb[4][2];
 #pragma unroll
   for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int key = nt * 8 + tig * 2 + e;
-      kb[nt][e] = key < kT ? key_bias_env[key] : -INFINITY;
+      kb[nt][e] = key < kT ? key_bias_env[key] * 1.4426950408889634f : -INFINITY;
     }
   const int m_tiles = (n_q + 15) >> 4;
   for (int mt = 0; mt < m_tiles; ++mt) {
@@ -101,7 +101,7 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        s[nt][e] = s[nt][e] * scale + kb[nt][e & 1];
+        s[nt][e] = fmaf(s[nt][e], scale, kb[nt][e & 1]);   // base-2 logits: scale and key bias carry log2(e)
         mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
       }
     float sum[2] = {0.f, 0.f};
@@ -114,14 +114,14 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        s[nt][e] = expf(s[nt][e] - mx[e >> 1]);
+        s[nt][e] = exp2f(s[nt][e] - mx[e >> 1]);
         sum[e >> 1] += s[nt][e];
       }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
       sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
-      sum[r] = 1.f / sum[r];
+      sum[r] = __frcp_rn(sum[r]);
     }
     uint32_t pa[2][4];
 #pragma unroll
@@ -285,6 +285,50 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
     bool ok = true;
     for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
       const int64_t env = (int64_t)t * EPT + env_l;
+      for (int g = 0; g < n_groups && ok; ++g, ++gi) {
+          const int buf = gi & 1;
+          if (!mbar_wait(smem_u32(&sh->acc_empty[buf]), ((gi >> 1) & 1) ^ 1, abort)) { give_up(sh, p.status, 5); ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * 256;
+          for (int kb = 0; kb < KB; ++kb, ++it) {
+            if (g == 0 && !mbar_wait(smem_u32(&sh->a_full[kb]), tile_i & 1, abort)) { give_up(sh, p.status, 6); ok = false; break; }
+            const int s = it % STAGES;
+            if (!mbar_wait(smem_u32(&sh->w_full[s]), (it / STAGES) & 1, abort)) { give_up(sh, p.status, 7); ok = false; break; }
+            tc_fence_after();
+            const uint64_t ad = smem_desc_sw128(sA + kb * CHUNK_BYTES), wd = smem_desc_sw128(ring + s * STAGE_BYTES);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mma_f16_ss(d_tmem, ad + 2 * k, wd + 2 * k, idesc, (kb | k) != 0);
+            tc_commit(smem_u32(&sh->w_empty[s]));
+            if (g == n_groups - 1) tc_commit(smem_u32(&sh->a_free[kb]));
+          }
+          if (ok) tc_commit(smem_u32(&sh->acc_full[buf]));
+        }
+      }
+      tc_commit(smem_u32(&sh->mma_done));
+      uint32_t spins = 0;
+      while (!mbar_try_wait(smem_u32(&sh->mma_done), 0) && ++spins < kSpinLimit) {}
+      if (spins >= kSpinLimit) give_up(sh, p.status, 8);
+    }
+  } else {
+    // ------------------------------------------------------------ workers: drain, then attend
+    const int wi = warp - 2;
+    const int q = warp & 3, half = wi >> 2;           // TMEM lane quadrant, column half (96 columns)
+    const int trow = q * 32 + lane;
+    const int env_l = wi >> 1, hh = wi & 1;           // this warp's (env, head) pair inside a group
+    uint32_t gi = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+      const int64_t env = (int64_t)t * EPT + env_l;
+      // pull the next tile's rows into L2: its TMA load is issued the moment this tile's last group
+      // releases the h tile, and should find them there
+      {
+        const int64_t tn = (int64_t)t + gridDim.x;
+        const int lines_per_row = (d * 2) >> 7;             // 128-byte lines per fp16 row
+        for (int i = wi * 32 + lane; tn < p.n_tiles && i < ROWS * lines_per_row; i += WORKERS * 32) {
+          const int64_t row = tn * ROWS + i / lines_per_row;
+          if (row < p.n_envs * kT) prefetch_l2(p.h + row * p.ldh + (i % lines_per_row) * 64);
+        }
+      }
       for (int g = 0; g < n_groups && ok; ++g, ++gi) {
         const int buf = gi & 1;
         // A failed wait must not leave other workers stuck at the CTA-level barriers below: the

@@ -48,7 +48,8 @@ constexpr int THREADS = (3 + EPI_WARPS) * 32;
 constexpr int STG_BYTES = 32 * 64;               // per-warp transposition buffer (32 rows x 64 B)
 constexpr int PARAM_FLOATS = 8 * 256 + 1024;     // bo, ln_g, ln_b, b2, g16[2], b16[2] (d each) + b0 (F)
 constexpr int PART_BYTES = 2 * 2 * BM * 8;       // LayerNorm partial sums exchanged between the two groups
-constexpr int SMEM_BYTES = SA_BYTES + SH_BYTES + STAGES * STAGE_BYTES + EPI_WARPS * STG_BYTES + PART_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = SA_BYTES + SH_BYTES + STAGES * STAGE_BYTES + EPI_WARPS * STG_BYTES + PARAM_FLOATS * 4 +
+                           PART_BYTES + 1024 + 256;
 constexpr int KERNEL_ID = 2;
 
 struct Shared {
@@ -80,13 +81,6 @@ struct TailParams {
   int n_tiles;
   int* status;
 };
-
-// Per-column parameters of the launch in constant memory (uniform reads go through the constant
-// cache and leave the shared-memory pipe to the tensor core):
-// [bo | ln_g | ln_b | b2 | g16_0 | b16_0 | g16_1 | b16_1] (256 floats each) then b0 (1024 floats).
-// Filled by stream-ordered device-to-device copies ahead of each launch; launches that overlap
-// on the GPU (different streams) would race on it.
-__constant__ float4 c_prm4[PARAM_FLOATS / 4];
 
 #ifdef BSRL_TRACE
 __device__ long long g_trace[2 * 8192];
@@ -152,8 +146,9 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
   uint8_t* sA_g = gen;
   uint8_t* sH_g = gen + SA_BYTES;
   uint8_t* stg_all = gen + SA_BYTES + SH_BYTES + STAGES * STAGE_BYTES;
-  float2* part = reinterpret_cast<float2*>(stg_all + EPI_WARPS * STG_BYTES);
-  Shared* sh = reinterpret_cast<Shared*>(stg_all + EPI_WARPS * STG_BYTES + PART_BYTES);
+  float* prm = reinterpret_cast<float*>(stg_all + EPI_WARPS * STG_BYTES);
+  float2* part = reinterpret_cast<float2*>(stg_all + EPI_WARPS * STG_BYTES + PARAM_FLOATS * 4);
+  Shared* sh = reinterpret_cast<Shared*>(stg_all + EPI_WARPS * STG_BYTES + PARAM_FLOATS * 4 + PART_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int d = p.d, KB = d >> 6, NC = p.F / HC, S1 = (KB + 1) >> 1;
   volatile int* abort = &sh->abort;
@@ -186,6 +181,19 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     tmem_alloc(smem_u32(&sh->tmem_base), 512);
     tmem_relinquish();
   }
+  // per-column parameters into shared memory: [bo | ln_g | ln_b | b2 | g16_0 | b16_0 | g16_1 | b16_1] (256
+  // floats each) then b0 (F floats); absent vectors read as gamma = 1, beta = 0
+  for (int i = threadIdx.x; i < 8 * 256; i += THREADS) {
+    const int which = i >> 8, c = i & 255;
+    float v = (which == 4 || which == 6) ? 1.f : 0.f;
+    if (c < d) {
+      const float* src = which == 0 ? p.bo : which == 1 ? p.ln_g : which == 2 ? p.ln_b : which == 3 ? p.b2
+                       : which == 4 ? p.g16[0] : which == 5 ? p.b16[0] : which == 6 ? p.g16[1] : p.b16[1];
+      if (src) v = src[c];
+    }
+    prm[i] = v;
+  }
+  for (int i = threadIdx.x; i < p.F; i += THREADS) prm[8 * 256 + i] = p.b0[i];
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -352,7 +360,8 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     uint8_t* stg = stg_all + (warp - 2) * STG_BYTES;
     const int sub8 = lane >> 2, piece = lane & 3;
     const int dh2 = d >> 1, c_lo = grp * dh2;               // this group's columns of the d-wide row
-    const float4 *P_bo = c_prm4, *P_g = c_prm4 + 64, *P_b = c_prm4 + 128, *P_b2 = c_prm4 + 192, *P_b0 = c_prm4 + 512;
+    const float4* prm4 = reinterpret_cast<const float4*>(prm);
+    const float4 *P_bo = prm4, *P_g = prm4 + 64, *P_b = prm4 + 128, *P_b2 = prm4 + 192, *P_b0 = prm4 + 512;
     uint32_t tile_i = 0, n_acc[2] = {0, 0}, n_free = 0;
     bool ok = true;
     const float inv_d = 1.0f / (float)d;
@@ -563,7 +572,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
           if (!p.out16[o]) continue;
           const bool ln = p.g16[o] != nullptr;
           const float sc = ln ? rstd : 1.f, sh0 = ln ? -mean * rstd : 0.f;
-          const float4 *P_go = c_prm4 + 256 + 128 * o, *P_bo16 = c_prm4 + 320 + 128 * o;
+          const float4 *P_go = prm4 + 256 + 128 * o, *P_bo16 = prm4 + 320 + 128 * o;
           for (int c = c_lo; c < c_lo + dh2; c += 32) {     // 32 columns = 64 bytes of fp16 per row
             uint32_t r[32];
             tmem_ld32(lane_base + xcol + c, r);
@@ -574,9 +583,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
                 const int f4 = (c >> 2) + 2 * j + e;
-                const float4 b2 = P_b2[f4];
-                const float4 g = ln ? P_go[f4] : make_float4(1.f, 1.f, 1.f, 1.f);
-                const float4 bb = ln ? P_bo16[f4] : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 b2 = P_b2[f4], g = P_go[f4], bb = P_bo16[f4];
                 y[4 * e] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e]) + b2.x, sc, sh0), g.x, bb.x);
                 y[4 * e + 1] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 1]) + b2.y, sc, sh0), g.y, bb.y);
                 y[4 * e + 2] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 2]) + b2.z, sc, sh0), g.z, bb.z);
@@ -644,16 +651,6 @@ int block_tail(const BlockTailArgs& a, cudaStream_t stream) {
   if (dev < 64 && !attr_set[dev]) {
     BSRL_CUDA_OK(cudaFuncSetAttribute(block_tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     attr_set[dev] = true;
-  }
-  // per-column parameters -> constant memory (stream-ordered device-to-device copies)
-  if (a.packed_params) {
-    BSRL_CUDA_OK(cudaMemcpyToSymbolAsync(c_prm4, a.packed_params, PARAM_FLOATS * 4, 0, cudaMemcpyDeviceToDevice, stream));
-  } else {
-    const float* src[9] = {a.bo, a.ln_g, a.ln_b, a.b2, a.g16[0], a.b16[0], a.g16[1], a.b16[1], a.b0};
-    for (int i = 0; i < 9; ++i)
-      if (src[i])
-        BSRL_CUDA_OK(cudaMemcpyToSymbolAsync(c_prm4, src[i], (size_t)(i < 8 ? a.d : a.F) * 4, (size_t)i * 1024,
-                                             cudaMemcpyDeviceToDevice, stream));
   }
   TailParams p;
   p.d = a.d; p.F = a.F; p.M = a.M;

@@ -53,9 +53,6 @@ struct BlockTailArgs {
   int64_t ld16[2];
   const float* g16[2];
   const float* b16[2];
-  // optional: all nine vectors pre-assembled as [bo|ln_g|ln_b|b2|g16_0|b16_0|g16_1|b16_1] (256 floats
-  // each) + b0 (1024 floats); the individual pointers above then only say which outputs are LayerNorms
-  const float* packed_params;
 };
 bool block_tail_ok(const BlockTailArgs& a);
 int block_tail(const BlockTailArgs& a, cudaStream_t stream);

@@ -169,7 +169,6 @@ Layout make_layout(const bsrl_config& c) {
     b.up = carve_mat(cv, l.F, d);
     b.down = carve_mat(cv, d, l.F);
     b.qkv_g = carve_mat(cv, 3 * d, d);
-    b.tail_prm = cv.take((8 * 256 + 1024) * 4);
   }
   l.trunk_proj = carve_mat(cv, l.D, kLead * d);
   l.trunk_ln1 = carve_norm(cv, l.D);
@@ -248,28 +247,6 @@ std::vector<CopySlot> make_copy_slots(const bsrl_config& c, const Layout& l, con
       if (params[i].name == name) return (int)i;
     return -1;
   };
-  // fused block tail: the launch's per-column vectors side by side (only where the kernel applies)
-  if (l.d <= 256 && l.F <= 1024) {
-    for (int i = 0; i < l.L; ++i) {
-      const std::string p = "blocks." + std::to_string(i);
-      auto vec = [&](const std::string& name, int which, int n) {
-        out.push_back({find(name), 0, n, 1, l.blocks[i].tail_prm + (int64_t)which * 1024, 0, false});
-      };
-      vec(p + ".out_proj.bias", 0, l.d);
-      vec(p + ".ln_ffn.weight", 1, l.d);
-      vec(p + ".ln_ffn.bias", 2, l.d);
-      vec(p + ".ffn.2.bias", 3, l.d);
-      if (i + 1 < l.L) {
-        vec("blocks." + std::to_string(i + 1) + ".ln_attn.weight", 4, l.d);
-        vec("blocks." + std::to_string(i + 1) + ".ln_attn.bias", 5, l.d);
-      }
-      if (i + 2 == l.L) {
-        vec("critic_ln.weight", 6, l.d);
-        vec("critic_ln.bias", 7, l.d);
-      }
-      vec(p + ".ffn.0.bias", 8, l.F);
-    }
-  }
   if (l.attn_G == 0) return out;
   const int d = l.d, gd = l.attn_G * (d / l.H), n_groups = d / gd;
   auto regroup = [&](const Mat& m, const std::string names[3]) {

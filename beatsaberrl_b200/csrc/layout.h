@@ -25,7 +25,6 @@ struct Norm {         // fp32 gamma, beta
 struct BlockW {
   Norm ln_attn, ln_ffn;
   Mat qkv, out, up, down;
-  int64_t tail_prm = 0;   // fp32 [bo|ln_ffn g|ln_ffn b|b2|next ln_attn g|b|critic_ln g|b] x 256 + b0 x 1024 (fused tail)
   Mat qkv_g;   // q|k|v rows regrouped per head group for the fused attention kernel (see attn_G)
 };
 struct Encoder {

@@ -13,7 +13,7 @@ namespace tc5 {
 // bounded wait that ran out (kernel id * 16 + role).  Kernels get its address as an argument;
 // bsrl_device_status() reads and clears it.
 
-constexpr uint32_t kSpinLimit = 1u << 24;  // try_wait polls before a wait gives up
+constexpr uint32_t kSpinLimit = 1u << 21;  // try_wait polls before a wait gives up (a fraction of a second)
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -101,6 +101,18 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// D(tmem) (+)= A(tmem) * B(smem)^T: the A operand (128 rows x 16 fp16, two per 32-bit column, 8 columns)
+// comes from tensor memory, only B is fetched from shared memory
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
