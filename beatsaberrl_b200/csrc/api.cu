@@ -546,6 +546,29 @@ int bsrl_forward_act(const bsrl_config* cfg, const void* arena, const void* obs,
   return run_forward(c, obs, obs_dtype, t);
 }
 
+int bsrl_forward_sample(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
+                        int64_t n_envs, const uint64_t* rng_state, int64_t* action_out, float* logits,
+                        float* logprob, float* entropy, float* ent_head, float* value, void* workspace,
+                        int64_t workspace_bytes, void* stream) {
+  Ctx c;
+  BSRL_TRY(make_ctx(c, cfg, arena, n_envs, workspace, workspace_bytes, stream));
+  if (!obs || !rng_state || !action_out || !logprob || !value) {
+    set_error("forward_sample: NULL obs / rng_state / action_out / logprob / value");
+    return BSRL_ERR_NULL;
+  }
+  if (n_envs == 0) return BSRL_OK;
+  HeadTailArgs t;
+  memset(&t, 0, sizeof(t));
+  t.rng = reinterpret_cast<const unsigned long long*>(rng_state);
+  t.action_out = reinterpret_cast<long long*>(action_out);
+  t.logits = logits;
+  t.logprob = logprob;
+  t.entropy = entropy;
+  t.ent_head = ent_head;
+  t.value = value;
+  return run_forward(c, obs, obs_dtype, t);
+}
+
 int32_t bsrl_token_lane(int32_t tok, int32_t k) { return token_lane_host(tok, k); }
 
 // ---- forward on the library's own fixed scratch (no caller workspace, nothing allocated) ----

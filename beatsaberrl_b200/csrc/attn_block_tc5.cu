@@ -286,50 +286,6 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
     for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
       const int64_t env = (int64_t)t * EPT + env_l;
       for (int g = 0; g < n_groups && ok; ++g, ++gi) {
-          const int buf = gi & 1;
-          if (!mbar_wait(smem_u32(&sh->acc_empty[buf]), ((gi >> 1) & 1) ^ 1, abort)) { give_up(sh, p.status, 5); ok = false; break; }
-          tc_fence_after();
-          const uint32_t d_tmem = tmem_base + buf * 256;
-          for (int kb = 0; kb < KB; ++kb, ++it) {
-            if (g == 0 && !mbar_wait(smem_u32(&sh->a_full[kb]), tile_i & 1, abort)) { give_up(sh, p.status, 6); ok = false; break; }
-            const int s = it % STAGES;
-            if (!mbar_wait(smem_u32(&sh->w_full[s]), (it / STAGES) & 1, abort)) { give_up(sh, p.status, 7); ok = false; break; }
-            tc_fence_after();
-            const uint64_t ad = smem_desc_sw128(sA + kb * CHUNK_BYTES), wd = smem_desc_sw128(ring + s * STAGE_BYTES);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) mma_f16_ss(d_tmem, ad + 2 * k, wd + 2 * k, idesc, (kb | k) != 0);
-            tc_commit(smem_u32(&sh->w_empty[s]));
-            if (g == n_groups - 1) tc_commit(smem_u32(&sh->a_free[kb]));
-          }
-          if (ok) tc_commit(smem_u32(&sh->acc_full[buf]));
-        }
-      }
-      tc_commit(smem_u32(&sh->mma_done));
-      uint32_t spins = 0;
-      while (!mbar_try_wait(smem_u32(&sh->mma_done), 0) && ++spins < kSpinLimit) {}
-      if (spins >= kSpinLimit) give_up(sh, p.status, 8);
-    }
-  } else {
-    // ------------------------------------------------------------ workers: drain, then attend
-    const int wi = warp - 2;
-    const int q = warp & 3, half = wi >> 2;           // TMEM lane quadrant, column half (96 columns)
-    const int trow = q * 32 + lane;
-    const int env_l = wi >> 1, hh = wi & 1;           // this warp's (env, head) pair inside a group
-    uint32_t gi = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
-      const int64_t env = (int64_t)t * EPT + env_l;
-      // pull the next tile's rows into L2: its TMA load is issued the moment this tile's last group
-      // releases the h tile, and should find them there
-      {
-        const int64_t tn = (int64_t)t + gridDim.x;
-        const int lines_per_row = (d * 2) >> 7;             // 128-byte lines per fp16 row
-        for (int i = wi * 32 + lane; tn < p.n_tiles && i < ROWS * lines_per_row; i += WORKERS * 32) {
-          const int64_t row = tn * ROWS + i / lines_per_row;
-          if (row < p.n_envs * kT) prefetch_l2(p.h + row * p.ldh + (i % lines_per_row) * 64);
-        }
-      }
-      for (int g = 0; g < n_groups && ok; ++g, ++gi) {
         const int buf = gi & 1;
         // A failed wait must not leave other workers stuck at the CTA-level barriers below: the
         // warp keeps going (on garbage) and everyone leaves together once one thread has sampled

@@ -22,6 +22,22 @@ __device__ __forceinline__ int load_action(const void* a, int dtype, int64_t idx
   }
 }
 
+// Philox4x32-10 counter-based generator: 4 random words for (counter, key)
+__device__ __forceinline__ uint4 philox4x32(uint4 c, uint2 k) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+    c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+    k.x += 0x9E3779B9u;
+    k.y += 0xBB67AE85u;
+  }
+  return c;
+}
+__device__ __forceinline__ float uniform01(uint32_t x) {   // in (0, 1)
+  return __uint2float_rn(x >> 8) * 5.9604645e-8f + 2.9802322e-8f;
+}
+
 __global__ void __launch_bounds__(256) head_tail_kernel(HeadTailArgs p) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
@@ -44,15 +60,35 @@ __global__ void __launch_bounds__(256) head_tail_kernel(HeadTailArgs p) {
         for (int i = 0; i < 7; ++i)
           if (i < p.k_max) dst[i] = v[i];
       }
-      if (p.logprob || p.entropy || p.ent_head) {
+      if (p.logprob || p.entropy || p.ent_head || p.rng) {
         float se = 0.f;
 #pragma unroll
         for (int i = 0; i < 7; ++i)
           if (i < k) se += expf(v[i] - mx);
         const float lse = mx + logf(se);
-        if (p.actions) {
-          int a = load_action(p.actions, p.act_dtype, env * kActHeads + lane);
-          a = min(max(a, 0), p.k_max - 1);
+        if (p.actions || p.rng) {
+          int a = 0;
+          if (p.actions) {
+            a = load_action(p.actions, p.act_dtype, env * kActHeads + lane);
+            a = min(max(a, 0), p.k_max - 1);
+          } else {
+            // Gumbel-max: argmax_i (logsm_i - log E_i), E ~ Exp(1); only the head's live lanes compete
+            const unsigned long long seed = p.rng[0], off = p.rng[1];
+            const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
+            const unsigned long long idx = (unsigned long long)env * kActHeads + lane;
+            uint32_t w[8];
+            uint4 r0 = philox4x32(make_uint4((uint32_t)idx, (uint32_t)(idx >> 32), (uint32_t)off, (uint32_t)(off >> 32) << 1), key);
+            uint4 r1 = philox4x32(make_uint4((uint32_t)idx, (uint32_t)(idx >> 32), (uint32_t)off, ((uint32_t)(off >> 32) << 1) | 1u), key);
+            w[0] = r0.x; w[1] = r0.y; w[2] = r0.z; w[3] = r0.w; w[4] = r1.x; w[5] = r1.y; w[6] = r1.z; w[7] = r1.w;
+            float best = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 7; ++i)
+              if (i < k) {
+                const float sc = (v[i] - lse) - logf(-logf(uniform01(w[i])));
+                if (sc > best) { best = sc; a = i; }
+              }
+            if (p.action_out) p.action_out[env * kActHeads + lane] = a;
+          }
           float pick = kMaskedLogit;
 #pragma unroll
           for (int i = 0; i < 7; ++i)

@@ -107,6 +107,8 @@ struct HeadTailArgs {
   int first[kActHeads];  // first packed column of each head
   const void* actions;   // (B, 29) or nullptr
   int act_dtype;
+  const unsigned long long* rng;   // device [seed, offset]: sample actions (Gumbel-max) when actions is null
+  long long* action_out;           // (B, 29) sampled actions
   float* logits;         // (B, 29, k_max) or nullptr
   float* logprob;        // (B) or nullptr
   float* entropy;        // (B) or nullptr

@@ -171,6 +171,7 @@ class NotePolicy(nn.Module):
         self._arena = None
         self._arena_version = None
         self._workspaces = {}
+        self._rng_state = None
 
     # ------------------------------------------------------------------ weights
     def _pack(self, force: bool = False) -> None:
@@ -257,24 +258,12 @@ class NotePolicy(nn.Module):
     @torch.no_grad()
     def get_action_and_value(self, obs, action=None, need_entropy=True):
         """With ``action`` given (the PPO recompute call) the log-softmax, the summed log-prob
-        and the entropy come out of the fused head kernel.  With ``action=None`` the action is
-        sampled by Gumbel-max on the log-softmax with torch's default generator, as the
-        reference does (python/policy.py:1475-1490)."""
+        and the entropy come out of the fused head kernel.  With ``action=None`` the actions are
+        drawn inside the head kernel by Gumbel-max on the log-softmax, as the reference does
+        (python/policy.py:1475-1490), from a Philox stream keyed by ``self.seed_sampler(seed)``
+        (default: seeded from torch's generator at first use)."""
         if action is None:
-            logits, value = self.forward_stacked(obs)
-            logsm = torch.log_softmax(logits, dim=-1)
-            g = torch.empty_like(logsm).exponential_()
-            score = logsm - g.log()
-            if min(self.head_sizes) < self.k_max:
-                score = score.masked_fill(logits < -1e8, -math.inf)
-            action = score.argmax(-1)
-            logprob = logsm.gather(-1, action.unsqueeze(-1)).squeeze(-1).sum(-1)
-            entropy = None
-            if need_entropy:
-                ent_h = -(logsm.exp() * logsm).sum(-1)
-                self._ent_h = ent_h
-                entropy = ent_h.sum(-1)
-            return action, logprob, entropy, value
+            return self._sample(obs, need_entropy)
         obs = self._check_obs(obs)
         self._pack()
         B, dev = obs.shape[0], obs.device
@@ -299,6 +288,38 @@ class NotePolicy(nn.Module):
         if need_entropy:
             self._ent_h = ent_h
         self._value_logits = vl
+        return action, logprob, entropy, value
+
+    def seed_sampler(self, seed: int) -> None:
+        """(Re)start the action-sampling stream: [seed, call counter] in a device tensor that the
+        head kernel reads, so a captured CUDA graph draws fresh numbers on every replay."""
+        dev = self.trunk_proj.weight.device
+        self._rng_state = torch.tensor([seed & 0x7FFFFFFFFFFFFFFF, 0], dtype=torch.int64, device=dev)
+
+    @torch.no_grad()
+    def _sample(self, obs, need_entropy):
+        obs = self._check_obs(obs)
+        self._pack()
+        B, dev = obs.shape[0], obs.device
+        if getattr(self, "_rng_state", None) is None or self._rng_state.device != dev:
+            self.seed_sampler(int(torch.randint(0, 2 ** 62, (1,)).item()))
+        f32 = dict(dtype=torch.float32, device=dev)
+        action = torch.empty(B, N_ACTION_HEADS, dtype=torch.int64, device=dev)
+        logprob, value = torch.empty(B, **f32), torch.empty(B, **f32)
+        entropy = torch.empty(B, **f32) if need_entropy else None
+        ent_h = torch.empty(B, N_ACTION_HEADS, **f32) if need_entropy else None
+        ws = self._workspace(B, dev)
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        with torch.cuda.device(dev):
+            nat.check(nat.lib.bsrl_forward_sample(
+                C.byref(self._cfg), self._arena.data_ptr(), obs.data_ptr(), self._obs_dtype(obs), B,
+                self._rng_state.data_ptr(), action.data_ptr(), None, logprob.data_ptr(), ptr(entropy),
+                ptr(ent_h), value.data_ptr(), ws.data_ptr(), ws.numel(),
+                torch.cuda.current_stream().cuda_stream))
+            self._rng_state[1] += 1          # next call (or graph replay) draws new numbers
+        if need_entropy:
+            self._ent_h = ent_h
+        self._value_logits = None
         return action, logprob, entropy, value
 
     # ------------------------------------------------------------------ introspection

@@ -133,6 +133,20 @@ int bsrl_forward_act(const bsrl_config* cfg, const void* arena, const void* obs,
                      float* value, float* value_logits,
                      void* workspace, int64_t workspace_bytes, void* stream);
 
+/* NotePolicy.get_action_and_value with action=None (python/policy.py:1475-1490), the rollout call:
+ * same forward, then actions are drawn in the head kernel by Gumbel-max on the log-softmax
+ * (argmax_i logsm_i - log E_i, E ~ Exp(1); lanes past a head's gear count never win), with the
+ * summed log-prob of the drawn actions and the entropy.  Random numbers are Philox4x32-10 keyed by
+ * rng_state[0] (seed) and counted by (env, head, rng_state[1]); rng_state is a DEVICE pointer to
+ * two uint64 that the caller advances between calls (e.g. rng_state[1] += 1 on the same stream),
+ * so a captured CUDA graph draws fresh numbers on every replay.  The stream of numbers differs from
+ * torch's generator, as the reference's own switch to Gumbel-max did.
+ * action_out (n_envs, 29) i64; logits, entropy, ent_head may be NULL. */
+int bsrl_forward_sample(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
+                        int64_t n_envs, const uint64_t* rng_state, int64_t* action_out, float* logits,
+                        float* logprob, float* entropy, float* ent_head, float* value, void* workspace,
+                        int64_t workspace_bytes, void* stream);
+
 /* --- single stages (unit tests and profiling) -------------------------------------- */
 
 /* Obs lane of feature k of lead token tok (0..4), or -1 past the token's width
