@@ -98,6 +98,8 @@ for _name, (_res, _args) in _sig.items():
 import os as _os
 if _os.environ.get("BSRL_ENGINE", "") == "mma":      # cross-check runs: warp-MMA kernels only
     lib.bsrl_set_engine(1)
+elif _os.environ.get("BSRL_ENGINE", "") == "pair":    # fused block tail on two-CTA clusters
+    lib.bsrl_set_engine(2)
 
 
 def last_error() -> str:

@@ -75,6 +75,7 @@ int timed(cudaStream_t st, double flops, double bytes, Fn&& fn) {
 
 // engine choice for one linear layer: tcgen05 where the shape fits, warp-MMA otherwise
 int g_engine = 0;   // 0 = automatic, 1 = warp-MMA kernel only (cross-check runs)
+int g_pair = 0;     // fused block tail on two-CTA clusters (cta_group::2): validated, measured slower, off by default
 int linear(const LinearArgs& p, cudaStream_t st) {
   return timed(st, 2.0 * p.M * p.N * p.K, linear_bytes(p), [&] {
     if (g_engine == 0 && p.M >= 128 && linear_tc5_ok(p)) return linear_tc5(p, st);
@@ -209,6 +210,7 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     a.w0 = c.W(b.up); a.b0 = c.Bv(b.up);
     a.w2 = c.W(b.down); a.b2 = c.Bv(b.down);
     a.eps = eps;
+    a.pair = g_pair;
     return a;
   };
   bool fused = false;
@@ -621,11 +623,12 @@ int bsrl_forward_fixed(const bsrl_config* cfg, const void* arena, const void* ob
 }
 
 int bsrl_set_engine(int32_t engine) {
-  if (engine != 0 && engine != 1) {
-    set_error("set_engine: 0 (automatic) or 1 (warp-MMA only)");
+  if (engine < 0 || engine > 2) {
+    set_error("set_engine: 0 (automatic), 1 (warp-MMA only) or 2 (automatic, block tail on CTA pairs)");
     return BSRL_ERR_UNSUPPORTED;
   }
-  g_engine = engine;
+  g_engine = engine == 1 ? 1 : 0;
+  g_pair = engine == 2 ? 1 : 0;
   return BSRL_OK;
 }
 
@@ -728,6 +731,7 @@ int bsrl_block_tail(const void* att_f16, const float* x, const void* wo_f16, con
   a.eps = eps;
   a.x_out = x_out;
   a.out16[0] = static_cast<__half*>(ln_out_f16); a.ld16[0] = d; a.g16[0] = out_g; a.b16[0] = out_b;
+  a.pair = g_pair;
   return block_tail(a, as_stream(stream));
 }
 

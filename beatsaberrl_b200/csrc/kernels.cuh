@@ -53,6 +53,7 @@ struct BlockTailArgs {
   int64_t ld16[2];
   const float* g16[2];
   const float* b16[2];
+  int pair;            // 1 = run on two-CTA clusters (cta_group::2) when there are at least two tiles
 };
 bool block_tail_ok(const BlockTailArgs& a);
 int block_tail(const BlockTailArgs& a, cudaStream_t stream);

@@ -203,7 +203,9 @@ int bsrl_block_tail(const void* att_f16, const float* x, const void* wo_f16, con
 
 /* Which GEMM kernel the forward's linear layers use: 0 (default) = the tcgen05/TMEM kernel
  * wherever the shape fits it (and the fused block-tail kernel), the warp-MMA kernel elsewhere;
- * 1 = the warp-MMA kernel and separate LayerNorm kernels everywhere.
+ * 1 = the warp-MMA kernel and separate LayerNorm kernels everywhere; 2 = as 0 but the fused block
+ * tail runs on two-CTA clusters (tcgen05 cta_group::2: each CTA fetches half of every weight tile;
+ * correct, but measured slower than one CTA per tile, so it is not the default).
  * Both are CUDA kernels of this library; 1 exists so tests can cross-check one against the
  * other.  No counterpart in the reference. */
 int bsrl_set_engine(int32_t engine);
