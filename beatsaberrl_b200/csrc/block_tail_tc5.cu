@@ -56,6 +56,7 @@ struct Shared {
   uint64_t w_full[MAX_STAGES], w_empty[MAX_STAGES];
   uint64_t a_full, a_free, x_ready, o_done, h2_ready, x_done, mma_done;
   uint64_t acc1_full[2], hid_ready[2], hid_free[2];   // hid_*: per 64-column half of the hidden chunk
+  uint64_t io_full[EPI_WARPS][3];                     // per epilogue warp: residual blocks landed in its buffers
   uint32_t tmem_base;
   int abort;
 };
@@ -79,19 +80,28 @@ struct TailParams {
   const float* g16[2];
   const float* b16[2];
   int n_tiles;
+  int x_tma;                // residual rows are read with TMA (identity row map)
   int* status;
 };
 
 #ifdef BSRL_TRACE
-__device__ long long g_trace[2 * 8192];
-__device__ int g_trace_n = 0;
-__device__ __forceinline__ void trace(int tag, long long val = -1) {
-  if (blockIdx.x != 0) return;
-  int i = atomicAdd(&g_trace_n, 1);
-  if (i < 8192) { g_trace[2 * i] = tag; g_trace[2 * i + 1] = val >= 0 ? val : clock64(); }
+// Timeline instrumentation (debug builds only): each traced thread appends (tag, clock) records to a
+// slot of its own with plain stores -- no atomics, so a record costs a few cycles, not a round trip.
+constexpr int TRACE_SLOTS = 10, TRACE_CAP = 2048;
+__device__ long long g_trace[TRACE_SLOTS * TRACE_CAP * 2];
+__device__ int g_trace_cnt[TRACE_SLOTS];
+__device__ __forceinline__ void trace(int slot, uint32_t& n, int tag, long long val = -1) {
+  if (blockIdx.x != 0 || slot < 0 || n >= (uint32_t)TRACE_CAP) return;
+  long long* e = g_trace + ((size_t)slot * TRACE_CAP + n) * 2;
+  e[0] = tag;
+  e[1] = val >= 0 ? val : clock64();
+  ++n;
+  g_trace_cnt[slot] = (int)n;
 }
-#define TRACE(...) trace(__VA_ARGS__)
+#define TRACE_INIT(slot) const int tr_slot = (slot); uint32_t tr_n = 0;
+#define TRACE(...) trace(tr_slot, tr_n, __VA_ARGS__)
 #else
+#define TRACE_INIT(slot)
 #define TRACE(...)
 #endif
 
@@ -144,6 +154,8 @@ template <int CTAS>
 __global__ void __launch_bounds__(THREADS, 1)
 block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_constant__ CUtensorMap tm_wo,
                   const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w2,
+                  const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_xo,
+                  const __grid_constant__ CUtensorMap tm_o0, const __grid_constant__ CUtensorMap tm_o1,
                   TailParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -188,12 +200,18 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       mbar_init(smem_u32(&sh->hid_ready[b]), 4 * CTAS);
       mbar_init(smem_u32(&sh->hid_free[b]), 1);
     }
+    for (int w = 0; w < EPI_WARPS; ++w)
+      for (int b = 0; b < 3; ++b) mbar_init(smem_u32(&sh->io_full[w][b]), 1);
     sh->abort = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_att);
     tma_prefetch_desc(&tm_wo);
     tma_prefetch_desc(&tm_w0);
     tma_prefetch_desc(&tm_w2);
+    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_xo);
+    tma_prefetch_desc(&tm_o0);
+    tma_prefetch_desc(&tm_o1);
   }
   if (warp == 1) {
     if (PAIR) {
@@ -221,6 +239,13 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
   __syncthreads();
   if (PAIR) cluster_sync_all();     // the peer's barriers exist before anything is signalled across
   tc_fence_after();
+#ifdef BSRL_SKEW
+  {   // experiment: start groups of CTAs out of phase
+    const long long wait = (long long)BSRL_SKEW * (blockIdx.x % BSRL_SKEW_GROUPS);
+    const long long t0 = clock64();
+    while (clock64() - t0 < wait) {}
+  }
+#endif
   const uint32_t tmem_base = sh->tmem_base;
   // completion of this CTA's TMA loads is counted on the leader's barriers
   auto lead_bar = [&](uint64_t* bar) -> uint32_t { return PAIR ? map_to_cta(smem_u32(bar), 0) : smem_u32(bar); };
@@ -310,6 +335,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     if (lane == 0 && leader) {
       uint32_t it = 0, tile_i = 0, n_hid = 0;
       bool ok = true;
+      TRACE_INIT(0);
       const uint32_t idesc_d = idesc_f16(BM * CTAS, d), idesc_h = idesc_f16(BM * CTAS, HC);
       // completion of the MMAs issued so far -> the barrier (of both CTAs, in a pair)
       auto commit = [&](uint64_t* bar) {
@@ -367,6 +393,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
           for (int kc = 0; kc < 2 && ok; ++kc) {    // xo += hidden chunk j * W2[:, chunk j]^T, one 64-column half at a time
             if (!mbar_wait(smem_u32(&sh->hid_ready[kc]), n_hid & 1, abort)) { give_up(sh, p.status, 9); ok = false; break; }
             tc_fence_after();
+            TRACE(140 + 2 * j + kc);
             ok = with_stage([&](uint32_t st) { mma_kblock<PAIR>(xcol, sH + kc * CHUNK_BYTES, st, idesc_d, true); });
             if (ok) commit(&sh->hid_free[kc]);   // this half of sH may be overwritten once retired
           }
@@ -374,6 +401,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
           TRACE(130 + j);
           if (ok && j + 2 < NC) {
             ok = g1(j + 2);
+            TRACE(170 + j);
             if (ok && j + 3 == NC) commit(&sh->a_free);   // last reader of h2 issued
           }
         }
@@ -393,6 +421,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     // 4 lanes cover 64 contiguous bytes of one row (lane = (row sub8 + 8 i, 16-byte piece)).
     const int grp = (warp - 2) >> 2;
     const int q = warp & 3;
+    TRACE_INIT(lane == 0 ? warp - 1 : -1);
     const int trow = q * 32 + lane;                         // row inside the tile
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     uint8_t* stg = stg_all + (warp - 2) * STG_BYTES;
@@ -404,12 +433,19 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     bool ok = true;
     const float inv_d = 1.0f / (float)d;
 
-    auto stg_write = [&](int row, int pc, uint4 v) {        // 16-byte piece pc (0..3) of row -> staging
-      *reinterpret_cast<uint4*>(stg + row * 64 + ((pc ^ ((row >> 1) & 3)) << 4)) = v;
+    // Three 2 KB transposition buffers per warp (32 rows x 64 B, 64-byte swizzle -- the layout of the
+    // 64-byte-wide TMA boxes): its slice of the staging area and, while no hidden chunk is live (from
+    // the tile's last FFN-down MMA to the next tile's first hidden chunk), 4 KB of sH.
+    auto io_buf = [&](int b) -> uint8_t* { return b == 0 ? stg : sH_g + (warp - 2) * 4096 + (b - 1) * 2048; };
+    auto buf_write = [&](uint8_t* buf, int row, int pc, uint4 v) {   // 16-byte piece pc (0..3) of row
+      *reinterpret_cast<uint4*>(buf + row * 64 + ((pc ^ ((row >> 1) & 3)) << 4)) = v;
     };
-    auto stg_read = [&](int row, int pc) -> uint4 {
-      return *reinterpret_cast<const uint4*>(stg + row * 64 + ((pc ^ ((row >> 1) & 3)) << 4));
+    auto buf_read = [&](const uint8_t* buf, int row, int pc) -> uint4 {
+      return *reinterpret_cast<const uint4*>(buf + row * 64 + ((pc ^ ((row >> 1) & 3)) << 4));
     };
+    auto stg_write = [&](int row, int pc, uint4 v) { buf_write(stg, row, pc, v); };
+    auto stg_read = [&](int row, int pc) -> uint4 { return buf_read(stg, row, pc); };
+    uint32_t n_io = 0;                                      // residual blocks this warp has consumed so far
     auto group_sync = [&]() { asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory"); };
     auto signal = [&](uint64_t* bar) {   // one arrival per warp (on the leader's barrier), after everyone's writes
       tc_fence_before();
@@ -432,7 +468,8 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       rstd = rsqrtf(fmaxf((sq + o.y) * inv_d - mean * mean, 0.f) + p.eps);
     };
     // pre-store (x + bo) of tile t, this group's columns, into TMEM columns col0 + ...
-    auto prestore = [&](int t, uint32_t col0) {
+    // (a) rows gathered through the row map: coalesced loads, transposed through the staging buffer
+    auto prestore_ldg = [&](int t, uint32_t col0) {
       const float* src[4];                                  // this lane's 4 rows in the transposed phase
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -471,9 +508,57 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       }
       tmem_wait_st();
     };
+    // (b) dense rows: 16-column blocks of this warp's 32 rows arrive by TMA in the three buffers, up to
+    // three in flight; block n (counted over the whole kernel) uses buffer n % 3, phase (n / 3) & 1
+    auto prestore_tma = [&](int t, uint32_t col0) -> bool {
+      const int row0 = t * BM + q * 32;
+      const int nb = dh2 >> 4;
+      auto issue = [&](int k) {                             // k-th block of this call
+        if (lane == 0) {
+          const uint32_t n = n_io + k;
+          const uint32_t bar = smem_u32(&sh->io_full[warp - 2][n % 3]);
+          mbar_expect_tx(bar, STG_BYTES);
+          tma_load_2d(smem_u32(io_buf(n % 3)), &tm_x, c_lo + 16 * k, row0, bar);
+        }
+      };
+      for (int k = 0; k < 3 && k < nb; ++k) issue(k);
+      int k = 0;
+      for (int c = c_lo; c < c_lo + dh2; c += 32) {
+        uint32_t r[32];
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb, ++k) {
+          const uint32_t n = n_io + k;
+          if (!mbar_wait_warp(smem_u32(&sh->io_full[warp - 2][n % 3]), (n / 3) & 1, abort)) {
+            if (lane == 0) give_up(sh, p.status, 15);
+            return false;
+          }
+          const uint8_t* buf = io_buf(n % 3);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 v = buf_read(buf, lane, j);
+            const float4 bo = P_bo[((c + 16 * hb) >> 2) + j];
+            r[16 * hb + 4 * j] = __float_as_uint(__uint_as_float(v.x) + bo.x);
+            r[16 * hb + 4 * j + 1] = __float_as_uint(__uint_as_float(v.y) + bo.y);
+            r[16 * hb + 4 * j + 2] = __float_as_uint(__uint_as_float(v.z) + bo.z);
+            r[16 * hb + 4 * j + 3] = __float_as_uint(__uint_as_float(v.w) + bo.w);
+          }
+          __syncwarp();                                     // everyone has read the buffer: refill it
+          if (k + 3 < nb) issue(k + 3);
+        }
+        tmem_st32(lane_base + col0 + c, r);
+      }
+      n_io += nb;
+      tmem_wait_st();
+      return true;
+    };
+    auto prestore = [&](int t, uint32_t col0) -> bool {
+      if (p.x_tma) return prestore_tma(t, col0);
+      prestore_ldg(t, col0);
+      return true;
+    };
 
     if (tile0 < t_end) {
-      prestore(tile0, 0u);
+      ok = prestore(tile0, 0u);
       signal(&sh->x_ready);
     }
     for (int t = tile0; t < t_end && ok; t += tstep, ++tile_i) {
@@ -483,7 +568,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       // ---- E1: h2 = LN_ffn(x1) -> sA   (X already holds x + bo + att Wo^T)
       TAIL_WAIT_WARP(&sh->o_done, par, 11);
       tc_fence_after();
-      if (warp == 2 && lane == 0) TRACE(200);
+      TRACE(200);
       {
         float sum = 0.f, sq = 0.f;
         for (int c = c_lo; c < c_lo + dh2; c += 32) {
@@ -518,7 +603,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       }
       publish_smem();
       signal(&sh->h2_ready);
-      if (warp == 2 && lane == 0) TRACE(201);
+      TRACE(201);
       // ---- hidden chunks: relu(acc + b0) -> sH; this group handles 64 of the chunk's 128 columns
       for (int j = 0; j < NC && ok; ++j) {
         const int b = j & 1;
@@ -529,7 +614,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         }
         ++n_acc[b];
         tc_fence_after();
-        if (warp == 2 && lane == 0) TRACE(210 + j);
+        TRACE(210 + j);
         uint32_t hp[32];                                    // 64 fp16 values of this row
 #pragma unroll
         for (int c = 0; c < 64; c += 32) {
@@ -552,7 +637,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
           break;
         }
         ++n_free;
-        if (warp == 2 && lane == 0) TRACE(220 + j);
+        TRACE(220 + j);
         {
           uint8_t* rowp = sH_g + grp * CHUNK_BYTES + (trow >> 3) * 1024 + (trow & 7) * 128;
 #pragma unroll
@@ -562,23 +647,45 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         }
         publish_smem();
         signal(&sh->hid_ready[grp]);
-        if (warp == 2 && lane == 0) TRACE(230 + j);
+        TRACE(230 + j);
       }
       if (!ok) break;
-      // both hidden-chunk buffers are consumed by both groups: pre-store the next tile's x there
-      if (t_next < t_end) {
-        group_sync();
-        prestore(t_next, acol);
-        signal(&sh->x_ready);
-      }
-      // ---- final: xo = X + b2 -> fp32 out (coalesced), then LayerNorm / fp16 outputs
+      // ---- all MMAs of the tile have retired: X holds x1 + FFN, sH and both hidden buffers are free
       TAIL_WAIT_WARP(&sh->x_done, par, 13);
       tc_fence_after();
-      if (warp == 2 && lane == 0) TRACE(250);
+      TRACE(250);
+      // pre-store the next tile's x over the hidden buffers; its out-projection then runs under the drain
+      if (t_next < t_end) {
+        TRACE(261);
+        ok = prestore(t_next, acol);
+        TRACE(262);
+        signal(&sh->x_ready);
+        if (!ok) break;
+      }
+      // ---- final: xo = X + b2 -> fp32 out, then LayerNorm / fp16 outputs, as TMA stores of 32-row blocks
       {
-        const int64_t row0 = (int64_t)t * BM + q * 32;      // first row of this warp
+        const int row0 = t * BM + q * 32;                   // first row of this warp
         const bool want_stats = p.g16[0] || p.g16[1];
         float sum = 0.f, sq = 0.f;
+        uint32_t n_st = 0;                                  // blocks stored by this warp in this drain
+        // buffer of the next block, once the store that used it three blocks ago has read it
+        auto next_buf = [&]() -> uint8_t* {
+          if (n_st >= 3) {
+            if (lane == 0) bulk_wait_read<2>();
+            __syncwarp();
+          }
+          return io_buf(n_st % 3);
+        };
+        // the warp's writes to the buffer -> one TMA store of 32 rows x 64 bytes (rows >= M are clipped)
+        auto store_block = [&](const CUtensorMap* map, int x) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(map, x, row0, smem_u32(io_buf(n_st % 3)));
+            bulk_commit();
+          }
+          ++n_st;
+        };
         if (p.x_out || want_stats) {
           for (int c = c_lo; c < c_lo + dh2; c += 32) {
             uint32_t r[32];
@@ -586,6 +693,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
             tmem_wait_ld();
 #pragma unroll
             for (int hb = 0; hb < 2; ++hb) {
+              uint8_t* buf = p.x_out ? next_buf() : nullptr;
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const float4 b2 = P_b2[((c + 16 * hb) >> 2) + j];
@@ -594,34 +702,29 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
                 sum += (v.x + v.y) + (v.z + v.w);
                 sq = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, sq))));
                 if (p.x_out)
-                  stg_write(lane, j, make_uint4(__float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z),
-                                                __float_as_uint(v.w)));
+                  buf_write(buf, lane, j, make_uint4(__float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z),
+                                                     __float_as_uint(v.w)));
               }
-              if (p.x_out) {
-                __syncwarp();
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const int rr = i * 8 + sub8;
-                  if (row0 + rr < p.M)
-                    *reinterpret_cast<uint4*>(p.x_out + (row0 + rr) * d + c + 16 * hb + piece * 4) = stg_read(rr, piece);
-                }
-                __syncwarp();
-              }
+              if (p.x_out) store_block(&tm_xo, c + 16 * hb);
             }
           }
         }
         float mean = 0.f, rstd = 1.f;
+        TRACE(252);
         if (want_stats) row_stats(1, sum, sq, mean, rstd);
+        TRACE(253);
 #pragma unroll 1
         for (int o = 0; o < 2; ++o) {
           if (!p.out16[o]) continue;
           const bool ln = p.g16[o] != nullptr;
           const float sc = ln ? rstd : 1.f, sh0 = ln ? -mean * rstd : 0.f;
           const float4 *P_go = prm4 + 256 + 128 * o, *P_bo16 = prm4 + 320 + 128 * o;
+          const CUtensorMap* tm_o = o ? &tm_o1 : &tm_o0;
           for (int c = c_lo; c < c_lo + dh2; c += 32) {     // 32 columns = 64 bytes of fp16 per row
             uint32_t r[32];
             tmem_ld32(lane_base + xcol + c, r);
             tmem_wait_ld();
+            uint8_t* buf = next_buf();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {                   // 8 columns -> one 16-byte fp16 piece
               float y[8];
@@ -634,23 +737,20 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
                 y[4 * e + 2] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 2]) + b2.z, sc, sh0), g.z, bb.z);
                 y[4 * e + 3] = fmaf(fmaf(__uint_as_float(r[8 * j + 4 * e + 3]) + b2.w, sc, sh0), g.w, bb.w);
               }
-              stg_write(lane, j, make_uint4(pack_half2(y[0], y[1]), pack_half2(y[2], y[3]),
-                                            pack_half2(y[4], y[5]), pack_half2(y[6], y[7])));
+              buf_write(buf, lane, j, make_uint4(pack_half2(y[0], y[1]), pack_half2(y[2], y[3]),
+                                                 pack_half2(y[4], y[5]), pack_half2(y[6], y[7])));
             }
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int rr = i * 8 + sub8;
-              if (row0 + rr < p.M)
-                *reinterpret_cast<uint4*>(p.out16[o] + (row0 + rr) * p.ld16[o] + c + piece * 8) = stg_read(rr, piece);
-            }
-            __syncwarp();
+            store_block(tm_o, c);
           }
         }
+        // the buffers (two of them inside sH) are reused by the next tile: all stores have read them
+        if (lane == 0) bulk_wait_read<0>();
+        __syncwarp();
       }
       tc_fence_before();
-      if (warp == 2 && lane == 0) TRACE(251);
+      TRACE(251);
     }
+    if (lane == 0) bulk_wait_all();                         // the stores are complete before the CTA exits
   }
 
   // ------------------------------------------------------------------ teardown
@@ -671,7 +771,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
 bool block_tail_ok(const BlockTailArgs& a) {
   if (a.d % 64 != 0 || a.d < 64 || a.d > 256) return false;
   if (a.F % 256 != 0 || a.F < 256 || a.F > 1024) return false;
-  if (a.M < 1 || a.M > (int64_t)0x7fffffff * 64) return false;
+  if (a.M < 1 || a.M > 0x7fffff00) return false;          // TMA row coordinates are 32-bit
   if (!aligned16(a.att) || !aligned16(a.x) || (a.ldx % 4) || (a.ld_att % 8)) return false;
   if (a.x_out && !aligned16(a.x_out)) return false;
   for (int o = 0; o < 2; ++o)
@@ -698,6 +798,14 @@ int block_tail(const BlockTailArgs& a, cudaStream_t stream) {
   if (!make_tmap_f16(&tm_wo, a.wo, a.d, a.d, a.d, pair ? a.d / 2 : a.d)) return BSRL_ERR_CUDA;
   if (!make_tmap_f16(&tm_w0, a.w0, a.F, a.d, a.d, pair ? HC / 2 : HC)) return BSRL_ERR_CUDA;
   if (!make_tmap_f16(&tm_w2, a.w2, a.d, a.F, a.F, pair ? a.d / 2 : a.d)) return BSRL_ERR_CUDA;
+  // residual rows in and the outputs move as 32-row x 64-byte TMA boxes; a map that is not needed
+  // aliases the attention tile's (the kernel only prefetches its descriptor)
+  const bool x_tma = a.xmap.group == 0x7fffffff && a.xmap.stride == 0 && a.xmap.first == 0;
+  CUtensorMap tm_x = tm_att, tm_xo = tm_att, tm_o[2] = {tm_att, tm_att};
+  if (x_tma && !make_tmap_rows64(&tm_x, a.x, 4, a.M, a.d, a.ldx, 32)) return BSRL_ERR_CUDA;
+  if (a.x_out && !make_tmap_rows64(&tm_xo, a.x_out, 4, a.M, a.d, a.d, 32)) return BSRL_ERR_CUDA;
+  for (int o = 0; o < 2; ++o)
+    if (a.out16[o] && !make_tmap_rows64(&tm_o[o], a.out16[o], 2, a.M, a.d, a.ld16[o], 32)) return BSRL_ERR_CUDA;
   static bool attr_set[64] = {};
   static int max_pairs[64] = {};
   int dev = 0;
@@ -732,6 +840,7 @@ int block_tail(const BlockTailArgs& a, cudaStream_t stream) {
     p.out16[o] = a.out16[o]; p.ld16[o] = a.ld16[o]; p.g16[o] = a.g16[o]; p.b16[o] = a.b16[o];
   }
   p.n_tiles = n_tiles;
+  p.x_tma = x_tma ? 1 : 0;
   p.status = status;
   if (pair && dev < 64 && max_pairs[dev] > 0) {
     const int n_pairs = (n_tiles + 1) / 2;
@@ -746,7 +855,7 @@ int block_tail(const BlockTailArgs& a, cudaStream_t stream) {
     attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    BSRL_CUDA_OK(cudaLaunchKernelEx(&cfg, block_tail_kernel<2>, tm_att, tm_wo, tm_w0, tm_w2, p));
+    BSRL_CUDA_OK(cudaLaunchKernelEx(&cfg, block_tail_kernel<2>, tm_att, tm_wo, tm_w0, tm_w2, tm_x, tm_xo, tm_o[0], tm_o[1], p));
     return BSRL_OK;
   }
   if (pair) {   // no room for clusters on this device: one CTA per tile, full-size weight boxes
@@ -755,20 +864,26 @@ int block_tail(const BlockTailArgs& a, cudaStream_t stream) {
     if (!make_tmap_f16(&tm_w2, a.w2, a.d, a.F, a.F, a.d)) return BSRL_ERR_CUDA;
   }
   int grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
-  block_tail_kernel<1><<<grid, THREADS, SMEM_BYTES, stream>>>(tm_att, tm_wo, tm_w0, tm_w2, p);
+  block_tail_kernel<1><<<grid, THREADS, SMEM_BYTES, stream>>>(tm_att, tm_wo, tm_w0, tm_w2, tm_x, tm_xo, tm_o[0], tm_o[1], p);
   BSRL_LAUNCH_OK("block_tail_kernel");
   return BSRL_OK;
 }
 
 #ifdef BSRL_TRACE
+// (tag + 10000 * slot, clock) pairs of all slots; resets the counters
 extern "C" int bsrl_trace_read(long long* out, int cap) {
+  static long long host[TRACE_SLOTS * TRACE_CAP * 2];
+  int cnt[TRACE_SLOTS];
+  cudaMemcpyFromSymbol(cnt, g_trace_cnt, sizeof(cnt));
+  cudaMemcpyFromSymbol(host, g_trace, sizeof(host));
   int n = 0;
-  cudaMemcpyFromSymbol(&n, g_trace_n, sizeof(int));
-  if (n > 8192) n = 8192;
-  if (n > cap) n = cap;
-  cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 2 * n);
-  int zero = 0;
-  cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(int));
+  for (int s = 0; s < TRACE_SLOTS; ++s)
+    for (int i = 0; i < cnt[s] && i < TRACE_CAP && n < cap; ++i, ++n) {
+      out[2 * n] = host[((size_t)s * TRACE_CAP + i) * 2] + 10000LL * s;
+      out[2 * n + 1] = host[((size_t)s * TRACE_CAP + i) * 2 + 1];
+    }
+  int zero[TRACE_SLOTS] = {};
+  cudaMemcpyToSymbol(g_trace_cnt, zero, sizeof(zero));
   return n;
 }
 #endif

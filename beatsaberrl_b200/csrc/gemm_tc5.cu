@@ -306,6 +306,28 @@ bool make_tmap_f16(CUtensorMap* map, const void* base, int64_t rows, int64_t col
   return true;
 }
 
+bool make_tmap_rows64(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows, int64_t cols,
+                      int64_t ld_elems, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return false;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld_elems * (cuuint64_t)elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(64 / elem_bytes), (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed (%d) for a (%lld x %lld) matrix of %d-byte elements, ld %lld", (int)r,
+              (long long)rows, (long long)cols, elem_bytes, (long long)ld_elems);
+    return false;
+  }
+  return true;
+}
+
 bool linear_tc5_ok(const LinearArgs& p) {
   if (!p.A || !p.W || !p.C || p.M < 1) return false;
   if (p.K % BK != 0 || p.N % 16 != 0 || p.N < 16) return false;

@@ -82,6 +82,22 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// 2-D tile store shared -> global (bulk async group of the issuing thread); rows / columns past the
+// tensor's extent are clipped
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until at most N of this thread's bulk groups still have to READ their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// waits until all of this thread's bulk groups are complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_l2(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
@@ -244,6 +260,12 @@ __device__ __forceinline__ uint32_t sw128_offset(int row, int col) {
 // 128-byte swizzle.  Returns false with the error message set.
 bool make_tmap_f16(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld_elems,
                    int box_rows);
+
+// Encodes a 2-D row-major (rows, cols) tensor map of 2- or 4-byte elements with a box of (box_rows x 64
+// BYTES) and the 64-byte swizzle: the layout of the per-warp transposition buffers (32 rows of 64 bytes,
+// 16-byte piece p of row r at r * 64 + ((p ^ ((r >> 1) & 3)) << 4)).
+bool make_tmap_rows64(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows, int64_t cols,
+                      int64_t ld_elems, int box_rows);
 
 // Address of the current device's status word (nullptr with the error message set on failure).
 int* device_status_ptr();
