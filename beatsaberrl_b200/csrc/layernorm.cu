@@ -10,7 +10,10 @@ namespace bsrl {
 namespace {
 constexpr int kMaxVec = 8;  // float4 per lane => rows up to 1024 wide
 
-__global__ void __launch_bounds__(256) layernorm_kernel(const float* __restrict__ x, int64_t ldx,
+// RPW rows per warp are in flight together: the kernel is latency-bound on its loads, and a second
+// (third, fourth) independent row per warp multiplies the bytes in flight.
+template <int RPW>
+__global__ void __launch_bounds__(256, RPW > 1 ? 4 : 1) layernorm_kernel(const float* __restrict__ x, int64_t ldx,
                                                        RowMap xmap, const float* __restrict__ gamma,
                                                        const float* __restrict__ beta, float eps,
                                                        int64_t rows, int d, __half* __restrict__ y,
@@ -18,41 +21,57 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const float* __restrict_
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const int nvec = d >> 2;
-  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
-       row += warps) {
-    const float4* xr = reinterpret_cast<const float4*>(x + xmap(row) * ldx);
-    float4 v[kMaxVec];
-    float s = 0.f;
+  constexpr int NV = RPW == 1 ? kMaxVec : 2;       // float4 per lane and row (RPW > 1: rows up to 256 wide)
+  for (int64_t row0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW; row0 < rows;
+       row0 += warps * RPW) {
+    float4 v[RPW][NV];
+    float s[RPW];
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      int c = lane + i * 32;
-      if (c < nvec) {
-        v[i] = xr[c];
-        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    for (int r = 0; r < RPW; ++r) {
+      s[r] = 0.f;
+      const int64_t row = row0 + r;
+      if (row < rows) {
+        const float4* xr = reinterpret_cast<const float4*>(x + xmap(row) * ldx);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c = lane + i * 32;
+          if (c < nvec) v[r][i] = xr[c];
+        }
       }
     }
-    const float mean = warp_sum(s) / d;
-    float q = 0.f;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      int c = lane + i * 32;
-      if (c < nvec) {
-        float a = v[i].x - mean, b = v[i].y - mean, e = v[i].z - mean, f = v[i].w - mean;
-        q += (a * a + b * b) + (e * e + f * f);
-      }
+    for (int r = 0; r < RPW; ++r)
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (lane + i * 32 < nvec && row0 + r < rows) s[r] += (v[r][i].x + v[r][i].y) + (v[r][i].z + v[r][i].w);
+    float mean[RPW], rstd[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) mean[r] = warp_sum(s[r]) / d;
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      float q = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (lane + i * 32 < nvec && row0 + r < rows) {
+          const float a = v[r][i].x - mean[r], b = v[r][i].y - mean[r], e = v[r][i].z - mean[r], f = v[r][i].w - mean[r];
+          q += (a * a + b * b) + (e * e + f * f);
+        }
+      rstd[r] = rsqrtf(warp_sum(q) / d + eps);
     }
-    const float rstd = rsqrtf(warp_sum(q) / d + eps);
-    uint2* yr = reinterpret_cast<uint2*>(y + row * ldy);
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      int c = lane + i * 32;
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + i * 32;
       if (c < nvec) {
-        float4 g = reinterpret_cast<const float4*>(gamma)[c];
-        float4 b = reinterpret_cast<const float4*>(beta)[c];
-        uint2 o;
-        o.x = pack_half2((v[i].x - mean) * rstd * g.x + b.x, (v[i].y - mean) * rstd * g.y + b.y);
-        o.y = pack_half2((v[i].z - mean) * rstd * g.z + b.z, (v[i].w - mean) * rstd * g.w + b.w);
-        yr[c] = o;
+        const float4 g = reinterpret_cast<const float4*>(gamma)[c];
+        const float4 b = reinterpret_cast<const float4*>(beta)[c];
+#pragma unroll
+        for (int r = 0; r < RPW; ++r)
+          if (row0 + r < rows) {
+            uint2 o;
+            o.x = pack_half2((v[r][i].x - mean[r]) * rstd[r] * g.x + b.x, (v[r][i].y - mean[r]) * rstd[r] * g.y + b.y);
+            o.y = pack_half2((v[r][i].z - mean[r]) * rstd[r] * g.z + b.z, (v[r][i].w - mean[r]) * rstd[r] * g.w + b.w);
+            reinterpret_cast<uint2*>(y + (row0 + r) * ldy)[c] = o;
+          }
       }
     }
   }
@@ -75,11 +94,18 @@ int layernorm_rows(const float* x, int64_t ldx, RowMap xmap, const float* gamma,
     return BSRL_ERR_ALIGN;
   }
   if (rows == 0) return BSRL_OK;
-  int64_t blocks = (rows + 7) / 8;
-  int64_t cap = (int64_t)sm_count() * 16;
-  if (blocks > cap) blocks = cap;
-  layernorm_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, ldx, xmap, gamma, beta, eps,
-                                                                     rows, d, y, ldy);
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (d <= 256 && rows >= cap * 8 * 4) {            // long, narrow inputs: four rows in flight per warp
+    int64_t blocks = (rows + 31) / 32;
+    if (blocks > cap) blocks = cap;
+    layernorm_kernel<4><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, ldx, xmap, gamma, beta, eps,
+                                                                          rows, d, y, ldy);
+  } else {
+    int64_t blocks = (rows + 7) / 8;
+    if (blocks > cap) blocks = cap;
+    layernorm_kernel<1><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, ldx, xmap, gamma, beta, eps,
+                                                                          rows, d, y, ldy);
+  }
   BSRL_LAUNCH_OK("layernorm_kernel");
   return BSRL_OK;
 }
