@@ -44,8 +44,9 @@ constexpr int token_lane(int tok, int k) {
   return -1;
 }
 
-// K-padded widths of the first encoder layers (multiples of 32 for the GEMM k-loop)
-constexpr int kSaberK = 64, kTorsoK = 32, kLegK = 64;
-constexpr int note_k(bool geo) { return geo ? 64 : 32; }
+// K-padded widths of the first encoder layers: one 64-wide k-block each, so that all of them run on
+// the tcgen05 GEMM (the warp-MMA kernel it would otherwise fall back to is several times slower here)
+constexpr int kSaberK = 64, kTorsoK = 64, kLegK = 64;
+constexpr int note_k(bool) { return 64; }
 
 }  // namespace bsrl
