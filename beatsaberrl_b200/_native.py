@@ -73,6 +73,8 @@ _sig = {
     "bsrl_forward_act": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, C.c_int32, _P, _P, _P, _P, _P, _P,
                                    _P, C.c_int64, _P]),
     "bsrl_forward_sample": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, _P, _P, _P, _P, _P, _P, _P, C.c_int64, _P]),
+    "bsrl_forward_rollout": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                                       _P, C.c_int64, _P]),
     "bsrl_token_lane": (C.c_int32, [C.c_int32, C.c_int32]),
     "bsrl_device_status": (C.c_int, []),
     "bsrl_set_engine": (C.c_int, [C.c_int32]),

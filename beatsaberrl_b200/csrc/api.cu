@@ -130,6 +130,7 @@ struct Ctx {
   void* ws;
   int64_t B;
   cudaStream_t st;
+  __half* obs16 = nullptr;   // optional fp16 copy of the obs rows, written by the tokenizer kernel
   const __half* W(const Mat& m, int row0 = 0) const { return at<__half>(arena, m.w) + (int64_t)row0 * m.pitch; }
   const float* Bv(const Mat& m, int row0 = 0) const { return at<float>(arena, m.b) + row0; }
   const float* G(const Norm& n) const { return at<float>(arena, n.g); }
@@ -154,6 +155,7 @@ int run_embed(const Ctx& c, const void* obs, int obs_dtype, float* x, float* key
   eb.leg = at<__half>(c.ws, w.f_leg);
   eb.note = at<__half>(c.ws, w.f_note);
   eb.key_bias = key_bias;
+  eb.obs16 = c.obs16;
   eb.ks = kSaberK; eb.kt = kTorsoK; eb.kl = kLegK; eb.kn = l.note_k;
   g_stage = kStGather;
   BSRL_TRY(timed(c.st, 0.0, (double)B * (kObs * 4 + (2 * kSaberK + kTorsoK + 2 * kLegK + kSlots * l.note_k) * 2 + kT * 4),
@@ -568,6 +570,38 @@ int bsrl_forward_sample(const bsrl_config* cfg, const void* arena, const void* o
   t.entropy = entropy;
   t.ent_head = ent_head;
   t.value = value;
+  return run_forward(c, obs, obs_dtype, t);
+}
+
+int bsrl_forward_rollout(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
+                         int64_t n_envs, const uint64_t* rng_state, int64_t* action_out, uint8_t* act_u8,
+                         float* logprob, float* entropy, float* ent_head, float* value, float* value_buf,
+                         const float* ret_sigma, const float* ret_mu, void* obs16, void* workspace,
+                         int64_t workspace_bytes, void* stream) {
+  Ctx c;
+  BSRL_TRY(make_ctx(c, cfg, arena, n_envs, workspace, workspace_bytes, stream));
+  if (!obs || !rng_state || !logprob || !value || (!action_out && !act_u8)) {
+    set_error("forward_rollout: NULL obs / rng_state / logprob / value, or no action output");
+    return BSRL_ERR_NULL;
+  }
+  if (obs16 && (reinterpret_cast<uintptr_t>(obs16) & 3)) {
+    set_error("forward_rollout: obs16 must be 4-byte aligned");
+    return BSRL_ERR_ALIGN;
+  }
+  if (n_envs == 0) return BSRL_OK;
+  c.obs16 = static_cast<__half*>(obs16);
+  HeadTailArgs t;
+  memset(&t, 0, sizeof(t));
+  t.rng = reinterpret_cast<const unsigned long long*>(rng_state);
+  t.action_out = reinterpret_cast<long long*>(action_out);
+  t.action_u8 = act_u8;
+  t.logprob = logprob;
+  t.entropy = entropy;
+  t.ent_head = ent_head;
+  t.value = value;
+  t.value_buf = value_buf;
+  t.ret_sigma = ret_sigma;
+  t.ret_mu = ret_mu;
   return run_forward(c, obs, obs_dtype, t);
 }
 

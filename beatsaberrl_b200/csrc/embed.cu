@@ -103,6 +103,10 @@ __global__ void __launch_bounds__(kWarps * 32) embed_gather_kernel(const void* _
       for (int i = lane; i < kObs; i += 32) o[i] = src[i];
     }
     __syncwarp();
+    if (out.obs16) {   // fp16 copy of the row (b_obs[t] of the rollout buffer, python/train_batch.py:2299)
+      uint32_t* d16 = reinterpret_cast<uint32_t*>(out.obs16 + env * kObs);
+      for (int i = lane; i < kObs / 2; i += 32) d16[i] = pack_half2(o[2 * i], o[2 * i + 1]);
+    }
     if (note_geo && lane < kSlots) slot_geometry(o, lane, z_asinh, geo + lane * kGeoFeat);
     // lead tokens: lane writes features 2*lane, 2*lane + 1
     {

@@ -6,6 +6,8 @@
 // 29-head sums are warp reductions.  The whole warp then turns the value-bin logits into the
 // HL-Gauss expectation softmax(bins) . linspace(-vmax, vmax, bins).
 //
+// With the rollout outputs set it also writes the trainer's per-tick buffer rows (uint8 actions,
+// de-normalised value: python/train_batch.py:2338-2350).
 // Reference: masked-lane fill python/policy.py:1337-1344, value expectation :1399-1403,
 // log-softmax / gather-sum / per-head entropy :1473-1516.  HBM-bound: reads
 // 4*(sum K_j + bins) bytes and writes 4*(29 k_max + ...) bytes per env.
@@ -88,6 +90,7 @@ __global__ void __launch_bounds__(256) head_tail_kernel(HeadTailArgs p) {
                 if (sc > best) { best = sc; a = i; }
               }
             if (p.action_out) p.action_out[env * kActHeads + lane] = a;
+            if (p.action_u8) p.action_u8[env * kActHeads + lane] = static_cast<unsigned char>(a);
           }
           float pick = kMaskedLogit;
 #pragma unroll
@@ -130,7 +133,12 @@ __global__ void __launch_bounds__(256) head_tail_kernel(HeadTailArgs p) {
     }
     se = warp_sum(se);
     sc = warp_sum(sc);
-    if (lane == 0) p.value[env] = sc / se;
+    if (lane == 0) {
+      const float v = sc / se;
+      p.value[env] = v;
+      // the trainer stores the de-normalised value: b_val[t] = v * ret_sig + ret_mu
+      if (p.value_buf) p.value_buf[env] = v * (p.ret_sigma ? *p.ret_sigma : 1.f) + (p.ret_mu ? *p.ret_mu : 0.f);
+    }
   }
 }
 }  // namespace

@@ -86,6 +86,7 @@ struct EmbedBuffers {
   __half* note;   // (24B, kn)
   float* key_bias;  // (B, 29)
   int ks, kt, kl, kn;
+  __half* obs16 = nullptr;   // optional (B, 630) fp16 copy of the observation rows (rollout buffer row)
 };
 int embed_gather(const void* obs, int obs_dtype, int64_t n_envs, int note_geo, float z_asinh,
                  const EmbedBuffers& out, cudaStream_t stream);
@@ -110,6 +111,10 @@ struct HeadTailArgs {
   int act_dtype;
   const unsigned long long* rng;   // device [seed, offset]: sample actions (Gumbel-max) when actions is null
   long long* action_out;           // (B, 29) sampled actions
+  unsigned char* action_u8;        // (B, 29) the same actions as bytes (rollout buffer row) or nullptr
+  float* value_buf;                // (B) value * ret_sigma + ret_mu (rollout buffer row) or nullptr
+  const float* ret_sigma;          // device scalars of the return normaliser; nullptr = 1 / 0
+  const float* ret_mu;
   float* logits;         // (B, 29, k_max) or nullptr
   float* logprob;        // (B) or nullptr
   float* entropy;        // (B) or nullptr

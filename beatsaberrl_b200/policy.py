@@ -322,6 +322,59 @@ class NotePolicy(nn.Module):
         self._value_logits = None
         return action, logprob, entropy, value
 
+    @torch.no_grad()
+    def rollout_step(self, obs, b_act=None, b_logp=None, b_val=None, b_obs=None, ret_sig=None, ret_mu=None,
+                     need_entropy=False):
+        """One rollout tick with the trainer's per-tick buffer stores fused into the forward's kernels.
+
+        Stands in for the loop body ``b_obs[t] = obs; a, logp, _, v = get_action_and_value(obs);
+        b_act[t], b_logp[t] = a, logp; b_val[t].copy_(v).mul_(ret_sig).add_(ret_mu)`` of the reference
+        trainer (python/train_batch.py:2299-2350).  Pass ROW VIEWS of the buffers: ``b_act`` (B, 29) uint8,
+        ``b_logp`` (B,) f32, ``b_val`` (B,) f32, ``b_obs`` (B, 630) f16; ``ret_sig`` / ``ret_mu`` are the 0-d
+        device tensors of the return normaliser (None = 1 / 0).  Any buffer may be None.  Returns
+        ``(action int64, logprob, entropy | None, value)`` like ``get_action_and_value``.
+        """
+        obs = self._check_obs(obs)
+        self._pack()
+        B, dev = obs.shape[0], obs.device
+        if getattr(self, "_rng_state", None) is None or self._rng_state.device != dev:
+            self.seed_sampler(int(torch.randint(0, 2 ** 62, (1,)).item()))
+        f32 = dict(dtype=torch.float32, device=dev)
+
+        def row(t, shape, dtype, name):
+            if t is None:
+                return None
+            if tuple(t.shape) != shape or t.dtype != dtype or t.device != dev or not t.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous {dtype} tensor of shape {shape} on {dev}")
+            return t
+
+        b_act = row(b_act, (B, N_ACTION_HEADS), torch.uint8, "b_act")
+        b_val = row(b_val, (B,), torch.float32, "b_val")
+        b_obs = row(b_obs, (B, OBS_DIM), torch.float16, "b_obs")
+        logprob = row(b_logp, (B,), torch.float32, "b_logp")
+        if logprob is None:
+            logprob = torch.empty(B, **f32)
+        for name, s in (("ret_sig", ret_sig), ("ret_mu", ret_mu)):
+            if s is not None and (s.numel() != 1 or s.dtype != torch.float32 or s.device != dev):
+                raise ValueError(f"{name} must be a one-element float32 tensor on {dev}")
+        action = torch.empty(B, N_ACTION_HEADS, dtype=torch.int64, device=dev)
+        value = torch.empty(B, **f32)
+        entropy = torch.empty(B, **f32) if need_entropy else None
+        ent_h = torch.empty(B, N_ACTION_HEADS, **f32) if need_entropy else None
+        ws = self._workspace(B, dev)
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        with torch.cuda.device(dev):
+            nat.check(nat.lib.bsrl_forward_rollout(
+                C.byref(self._cfg), self._arena.data_ptr(), obs.data_ptr(), self._obs_dtype(obs), B,
+                self._rng_state.data_ptr(), action.data_ptr(), ptr(b_act), logprob.data_ptr(), ptr(entropy),
+                ptr(ent_h), value.data_ptr(), ptr(b_val), ptr(ret_sig), ptr(ret_mu), ptr(b_obs),
+                ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream))
+            self._rng_state[1] += 1
+        if need_entropy:
+            self._ent_h = ent_h
+        self._value_logits = None
+        return action, logprob, entropy, value
+
     # ------------------------------------------------------------------ introspection
     def mac_per_env(self) -> int:
         return int(nat.lib.bsrl_mac_per_env(C.byref(self._cfg)))

@@ -147,6 +147,25 @@ int bsrl_forward_sample(const bsrl_config* cfg, const void* arena, const void* o
                         float* logprob, float* entropy, float* ent_head, float* value, void* workspace,
                         int64_t workspace_bytes, void* stream);
 
+/* One rollout tick with the trainer's per-tick buffer stores fused in -- the loop body of the
+ * rollout (python/train_batch.py:2299-2350: b_obs[t] = obs; a, logp, _, v = get_action_and_value(obs);
+ * b_act[t], b_logp[t] = a, logp; b_val[t].copy_(v).mul_(ret_sig).add_(ret_mu)).  Samples like
+ * bsrl_forward_sample and writes, from the same kernels:
+ *   act_u8    (n_envs, 29) u8   row t of the uint8 action buffer (python/train_batch.py:1963-1970)
+ *   logprob   (n_envs)     f32  row t of b_logp
+ *   value_buf (n_envs)     f32  row t of b_val: value * *ret_sigma + *ret_mu (DEVICE scalars of the
+ *                               return normaliser, python/train_batch.py:1986-1988; NULL = 1 / 0)
+ *   obs16     (n_envs, 630) f16 row t of the half-precision obs buffer (--fp16 all,
+ *                               python/train_batch.py:1953-1962), written by the tokenizer kernel that
+ *                               reads the row anyway
+ * action_out (n_envs, 29) i64 feeds the env step.  action_out or act_u8 must be given; act_u8,
+ * value_buf, obs16, entropy and ent_head may be NULL. */
+int bsrl_forward_rollout(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
+                         int64_t n_envs, const uint64_t* rng_state, int64_t* action_out, uint8_t* act_u8,
+                         float* logprob, float* entropy, float* ent_head, float* value, float* value_buf,
+                         const float* ret_sigma, const float* ret_mu, void* obs16, void* workspace,
+                         int64_t workspace_bytes, void* stream);
+
 /* --- single stages (unit tests and profiling) -------------------------------------- */
 
 /* Obs lane of feature k of lead token tok (0..4), or -1 past the token's width

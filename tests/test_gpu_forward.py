@@ -163,6 +163,37 @@ def test_fused_sampling_distribution_and_determinism():
     torch.testing.assert_close(ent1, ent_given, atol=1e-5, rtol=1e-6)
 
 
+def test_rollout_step_writes_buffer_rows():
+    """The fused rollout tick draws the same actions as get_action_and_value under the same seed and
+    counter, and its buffer rows are what the reference's loop body stores: uint8 actions, log-prob,
+    value * ret_sig + ret_mu, the fp16 obs row (python/train_batch.py:2299-2350)."""
+    cfg, sd = golden_case("tiny_geo_mixed")
+    m = cuda_policy(cfg, sd)
+    B, T = 777, 3
+    obs = po.make_obs(B, 7, padded=True).cuda()
+    b_act = torch.zeros(T, B, 29, dtype=torch.uint8, device="cuda")
+    b_logp = torch.zeros(T, B, device="cuda")
+    b_val = torch.zeros(T + 1, B, device="cuda")
+    b_obs = torch.zeros(T, B, 630, dtype=torch.float16, device="cuda")
+    ret_sig = torch.tensor(2.5, device="cuda")
+    ret_mu = torch.tensor(-0.75, device="cuda")
+    m.seed_sampler(99)
+    a_ref, lp_ref, ent_ref, v_ref = m.get_action_and_value(obs)
+    m.seed_sampler(99)
+    t = 1
+    a, lp, ent, v = m.rollout_step(obs, b_act[t], b_logp[t], b_val[t], b_obs[t], ret_sig, ret_mu, need_entropy=True)
+    assert torch.equal(a, a_ref) and torch.equal(lp, lp_ref) and torch.equal(v, v_ref) and torch.equal(ent, ent_ref)
+    assert torch.equal(b_act[t].long(), a) and torch.equal(b_logp[t], lp)
+    torch.testing.assert_close(b_val[t], v * 2.5 - 0.75, atol=1e-6, rtol=1e-6)
+    assert torch.equal(b_obs[t], obs.half())
+    # the other rows are untouched; all outputs optional
+    assert not b_act[0].any() and not b_act[2].any() and not b_val[0].any() and not b_obs[2].any()
+    a2, lp2, ent2, v2 = m.rollout_step(obs)
+    assert ent2 is None and a2.shape == (B, 29) and not torch.equal(a2, a)
+    with pytest.raises(ValueError):
+        m.rollout_step(obs, b_act=b_act[t].int())
+
+
 def test_full_size_properties():
     """At the padded-objects size (131,072 envs, uniform 0..24 live slots): outputs finite, an
     env's result independent of its position in the batch (rows re-ordered -> outputs re-ordered,
