@@ -230,7 +230,7 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     a.out = out; a.ldo = d;
     return a;
   };
-  const bool fused_qkv = g_engine == 0 && l.attn_G == 2 && attn_block_ok(attn_args(h, l.blocks[0].qkv_g, 0, kT, att));
+  const bool fused_qkv = g_engine == 0 && l.attn_G > 0 && attn_block_ok(attn_args(h, l.blocks[0].qkv_g, 0, kT, att));
   __half* hv = at<__half>(c.ws, w.enc_hid);   // critic LayerNorm rows (encoder scratch is free by now)
   bool have_h = false, have_hv = false;
 

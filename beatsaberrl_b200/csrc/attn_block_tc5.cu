@@ -28,15 +28,21 @@ using namespace tc5;
 constexpr int EPT = 4;                  // envs per tile
 constexpr int ROWS = EPT * kT;          // 116 live rows
 constexpr int BM = 128;
-constexpr int DH = 32, G = 2, GD = G * DH, NG = 3 * GD;   // 192 columns per head group
 constexpr int STAGES = 4;
-constexpr int STAGE_BYTES = NG * 128;   // 24 KB: 192 weight rows x 64 k-columns
 constexpr int CHUNK_BYTES = BM * 128;   // 16 KB: 128 rows x 64 k-columns
-constexpr int LDQ = NG * 2 + 16;        // 400-byte rows of the q|k|v tile (ldmatrix conflict-free)
-constexpr int SQ_BYTES = BM * LDQ;
 constexpr int WORKERS = 8;
 constexpr int THREADS = (2 + WORKERS) * 32;
-constexpr int SMEM_BYTES = 4 * CHUNK_BYTES + STAGES * STAGE_BYTES + SQ_BYTES + 768 * 4 + 1024 + 256;
+// Head group of G heads of width DH: 3 G DH projection columns per group -- (32, 2): 192, two heads;
+// (48, 1): 144, one head (the reference's production shape, 4 heads of 48).
+template <int DH_, int G_>
+struct Shape {
+  static constexpr int DH = DH_, G = G_, GD = G * DH, NG = 3 * GD;
+  static constexpr int STAGE_BYTES = NG * 128;   // NG weight rows x 64 k-columns (24 KB / 18 KB)
+  static constexpr int LDQ = NG * 2 + 16;        // row pitch of the q|k|v tile: 400 / 304 bytes, ldmatrix conflict-free
+  static constexpr int SQ_BYTES = BM * LDQ;
+  static constexpr int SMEM_BYTES = 4 * CHUNK_BYTES + STAGES * STAGE_BYTES + SQ_BYTES + 768 * 4 + 1024 + 256;
+  static_assert(NG % 16 == 0 && NG <= 256 && STAGE_BYTES % 1024 == 0, "group width");
+};
 constexpr int KERNEL_ID = 3;
 
 struct Shared {
@@ -101,7 +107,7 @@ __device__ __forceinline__ float rcp_approx(float x) {
 // addresses (shared window) of the pair's first row / first column; rows are LDQ bytes apart.
 // The MT 16-row query tiles are processed side by side: two independent dependency chains per warp
 // (the kernel is latency-bound here) and each K / V fragment is fetched once for both.
-template <int MT>
+template <int MT, int DH, int LDQ>
 __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t sv, const float (&kb)[4][2],
                                             int n_q, __half* out_env, int ldo, int lane TRACE_PARAMS) {
   const int g = lane >> 2, tig = lane & 3;
@@ -207,8 +213,11 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
     }
 }
 
+template <int DH, int G>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_w, Params p) {
+  using S = Shape<DH, G>;
+  constexpr int GD = S::GD, NG = S::NG, STAGE_BYTES = S::STAGE_BYTES, LDQ = S::LDQ, SQ_BYTES = S::SQ_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -333,9 +342,14 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
   } else {
     // ------------------------------------------------------------ workers: drain, then attend
     const int wi = warp - 2;
-    const int q = warp & 3, half = wi >> 2;           // TMEM lane quadrant, column half (96 columns)
+    const int q = warp & 3, half = wi >> 2;           // TMEM lane quadrant, column half
     const int trow = q * 32 + lane;
-    const int env_l = wi >> 1, hh = wi & 1;           // this warp's (env, head) pair inside a group
+    // drain: the group's NG columns in 16-column units, split between the two halves (6 + 6 or 5 + 4)
+    constexpr int UNITS = NG / 16, U0 = (UNITS + 1) / 2;
+    const int u_first = half ? U0 : 0, u_count = half ? UNITS - U0 : U0;
+    // attention: G = 2: one (env, head) pair per warp, both 16-row query tiles; G = 1: one env per two
+    // warps, one query tile each
+    const int env_l = wi >> 1, hh = G == 2 ? (wi & 1) : 0, mt_own = G == 2 ? 0 : (wi & 1);
     uint32_t gi = 0;
     bool ok = true;
     TRACE_INIT(lane == 0 ? wi + 1 : -1);
@@ -359,21 +373,36 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
         if (!mbar_wait_warp(smem_u32(&sh->acc_full[buf]), (gi >> 1) & 1, abort) && lane == 0) give_up(sh, p.status, 9);
         tc_fence_after();
         TRACE(200 + g);
+        {
+          const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + u_first * 16;
+          const float* bias_u = s_bias + g * NG + u_first * 16;
+          uint8_t* dst_u = sQ_g + trow * LDQ + (u_first * 16) * 2;
+          // 16 columns -> bias, fp16, two 16-byte pieces of this thread's row
+          auto put16 = [&](const uint32_t* v, int u) {
+            const float4* b4 = reinterpret_cast<const float4*>(bias_u + u * 16);
 #pragma unroll
-        for (int c = 0; c < 96; c += 32) {
-          uint32_t r[32];
-          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + half * 96 + c, r);
-          tmem_wait_ld();
-          const float4* b4 = reinterpret_cast<const float4*>(s_bias + g * NG + half * 96 + c);
-          uint8_t* dst = sQ_g + trow * LDQ + (half * 96 + c) * 2;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float4 b0 = b4[2 * j], b1 = b4[2 * j + 1];
-            *reinterpret_cast<uint4*>(dst + 16 * j) = make_uint4(
-                pack_half2(__uint_as_float(r[8 * j]) + b0.x, __uint_as_float(r[8 * j + 1]) + b0.y),
-                pack_half2(__uint_as_float(r[8 * j + 2]) + b0.z, __uint_as_float(r[8 * j + 3]) + b0.w),
-                pack_half2(__uint_as_float(r[8 * j + 4]) + b1.x, __uint_as_float(r[8 * j + 5]) + b1.y),
-                pack_half2(__uint_as_float(r[8 * j + 6]) + b1.z, __uint_as_float(r[8 * j + 7]) + b1.w));
+            for (int j = 0; j < 2; ++j) {
+              const float4 b0 = b4[2 * j], b1 = b4[2 * j + 1];
+              *reinterpret_cast<uint4*>(dst_u + u * 32 + 16 * j) = make_uint4(
+                  pack_half2(__uint_as_float(v[8 * j]) + b0.x, __uint_as_float(v[8 * j + 1]) + b0.y),
+                  pack_half2(__uint_as_float(v[8 * j + 2]) + b0.z, __uint_as_float(v[8 * j + 3]) + b0.w),
+                  pack_half2(__uint_as_float(v[8 * j + 4]) + b1.x, __uint_as_float(v[8 * j + 5]) + b1.y),
+                  pack_half2(__uint_as_float(v[8 * j + 6]) + b1.z, __uint_as_float(v[8 * j + 7]) + b1.w));
+            }
+          };
+          int u = 0;
+          for (; u + 2 <= u_count; u += 2) {
+            uint32_t r[32];
+            tmem_ld32(tcol + u * 16, r);
+            tmem_wait_ld();
+            put16(r, u);
+            put16(r + 16, u + 1);
+          }
+          if (u < u_count) {
+            uint32_t r[16];
+            tmem_ld16(tcol + u * 16, r);
+            tmem_wait_ld();
+            put16(r, u);
           }
         }
         tc_fence_before();
@@ -389,11 +418,12 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
         }
         if (env < p.n_envs) {
           const uint32_t rows = sQ + (env_l * kT) * LDQ;
-          const uint32_t sq_pair = rows + p.q_first * LDQ + (hh * DH) * 2, sk_pair = rows + (GD + hh * DH) * 2,
-                         sv_pair = rows + (2 * GD + hh * DH) * 2;
-          __half* out_pair = p.out + env * p.n_q * (int64_t)p.ldo + (g * G + hh) * DH;
-          if (p.n_q > 16) attend_pair<2>(sq_pair, sk_pair, sv_pair, kb, p.n_q, out_pair, p.ldo, lane TRACE_ARGS);
-          else attend_pair<1>(sq_pair, sk_pair, sv_pair, kb, p.n_q, out_pair, p.ldo, lane TRACE_ARGS);
+          const uint32_t sq_pair = rows + (p.q_first + mt_own * 16) * LDQ + (hh * DH) * 2,
+                         sk_pair = rows + (GD + hh * DH) * 2, sv_pair = rows + (2 * GD + hh * DH) * 2;
+          __half* out_pair = p.out + (env * p.n_q + mt_own * 16) * (int64_t)p.ldo + (g * G + hh) * DH;
+          const int n_q = p.n_q - mt_own * 16;      // query rows left from this warp's first one
+          if (G == 2 && n_q > 16) attend_pair<2, DH, LDQ>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane TRACE_ARGS);
+          else if (n_q > 0) attend_pair<1, DH, LDQ>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane TRACE_ARGS);
         }
         TRACE(230 + g);
         __syncwarp();
@@ -415,7 +445,9 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
 }  // namespace
 
 bool attn_block_ok(const AttnBlockArgs& a) {
-  if (a.d % 64 != 0 || a.d < 64 || a.d > 256 || a.n_heads * DH != a.d || a.n_heads % G != 0) return false;
+  if (a.d % 64 != 0 || a.d < 64 || a.d > 256 || a.n_heads < 1 || a.d % a.n_heads != 0) return false;
+  const int dh = a.d / a.n_heads;
+  if (!((dh == 32 && a.n_heads % 2 == 0) || dh == 48)) return false;
   if (a.n_envs < 1 || a.n_envs > 0x7fffffffLL / (ROWS * 2)) return false;
   if (a.q_first < 0 || a.n_q < 1 || a.q_first + a.n_q > kT) return false;
   if (!aligned16(a.h) || !aligned16(a.wg) || !aligned16(a.bg) || !aligned16(a.out) || (a.ldh % 8) || (a.ldo % 8)) return false;
@@ -428,19 +460,21 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
     return BSRL_ERR_NULL;
   }
   if (!attn_block_ok(a)) {
-    set_error("attn_block: shape d=%d heads=%d does not fit the fused kernel (head_dim 32, d <= 256)", a.d, a.n_heads);
+    set_error("attn_block: shape d=%d heads=%d does not fit the fused kernel (head_dim 32 or 48, d <= 256)", a.d, a.n_heads);
     return BSRL_ERR_UNSUPPORTED;
   }
   int* status = device_status_ptr();
   if (!status) return BSRL_ERR_CUDA;
+  const int dh = a.d / a.n_heads;
   CUtensorMap tm_h, tm_w;
   if (!make_tmap_f16(&tm_h, a.h, a.n_envs * kT, a.d, a.ldh, BM)) return BSRL_ERR_CUDA;
-  if (!make_tmap_f16(&tm_w, a.wg, 3 * a.d, a.d, a.d, NG)) return BSRL_ERR_CUDA;
+  if (!make_tmap_f16(&tm_w, a.wg, 3 * a.d, a.d, a.d, dh == 32 ? Shape<32, 2>::NG : Shape<48, 1>::NG)) return BSRL_ERR_CUDA;
   static bool attr_set[64] = {};
   int dev = 0;
   BSRL_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 64 && !attr_set[dev]) {
-    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel<32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<32, 2>::SMEM_BYTES));
+    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel<48, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<48, 1>::SMEM_BYTES));
     attr_set[dev] = true;
   }
   Params p;
@@ -450,7 +484,8 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
   p.bias = a.bg; p.key_bias = a.key_bias; p.out = a.out; p.ldo = a.ldo;
   p.status = status;
   const int grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
-  attn_block_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_h, tm_w, p);
+  if (dh == 32) attn_block_kernel<32, 2><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, p);
+  else attn_block_kernel<48, 1><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, p);
   BSRL_LAUNCH_OK("attn_block_kernel");
   return BSRL_OK;
 }

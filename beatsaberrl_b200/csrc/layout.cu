@@ -184,8 +184,13 @@ Layout make_layout(const bsrl_config& c) {
   l.critic_m1 = carve_mat(cv, l.D, l.D);
   l.critic_m2 = carve_mat(cv, l.bins, l.D, 0, l.bins_pad);
   l.critic_qkv_g = carve_mat(cv, 3 * d, d);
-  // fused QKV+attention kernel: head_dim 32, two heads per group (192 output columns per group)
-  l.attn_G = (d / l.H == 32 && l.H % 2 == 0 && d % 64 == 0 && d <= 256) ? 2 : 0;
+  // fused QKV+attention kernel: head_dim 32, two heads per group (192 output columns per group), or
+  // head_dim 48, one head per group (144 columns)
+  l.attn_G = 0;
+  if (d % 64 == 0 && d <= 256 && d % l.H == 0) {
+    if (d / l.H == 32 && l.H % 2 == 0) l.attn_G = 2;
+    else if (d / l.H == 48) l.attn_G = 1;
+  }
   l.bytes = cv.off;
   return l;
 }

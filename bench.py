@@ -35,6 +35,8 @@ WORKLOADS = {
     "cfg3": ("cfg3", 131072, 1, True, True, 2),
     "cfg4": ("cfg4", 32768, 3, False, False, 3),
     "cfg5": ("cfg5", 131072, 1, True, False, 1),
+    # the reference's production shape (d 192, 6 blocks, 4 heads of 48, trunk 384, note-geo; python/train_batch.py:521-525)
+    "recipe": ("recipe", 32768, 5, False, False, 5),
 }
 
 

@@ -198,11 +198,13 @@ int bsrl_linear(const void* a_f16, const void* w_f16, const float* bias, const f
 int bsrl_attention(const void* qkv_f16, const float* key_bias, int64_t n_envs, int32_t d,
                    int32_t n_heads, int32_t q_first, int32_t n_q, void* out_f16, void* stream);
 
-/* Fused packed projection + attention of one block (head_dim 32, embed <= 256), one tcgen05 kernel:
+/* Fused packed projection + attention of one block (head_dim 32 with an even head count, or head_dim
+ * 48; embed <= 256), one tcgen05 kernel:
  *   out = MHA(h Wq^T + bq, h Wk^T + bk, h Wv^T + bv; key_bias), queries = rows [q_first, q_first + n_q)
- * h (n_envs*29, d) f16 -> out (n_envs*n_q, d) f16.  The weights come REGROUPED per pair of heads:
- * rows [192 g, 192 g + 64) = Wq rows of heads 2g, 2g+1; the next 64 = Wk rows; the next 64 = Wv
- * rows; the bias likewise (bsrl_pack_weights builds these copies in the arena).
+ * h (n_envs*29, d) f16 -> out (n_envs*n_q, d) f16.  The weights come REGROUPED per head group (two
+ * heads of 32, or one head of 48; w = the group's width, 64 or 48): rows [3 w g, 3 w g + w) = Wq rows
+ * of group g, the next w = its Wk rows, the next w = its Wv rows; the bias likewise
+ * (bsrl_pack_weights builds these copies in the arena).
  * Replaces fp16_packed_linear + attn29_packed / packed_sdpa (python/policy.py:586-600, :645-692). */
 int bsrl_qkv_attention(const void* h_f16, const void* w_grouped_f16, const float* b_grouped,
                        const float* key_bias, int64_t n_envs, int32_t d, int32_t n_heads, int32_t q_first,

@@ -153,7 +153,10 @@ def test_block_tail(native, m, d, f, ln_out):
 
 
 @pytest.mark.parametrize("B,d,H,q_first,n_q", [(1, 64, 2, 0, 29), (4, 256, 8, 0, 29), (37, 256, 8, 0, 29),
-                                               (50, 128, 4, 0, 5), (33, 256, 8, 2, 1), (3000, 256, 8, 0, 29)])
+                                               (50, 128, 4, 0, 5), (33, 256, 8, 2, 1), (3000, 256, 8, 0, 29),
+                                               # head_dim 48 (one head per group): the production shape
+                                               (5, 192, 4, 0, 29), (1001, 192, 4, 0, 29), (70, 192, 4, 0, 5),
+                                               (9, 192, 4, 2, 1)])
 def test_qkv_attention(native, B, d, H, q_first, n_q):
     """Fused projection + attention kernel against torch fp32 on the same fp16 operands."""
     g = torch.Generator().manual_seed(B + d + n_q)
@@ -163,11 +166,12 @@ def test_qkv_attention(native, B, d, H, q_first, n_q):
     n_live = torch.randint(0, 25, (B,), generator=g)
     kb = torch.zeros(B, 29)
     kb[:, 5:] = ((torch.arange(24)[None, :] < n_live[:, None]).float() - 1.0) * 16384.0
-    # regroup per pair of heads: [q rows | k rows | v rows] of heads 2g, 2g+1
+    # regroup per head group (two heads of 32, or one of 48): [q rows | k rows | v rows] of the group
+    gd = 64 if d // H == 32 else d // H
     idx = []
-    for grp in range(d // 64):
+    for grp in range(d // gd):
         for sct in range(3):
-            idx += list(range(sct * d + grp * 64, sct * d + grp * 64 + 64))
+            idx += list(range(sct * d + grp * gd, sct * d + grp * gd + gd))
     idx = torch.tensor(idx)
     wg, bg = w[idx].contiguous().cuda(), bias[idx].contiguous().cuda()
     out = torch.empty(B * n_q, d, dtype=torch.float16, device="cuda")
