@@ -159,7 +159,7 @@ int run_embed(const Ctx& c, const void* obs, int obs_dtype, float* x, float* key
   eb.ks = kSaberK; eb.kt = kTorsoK; eb.kl = kLegK; eb.kn = l.note_k;
   g_stage = kStGather;
   BSRL_TRY(timed(c.st, 0.0, (double)B * (kObs * 4 + (2 * kSaberK + kTorsoK + 2 * kLegK + kSlots * l.note_k) * 2 + kT * 4),
-                 [&] { return embed_gather(obs, obs_dtype, B, c.cfg->note_geo, c.cfg->z_asinh, eb, c.st); }));
+                 [&] { return embed_gather(obs, obs_dtype, B, c.cfg->note_geo, c.cfg->game_flux, c.cfg->z_asinh, eb, c.st); }));
   g_stage = kStEncoder;
   __half* hid = at<__half>(c.ws, w.enc_hid);
   struct Part { const Encoder* e; const __half* f; int kpad; int64_t rows; int64_t row0; int group; int first; };
@@ -177,6 +177,12 @@ int run_embed(const Ctx& c, const void* obs, int obs_dtype, float* x, float* key
     LinearArgs a1 = linear_args(hp, d, c.W(p.e->l1), p.e->l1.pitch, c.Bv(p.e->l1), x, d, 1, 0, p.rows, d, d);
     a1.cmap = RowMap{p.group, kT, p.first};
     BSRL_TRY(linear(a1, c.st));
+  }
+  if (c.cfg->emb_ln) {   // tokens = emb_ln(tokens), in place on the fp32 stream (python/policy.py:1261-1262)
+    g_stage = kStLayerNorm;
+    BSRL_TRY(timed(c.st, 0.0, (double)B * kT * d * 8, [&] {
+      return layernorm_rows_f32(x, d, c.G(l.emb_ln), c.Be(l.emb_ln), c.cfg->eps, B * kT, d, x, d, c.st);
+    }));
   }
   return BSRL_OK;
 }
@@ -294,6 +300,9 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
       BlockTailArgs a = tail_args(b, Rl);
       a.xmap = lead_rows;
       a.out16[0] = lead16; a.ld16[0] = d;     // plain fp16 rows: the trunk's GEMM operand
+      if (c.cfg->final_ln) {                  // ... or final_ln of them (python/policy.py:1306-1307)
+        a.g16[0] = c.G(l.final_ln); a.b16[0] = c.Be(l.final_ln);
+      }
       BSRL_TRY(fused_tail(a, c.st));
     } else {
       LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x_lead, d, 1, 0, Rl, d, d);
@@ -305,8 +314,13 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
       BSRL_TRY(linear(linear_args(h_lead, d, c.W(b.up), d, c.Bv(b.up), hid, F, 0, 1, Rl, F, d), c.st));
       LinearArgs pd = linear_args(hid, F, c.W(b.down), F, c.Bv(b.down), lead16, d, 0, 0, Rl, d, F);
       pd.R = x_lead; pd.ldr = d;
+      if (c.cfg->final_ln) {   // keep the fp32 rows and normalise them into the trunk operand
+        pd.C = x_lead; pd.ldc = d; pd.out_f32 = 1;
+      }
       g_stage = kStFfnDown;
       BSRL_TRY(linear(pd, c.st));
+      if (c.cfg->final_ln)
+        BSRL_TRY(layernorm(x_lead, d, ident, c.G(l.final_ln), c.Be(l.final_ln), eps, Rl, d, lead16, d, c.st));
     }
   }
 

@@ -41,12 +41,14 @@ __device__ __forceinline__ float tab(const float* o, int tok, int k) {
   return l >= 0 ? o[l] : (l == -2 ? 1.f : 0.f);
 }
 
-// 22 geometry lanes of one slot (standard game): per hand 7, then per hand 4.
-__device__ void slot_geometry(const float* o, int slot, float z_asinh, float* out) {
+// 22 geometry lanes of one slot: per hand 7, then per hand 4.  flux: a bar slot (lane 9 > 0.5) is aimed
+// at lanes 12, 13, where it must be crossed (python/policy.py:357-360).
+__device__ void slot_geometry(const float* o, int slot, float z_asinh, bool flux, float* out) {
   const float XN = 1.0f, YN = 0.75f, ZS = 8.0f, VN = 6.0f, HANDLE = 0.16f;
   const float* n = o + kOffNotes + slot * kNoteFeat;
   const float z_m = sinhf(n[2]) * z_asinh;
-  const float px = n[0] * XN, py = n[1] * YN, pz = z_m;
+  const bool bar = flux && n[9] > 0.5f;
+  const float px = (bar ? n[12] : n[0]) * XN, py = (bar ? n[13] : n[1]) * YN, pz = z_m;
   const float cx = n[6], cy = n[7];
   const float live = 1.0f - n[14];
   const float speed = fmaxf(-n[3] * ZS, 1e-3f);
@@ -107,7 +109,7 @@ __global__ void __launch_bounds__(kWarps * 32) embed_gather_kernel(const void* _
       uint32_t* d16 = reinterpret_cast<uint32_t*>(out.obs16 + env * kObs);
       for (int i = lane; i < kObs / 2; i += 32) d16[i] = pack_half2(o[2 * i], o[2 * i + 1]);
     }
-    if (note_geo && lane < kSlots) slot_geometry(o, lane, z_asinh, geo + lane * kGeoFeat);
+    if (note_geo && lane < kSlots) slot_geometry(o, lane, z_asinh, (note_geo & 2) != 0, geo + lane * kGeoFeat);
     // lead tokens: lane writes features 2*lane, 2*lane + 1
     {
       const int k = lane * 2;
@@ -154,7 +156,7 @@ int token_lane_host(int tok, int k) {
   return h_lanes.v[tok][k];
 }
 
-int embed_gather(const void* obs, int obs_dtype, int64_t n_envs, int note_geo, float z_asinh,
+int embed_gather(const void* obs, int obs_dtype, int64_t n_envs, int note_geo, int flux, float z_asinh,
                  const EmbedBuffers& out, cudaStream_t stream) {
   if (!obs || !out.saber || !out.torso || !out.leg || !out.note || !out.key_bias) {
     set_error("embed: NULL operand");
@@ -169,6 +171,7 @@ int embed_gather(const void* obs, int obs_dtype, int64_t n_envs, int note_geo, f
     return BSRL_ERR_SHAPE;
   }
   if (n_envs <= 0) return n_envs == 0 ? BSRL_OK : BSRL_ERR_SHAPE;
+  note_geo = note_geo ? (flux ? 3 : 1) : 0;   // bit 1 tells the kernel to use the Flux variant
   int64_t blocks = (n_envs + kWarps - 1) / kWarps;
   int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;

@@ -74,9 +74,12 @@ struct AttnBlockArgs {
 bool attn_block_ok(const AttnBlockArgs& a);
 int attn_block(const AttnBlockArgs& a, cudaStream_t stream);
 
-// y(f16, ldy) = LayerNorm(x(f32, ldx)) per row, fp32 statistics.
+// y(f16, ldy) = LayerNorm(x(f32, ldx)) per row, fp32 statistics; layernorm_rows_f32 writes fp32 rows
+// (in place allowed).
 int layernorm_rows(const float* x, int64_t ldx, RowMap xmap, const float* gamma, const float* beta,
                    float eps, int64_t rows, int d, __half* y, int64_t ldy, cudaStream_t stream);
+int layernorm_rows_f32(const float* x, int64_t ldx, const float* gamma, const float* beta, float eps,
+                       int64_t rows, int d, float* y, int64_t ldy, cudaStream_t stream);
 
 // Tokenizer: obs -> per-encoder fp16 feature rows + additive key bias.
 struct EmbedBuffers {
@@ -88,7 +91,7 @@ struct EmbedBuffers {
   int ks, kt, kl, kn;
   __half* obs16 = nullptr;   // optional (B, 630) fp16 copy of the observation rows (rollout buffer row)
 };
-int embed_gather(const void* obs, int obs_dtype, int64_t n_envs, int note_geo, float z_asinh,
+int embed_gather(const void* obs, int obs_dtype, int64_t n_envs, int note_geo, int flux, float z_asinh,
                  const EmbedBuffers& out, cudaStream_t stream);
 int token_lane_host(int tok, int k);
 

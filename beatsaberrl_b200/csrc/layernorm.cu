@@ -12,7 +12,8 @@ constexpr int kMaxVec = 8;  // float4 per lane => rows up to 1024 wide
 
 // RPW rows per warp are in flight together: the kernel is latency-bound on its loads, and a second
 // (third, fourth) independent row per warp multiplies the bytes in flight.
-template <int RPW>
+// F32: the output rows are fp32 (y points at floats) instead of fp16.
+template <int RPW, bool F32>
 __global__ void __launch_bounds__(256, RPW > 1 ? 4 : 1) layernorm_kernel(const float* __restrict__ x, int64_t ldx,
                                                        RowMap xmap, const float* __restrict__ gamma,
                                                        const float* __restrict__ beta, float eps,
@@ -67,10 +68,16 @@ __global__ void __launch_bounds__(256, RPW > 1 ? 4 : 1) layernorm_kernel(const f
 #pragma unroll
         for (int r = 0; r < RPW; ++r)
           if (row0 + r < rows) {
-            uint2 o;
-            o.x = pack_half2((v[r][i].x - mean[r]) * rstd[r] * g.x + b.x, (v[r][i].y - mean[r]) * rstd[r] * g.y + b.y);
-            o.y = pack_half2((v[r][i].z - mean[r]) * rstd[r] * g.z + b.z, (v[r][i].w - mean[r]) * rstd[r] * g.w + b.w);
-            reinterpret_cast<uint2*>(y + (row0 + r) * ldy)[c] = o;
+            const float o0 = (v[r][i].x - mean[r]) * rstd[r] * g.x + b.x, o1 = (v[r][i].y - mean[r]) * rstd[r] * g.y + b.y;
+            const float o2 = (v[r][i].z - mean[r]) * rstd[r] * g.z + b.z, o3 = (v[r][i].w - mean[r]) * rstd[r] * g.w + b.w;
+            if (F32) {
+              reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + (row0 + r) * ldy)[c] = make_float4(o0, o1, o2, o3);
+            } else {
+              uint2 o;
+              o.x = pack_half2(o0, o1);
+              o.y = pack_half2(o2, o3);
+              reinterpret_cast<uint2*>(y + (row0 + r) * ldy)[c] = o;
+            }
           }
       }
     }
@@ -78,8 +85,28 @@ __global__ void __launch_bounds__(256, RPW > 1 ? 4 : 1) layernorm_kernel(const f
 }
 }  // namespace
 
+namespace {
+template <bool F32>
+int launch_layernorm(const float* x, int64_t ldx, RowMap xmap, const float* gamma, const float* beta,
+                     float eps, int64_t rows, int d, __half* y, int64_t ldy, cudaStream_t stream);
+}
 int layernorm_rows(const float* x, int64_t ldx, RowMap xmap, const float* gamma, const float* beta,
                    float eps, int64_t rows, int d, __half* y, int64_t ldy, cudaStream_t stream) {
+  return launch_layernorm<false>(x, ldx, xmap, gamma, beta, eps, rows, d, y, ldy, stream);
+}
+// fp32 rows out (may be in place: every row is read completely before it is written)
+int layernorm_rows_f32(const float* x, int64_t ldx, const float* gamma, const float* beta, float eps,
+                       int64_t rows, int d, float* y, int64_t ldy, cudaStream_t stream) {
+  if ((reinterpret_cast<uintptr_t>(y) & 15) || (ldy % 4)) {
+    set_error("layernorm: fp32 output rows must be 16-byte aligned");
+    return BSRL_ERR_ALIGN;
+  }
+  return launch_layernorm<true>(x, ldx, identity_map(), gamma, beta, eps, rows, d, reinterpret_cast<__half*>(y), ldy, stream);
+}
+namespace {
+template <bool F32>
+int launch_layernorm(const float* x, int64_t ldx, RowMap xmap, const float* gamma, const float* beta,
+                     float eps, int64_t rows, int d, __half* y, int64_t ldy, cudaStream_t stream) {
   if (!x || !gamma || !beta || !y) {
     set_error("layernorm: NULL operand");
     return BSRL_ERR_NULL;
@@ -98,16 +125,17 @@ int layernorm_rows(const float* x, int64_t ldx, RowMap xmap, const float* gamma,
   if (d <= 256 && rows >= cap * 8 * 4) {            // long, narrow inputs: four rows in flight per warp
     int64_t blocks = (rows + 31) / 32;
     if (blocks > cap) blocks = cap;
-    layernorm_kernel<4><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, ldx, xmap, gamma, beta, eps,
+    layernorm_kernel<4, F32><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, ldx, xmap, gamma, beta, eps,
                                                                           rows, d, y, ldy);
   } else {
     int64_t blocks = (rows + 7) / 8;
     if (blocks > cap) blocks = cap;
-    layernorm_kernel<1><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, ldx, xmap, gamma, beta, eps,
+    layernorm_kernel<1, F32><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, ldx, xmap, gamma, beta, eps,
                                                                           rows, d, y, ldy);
   }
   BSRL_LAUNCH_OK("layernorm_kernel");
   return BSRL_OK;
 }
+}  // namespace
 
 }  // namespace bsrl

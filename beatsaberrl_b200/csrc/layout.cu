@@ -91,6 +91,10 @@ int validate_config(const bsrl_config* c) {
     set_error("config: z_asinh must be > 0 (metres), got %g", c->z_asinh);
     return BSRL_ERR_SHAPE;
   }
+  if ((c->emb_ln | c->final_ln | c->game_flux) & ~1) {
+    set_error("config: emb_ln / final_ln / game_flux must be 0 or 1");
+    return BSRL_ERR_SHAPE;
+  }
   if (!(c->value_vmax > 0.f) || !(c->eps > 0.f)) {
     set_error("config: value_vmax and eps must be > 0");
     return BSRL_ERR_SHAPE;
@@ -177,6 +181,8 @@ Layout make_layout(const bsrl_config& c) {
   l.trunk_ln2 = carve_norm(cv, l.D);
   l.heads = carve_mat(cv, l.n_head_cols, l.D, 0, l.head_cols_pad);
   l.critic_ln = carve_norm(cv, d);
+  if (c.emb_ln) l.emb_ln = carve_norm(cv, d);
+  if (c.final_ln) l.final_ln = carve_norm(cv, d);
   l.critic_q = carve_mat(cv, d, d);
   l.critic_kv = carve_mat(cv, 2 * d, d);
   l.critic_out = carve_mat(cv, d, d);
@@ -234,6 +240,8 @@ std::vector<ParamSlot> make_param_slots(const bsrl_config& c, const Layout& l) {
   for (int j = 0; j < kActHeads; ++j)
     lin("heads." + std::to_string(j), l.heads, c.head_gears[j], l.D, l.head_first[j]);
   norm("critic_ln", l.critic_ln);
+  if (c.emb_ln) norm("emb_ln", l.emb_ln);
+  if (c.final_ln) norm("final_ln", l.final_ln);
   lin("critic_q", l.critic_q, d, d, 0);
   lin("critic_k", l.critic_kv, d, d, 0);
   lin("critic_v", l.critic_kv, d, d, d);

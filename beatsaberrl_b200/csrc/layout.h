@@ -37,6 +37,7 @@ struct Layout {
   std::vector<BlockW> blocks;
   Mat trunk_proj, trunk_fc1, trunk_fc2, heads;
   Norm trunk_ln1, trunk_ln2, critic_ln;
+  Norm emb_ln, final_ln;   // optional (width 0 when the option is off)
   Mat critic_q, critic_kv, critic_out, critic_m0, critic_m1, critic_m2;
   Mat critic_qkv_g;   // critic q|k|v regrouped like BlockW::qkv_g
   int attn_G = 0;     // heads per group of the fused QKV+attention kernel; 0 = shape not supported

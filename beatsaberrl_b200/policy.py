@@ -101,9 +101,8 @@ class NotePolicy(nn.Module):
         assert n_gears in (3, 5, 7), f"n_gears must be 3/5/7, got {n_gears}"
         assert value_bins > 1, f"value_bins must be > 1, got {value_bins}"
         # options of the reference that change the forward and are not built here
-        for flag, name in ((emb_ln, "emb_ln"), (value_residual, "value_residual"),
-                           (final_ln, "final_ln"), (trunk_arch != "simba", "trunk_arch='simbav2'"),
-                           (game != "standard", "game='flux'"),
+        for flag, name in ((value_residual, "value_residual"),
+                           (trunk_arch != "simba", "trunk_arch='simbav2'"),
                            (fp16_accum != "off", "fp16_accum (accumulation is always fp32)")):
             if flag:
                 raise NotImplementedError(f"NotePolicy option {name} is not built in this library")
@@ -124,7 +123,7 @@ class NotePolicy(nn.Module):
                      "trunk_hidden": H, "value_bins": int(value_bins),
                      "value_vmax": float(value_vmax), "value_sigma": float(value_sigma),
                      "game": game, "fp16_accum": fp16_accum, "fused_ffn": fused_ffn,
-                     "emb_ln": False, "value_residual": False, "final_ln": False}
+                     "emb_ln": bool(emb_ln), "value_residual": False, "final_ln": bool(final_ln)}
         if head_gears != (n_gears,) * N_ACTION_HEADS:
             self.arch["head_gears"] = list(head_gears)
         self.value_bins = int(value_bins)
@@ -139,7 +138,9 @@ class NotePolicy(nn.Module):
         self.saber_mlp = _mlp([SABER_FEAT + 2, embed, embed])
         self.torso_mlp = _mlp([TORSO_FEAT, embed, embed])
         self.leg_mlp = _mlp([LEG_FEAT + 2, embed, embed])
+        self.emb_ln = nn.LayerNorm(embed) if emb_ln else None          # --emb-ln (python/policy.py:962)
         self.blocks = nn.ModuleList(_Block(embed, ffn_mult) for _ in range(n_blocks))
+        self.final_ln = nn.LayerNorm(embed) if final_ln else None      # --final-ln (python/policy.py:969)
         self.trunk_arch = trunk_arch
         self.trunk_proj = nn.Linear(self.n_lead * embed, trunk_dim)
         self.trunk_ln1 = nn.LayerNorm(trunk_dim)
@@ -165,7 +166,8 @@ class NotePolicy(nn.Module):
         self.keep_value_logits = False   # set True to have forwards fill _value_logits
         self._cfg = nat.make_config(embed, n_heads, n_blocks, ffn_mult, trunk_dim, H, self.value_bins,
                                     note_geo, head_gears, float(z_asinh), float(value_vmax),
-                                    float(self.blocks[0].ln_attn.eps))
+                                    float(self.blocks[0].ln_attn.eps), emb_ln=emb_ln, final_ln=final_ln,
+                                    game_flux=(game == "flux"))
         nat.check(nat.lib.bsrl_config_validate(C.byref(self._cfg)))
         self._param_table = nat.param_table(self._cfg)
         self._arena = None

@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define BSRL_ABI_VERSION 1
+#define BSRL_ABI_VERSION 2
 #define BSRL_OBS_DIM 630
 #define BSRL_N_TOKENS 29
 #define BSRL_N_LEAD 5
@@ -62,6 +62,10 @@ typedef struct bsrl_config {
   float z_asinh;         /* obs z encoding constant (metres) */
   float value_vmax;      /* bin centres = linspace(-vmax, vmax, bins) */
   float eps;             /* LayerNorm epsilon */
+  /* A/B options of the reference constructor, all 0 by default (python/policy.py:804-805): */
+  int32_t emb_ln;        /* 1 = LayerNorm on the token embeddings (--emb-ln, :1261-1262) */
+  int32_t final_ln;      /* 1 = LayerNorm on the lead rows leaving the last block (--final-ln, :1306-1307) */
+  int32_t game_flux;     /* 1 = the Flux game's note-geo variant: bar slots aim at lanes 12, 13 (:357-360) */
 } bsrl_config;
 
 /* --- library -------------------------------------------------------------------- */

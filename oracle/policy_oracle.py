@@ -129,6 +129,9 @@ class PolicyConfig:
     z_asinh: float = 8.0
     head_gears: tuple | None = None
     eps: float = 1e-5
+    emb_ln: bool = False        # LayerNorm on the token embeddings (python/policy.py:962, :1261-1262)
+    final_ln: bool = False      # LayerNorm on the lead rows leaving the last block (:969, :1306-1307)
+    game: str = "standard"      # "flux": bar slots aim the geometry lanes at lanes 12, 13 (:357-360)
 
     def __post_init__(self):
         if self.head_gears is None:
@@ -154,7 +157,8 @@ class PolicyConfig:
                     n_heads=self.n_heads, n_gears=self.n_gears, ffn_mult=self.ffn_mult,
                     note_geo=self.note_geo, value_bins=self.value_bins,
                     value_vmax=self.value_vmax, trunk_hidden=self.trunk_hidden,
-                    z_asinh=self.z_asinh, head_gears=self.head_gears)
+                    z_asinh=self.z_asinh, head_gears=self.head_gears, emb_ln=self.emb_ln,
+                    final_ln=self.final_ln, game=self.game)
 
 
 # the five benchmark configurations in reference-drop-in form (T = 29, n_lead = 5)
@@ -207,12 +211,16 @@ def linear_specs(cfg: PolicyConfig):
 
 
 def layernorm_specs(cfg: PolicyConfig):
-    """(prefix, width) of every LayerNorm of the default architecture."""
+    """(prefix, width) of every LayerNorm (their init draws no random numbers, so the order is free)."""
     out = []
     for i in range(cfg.n_blocks):
         out += [(f"blocks.{i}.ln_attn", cfg.embed), (f"blocks.{i}.ln_ffn", cfg.embed)]
     out += [("trunk_ln1", cfg.trunk_dim), ("trunk_ln2", cfg.trunk_dim),
             ("critic_ln", cfg.embed)]
+    if cfg.emb_ln:
+        out.append(("emb_ln", cfg.embed))
+    if cfg.final_ln:
+        out.append(("final_ln", cfg.embed))
     return out
 
 
@@ -290,14 +298,19 @@ def _mlp2(sd, name, x):
     return _lin(sd, name + ".2", F.relu(_lin(sd, name + ".0", x)))
 
 
-def note_geo(notes, sabers, z_asinh: float, z_off):
+def note_geo(notes, sabers, z_asinh: float, z_off, flux: bool = False):
     """22 derived lanes per (env, slot): per hand [dx/2, dy/2, asinh(dz/8), asinh(|dp|/8),
     t_plane/3, vhat.cut, blade.cut] then per hand [along, perp, cut-plane distance,
-    v_tip.cut] (python/policy.py:329-404, standard game).  notes (B,24,18), sabers
+    v_tip.cut] (python/policy.py:329-404; ``flux`` = the Flux game's variant).  notes (B,24,18), sabers
     (B,2,47), z_off (B,) -> (B,24,22), all fp32."""
     XN, YN, ZS, VN, HANDLE = 1.0, 0.75, 8.0, 6.0, 0.16
     z_m = torch.sinh(notes[..., 2]) * float(z_asinh)
-    npos = torch.stack([notes[..., 0] * XN, notes[..., 1] * YN, z_m], -1)
+    tx, ty = notes[..., 0], notes[..., 1]
+    if flux:   # a bar slot is aimed at where it must be crossed (python/policy.py:357-360)
+        is_bar = notes[..., 9] > 0.5
+        tx = torch.where(is_bar, notes[..., 12], tx)
+        ty = torch.where(is_bar, notes[..., 13], ty)
+    npos = torch.stack([tx * XN, ty * YN, z_m], -1)
     cut = torch.stack([notes[..., 6], notes[..., 7], torch.zeros_like(z_m)], -1)
     live = 1.0 - notes[..., 14:15]
     speed = (-notes[..., 3:4] * ZS).clamp_min(1e-3)
@@ -338,7 +351,7 @@ def token_features(cfg: PolicyConfig, obs):
     legs = torch.stack([obs[:, token_lanes("leg_l")], obs[:, token_lanes("leg_r")]], 1)
     notes = obs[:, OFF_NOTES:OFF_MASK].reshape(B, N_SLOTS, NOTE_FEAT)
     if cfg.note_geo:
-        notes = torch.cat([notes, note_geo(notes, sab, cfg.z_asinh, obs[:, OBS_HEAD_Z])], -1)
+        notes = torch.cat([notes, note_geo(notes, sab, cfg.z_asinh, obs[:, OBS_HEAD_Z], cfg.game == "flux")], -1)
     return dict(saber=torch.cat([sab, eye], -1), torso=obs[:, token_lanes("torso")],
                 leg=torch.cat([legs, eye], -1), note=notes,
                 mask=obs[:, OFF_MASK:OFF_MASK + N_SLOTS])
@@ -429,11 +442,15 @@ def forward_stacked(sd, cfg: PolicyConfig, obs, want: bool = False):
     B = obs.shape[0]
     keep = {}
     x, bias = embed_tokens(sd, cfg, obs)
+    if cfg.emb_ln:
+        x = _ln(sd, "emb_ln", x, cfg.eps)
     keep["tokens"], keep["key_bias"] = x, bias
     for i in range(cfg.n_blocks - 1):
         x = block_forward(sd, cfg, i, x, bias)
         keep[f"x{i + 1}"] = x
     lead = block_forward(sd, cfg, cfg.n_blocks - 1, x, bias, n_queries=N_LEAD)
+    if cfg.final_ln:
+        lead = _ln(sd, "final_ln", lead, cfg.eps)
     keep["lead"] = lead
     h = trunk(sd, cfg, lead.reshape(B, -1))
     keep["trunk"] = h

@@ -23,17 +23,22 @@ sys.path.insert(0, str(ROOT))
 from oracle import policy_oracle as po  # noqa: E402
 
 CASES = [
-    # name, config, note_geo, head_gears, xavier, weight seed, ln_jitter, B, padded, obs seed
-    ("tiny_plain", "tiny", False, None, False, 11, 0.0, 16, True, 21),
-    ("tiny_geo_mixed", "tiny", True, (5,) * 8 + (7,) + (5,) * 6 + (7,) + (5,) * 13, True, 12, 0.1, 16, True, 22),
-    ("cfg1", "cfg1", False, None, False, 0, 0.0, 8, False, 0),
+    # name, config, note_geo, head_gears, xavier, weight seed, ln_jitter, B, padded, obs seed, options
+    ("tiny_plain", "tiny", False, None, False, 11, 0.0, 16, True, 21, {}),
+    ("tiny_geo_mixed", "tiny", True, (5,) * 8 + (7,) + (5,) * 6 + (7,) + (5,) * 13, True, 12, 0.1, 16, True, 22, {}),
+    ("cfg1", "cfg1", False, None, False, 0, 0.0, 8, False, 0, {}),
+    # the A/B options that change the forward: --emb-ln, --final-ln, --game flux (note-geo variant)
+    ("tiny_options", "tiny", True, None, False, 13, 0.1, 16, True, 23,
+     dict(emb_ln=True, final_ln=True, game="flux")),
 ]
 
 
-def case_config(cfg_name, geo, hg):
+def case_config(cfg_name, geo, hg, opts=None):
     cfg = po.named_config(cfg_name)
     cfg.note_geo = geo
     cfg.head_gears = hg
+    for k, v in (opts or {}).items():
+        setattr(cfg, k, v)
     cfg.__post_init__()
     return cfg
 
@@ -45,8 +50,8 @@ def main():
     import policy as rp  # the reference module
 
     out = {}
-    for name, cfg_name, geo, hg, xav, seed, jit, B, padded, oseed in CASES:
-        cfg = case_config(cfg_name, geo, hg)
+    for name, cfg_name, geo, hg, xav, seed, jit, B, padded, oseed, opts in CASES:
+        cfg = case_config(cfg_name, geo, hg, opts)
         torch.manual_seed(seed)
         m = rp.NotePolicy(**cfg.ref_kwargs()).eval()
         if xav:

@@ -14,20 +14,24 @@ GOLDEN_CASES = {
     "tiny_geo_mixed": dict(cfg="tiny", geo=True, hg=(5,) * 8 + (7,) + (5,) * 6 + (7,) + (5,) * 13,
                            xavier=True, seed=12, jitter=0.1),
     "cfg1": dict(cfg="cfg1", geo=False, hg=None, xavier=False, seed=0, jitter=0.0),
+    "tiny_options": dict(cfg="tiny", geo=True, hg=None, xavier=False, seed=13, jitter=0.1,
+                         opts=dict(emb_ln=True, final_ln=True, game="flux")),
 }
 
 
-def make_cfg(name, geo=False, hg=None):
+def make_cfg(name, geo=False, hg=None, opts=None):
     cfg = po.named_config(name)
     cfg.note_geo = geo
     cfg.head_gears = hg
+    for k, v in (opts or {}).items():
+        setattr(cfg, k, v)
     cfg.__post_init__()
     return cfg
 
 
 def golden_case(name):
     c = GOLDEN_CASES[name]
-    cfg = make_cfg(c["cfg"], c["geo"], c["hg"])
+    cfg = make_cfg(c["cfg"], c["geo"], c["hg"], c.get("opts"))
     sd = po.build_state_dict(cfg, c["seed"], xavier=c["xavier"], ln_jitter=c["jitter"])
     return cfg, sd
 

@@ -20,7 +20,7 @@ def test_every_declared_symbol_is_exported(native):
     assert len(names) >= 15
     for n in names:
         assert hasattr(native.lib, n), n
-    assert native.lib.bsrl_abi_version() == 1
+    assert native.lib.bsrl_abi_version() == 2
 
 
 def test_token_lanes_match_oracle(native):
@@ -113,7 +113,7 @@ def test_policy_facade_host_side(native):
     with pytest.raises(RuntimeError):   # no CPU path
         m.forward_stacked(torch.zeros(2, 630))
     with pytest.raises(NotImplementedError):
-        NotePolicy(emb_ln=True)
+        NotePolicy(value_residual=True)
     with pytest.raises(ValueError):
         NotePolicy(trunk_arch="mlp")
     with pytest.raises(ValueError):
