@@ -239,15 +239,28 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   const bool fused_qkv = g_engine == 0 && l.attn_G > 0 && attn_block_ok(attn_args(h, l.blocks[0].qkv_g, 0, kT, att));
   __half* hv = at<__half>(c.ws, w.enc_hid);   // critic LayerNorm rows (encoder scratch is free by now)
   bool have_h = false, have_hv = false;
+  // value residual (python/policy.py:1263-1275): block 0 hands its attention values to every later block
+  __half* v0buf = l.value_residual ? at<__half>(c.ws, w.v0) : nullptr;
+  auto vres_fused = [&](AttnBlockArgs a, int i) {
+    if (v0buf && i == 0) a.v_out = v0buf;
+    if (v0buf && i > 0) { a.v0 = v0buf; a.vres = at<float>(c.arena, l.blocks[i].vres); }
+    return a;
+  };
+  auto vres_unfused = [&](int i) -> int {     // on the packed q|k|v buffer, between projection and attention
+    if (!v0buf) return BSRL_OK;
+    return vres_mix(qkv + 2 * d, 3 * d, R, d, i == 0 ? v0buf : nullptr, i > 0 ? v0buf : nullptr,
+                    i > 0 ? at<float>(c.arena, l.blocks[i].vres) : nullptr, c.st);
+  };
 
   for (int i = 0; i + 1 < l.L; ++i) {
     const BlockW& b = l.blocks[i];
     if (!have_h) BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
     if (fused_qkv) {
-      BSRL_TRY(fused_attn(attn_args(h, b.qkv_g, 0, kT, att), c.st));
+      BSRL_TRY(fused_attn(vres_fused(attn_args(h, b.qkv_g, 0, kT, att), i), c.st));
     } else {
       g_stage = kStQkv;
       BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, R, 3 * d, d), c.st));
+      BSRL_TRY(vres_unfused(i));
       BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 0, kT, att, d, c.st));
     }
     if (fused) {
@@ -286,7 +299,7 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     if (fused_qkv) {
       // q is projected for all 29 rows (a third of this kernel's MMAs, no extra HBM traffic);
       // only the 5 lead rows are attended and written
-      BSRL_TRY(fused_attn(attn_args(h, b.qkv_g, 0, kLead, att), c.st));
+      BSRL_TRY(fused_attn(vres_fused(attn_args(h, b.qkv_g, 0, kLead, att), l.L - 1), c.st));
     } else {
       g_stage = kStQkv;
       BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv, d), d, c.Bv(b.qkv, d), qkv + d, 3 * d, 0, 0, R, 2 * d, d), c.st));
@@ -294,6 +307,7 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
       pq.amap = lead_rows;
       pq.cmap = lead_rows;
       BSRL_TRY(linear(pq, c.st));
+      BSRL_TRY(vres_unfused(l.L - 1));
       BSRL_TRY(attention(qkv, 3 * d, key_bias, B, d, l.H, 0, kLead, att, d, c.st));
     }
     if (fused) {

@@ -200,4 +200,54 @@ int attention29(const __half* qkv, int ld_qkv, const float* key_bias, int64_t n_
   return BSRL_ERR_UNSUPPORTED;
 }
 
+// Value residual on the unfused path (python/policy.py:604-615, _VMix): the v columns of the packed
+// projection are copied out as the block's own values (v_out) and / or replaced by
+// vres[0] * v + vres[1] * v0 (fp32 arithmetic, rounded once).  8 columns per thread.
+namespace {
+__global__ void vres_mix_kernel(__half* __restrict__ v, int ld, int64_t rows, int d,
+                                __half* __restrict__ v_out, const __half* __restrict__ v0,
+                                const float* __restrict__ vres) {
+  const float a = vres ? vres[0] : 1.f, b = vres ? vres[1] : 0.f;
+  const int per_row = d >> 3;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * per_row;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / per_row;
+    const int c = (int)(i % per_row) * 8;
+    uint4 w = *reinterpret_cast<const uint4*>(v + row * ld + c);
+    if (v_out) *reinterpret_cast<uint4*>(v_out + row * d + c) = w;
+    if (v0) {
+      const uint4 o = *reinterpret_cast<const uint4*>(v0 + row * d + c);
+      uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+      const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&ww[e]));
+        const float2 y = __half22float2(*reinterpret_cast<const __half2*>(&ow[e]));
+        ww[e] = pack_half2(fmaf(a, x.x, b * y.x), fmaf(a, x.y, b * y.y));
+      }
+      *reinterpret_cast<uint4*>(v + row * ld + c) = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+    }
+  }
+}
+}  // namespace
+
+int vres_mix(__half* v, int ld, int64_t rows, int d, __half* v_out, const __half* v0, const float* vres,
+             cudaStream_t stream) {
+  if (!v || (v0 && !vres)) {
+    set_error("vres_mix: NULL operand");
+    return BSRL_ERR_NULL;
+  }
+  if (!aligned16(v) || (ld % 8) || (d % 8) || (v_out && !aligned16(v_out)) || (v0 && !aligned16(v0))) {
+    set_error("vres_mix: buffers must be 16-byte aligned");
+    return BSRL_ERR_ALIGN;
+  }
+  if (rows == 0 || (!v_out && !v0)) return BSRL_OK;
+  int64_t blocks = (rows * (d >> 3) + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  vres_mix_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(v, ld, rows, d, v_out, v0, vres);
+  BSRL_LAUNCH_OK("vres_mix_kernel");
+  return BSRL_OK;
+}
+
 }  // namespace bsrl

@@ -60,6 +60,9 @@ struct Params {
   const float* key_bias;   // (n_envs, 29)
   __half* out;             // (n_envs * n_q, ldo)
   int ldo;
+  __half* v_out;           // value residual: own values out / block 0's values in + the two mix scalars
+  const __half* v0;
+  const float* vres;
   int* status;
 };
 
@@ -213,7 +216,8 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
     }
 }
 
-template <int DH, int G>
+// VRES: the value-residual code of the drain is compiled in (it costs ~14 % of the kernel even when idle)
+template <int DH, int G, bool VRES>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_w, Params p) {
   using S = Shape<DH, G>;
@@ -352,6 +356,7 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
     const int env_l = wi >> 1, hh = G == 2 ? (wi & 1) : 0, mt_own = G == 2 ? 0 : (wi & 1);
     uint32_t gi = 0;
     bool ok = true;
+    const float vres_a = (VRES && p.vres) ? p.vres[0] : 1.f, vres_b = (VRES && p.vres) ? p.vres[1] : 0.f;
     TRACE_INIT(lane == 0 ? wi + 1 : -1);
     for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
       const int64_t env = (int64_t)t * EPT + env_l;
@@ -380,14 +385,33 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
           // 16 columns -> bias, fp16, two 16-byte pieces of this thread's row
           auto put16 = [&](const uint32_t* v, int u) {
             const float4* b4 = reinterpret_cast<const float4*>(bias_u + u * 16);
+            // value residual (python/policy.py:604-615): the group's v columns are written out as
+            // this block's own values and / or mixed with block 0's before the attention reads them
+            const int vcol = (u_first + u) * 16 - 2 * GD;           // column inside the group's v section
+            const bool vres_rows = VRES && vcol >= 0 && trow < ROWS && (int64_t)t * EPT + trow / kT < p.n_envs;
+            const int64_t goff = ((int64_t)t * ROWS + trow) * d + g * GD + vcol;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
               const float4 b0 = b4[2 * j], b1 = b4[2 * j + 1];
-              *reinterpret_cast<uint4*>(dst_u + u * 32 + 16 * j) = make_uint4(
-                  pack_half2(__uint_as_float(v[8 * j]) + b0.x, __uint_as_float(v[8 * j + 1]) + b0.y),
-                  pack_half2(__uint_as_float(v[8 * j + 2]) + b0.z, __uint_as_float(v[8 * j + 3]) + b0.w),
-                  pack_half2(__uint_as_float(v[8 * j + 4]) + b1.x, __uint_as_float(v[8 * j + 5]) + b1.y),
-                  pack_half2(__uint_as_float(v[8 * j + 6]) + b1.z, __uint_as_float(v[8 * j + 7]) + b1.w));
+              float f[8] = {__uint_as_float(v[8 * j]) + b0.x,     __uint_as_float(v[8 * j + 1]) + b0.y,
+                            __uint_as_float(v[8 * j + 2]) + b0.z, __uint_as_float(v[8 * j + 3]) + b0.w,
+                            __uint_as_float(v[8 * j + 4]) + b1.x, __uint_as_float(v[8 * j + 5]) + b1.y,
+                            __uint_as_float(v[8 * j + 6]) + b1.z, __uint_as_float(v[8 * j + 7]) + b1.w};
+              if (VRES && vres_rows && p.v_out)
+                *reinterpret_cast<uint4*>(p.v_out + goff + 8 * j) =
+                    make_uint4(pack_half2(f[0], f[1]), pack_half2(f[2], f[3]), pack_half2(f[4], f[5]), pack_half2(f[6], f[7]));
+              if (VRES && vres_rows && p.v0) {
+                const uint4 o = *reinterpret_cast<const uint4*>(p.v0 + goff + 8 * j);
+                const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 ov = __half22float2(*reinterpret_cast<const __half2*>(&ow[e]));
+                  f[2 * e] = fmaf(vres_a, f[2 * e], vres_b * ov.x);
+                  f[2 * e + 1] = fmaf(vres_a, f[2 * e + 1], vres_b * ov.y);
+                }
+              }
+              *reinterpret_cast<uint4*>(dst_u + u * 32 + 16 * j) =
+                  make_uint4(pack_half2(f[0], f[1]), pack_half2(f[2], f[3]), pack_half2(f[4], f[5]), pack_half2(f[6], f[7]));
             }
           };
           int u = 0;
@@ -473,8 +497,10 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
   int dev = 0;
   BSRL_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 64 && !attr_set[dev]) {
-    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel<32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<32, 2>::SMEM_BYTES));
-    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel<48, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<48, 1>::SMEM_BYTES));
+    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel<32, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<32, 2>::SMEM_BYTES));
+    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel<32, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<32, 2>::SMEM_BYTES));
+    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel<48, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<48, 1>::SMEM_BYTES));
+    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel<48, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<48, 1>::SMEM_BYTES));
     attr_set[dev] = true;
   }
   Params p;
@@ -482,10 +508,14 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
   p.n_envs = a.n_envs;
   p.n_tiles = (int)((a.n_envs + EPT - 1) / EPT);
   p.bias = a.bg; p.key_bias = a.key_bias; p.out = a.out; p.ldo = a.ldo;
+  p.v_out = a.v_out; p.v0 = a.v0; p.vres = a.vres;
   p.status = status;
   const int grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
-  if (dh == 32) attn_block_kernel<32, 2><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, p);
-  else attn_block_kernel<48, 1><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, p);
+  const bool vres = a.v_out || a.v0;
+  if (dh == 32 && !vres) attn_block_kernel<32, 2, false><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, p);
+  else if (dh == 32) attn_block_kernel<32, 2, true><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, p);
+  else if (!vres) attn_block_kernel<48, 1, false><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, p);
+  else attn_block_kernel<48, 1, true><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, p);
   BSRL_LAUNCH_OK("attn_block_kernel");
   return BSRL_OK;
 }

@@ -70,7 +70,15 @@ struct AttnBlockArgs {
   int q_first, n_q;      // query rows of each env
   __half* out;           // (n_envs*n_q, ldo)
   int ldo;
+  // value residual (all optional): the block's own values written to v_out (n_envs*29, d) f16; values
+  // replaced by vres[0] * v + vres[1] * v0 before the attention (v0 (n_envs*29, d) f16, vres 2 device floats)
+  __half* v_out = nullptr;
+  const __half* v0 = nullptr;
+  const float* vres = nullptr;
 };
+// v columns of a packed projection: copy out (v_out) and / or mix with v0 in place (value residual)
+int vres_mix(__half* v, int ld, int64_t rows, int d, __half* v_out, const __half* v0, const float* vres,
+             cudaStream_t stream);
 bool attn_block_ok(const AttnBlockArgs& a);
 int attn_block(const AttnBlockArgs& a, cudaStream_t stream);
 

@@ -91,8 +91,8 @@ int validate_config(const bsrl_config* c) {
     set_error("config: z_asinh must be > 0 (metres), got %g", c->z_asinh);
     return BSRL_ERR_SHAPE;
   }
-  if ((c->emb_ln | c->final_ln | c->game_flux) & ~1) {
-    set_error("config: emb_ln / final_ln / game_flux must be 0 or 1");
+  if ((c->emb_ln | c->final_ln | c->game_flux | c->value_residual) & ~1) {
+    set_error("config: emb_ln / final_ln / game_flux / value_residual must be 0 or 1");
     return BSRL_ERR_SHAPE;
   }
   if (!(c->value_vmax > 0.f) || !(c->eps > 0.f)) {
@@ -173,7 +173,9 @@ Layout make_layout(const bsrl_config& c) {
     b.up = carve_mat(cv, l.F, d);
     b.down = carve_mat(cv, d, l.F);
     b.qkv_g = carve_mat(cv, 3 * d, d);
+    if (c.value_residual && i > 0) b.vres = cv.take(8);
   }
+  l.value_residual = c.value_residual;
   l.trunk_proj = carve_mat(cv, l.D, kLead * d);
   l.trunk_ln1 = carve_norm(cv, l.D);
   l.trunk_fc1 = carve_mat(cv, l.Hh, l.D);
@@ -229,6 +231,10 @@ std::vector<ParamSlot> make_param_slots(const bsrl_config& c, const Layout& l) {
     lin(p + ".v_proj", b.qkv, d, d, 2 * d);
     lin(p + ".out_proj", b.out, d, d, 0);
     norm(p + ".ln_ffn", b.ln_ffn);
+    if (b.vres >= 0) {
+      s.push_back({p + ".vres_a", 1, 1, b.vres, 0, false});
+      s.push_back({p + ".vres_b", 1, 1, b.vres + 4, 0, false});
+    }
     lin(p + ".ffn.0", b.up, l.F, d, 0);
     lin(p + ".ffn.2", b.down, d, l.F, 0);
   }
@@ -311,6 +317,7 @@ Workspace make_workspace(const Layout& l, int64_t B) {
   w.raw = cv.take(B * l.head_cols_pad * 4);
   w.vraw = cv.take(B * l.bins_pad * 4);
   w.att_c = cv.take(B * d * 2);
+  w.v0 = cv.take(l.value_residual ? R * d * 2 : 0);
   w.bytes = cv.off;
   return w;
 }

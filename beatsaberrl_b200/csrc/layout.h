@@ -26,6 +26,7 @@ struct BlockW {
   Norm ln_attn, ln_ffn;
   Mat qkv, out, up, down;
   Mat qkv_g;   // q|k|v rows regrouped per head group for the fused attention kernel (see attn_G)
+  int64_t vres = -1;   // value residual: fp32 {vres_a, vres_b} of this block (blocks after the first), or -1
 };
 struct Encoder {
   Mat l0, l1;
@@ -41,6 +42,7 @@ struct Layout {
   Mat critic_q, critic_kv, critic_out, critic_m0, critic_m1, critic_m2;
   Mat critic_qkv_g;   // critic q|k|v regrouped like BlockW::qkv_g
   int attn_G = 0;     // heads per group of the fused QKV+attention kernel; 0 = shape not supported
+  int value_residual = 0;
   int head_first[kActHeads];
   int64_t bytes = 0;
 };
@@ -71,6 +73,7 @@ std::vector<CopySlot> make_copy_slots(const bsrl_config& c, const Layout& l, con
 struct Workspace {
   int64_t key_bias, f_saber, f_torso, f_leg, f_note, enc_hid, x, h, qkv, att, hid;
   int64_t x_lead, h_lead, lead16, xt, u, r, z, m1, m2, raw, vraw, att_c;
+  int64_t v0;   // block 0's attention values (B*29, d) fp16 (value residual only)
   int64_t bytes;
 };
 Workspace make_workspace(const Layout& l, int64_t n_envs);

@@ -64,7 +64,7 @@ def _mlp(sizes):
 class _Block(nn.Module):
     """Parameter holder of one pre-LN block (names as python/policy.py:498-507)."""
 
-    def __init__(self, d: int, ffn_mult: int):
+    def __init__(self, d: int, ffn_mult: int, value_residual: bool = False):
         super().__init__()
         self.ln_attn = nn.LayerNorm(d)
         self.q_proj = nn.Linear(d, d)
@@ -73,6 +73,9 @@ class _Block(nn.Module):
         self.out_proj = nn.Linear(d, d)
         self.ln_ffn = nn.LayerNorm(d)
         self.ffn = _mlp([d, ffn_mult * d, d])
+        if value_residual:      # registered last, only when on (python/policy.py:512-520)
+            self.vres_a = nn.Parameter(torch.ones(1))
+            self.vres_b = nn.Parameter(torch.zeros(1))
 
 
 _ACT_DTYPES = {torch.uint8: nat.U8, torch.int32: nat.I32, torch.int64: nat.I64}
@@ -101,8 +104,7 @@ class NotePolicy(nn.Module):
         assert n_gears in (3, 5, 7), f"n_gears must be 3/5/7, got {n_gears}"
         assert value_bins > 1, f"value_bins must be > 1, got {value_bins}"
         # options of the reference that change the forward and are not built here
-        for flag, name in ((value_residual, "value_residual"),
-                           (trunk_arch != "simba", "trunk_arch='simbav2'"),
+        for flag, name in ((trunk_arch != "simba", "trunk_arch='simbav2'"),
                            (fp16_accum != "off", "fp16_accum (accumulation is always fp32)")):
             if flag:
                 raise NotImplementedError(f"NotePolicy option {name} is not built in this library")
@@ -123,7 +125,7 @@ class NotePolicy(nn.Module):
                      "trunk_hidden": H, "value_bins": int(value_bins),
                      "value_vmax": float(value_vmax), "value_sigma": float(value_sigma),
                      "game": game, "fp16_accum": fp16_accum, "fused_ffn": fused_ffn,
-                     "emb_ln": bool(emb_ln), "value_residual": False, "final_ln": bool(final_ln)}
+                     "emb_ln": bool(emb_ln), "value_residual": bool(value_residual), "final_ln": bool(final_ln)}
         if head_gears != (n_gears,) * N_ACTION_HEADS:
             self.arch["head_gears"] = list(head_gears)
         self.value_bins = int(value_bins)
@@ -139,7 +141,8 @@ class NotePolicy(nn.Module):
         self.torso_mlp = _mlp([TORSO_FEAT, embed, embed])
         self.leg_mlp = _mlp([LEG_FEAT + 2, embed, embed])
         self.emb_ln = nn.LayerNorm(embed) if emb_ln else None          # --emb-ln (python/policy.py:962)
-        self.blocks = nn.ModuleList(_Block(embed, ffn_mult) for _ in range(n_blocks))
+        self.value_residual = bool(value_residual)
+        self.blocks = nn.ModuleList(_Block(embed, ffn_mult, self.value_residual and i > 0) for i in range(n_blocks))
         self.final_ln = nn.LayerNorm(embed) if final_ln else None      # --final-ln (python/policy.py:969)
         self.trunk_arch = trunk_arch
         self.trunk_proj = nn.Linear(self.n_lead * embed, trunk_dim)
@@ -167,7 +170,7 @@ class NotePolicy(nn.Module):
         self._cfg = nat.make_config(embed, n_heads, n_blocks, ffn_mult, trunk_dim, H, self.value_bins,
                                     note_geo, head_gears, float(z_asinh), float(value_vmax),
                                     float(self.blocks[0].ln_attn.eps), emb_ln=emb_ln, final_ln=final_ln,
-                                    game_flux=(game == "flux"))
+                                    game_flux=(game == "flux"), value_residual=value_residual)
         nat.check(nat.lib.bsrl_config_validate(C.byref(self._cfg)))
         self._param_table = nat.param_table(self._cfg)
         self._arena = None

@@ -66,6 +66,8 @@ typedef struct bsrl_config {
   int32_t emb_ln;        /* 1 = LayerNorm on the token embeddings (--emb-ln, :1261-1262) */
   int32_t final_ln;      /* 1 = LayerNorm on the lead rows leaving the last block (--final-ln, :1306-1307) */
   int32_t game_flux;     /* 1 = the Flux game's note-geo variant: bar slots aim at lanes 12, 13 (:357-360) */
+  int32_t value_residual; /* 1 = blocks after the first mix block 0's attention values in,
+                           * v <- vres_a v + vres_b v0 (--value-residual, :512-520, :604-615) */
 } bsrl_config;
 
 /* --- library -------------------------------------------------------------------- */

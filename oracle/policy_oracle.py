@@ -132,6 +132,7 @@ class PolicyConfig:
     emb_ln: bool = False        # LayerNorm on the token embeddings (python/policy.py:962, :1261-1262)
     final_ln: bool = False      # LayerNorm on the lead rows leaving the last block (:969, :1306-1307)
     game: str = "standard"      # "flux": bar slots aim the geometry lanes at lanes 12, 13 (:357-360)
+    value_residual: bool = False  # blocks after the first mix block 0's values in: v <- a v + b v0 (:512-520, :611)
 
     def __post_init__(self):
         if self.head_gears is None:
@@ -158,7 +159,7 @@ class PolicyConfig:
                     note_geo=self.note_geo, value_bins=self.value_bins,
                     value_vmax=self.value_vmax, trunk_hidden=self.trunk_hidden,
                     z_asinh=self.z_asinh, head_gears=self.head_gears, emb_ln=self.emb_ln,
-                    final_ln=self.final_ln, game=self.game)
+                    final_ln=self.final_ln, game=self.game, value_residual=self.value_residual)
 
 
 # the five benchmark configurations in reference-drop-in form (T = 29, n_lead = 5)
@@ -246,6 +247,13 @@ def build_state_dict(cfg: PolicyConfig, seed: int, xavier: bool = False,
         sd[prefix + ".weight"] = m.weight.detach().clone()
         sd[prefix + ".bias"] = m.bias.detach().clone()
     g = torch.Generator().manual_seed(seed + 7919)
+    if cfg.value_residual:   # (a, b) = (1, 0) at init; the jitter moves them so tests exercise the mix
+        for i in range(1, cfg.n_blocks):
+            sd[f"blocks.{i}.vres_a"] = torch.ones(1)
+            sd[f"blocks.{i}.vres_b"] = torch.zeros(1)
+            if ln_jitter > 0:
+                sd[f"blocks.{i}.vres_a"] += ln_jitter * torch.randn(1, generator=g)
+                sd[f"blocks.{i}.vres_b"] += 0.3 + ln_jitter * torch.randn(1, generator=g)
     for prefix, w in layernorm_specs(cfg):
         sd[prefix + ".weight"] = torch.ones(w)
         sd[prefix + ".bias"] = torch.zeros(w)
@@ -382,21 +390,26 @@ def attention(q, k, v, bias, n_heads: int):
     return (torch.softmax(s, -1) @ vh).transpose(1, 2).reshape(B, Tq, d)
 
 
-def block_forward(sd, cfg: PolicyConfig, i: int, x, bias, n_queries: int = 0):
+def block_forward(sd, cfg: PolicyConfig, i: int, x, bias, n_queries: int = 0, v0=None, want_v: bool = False):
     """One resolved pre-LN block.  ``x`` is the resolved residual stream entering the
     block (the reference defers the previous FFN's residual add into this block's LN
     pass; in fp32 that is the same sum).  Returns the resolved stream leaving the block,
-    restricted to the first ``n_queries`` rows when > 0."""
+    restricted to the first ``n_queries`` rows when > 0.  ``v0``: block 0's attention values,
+    mixed into this block's (value residual); ``want_v``: also return this block's own values."""
     p = f"blocks.{i}"
     h = _ln(sd, p + ".ln_attn", x, cfg.eps)
     k, v = _lin(sd, p + ".k_proj", h), _lin(sd, p + ".v_proj", h)
+    v_own = v
+    if v0 is not None:
+        v = sd[p + ".vres_a"] * v + sd[p + ".vres_b"] * v0
     if n_queries:
         x, h = x[:, :n_queries], h[:, :n_queries]
     q = _lin(sd, p + ".q_proj", h)
     att = _lin(sd, p + ".out_proj", attention(q, k, v, bias, cfg.n_heads))
     x = x + att
     h2 = _ln(sd, p + ".ln_ffn", x, cfg.eps)
-    return x + _mlp2(sd, p + ".ffn", h2)
+    out = x + _mlp2(sd, p + ".ffn", h2)
+    return (out, v_own) if want_v else out
 
 
 def trunk(sd, cfg: PolicyConfig, lead):
@@ -445,10 +458,14 @@ def forward_stacked(sd, cfg: PolicyConfig, obs, want: bool = False):
     if cfg.emb_ln:
         x = _ln(sd, "emb_ln", x, cfg.eps)
     keep["tokens"], keep["key_bias"] = x, bias
+    v0 = None
     for i in range(cfg.n_blocks - 1):
-        x = block_forward(sd, cfg, i, x, bias)
+        if cfg.value_residual and i == 0:
+            x, v0 = block_forward(sd, cfg, i, x, bias, want_v=True)
+        else:
+            x = block_forward(sd, cfg, i, x, bias, v0=v0)
         keep[f"x{i + 1}"] = x
-    lead = block_forward(sd, cfg, cfg.n_blocks - 1, x, bias, n_queries=N_LEAD)
+    lead = block_forward(sd, cfg, cfg.n_blocks - 1, x, bias, n_queries=N_LEAD, v0=v0)
     if cfg.final_ln:
         lead = _ln(sd, "final_ln", lead, cfg.eps)
     keep["lead"] = lead

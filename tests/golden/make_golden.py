@@ -30,6 +30,8 @@ CASES = [
     # the A/B options that change the forward: --emb-ln, --final-ln, --game flux (note-geo variant)
     ("tiny_options", "tiny", True, None, False, 13, 0.1, 16, True, 23,
      dict(emb_ln=True, final_ln=True, game="flux")),
+    # --value-residual on a 3-block model (blocks 1 and 2 mix block 0's values in; (a, b) moved off (1, 0))
+    ("tiny_vres", "tiny", False, None, False, 14, 0.1, 16, True, 24, dict(value_residual=True, n_blocks=3)),
 ]
 
 

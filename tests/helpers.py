@@ -16,6 +16,8 @@ GOLDEN_CASES = {
     "cfg1": dict(cfg="cfg1", geo=False, hg=None, xavier=False, seed=0, jitter=0.0),
     "tiny_options": dict(cfg="tiny", geo=True, hg=None, xavier=False, seed=13, jitter=0.1,
                          opts=dict(emb_ln=True, final_ln=True, game="flux")),
+    "tiny_vres": dict(cfg="tiny", geo=False, hg=None, xavier=False, seed=14, jitter=0.1,
+                      opts=dict(value_residual=True, n_blocks=3)),
 }
 
 

@@ -113,7 +113,7 @@ def test_policy_facade_host_side(native):
     with pytest.raises(RuntimeError):   # no CPU path
         m.forward_stacked(torch.zeros(2, 630))
     with pytest.raises(NotImplementedError):
-        NotePolicy(value_residual=True)
+        NotePolicy(trunk_arch="simbav2")
     with pytest.raises(ValueError):
         NotePolicy(trunk_arch="mlp")
     with pytest.raises(ValueError):

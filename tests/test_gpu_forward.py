@@ -167,9 +167,9 @@ def test_fused_sampling_distribution_and_determinism():
                                         ("recipe", True, 200),    # fused, head_dim 48
                                         ("cfg4", False, 96)])     # separate GEMM / LayerNorm / attention kernels
 def test_constructor_options(name, geo, B):
-    """--emb-ln, --final-ln and the Flux note-geo variant (python/policy.py:962, :969, :357-360) on
+    """--emb-ln, --final-ln, --value-residual and the Flux note-geo variant (python/policy.py:962, :969, :512-520, :357-360) on
     every kernel path, against the oracle (which the options golden case pins to the reference)."""
-    cfg = make_cfg(name, geo, opts=dict(emb_ln=True, final_ln=True, game="flux"))
+    cfg = make_cfg(name, geo, opts=dict(emb_ln=True, final_ln=True, game="flux", value_residual=True))
     sd = po.build_state_dict(cfg, 17, ln_jitter=0.1)
     m = cuda_policy(cfg, sd)
     obs = po.make_obs(B, 31, padded=True)
@@ -178,7 +178,7 @@ def test_constructor_options(name, geo, B):
     assert_parity(logits, value, ref_l, ref_v, argmax_min=0.995)   # few heads at these batch sizes
     # the options really are in the path: switching them off changes the output
     plain = make_cfg(name, geo)
-    l0, _ = cuda_policy(plain, {k: v for k, v in sd.items() if not k.startswith(("emb_ln", "final_ln"))}).forward_stacked(obs.cuda())
+    l0, _ = cuda_policy(plain, {k: v for k, v in sd.items() if not k.startswith(("emb_ln", "final_ln")) and "vres_" not in k}).forward_stacked(obs.cuda())
     assert (l0 - logits).abs().max() > 1e-2
 
 
