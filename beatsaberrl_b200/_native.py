@@ -31,12 +31,12 @@ class Config(C.Structure):
                 ("head_gears", C.c_int32 * N_ACT_HEADS),
                 ("z_asinh", C.c_float), ("value_vmax", C.c_float), ("eps", C.c_float),
                 ("emb_ln", C.c_int32), ("final_ln", C.c_int32), ("game_flux", C.c_int32),
-                ("value_residual", C.c_int32)]
+                ("value_residual", C.c_int32), ("trunk_v2", C.c_int32)]
 
 
 def make_config(embed, n_heads, n_blocks, ffn_mult, trunk_dim, trunk_hidden, value_bins, note_geo,
                 head_gears, z_asinh=8.0, value_vmax=6.0, eps=1e-5, emb_ln=False, final_ln=False,
-                game_flux=False, value_residual=False) -> Config:
+                game_flux=False, value_residual=False, trunk_v2=False) -> Config:
     c = Config()
     c.embed, c.n_heads, c.n_blocks, c.ffn_mult = embed, n_heads, n_blocks, ffn_mult
     c.trunk_dim, c.trunk_hidden, c.value_bins, c.note_geo = trunk_dim, trunk_hidden, value_bins, int(note_geo)
@@ -45,6 +45,7 @@ def make_config(embed, n_heads, n_blocks, ffn_mult, trunk_dim, trunk_hidden, val
     c.z_asinh, c.value_vmax, c.eps = z_asinh, value_vmax, eps
     c.emb_ln, c.final_ln, c.game_flux = int(emb_ln), int(final_ln), int(game_flux)
     c.value_residual = int(value_residual)
+    c.trunk_v2 = int(trunk_v2)
     return c
 
 

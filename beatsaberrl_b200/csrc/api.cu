@@ -346,14 +346,23 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   const int ldz = d + D;
   g_stage = kStTrunk;
   BSRL_TRY(linear(linear_args(lead16, kLead * d, c.W(l.trunk_proj), kLead * d, c.Bv(l.trunk_proj), xt, D, 1, 0, B, D, kLead * d), c.st));
-  BSRL_TRY(layernorm(xt, D, ident, c.G(l.trunk_ln1), c.Be(l.trunk_ln1), eps, B, D, u, D, c.st));
-  BSRL_TRY(linear(linear_args(u, D, c.W(l.trunk_fc1), D, c.Bv(l.trunk_fc1), r, l.Hh, 0, 1, B, l.Hh, D), c.st));
-  {
+  if (l.trunk_v2) {
+    // SimBaV2 (python/policy.py:1140-1155): x = l2n(s_in W_in z); y = l2n(W2 relu(s_1 W1 x));
+    // x = l2n(x + alpha (y - x)); h = sqrt(D) x.  GEMMs on fp16 operands, everything else fp32.
+    float* t32 = at<float>(c.ws, w.t32);
+    BSRL_TRY(simba2_rows(0, xt, xt, at<float>(c.arena, l.v2_s_in), 0.f, B, D, u, D, c.st));
+    BSRL_TRY(linear(linear_args(u, D, c.W(l.trunk_fc1), D, c.Bv(l.trunk_fc1), t32, l.Hh, 1, 0, B, l.Hh, D), c.st));
+    BSRL_TRY(scale_relu_rows(t32, at<float>(c.arena, l.v2_s_1), B, l.Hh, r, c.st));
+    BSRL_TRY(linear(linear_args(r, l.Hh, c.W(l.trunk_fc2), l.Hh, c.Bv(l.trunk_fc2), t32, D, 1, 0, B, D, l.Hh), c.st));
+    BSRL_TRY(simba2_rows(1, t32, xt, at<float>(c.arena, l.v2_alpha), 0.5f * sqrtf((float)D), B, D, z + d, ldz, c.st));
+  } else {
+    BSRL_TRY(layernorm(xt, D, ident, c.G(l.trunk_ln1), c.Be(l.trunk_ln1), eps, B, D, u, D, c.st));
+    BSRL_TRY(linear(linear_args(u, D, c.W(l.trunk_fc1), D, c.Bv(l.trunk_fc1), r, l.Hh, 0, 1, B, l.Hh, D), c.st));
     LinearArgs p2 = linear_args(r, l.Hh, c.W(l.trunk_fc2), l.Hh, c.Bv(l.trunk_fc2), xt, D, 1, 0, B, D, l.Hh);
     p2.R = xt; p2.ldr = D;
     BSRL_TRY(linear(p2, c.st));
+    BSRL_TRY(layernorm(xt, D, ident, c.G(l.trunk_ln2), c.Be(l.trunk_ln2), eps, B, D, z + d, ldz, c.st));
   }
-  BSRL_TRY(layernorm(xt, D, ident, c.G(l.trunk_ln2), c.Be(l.trunk_ln2), eps, B, D, z + d, ldz, c.st));
   float* raw = at<float>(c.ws, w.raw);
   BSRL_TRY(linear(linear_args(z + d, ldz, c.W(l.heads), D, c.Bv(l.heads), raw, l.head_cols_pad, 1, 0, B, l.head_cols_pad, D), c.st));
 

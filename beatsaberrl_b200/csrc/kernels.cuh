@@ -89,6 +89,12 @@ int layernorm_rows(const float* x, int64_t ldx, RowMap xmap, const float* gamma,
 int layernorm_rows_f32(const float* x, int64_t ldx, const float* gamma, const float* beta, float eps,
                        int64_t rows, int d, float* y, int64_t ldy, cudaStream_t stream);
 
+// SimBaV2 trunk rows (python/policy.py:1140-1155).  mode 0: x = l2n(in * vec) -> x (fp32) and out16;
+// mode 1: y = l2n(in), x' = l2n(x + vec c_alpha (y - x)), out16 = sqrt(d) x'.  scale_relu_rows: relu(in * s).
+int simba2_rows(int mode, const float* in, float* x, const float* vec, float c_alpha, int64_t rows, int d,
+                __half* out16, int64_t ld16, cudaStream_t stream);
+int scale_relu_rows(const float* in, const float* s, int64_t rows, int n, __half* out16, cudaStream_t stream);
+
 // Tokenizer: obs -> per-encoder fp16 feature rows + additive key bias.
 struct EmbedBuffers {
   __half* saber;  // (2B, ks)

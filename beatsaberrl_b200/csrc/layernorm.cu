@@ -138,4 +138,118 @@ int launch_layernorm(const float* x, int64_t ldx, RowMap xmap, const float* gamm
 }
 }  // namespace
 
+// ---- SimBaV2 trunk row operations (NotePolicy._trunk_v2, python/policy.py:1140-1155), warp per row ----
+// l2n(v) = v / max(|v|, 1e-6) (F.normalize).  mode 0: x = l2n(in * s) -> x (fp32, in place allowed) and
+// x16.  mode 1: y = l2n(in); x = l2n(x + alpha c_alpha (y - x)); out16 = sqrt(d) x.
+namespace {
+__global__ void __launch_bounds__(256) simba2_rows_kernel(int mode, const float* in, float* x,
+                                                         const float* __restrict__ vec, float c_alpha,
+                                                         int64_t rows, int d, __half* __restrict__ out16,
+                                                         int64_t ld16) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int nvec = d >> 2;
+  const float4* v4 = reinterpret_cast<const float4*>(vec);
+  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const float4* ir = reinterpret_cast<const float4*>(in + row * d);
+    float4* xr = reinterpret_cast<float4*>(x + row * d);
+    float4 a[kMaxVec], b[kMaxVec];
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+        a[i] = ir[c];
+        if (mode == 0) {
+          const float4 s = v4[c];
+          a[i].x *= s.x; a[i].y *= s.y; a[i].z *= s.z; a[i].w *= s.w;
+        }
+        q += (a[i].x * a[i].x + a[i].y * a[i].y) + (a[i].z * a[i].z + a[i].w * a[i].w);
+      }
+    }
+    const float inv = 1.f / fmaxf(sqrtf(warp_sum(q)), 1e-6f);
+    if (mode == 0) {
+#pragma unroll
+      for (int i = 0; i < kMaxVec; ++i) {
+        const int c = lane + i * 32;
+        if (c < nvec) {
+          const float4 o = make_float4(a[i].x * inv, a[i].y * inv, a[i].z * inv, a[i].w * inv);
+          xr[c] = o;
+          reinterpret_cast<uint2*>(out16 + row * ld16)[c] = make_uint2(pack_half2(o.x, o.y), pack_half2(o.z, o.w));
+        }
+      }
+      continue;
+    }
+    float q2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+        const float4 xv = xr[c], al = v4[c];
+        b[i].x = xv.x + al.x * c_alpha * (a[i].x * inv - xv.x);
+        b[i].y = xv.y + al.y * c_alpha * (a[i].y * inv - xv.y);
+        b[i].z = xv.z + al.z * c_alpha * (a[i].z * inv - xv.z);
+        b[i].w = xv.w + al.w * c_alpha * (a[i].w * inv - xv.w);
+        q2 += (b[i].x * b[i].x + b[i].y * b[i].y) + (b[i].z * b[i].z + b[i].w * b[i].w);
+      }
+    }
+    const float sc = sqrtf((float)d) / fmaxf(sqrtf(warp_sum(q2)), 1e-6f);
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec)
+        reinterpret_cast<uint2*>(out16 + row * ld16)[c] =
+            make_uint2(pack_half2(b[i].x * sc, b[i].y * sc), pack_half2(b[i].z * sc, b[i].w * sc));
+    }
+  }
+}
+
+// out16 = relu(in * s), elementwise on (rows, n) fp32 -> fp16
+__global__ void scale_relu_kernel(const float* __restrict__ in, const float* __restrict__ s, int64_t rows, int n,
+                                  __half* __restrict__ out16) {
+  const int per_row = n >> 2;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * per_row;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % per_row);
+    const float4 v = reinterpret_cast<const float4*>(in)[i], sv = reinterpret_cast<const float4*>(s)[c];
+    reinterpret_cast<uint2*>(out16)[i] = make_uint2(pack_half2(fmaxf(v.x * sv.x, 0.f), fmaxf(v.y * sv.y, 0.f)),
+                                                   pack_half2(fmaxf(v.z * sv.z, 0.f), fmaxf(v.w * sv.w, 0.f)));
+  }
+}
+}  // namespace
+
+int simba2_rows(int mode, const float* in, float* x, const float* vec, float c_alpha, int64_t rows, int d,
+                __half* out16, int64_t ld16, cudaStream_t stream) {
+  if (!in || !x || !vec || !out16) {
+    set_error("simba2_rows: NULL operand");
+    return BSRL_ERR_NULL;
+  }
+  if (d <= 0 || d % 4 != 0 || d > kMaxVec * 128 || (ld16 % 4) || !aligned16(in) || !aligned16(x) || !aligned16(vec) ||
+      (reinterpret_cast<uintptr_t>(out16) & 7)) {
+    set_error("simba2_rows: width %d / alignment unsupported", d);
+    return BSRL_ERR_SHAPE;
+  }
+  if (rows == 0) return BSRL_OK;
+  int64_t blocks = (rows + 7) / 8;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  simba2_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(mode, in, x, vec, c_alpha, rows, d, out16, ld16);
+  BSRL_LAUNCH_OK("simba2_rows_kernel");
+  return BSRL_OK;
+}
+
+int scale_relu_rows(const float* in, const float* s, int64_t rows, int n, __half* out16, cudaStream_t stream) {
+  if (!in || !s || !out16 || (n % 4) || !aligned16(in) || !aligned16(s) || (reinterpret_cast<uintptr_t>(out16) & 7)) {
+    set_error("scale_relu_rows: bad operand");
+    return BSRL_ERR_SHAPE;
+  }
+  if (rows == 0) return BSRL_OK;
+  int64_t blocks = (rows * (n >> 2) + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  scale_relu_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(in, s, rows, n, out16);
+  BSRL_LAUNCH_OK("scale_relu_kernel");
+  return BSRL_OK;
+}
+
 }  // namespace bsrl

@@ -91,8 +91,8 @@ int validate_config(const bsrl_config* c) {
     set_error("config: z_asinh must be > 0 (metres), got %g", c->z_asinh);
     return BSRL_ERR_SHAPE;
   }
-  if ((c->emb_ln | c->final_ln | c->game_flux | c->value_residual) & ~1) {
-    set_error("config: emb_ln / final_ln / game_flux / value_residual must be 0 or 1");
+  if ((c->emb_ln | c->final_ln | c->game_flux | c->value_residual | c->trunk_v2) & ~1) {
+    set_error("config: emb_ln / final_ln / game_flux / value_residual / trunk_v2 must be 0 or 1");
     return BSRL_ERR_SHAPE;
   }
   if (!(c->value_vmax > 0.f) || !(c->eps > 0.f)) {
@@ -181,6 +181,12 @@ Layout make_layout(const bsrl_config& c) {
   l.trunk_fc1 = carve_mat(cv, l.Hh, l.D);
   l.trunk_fc2 = carve_mat(cv, l.D, l.Hh);
   l.trunk_ln2 = carve_norm(cv, l.D);
+  l.trunk_v2 = c.trunk_v2;
+  if (c.trunk_v2) {
+    l.v2_s_in = cv.take((int64_t)l.D * 4);
+    l.v2_s_1 = cv.take((int64_t)l.Hh * 4);
+    l.v2_alpha = cv.take((int64_t)l.D * 4);
+  }
   l.heads = carve_mat(cv, l.n_head_cols, l.D, 0, l.head_cols_pad);
   l.critic_ln = carve_norm(cv, d);
   if (c.emb_ln) l.emb_ln = carve_norm(cv, d);
@@ -238,11 +244,20 @@ std::vector<ParamSlot> make_param_slots(const bsrl_config& c, const Layout& l) {
     lin(p + ".ffn.0", b.up, l.F, d, 0);
     lin(p + ".ffn.2", b.down, d, l.F, 0);
   }
-  lin("trunk_proj", l.trunk_proj, l.D, kLead * d, 0);
-  norm("trunk_ln1", l.trunk_ln1);
-  lin("trunk_fc1", l.trunk_fc1, l.Hh, l.D, 0);
-  lin("trunk_fc2", l.trunk_fc2, l.D, l.Hh, 0);
-  norm("trunk_ln2", l.trunk_ln2);
+  if (l.trunk_v2) {
+    lin("trunk_in", l.trunk_proj, l.D, kLead * d, 0);
+    lin("trunk_w1", l.trunk_fc1, l.Hh, l.D, 0);
+    lin("trunk_w2", l.trunk_fc2, l.D, l.Hh, 0);
+    s.push_back({"trunk_s_in", l.D, 1, l.v2_s_in, 0, false});
+    s.push_back({"trunk_s_1", l.Hh, 1, l.v2_s_1, 0, false});
+    s.push_back({"trunk_alpha", l.D, 1, l.v2_alpha, 0, false});
+  } else {
+    lin("trunk_proj", l.trunk_proj, l.D, kLead * d, 0);
+    norm("trunk_ln1", l.trunk_ln1);
+    lin("trunk_fc1", l.trunk_fc1, l.Hh, l.D, 0);
+    lin("trunk_fc2", l.trunk_fc2, l.D, l.Hh, 0);
+    norm("trunk_ln2", l.trunk_ln2);
+  }
   for (int j = 0; j < kActHeads; ++j)
     lin("heads." + std::to_string(j), l.heads, c.head_gears[j], l.D, l.head_first[j]);
   norm("critic_ln", l.critic_ln);
@@ -318,6 +333,7 @@ Workspace make_workspace(const Layout& l, int64_t B) {
   w.vraw = cv.take(B * l.bins_pad * 4);
   w.att_c = cv.take(B * d * 2);
   w.v0 = cv.take(l.value_residual ? R * d * 2 : 0);
+  w.t32 = cv.take(l.trunk_v2 ? B * (int64_t)(l.D > l.Hh ? l.D : l.Hh) * 4 : 0);
   w.bytes = cv.off;
   return w;
 }

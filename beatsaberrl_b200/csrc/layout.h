@@ -43,6 +43,8 @@ struct Layout {
   Mat critic_qkv_g;   // critic q|k|v regrouped like BlockW::qkv_g
   int attn_G = 0;     // heads per group of the fused QKV+attention kernel; 0 = shape not supported
   int value_residual = 0;
+  int trunk_v2 = 0;                    // SimBaV2 trunk: trunk_proj / fc1 / fc2 hold W_in / W1 / W2 ...
+  int64_t v2_s_in = -1, v2_s_1 = -1, v2_alpha = -1;   // ... and these its fp32 scalers (D, Hh, D)
   int head_first[kActHeads];
   int64_t bytes = 0;
 };
@@ -74,6 +76,7 @@ struct Workspace {
   int64_t key_bias, f_saber, f_torso, f_leg, f_note, enc_hid, x, h, qkv, att, hid;
   int64_t x_lead, h_lead, lead16, xt, u, r, z, m1, m2, raw, vraw, att_c;
   int64_t v0;   // block 0's attention values (B*29, d) fp16 (value residual only)
+  int64_t t32;  // SimBaV2 trunk: fp32 GEMM outputs (B, max(D, Hh))
   int64_t bytes;
 };
 Workspace make_workspace(const Layout& l, int64_t n_envs);

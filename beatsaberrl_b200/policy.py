@@ -104,10 +104,9 @@ class NotePolicy(nn.Module):
         assert n_gears in (3, 5, 7), f"n_gears must be 3/5/7, got {n_gears}"
         assert value_bins > 1, f"value_bins must be > 1, got {value_bins}"
         # options of the reference that change the forward and are not built here
-        for flag, name in ((trunk_arch != "simba", "trunk_arch='simbav2'"),
-                           (fp16_accum != "off", "fp16_accum (accumulation is always fp32)")):
-            if flag:
-                raise NotImplementedError(f"NotePolicy option {name} is not built in this library")
+        if fp16_accum != "off":     # the one option of the reference's forward that is not built
+            raise NotImplementedError("NotePolicy option fp16_accum is not built in this library "
+                                      "(accumulation is always fp32)")
         if head_gears is None:
             head_gears = (n_gears,) * N_ACTION_HEADS
         head_gears = tuple(int(k) for k in head_gears)
@@ -145,11 +144,26 @@ class NotePolicy(nn.Module):
         self.blocks = nn.ModuleList(_Block(embed, ffn_mult, self.value_residual and i > 0) for i in range(n_blocks))
         self.final_ln = nn.LayerNorm(embed) if final_ln else None      # --final-ln (python/policy.py:969)
         self.trunk_arch = trunk_arch
-        self.trunk_proj = nn.Linear(self.n_lead * embed, trunk_dim)
-        self.trunk_ln1 = nn.LayerNorm(trunk_dim)
-        self.trunk_fc1 = nn.Linear(trunk_dim, H)
-        self.trunk_fc2 = nn.Linear(H, trunk_dim)
-        self.trunk_ln2 = nn.LayerNorm(trunk_dim)
+        if trunk_arch == "simba":
+            self.trunk_proj = nn.Linear(self.n_lead * embed, trunk_dim)
+            self.trunk_ln1 = nn.LayerNorm(trunk_dim)
+            self.trunk_fc1 = nn.Linear(trunk_dim, H)
+            self.trunk_fc2 = nn.Linear(H, trunk_dim)
+            self.trunk_ln2 = nn.LayerNorm(trunk_dim)
+        else:
+            # SimBaV2 (python/policy.py:1003-1021): orthogonal, row-normalised matrices with frozen zero
+            # biases, per-feature scalers; same creation order, so a seeded init matches the reference's
+            self.trunk_in = nn.Linear(self.n_lead * embed, trunk_dim)
+            self.trunk_w1 = nn.Linear(trunk_dim, H)
+            self.trunk_w2 = nn.Linear(H, trunk_dim)
+            for lin in (self.trunk_in, self.trunk_w1, self.trunk_w2):
+                nn.init.orthogonal_(lin.weight)
+                nn.init.zeros_(lin.bias)
+                lin.bias.requires_grad_(False)
+            self.trunk_s_in = nn.Parameter(torch.full((trunk_dim,), math.sqrt(2.0 / trunk_dim)))
+            self.trunk_s_1 = nn.Parameter(torch.full((H,), math.sqrt(2.0 / H)))
+            self.trunk_alpha = nn.Parameter(torch.full((trunk_dim,), 1.0 / math.sqrt(trunk_dim)))
+            self.project_trunk_weights()
         self.heads = nn.ModuleList(nn.Linear(trunk_dim, n) for n in self.head_sizes)
         self.critic_ln = nn.LayerNorm(embed)
         self.critic_q = nn.Linear(embed, embed)
@@ -170,7 +184,8 @@ class NotePolicy(nn.Module):
         self._cfg = nat.make_config(embed, n_heads, n_blocks, ffn_mult, trunk_dim, H, self.value_bins,
                                     note_geo, head_gears, float(z_asinh), float(value_vmax),
                                     float(self.blocks[0].ln_attn.eps), emb_ln=emb_ln, final_ln=final_ln,
-                                    game_flux=(game == "flux"), value_residual=value_residual)
+                                    game_flux=(game == "flux"), value_residual=value_residual,
+                                    trunk_v2=(trunk_arch == "simbav2"))
         nat.check(nat.lib.bsrl_config_validate(C.byref(self._cfg)))
         self._param_table = nat.param_table(self._cfg)
         self._arena = None
@@ -180,7 +195,7 @@ class NotePolicy(nn.Module):
 
     # ------------------------------------------------------------------ weights
     def _pack(self, force: bool = False) -> None:
-        dev = self.trunk_proj.weight.device
+        dev = self.critic_q.weight.device
         if dev.type != "cuda":
             raise RuntimeError("NotePolicy runs on a CUDA device only (no CPU path): call .cuda() first")
         key = (_weights_version, dev)
@@ -298,7 +313,7 @@ class NotePolicy(nn.Module):
     def seed_sampler(self, seed: int) -> None:
         """(Re)start the action-sampling stream: [seed, call counter] in a device tensor that the
         head kernel reads, so a captured CUDA graph draws fresh numbers on every replay."""
-        dev = self.trunk_proj.weight.device
+        dev = self.critic_q.weight.device
         self._rng_state = torch.tensor([seed & 0x7FFFFFFFFFFFFFFF, 0], dtype=torch.int64, device=dev)
 
     @torch.no_grad()
@@ -326,6 +341,20 @@ class NotePolicy(nn.Module):
             self._ent_h = ent_h
         self._value_logits = None
         return action, logprob, entropy, value
+
+    def trunk_projected(self):
+        """The Linears whose rows project_trunk_weights keeps unit-norm ([] for the SimBa trunk)."""
+        return [self.trunk_in, self.trunk_w1, self.trunk_w2] if self.trunk_arch == "simbav2" else []
+
+    @torch.no_grad()
+    def project_trunk_weights(self) -> bool:
+        """SimBaV2 weight projection (python/policy.py:1165-1177): every output row of W_in / W1 / W2 back onto
+        the unit sphere, biases to 0, in place; the caller bumps the weights version afterwards."""
+        lins = self.trunk_projected()
+        for lin in lins:
+            lin.weight.div_(lin.weight.norm(dim=1, keepdim=True).clamp_min(1e-12))
+            lin.bias.zero_()
+        return bool(lins)
 
     @torch.no_grad()
     def rollout_step(self, obs, b_act=None, b_logp=None, b_val=None, b_obs=None, ret_sig=None, ret_mu=None,

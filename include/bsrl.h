@@ -68,6 +68,8 @@ typedef struct bsrl_config {
   int32_t game_flux;     /* 1 = the Flux game's note-geo variant: bar slots aim at lanes 12, 13 (:357-360) */
   int32_t value_residual; /* 1 = blocks after the first mix block 0's attention values in,
                            * v <- vres_a v + vres_b v0 (--value-residual, :512-520, :604-615) */
+  int32_t trunk_v2;      /* 1 = SimBaV2 readout trunk (--trunk-arch simbav2, :984-1021, :1140-1155):
+                           * parameters trunk_in / trunk_w1 / trunk_w2, trunk_s_in, trunk_s_1, trunk_alpha */
 } bsrl_config;
 
 /* --- library -------------------------------------------------------------------- */

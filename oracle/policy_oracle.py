@@ -133,6 +133,7 @@ class PolicyConfig:
     final_ln: bool = False      # LayerNorm on the lead rows leaving the last block (:969, :1306-1307)
     game: str = "standard"      # "flux": bar slots aim the geometry lanes at lanes 12, 13 (:357-360)
     value_residual: bool = False  # blocks after the first mix block 0's values in: v <- a v + b v0 (:512-520, :611)
+    trunk_arch: str = "simba"    # "simbav2": hyperspherical trunk (python/policy.py:984-1021, :1140-1155)
 
     def __post_init__(self):
         if self.head_gears is None:
@@ -159,7 +160,8 @@ class PolicyConfig:
                     note_geo=self.note_geo, value_bins=self.value_bins,
                     value_vmax=self.value_vmax, trunk_hidden=self.trunk_hidden,
                     z_asinh=self.z_asinh, head_gears=self.head_gears, emb_ln=self.emb_ln,
-                    final_ln=self.final_ln, game=self.game, value_residual=self.value_residual)
+                    final_ln=self.final_ln, game=self.game, value_residual=self.value_residual,
+                    trunk_arch=self.trunk_arch)
 
 
 # the five benchmark configurations in reference-drop-in form (T = 29, n_lead = 5)
@@ -200,9 +202,10 @@ def linear_specs(cfg: PolicyConfig):
         for nm in ("q_proj", "k_proj", "v_proj", "out_proj"):
             s.append((f"{p}.{nm}", d, d))
         mlp(f"{p}.ffn", [d, cfg.ffn_mult * d, d])
-    s.append(("trunk_proj", N_LEAD * d, D))
-    s.append(("trunk_fc1", D, Hh))
-    s.append(("trunk_fc2", Hh, D))
+    if cfg.trunk_arch == "simbav2":
+        s += [("trunk_in", N_LEAD * d, D), ("trunk_w1", D, Hh), ("trunk_w2", Hh, D)]
+    else:
+        s += [("trunk_proj", N_LEAD * d, D), ("trunk_fc1", D, Hh), ("trunk_fc2", Hh, D)]
     for j, k in enumerate(cfg.head_gears):
         s.append((f"heads.{j}", D, k))
     for nm in ("critic_q", "critic_k", "critic_v", "critic_out"):
@@ -216,8 +219,9 @@ def layernorm_specs(cfg: PolicyConfig):
     out = []
     for i in range(cfg.n_blocks):
         out += [(f"blocks.{i}.ln_attn", cfg.embed), (f"blocks.{i}.ln_ffn", cfg.embed)]
-    out += [("trunk_ln1", cfg.trunk_dim), ("trunk_ln2", cfg.trunk_dim),
-            ("critic_ln", cfg.embed)]
+    if cfg.trunk_arch != "simbav2":
+        out += [("trunk_ln1", cfg.trunk_dim), ("trunk_ln2", cfg.trunk_dim)]
+    out.append(("critic_ln", cfg.embed))
     if cfg.emb_ln:
         out.append(("emb_ln", cfg.embed))
     if cfg.final_ln:
@@ -238,6 +242,16 @@ def build_state_dict(cfg: PolicyConfig, seed: int, xavier: bool = False,
     for prefix, fin, fout in linear_specs(cfg):
         m = nn.Linear(fin, fout)
         lins.append((prefix, m))
+        if prefix == "trunk_w2":
+            # SimBaV2: orthogonal init of the three trunk matrices right after their creation (the
+            # draws sit at this point of the RNG stream), zero frozen biases, rows projected onto the
+            # unit sphere (python/policy.py:1003-1021, :1165-1177)
+            for _, tm in lins[-3:]:
+                nn.init.orthogonal_(tm.weight)
+                nn.init.zeros_(tm.bias)
+            with torch.no_grad():
+                for _, tm in lins[-3:]:
+                    tm.weight.div_(tm.weight.norm(dim=1, keepdim=True).clamp_min(1e-12))
     if xavier:
         # reference modules() order == ctor registration order for the Linears
         for _, m in lins:
@@ -247,6 +261,14 @@ def build_state_dict(cfg: PolicyConfig, seed: int, xavier: bool = False,
         sd[prefix + ".weight"] = m.weight.detach().clone()
         sd[prefix + ".bias"] = m.bias.detach().clone()
     g = torch.Generator().manual_seed(seed + 7919)
+    if cfg.trunk_arch == "simbav2":
+        D, Hh = cfg.trunk_dim, cfg.trunk_hidden
+        sd["trunk_s_in"] = torch.full((D,), math.sqrt(2.0 / D))
+        sd["trunk_s_1"] = torch.full((Hh,), math.sqrt(2.0 / Hh))
+        sd["trunk_alpha"] = torch.full((D,), 1.0 / math.sqrt(D))
+        if ln_jitter > 0:
+            for k in ("trunk_s_in", "trunk_s_1", "trunk_alpha"):
+                sd[k] = sd[k] * (1.0 + ln_jitter * torch.randn(sd[k].shape, generator=g))
     if cfg.value_residual:   # (a, b) = (1, 0) at init; the jitter moves them so tests exercise the mix
         for i in range(1, cfg.n_blocks):
             sd[f"blocks.{i}.vres_a"] = torch.ones(1)
@@ -412,8 +434,23 @@ def block_forward(sd, cfg: PolicyConfig, i: int, x, bias, n_queries: int = 0, v0
     return (out, v_own) if want_v else out
 
 
+def trunk_v2(sd, cfg: PolicyConfig, z):
+    """SimBaV2 readout trunk (python/policy.py:1140-1155): x = l2n(s_in W_in z);
+    y = l2n(W2 relu(s_1 W1 x)); x = l2n(x + alpha (y - x)); h = sqrt(D) x, alpha = 0.5 sqrt(D) trunk_alpha."""
+    D = cfg.trunk_dim
+    l2n = lambda v: F.normalize(v, dim=-1, eps=1e-6)
+    x = l2n(_lin(sd, "trunk_in", z) * sd["trunk_s_in"])
+    u = F.relu(_lin(sd, "trunk_w1", x) * sd["trunk_s_1"])
+    y = l2n(_lin(sd, "trunk_w2", u))
+    alpha = sd["trunk_alpha"] * (0.5 * math.sqrt(D))
+    x = l2n(x + alpha * (y - x))
+    return x * math.sqrt(D)
+
+
 def trunk(sd, cfg: PolicyConfig, lead):
-    """(B, 5d) -> (B, D): proj -> LN1 -> fc1 -> ReLU -> fc2 -> +res -> LN2."""
+    """(B, 5d) -> (B, D): proj -> LN1 -> fc1 -> ReLU -> fc2 -> +res -> LN2 (or the SimBaV2 trunk)."""
+    if cfg.trunk_arch == "simbav2":
+        return trunk_v2(sd, cfg, lead)
     x = _lin(sd, "trunk_proj", lead)
     u = _ln(sd, "trunk_ln1", x, cfg.eps)
     dlt = _lin(sd, "trunk_fc2", F.relu(_lin(sd, "trunk_fc1", u)))

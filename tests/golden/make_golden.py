@@ -32,6 +32,8 @@ CASES = [
      dict(emb_ln=True, final_ln=True, game="flux")),
     # --value-residual on a 3-block model (blocks 1 and 2 mix block 0's values in; (a, b) moved off (1, 0))
     ("tiny_vres", "tiny", False, None, False, 14, 0.1, 16, True, 24, dict(value_residual=True, n_blocks=3)),
+    # --trunk-arch simbav2 (orthogonal, row-normalised trunk matrices; scalers moved off their init)
+    ("tiny_simbav2", "tiny", False, None, False, 15, 0.1, 16, True, 25, dict(trunk_arch="simbav2")),
 ]
 
 

@@ -18,6 +18,8 @@ GOLDEN_CASES = {
                          opts=dict(emb_ln=True, final_ln=True, game="flux")),
     "tiny_vres": dict(cfg="tiny", geo=False, hg=None, xavier=False, seed=14, jitter=0.1,
                       opts=dict(value_residual=True, n_blocks=3)),
+    "tiny_simbav2": dict(cfg="tiny", geo=False, hg=None, xavier=False, seed=15, jitter=0.1,
+                         opts=dict(trunk_arch="simbav2")),
 }
 
 

@@ -113,7 +113,7 @@ def test_policy_facade_host_side(native):
     with pytest.raises(RuntimeError):   # no CPU path
         m.forward_stacked(torch.zeros(2, 630))
     with pytest.raises(NotImplementedError):
-        NotePolicy(trunk_arch="simbav2")
+        NotePolicy(fp16_accum="all")
     with pytest.raises(ValueError):
         NotePolicy(trunk_arch="mlp")
     with pytest.raises(ValueError):

@@ -182,6 +182,24 @@ def test_constructor_options(name, geo, B):
     assert (l0 - logits).abs().max() > 1e-2
 
 
+def test_simbav2_trunk():
+    """--trunk-arch simbav2 (python/policy.py:1140-1155) at a production-like width, against the oracle
+    (pinned to the reference by the golden case tiny_simbav2); the facade's seeded init equals the oracle's."""
+    cfg = make_cfg("recipe", True, opts=dict(trunk_arch="simbav2"))
+    sd = po.build_state_dict(cfg, 19, ln_jitter=0.1)
+    m = cuda_policy(cfg, sd)
+    obs = po.make_obs(400, 33, padded=True)
+    ref_l, ref_v = po.forward_stacked(sd, cfg, obs)
+    logits, value = m.forward_stacked(obs.cuda())
+    assert_parity(logits, value, ref_l, ref_v, argmax_min=0.995)
+    from beatsaberrl_b200.policy import NotePolicy
+    torch.manual_seed(19)
+    fresh = NotePolicy(**cfg.ref_kwargs()).state_dict()
+    plain = po.build_state_dict(cfg, 19)
+    for k in ("trunk_in.weight", "trunk_w2.weight", "trunk_s_1", "trunk_alpha", "heads.0.weight"):
+        assert torch.equal(fresh[k], plain[k]), k
+
+
 def test_rollout_step_writes_buffer_rows():
     """The fused rollout tick draws the same actions as get_action_and_value under the same seed and
     counter, and its buffer rows are what the reference's loop body stores: uint8 actions, log-prob,
