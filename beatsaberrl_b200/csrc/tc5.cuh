@@ -41,26 +41,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
 // Bounded wait: false when the limit ran out or another role already gave up (*abort != 0).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
-#ifdef BSRL_SPIN_TEST
-    if (mbar_test_wait(bar, parity)) return true;
-    __nanosleep(20);
-#else
-    if (mbar_try_wait(bar, parity)) return true;
-#endif
+    if (mbar_try_wait(bar, parity)) return true;   // the hardware parks the thread inside try_wait
     if ((i & 1023u) == 1023u && *abort) return false;
   }
   return false;
