@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(256, RPW > 1 ? 4 : 1) layernorm_kernel(const f
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const int nvec = d >> 2;
-  constexpr int NV = RPW == 1 ? kMaxVec : 2;       // float4 per lane and row (RPW > 1: rows up to 256 wide)
+  constexpr int NV = kMaxVec / RPW;                // float4 per lane and row: rows up to 1024 / 512 / 256 wide
   for (int64_t row0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW; row0 < rows;
        row0 += warps * RPW) {
     float4 v[RPW][NV];
@@ -122,17 +122,13 @@ int launch_layernorm(const float* x, int64_t ldx, RowMap xmap, const float* gamm
   }
   if (rows == 0) return BSRL_OK;
   const int64_t cap = (int64_t)sm_count() * 16;
-  if (d <= 256 && rows >= cap * 8 * 4) {            // long, narrow inputs: four rows in flight per warp
-    int64_t blocks = (rows + 31) / 32;
-    if (blocks > cap) blocks = cap;
-    layernorm_kernel<4, F32><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, ldx, xmap, gamma, beta, eps,
-                                                                          rows, d, y, ldy);
-  } else {
-    int64_t blocks = (rows + 7) / 8;
-    if (blocks > cap) blocks = cap;
-    layernorm_kernel<1, F32><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, ldx, xmap, gamma, beta, eps,
-                                                                          rows, d, y, ldy);
-  }
+  const int rpw = rows < cap * 8 * 4 ? 1 : d <= 256 ? 4 : d <= 512 ? 2 : 1;   // long inputs: several rows per warp
+  int64_t blocks = (rows + 8 * rpw - 1) / (8 * rpw);
+  if (blocks > cap) blocks = cap;
+  const unsigned nb = static_cast<unsigned>(blocks);
+  if (rpw == 4) layernorm_kernel<4, F32><<<nb, 256, 0, stream>>>(x, ldx, xmap, gamma, beta, eps, rows, d, y, ldy);
+  else if (rpw == 2) layernorm_kernel<2, F32><<<nb, 256, 0, stream>>>(x, ldx, xmap, gamma, beta, eps, rows, d, y, ldy);
+  else layernorm_kernel<1, F32><<<nb, 256, 0, stream>>>(x, ldx, xmap, gamma, beta, eps, rows, d, y, ldy);
   BSRL_LAUNCH_OK("layernorm_kernel");
   return BSRL_OK;
 }
