@@ -46,9 +46,13 @@ __device__ __forceinline__ void give_up(Shared* sh, int* status, int role) {
   sh->abort = 1;
 }
 
+// HAS_R: a residual is added in the epilogue (its prefetch registers and address arithmetic are compiled
+// out otherwise: they cost the residual-free fp32 epilogue ~15 %).
+template <bool HAS_R>
 __global__ void __launch_bounds__(THREADS, 1)
 linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
-                  LinearArgs p, int m_tiles, int n_tiles, int* status) {
+                  const __grid_constant__ CUtensorMap tm_c, int tma_c, LinearArgs p, int m_tiles, int n_tiles,
+                  int* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;
@@ -158,7 +162,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const int q = warp & 3;                    // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;          // which half of the tile's columns
     uint8_t* stg = staging + (warp - 2) * STG_BYTES;
-    const bool wide = p.out_f32 || p.R;        // stage fp32 (32 columns per block) instead of fp16 (64)
+    const bool wide = p.out_f32 || HAS_R;        // stage fp32 (32 columns per block) instead of fp16 (64)
     const int cw = wide ? 32 : 64;
     const int sub = lane >> 3, piece = lane & 7;   // transposed phase: row sub + 4 i, 16-byte piece
     uint32_t tile_i = 0;
@@ -174,7 +178,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       for (int i = 0; i < 8; ++i) {
         const int64_t row = m0 + q * 32 + i * 4 + sub;
         crow[i] = row < p.M ? p.cmap(row) * (int64_t)p.ldc : -1;
-        rrow[i] = (p.R && row < p.M) ? p.rmap(row) * (int64_t)p.ldr : 0;
+        rrow[i] = (HAS_R && row < p.M) ? p.rmap(row) * (int64_t)p.ldr : 0;
       }
       if (!mbar_wait_warp(smem_u32(&sh->tmem_full[buf]), acc_ph, abort)) {
         if (lane == 0) give_up(sh, status, 5);
@@ -191,7 +195,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         // hides behind the TMEM load and the staging pass (fetched inside the store loop they made the
         // epilogue 3.6x slower than the residual-free one)
         float4 rv[8];
-        if (p.R) {
+        if (HAS_R) {
           const int pc = col + piece * 4;
 #pragma unroll
           for (int i = 0; i < 8; ++i)
@@ -220,6 +224,10 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
           }
+          if (tma_c && s32 == 0) {   // the previous block's TMA store has read the staging buffer
+            if (lane == 0) bulk_wait_read<0>();
+            __syncwarp();
+          }
           if (wide) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
@@ -232,6 +240,17 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   make_uint4(pack_half2(v[8 * j], v[8 * j + 1]), pack_half2(v[8 * j + 2], v[8 * j + 3]),
                              pack_half2(v[8 * j + 4], v[8 * j + 5]), pack_half2(v[8 * j + 6], v[8 * j + 7]));
           }
+        }
+        if (tma_c) {
+          // ---- phase 2 (dense output, no residual): the staged 32 x 128-byte block leaves as one TMA
+          // store; rows past M and columns past N are clipped by the tensor map
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && m0 + q * 32 < p.M) {
+            tma_store_2d(&tm_c, col, (int)(m0 + q * 32), smem_u32(stg));
+            bulk_commit();
+          }
+          continue;
         }
         __syncwarp();
         // ---- phase 2: 8 lanes per row, one 16-byte piece each
@@ -247,7 +266,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             } else {
               float4 f = make_float4(__uint_as_float(raw16.x), __uint_as_float(raw16.y),
                                      __uint_as_float(raw16.z), __uint_as_float(raw16.w));
-              if (p.R) {
+              if (HAS_R) {
                 f.x += rv[i].x; f.y += rv[i].y; f.z += rv[i].z; f.w += rv[i].w;
               }
               if (p.out_f32)
@@ -264,6 +283,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
     }
+    if (tma_c && lane == 0) bulk_wait_all();      // the stores are complete before the CTA exits
   }
 
   // ------------------------------------------------------------------ teardown
@@ -318,6 +338,11 @@ bool make_tmap_f16(CUtensorMap* map, const void* base, int64_t rows, int64_t col
 
 bool make_tmap_rows64(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows, int64_t cols,
                       int64_t ld_elems, int box_rows) {
+  return make_tmap_rows(map, base, elem_bytes, rows, cols, ld_elems, box_rows, 64);
+}
+
+bool make_tmap_rows(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows, int64_t cols,
+                    int64_t ld_elems, int box_rows, int row_bytes) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from the driver");
@@ -325,11 +350,12 @@ bool make_tmap_rows64(CUtensorMap* map, const void* base, int elem_bytes, int64_
   }
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld_elems * (cuuint64_t)elem_bytes};
-  cuuint32_t box[2] = {(cuuint32_t)(64 / elem_bytes), (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)(row_bytes / elem_bytes), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed (%d) for a (%lld x %lld) matrix of %d-byte elements, ld %lld", (int)r,
               (long long)rows, (long long)cols, elem_bytes, (long long)ld_elems);
@@ -359,11 +385,17 @@ int linear_tc5(const LinearArgs& p, cudaStream_t stream) {
   CUtensorMap tm_a, tm_w;
   if (!make_tmap_f16(&tm_a, p.A, p.M, p.K, p.lda, BM)) return BSRL_ERR_CUDA;
   if (!make_tmap_f16(&tm_w, p.W, p.N, p.K, p.ldw, BN)) return BSRL_ERR_CUDA;
+  // dense output rows without a residual leave as TMA stores of the epilogue's 32 x 128-byte staging blocks
+  const bool tma_c = !p.R && p.cmap.group == 0x7fffffff && p.cmap.stride == 0 && p.cmap.first == 0 &&
+                     p.M <= 0x7fffff00;
+  CUtensorMap tm_c = tm_a;
+  if (tma_c && !make_tmap_rows(&tm_c, p.C, p.out_f32 ? 4 : 2, p.M, p.N, p.ldc, 32, 128)) return BSRL_ERR_CUDA;
   static bool attr_set[64] = {};
   int dev = 0;
   BSRL_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 64 && !attr_set[dev]) {
-    BSRL_CUDA_OK(cudaFuncSetAttribute(linear_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    BSRL_CUDA_OK(cudaFuncSetAttribute(linear_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    BSRL_CUDA_OK(cudaFuncSetAttribute(linear_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     attr_set[dev] = true;
   }
   const int64_t m_tiles = (p.M + BM - 1) / BM;
@@ -374,7 +406,11 @@ int linear_tc5(const LinearArgs& p, cudaStream_t stream) {
   }
   int64_t grid = m_tiles * n_tiles;
   if (grid > sm_count()) grid = sm_count();
-  linear_tc5_kernel<<<(unsigned)grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_w, p, (int)m_tiles, n_tiles, status);
+  if (p.R)
+    linear_tc5_kernel<true><<<(unsigned)grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_w, tm_c, 0, p, (int)m_tiles, n_tiles, status);
+  else
+    linear_tc5_kernel<false><<<(unsigned)grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_w, tm_c, tma_c ? 1 : 0, p, (int)m_tiles,
+                                                                             n_tiles, status);
   BSRL_LAUNCH_OK("linear_tc5_kernel");
   return BSRL_OK;
 }
