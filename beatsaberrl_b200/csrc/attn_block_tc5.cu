@@ -11,13 +11,14 @@
 // registers) while the tensor core already projects the next group into the other TMEM buffer.
 //
 //   warp 0      TMA producer: the h tile (d/64 swizzled chunks, loaded once per tile) and the
-//               regrouped weight tiles (192 x 64 per stage, 4-stage ring)
+//               regrouped weight tiles (192 x 64 or 144 x 64 per stage, 3- or 4-stage ring)
 //   warp 1      MMA issuer: tcgen05.mma M = 128, N = 192, K = 16
 //   warps 2..9  drain the accumulator (+ bias, fp16) into the q|k|v tile, then attend
 //
 // HBM traffic per token: read h (2d B), write att (2d B).  Replaces fp16_packed_linear + attn29 /
 // packed_sdpa (python/policy.py:586-600, :645-692; python/beat_arena_env/csrc/small_attn.cu).
-// All waits are bounded (tc5.cuh); head_dim 32 only.
+// With all 29 query rows and two heads of 32 per group, the group's output (116 rows x 128 bytes) is staged
+// in shared memory and leaves as one TMA store.  All waits are bounded (tc5.cuh).
 #include "kernels.cuh"
 #include "tc5.cuh"
 
@@ -28,7 +29,7 @@ using namespace tc5;
 constexpr int EPT = 4;                  // envs per tile
 constexpr int ROWS = EPT * kT;          // 116 live rows
 constexpr int BM = 128;
-constexpr int STAGES = 4;
+constexpr int MAX_STAGES = 4;           // weight ring: 3 stages of 24 KB (head_dim 32) or 4 of 18 KB (head_dim 48), as measured
 constexpr int CHUNK_BYTES = BM * 128;   // 16 KB: 128 rows x 64 k-columns
 constexpr int WORKERS = 8;
 constexpr int THREADS = (2 + WORKERS) * 32;
@@ -37,16 +38,18 @@ constexpr int THREADS = (2 + WORKERS) * 32;
 template <int DH_, int G_>
 struct Shape {
   static constexpr int DH = DH_, G = G_, GD = G * DH, NG = 3 * GD;
+  static constexpr int STAGES = DH == 32 ? 3 : 4;
   static constexpr int STAGE_BYTES = NG * 128;   // NG weight rows x 64 k-columns (24 KB / 18 KB)
   static constexpr int LDQ = NG * 2 + 16;        // row pitch of the q|k|v tile: 400 / 304 bytes, ldmatrix conflict-free
   static constexpr int SQ_BYTES = BM * LDQ;
-  static constexpr int SMEM_BYTES = 4 * CHUNK_BYTES + STAGES * STAGE_BYTES + SQ_BYTES + 768 * 4 + 1024 + 256;
+  static constexpr int SO_BYTES = BM * 128;      // attention output of one group: 128 rows x 128 B, 128-byte swizzle
+  static constexpr int SMEM_BYTES = 4 * CHUNK_BYTES + STAGES * STAGE_BYTES + SO_BYTES + SQ_BYTES + 768 * 4 + 1024 + 256;
   static_assert(NG % 16 == 0 && NG <= 256 && STAGE_BYTES % 1024 == 0, "group width");
 };
 constexpr int KERNEL_ID = 3;
 
 struct Shared {
-  uint64_t w_full[STAGES], w_empty[STAGES], a_full[4], a_free[4], acc_full[2], acc_empty[2], attn_done[2], mma_done;
+  uint64_t w_full[MAX_STAGES], w_empty[MAX_STAGES], a_full[4], a_free[4], acc_full[2], acc_empty[2], attn_done[2], mma_done;
   uint32_t tmem_base;
   int abort;
   int quit;   // abort flag as sampled by one thread before a CTA-level barrier, so all workers leave together
@@ -63,6 +66,7 @@ struct Params {
   __half* v_out;           // value residual: own values out / block 0's values in + the two mix scalars
   const __half* v0;
   const float* vres;
+  int out_tma;             // the group's output leaves as one TMA store from shared memory (all 29 query rows, two heads of 32)
   int* status;
 };
 
@@ -110,9 +114,9 @@ __device__ __forceinline__ float rcp_approx(float x) {
 // addresses (shared window) of the pair's first row / first column; rows are LDQ bytes apart.
 // The MT 16-row query tiles are processed side by side: two independent dependency chains per warp
 // (the kernel is latency-bound here) and each K / V fragment is fetched once for both.
-template <int MT, int DH, int LDQ>
+template <int MT, int DH, int LDQ, bool STAGE_OUT>
 __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t sv, const float (&kb)[4][2],
-                                            int n_q, __half* out_env, int ldo, int lane TRACE_PARAMS) {
+                                            int n_q, __half* out_env, int ldo, int lane, uint8_t* so, int so_row0, int so_piece0 TRACE_PARAMS) {
   const int g = lane >> 2, tig = lane & 3;
   const float scale = rsqrtf((float)DH) * 1.4426950408889634f;   // 1/sqrt(dh) * log2(e)
   float s[MT][4][4];
@@ -207,7 +211,16 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int qrow = mt * 16 + g + r * 8;
-      if (qrow < n_q) {
+      if (STAGE_OUT && qrow < n_q && so) {
+        // staged for the group's TMA store: 128-byte rows, 16-byte piece p of row r at ((p ^ (r & 7)) << 4);
+        // the 8 rows of a store instruction hit 32 different banks
+        const int row = so_row0 + qrow;
+        uint8_t* orow = so + row * 128 + tig * 4;
+#pragma unroll
+        for (int nt = 0; nt < DH / 8; ++nt)
+          *reinterpret_cast<uint32_t*>(orow + (((so_piece0 + nt) ^ (row & 7)) << 4)) =
+              pack_half2(o[mt][nt][r * 2], o[mt][nt][r * 2 + 1]);
+      } else if (qrow < n_q) {
         __half* orow = out_env + (int64_t)qrow * ldo + tig * 2;
 #pragma unroll
         for (int nt = 0; nt < DH / 8; ++nt)
@@ -219,15 +232,17 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
 // VRES: the value-residual code of the drain is compiled in (it costs ~14 % of the kernel even when idle)
 template <int DH, int G, bool VRES>
 __global__ void __launch_bounds__(THREADS, 1)
-attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_w, Params p) {
+attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_w,
+                  const __grid_constant__ CUtensorMap tm_o, Params p) {
   using S = Shape<DH, G>;
-  constexpr int GD = S::GD, NG = S::NG, STAGE_BYTES = S::STAGE_BYTES, LDQ = S::LDQ, SQ_BYTES = S::SQ_BYTES;
+  constexpr int STAGES = S::STAGES, GD = S::GD, NG = S::NG, STAGE_BYTES = S::STAGE_BYTES, LDQ = S::LDQ, SQ_BYTES = S::SQ_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw);
-  const uint32_t sA = base, ring = base + 4 * CHUNK_BYTES, sQ = ring + STAGES * STAGE_BYTES;
-  uint8_t* sQ_g = gen + 4 * CHUNK_BYTES + STAGES * STAGE_BYTES;
+  const uint32_t sA = base, ring = base + 4 * CHUNK_BYTES, sO = ring + STAGES * STAGE_BYTES, sQ = sO + S::SO_BYTES;
+  uint8_t* sO_g = gen + 4 * CHUNK_BYTES + STAGES * STAGE_BYTES;
+  uint8_t* sQ_g = sO_g + S::SO_BYTES;
   float* s_bias = reinterpret_cast<float*>(sQ_g + SQ_BYTES);
   Shared* sh = reinterpret_cast<Shared*>(sQ_g + SQ_BYTES + 768 * 4);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -434,6 +449,7 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
         if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[buf]));     // the TMEM buffer may be refilled
         if (wi == 0 && lane == 0) sh->quit = *abort;
         TRACE(210 + g);
+        if (p.out_tma && wi == 0 && lane == 0) bulk_wait_read<0>();     // the previous group's output store has read sO
         asm volatile("bar.sync 1, %0;" ::"n"(WORKERS * 32) : "memory");  // q|k|v tile complete
         TRACE(220 + g);
         if (*reinterpret_cast<volatile int*>(&sh->quit)) {
@@ -446,16 +462,23 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
                          sk_pair = rows + (GD + hh * DH) * 2, sv_pair = rows + (2 * GD + hh * DH) * 2;
           __half* out_pair = p.out + (env * p.n_q + mt_own * 16) * (int64_t)p.ldo + (g * G + hh) * DH;
           const int n_q = p.n_q - mt_own * 16;      // query rows left from this warp's first one
-          if (G == 2 && n_q > 16) attend_pair<2, DH, LDQ>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane TRACE_ARGS);
-          else if (n_q > 0) attend_pair<1, DH, LDQ>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane TRACE_ARGS);
+          uint8_t* so_tile = (G == 2 && p.out_tma) ? sO_g : nullptr;
+          if (G == 2 && n_q > 16) attend_pair<2, DH, LDQ, G == 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * kT + mt_own * 16, hh * (DH / 8) TRACE_ARGS);
+          else if (n_q > 0) attend_pair<1, DH, LDQ, G == 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * kT + mt_own * 16, hh * (DH / 8) TRACE_ARGS);
         }
         TRACE(230 + g);
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh->attn_done[buf]));
+        if (p.out_tma) fence_proxy_async_smem();                         // this thread's sO writes -> the TMA engine
         asm volatile("bar.sync 1, %0;" ::"n"(WORKERS * 32) : "memory");  // tile may be overwritten
+        if (p.out_tma && wi == 0 && lane == 0) {                         // rows past the last env are clipped
+          tma_store_2d(&tm_o, g * GD, t * ROWS, sO);
+          bulk_commit();
+        }
         TRACE(240 + g);
       }
     }
+    if (p.out_tma && wi == 0 && lane == 0) bulk_wait_all();   // the output stores are complete before the CTA exits
   }
 
   // ------------------------------------------------------------------ teardown
@@ -493,6 +516,10 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
   CUtensorMap tm_h, tm_w;
   if (!make_tmap_f16(&tm_h, a.h, a.n_envs * kT, a.d, a.ldh, BM)) return BSRL_ERR_CUDA;
   if (!make_tmap_f16(&tm_w, a.wg, 3 * a.d, a.d, a.d, dh == 32 ? Shape<32, 2>::NG : Shape<48, 1>::NG)) return BSRL_ERR_CUDA;
+  // all 29 query rows of two heads of 32: a group's output is 116 contiguous rows x 128 bytes = one TMA store
+  const bool out_tma = dh == 32 && a.q_first == 0 && a.n_q == kT && a.n_envs * kT <= 0x7fffff00;
+  CUtensorMap tm_o = tm_h;
+  if (out_tma && !make_tmap_rows(&tm_o, a.out, 2, a.n_envs * kT, a.d, a.ldo, ROWS, 128)) return BSRL_ERR_CUDA;
   static bool attr_set[64] = {};
   int dev = 0;
   BSRL_CUDA_OK(cudaGetDevice(&dev));
@@ -509,13 +536,14 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
   p.n_tiles = (int)((a.n_envs + EPT - 1) / EPT);
   p.bias = a.bg; p.key_bias = a.key_bias; p.out = a.out; p.ldo = a.ldo;
   p.v_out = a.v_out; p.v0 = a.v0; p.vres = a.vres;
+  p.out_tma = out_tma ? 1 : 0;
   p.status = status;
   const int grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
   const bool vres = a.v_out || a.v0;
-  if (dh == 32 && !vres) attn_block_kernel<32, 2, false><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, p);
-  else if (dh == 32) attn_block_kernel<32, 2, true><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, p);
-  else if (!vres) attn_block_kernel<48, 1, false><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, p);
-  else attn_block_kernel<48, 1, true><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, p);
+  if (dh == 32 && !vres) attn_block_kernel<32, 2, false><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
+  else if (dh == 32) attn_block_kernel<32, 2, true><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
+  else if (!vres) attn_block_kernel<48, 1, false><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
+  else attn_block_kernel<48, 1, true><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
   BSRL_LAUNCH_OK("attn_block_kernel");
   return BSRL_OK;
 }
