@@ -114,7 +114,8 @@ __device__ __forceinline__ float rcp_approx(float x) {
 // addresses (shared window) of the pair's first row / first column; rows are LDQ bytes apart.
 // The MT 16-row query tiles are processed side by side: two independent dependency chains per warp
 // (the kernel is latency-bound here) and each K / V fragment is fetched once for both.
-template <int MT, int DH, int LDQ, bool STAGE_OUT>
+// OB: bytes per row of the staged group output (128: two heads of 32, swizzled; 96: one head of 48, dense)
+template <int MT, int DH, int LDQ, int OB>
 __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t sv, const float (&kb)[4][2],
                                             int n_q, __half* out_env, int ldo, int lane, uint8_t* so, int so_row0, int so_piece0 TRACE_PARAMS) {
   const int g = lane >> 2, tig = lane & 3;
@@ -211,14 +212,14 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int qrow = mt * 16 + g + r * 8;
-      if (STAGE_OUT && qrow < n_q && so) {
-        // staged for the group's TMA store: 128-byte rows, 16-byte piece p of row r at ((p ^ (r & 7)) << 4);
-        // the 8 rows of a store instruction hit 32 different banks
+      if (qrow < n_q && so) {
+        // staged for the group's TMA store.  128-byte rows: 16-byte piece p of row r at ((p ^ (r & 7)) << 4),
+        // the 8 rows of a store instruction hit 32 different banks; 96-byte rows: dense (2-way conflicts)
         const int row = so_row0 + qrow;
-        uint8_t* orow = so + row * 128 + tig * 4;
+        uint8_t* orow = so + row * OB + tig * 4;
 #pragma unroll
         for (int nt = 0; nt < DH / 8; ++nt)
-          *reinterpret_cast<uint32_t*>(orow + (((so_piece0 + nt) ^ (row & 7)) << 4)) =
+          *reinterpret_cast<uint32_t*>(orow + (OB == 128 ? (((so_piece0 + nt) ^ (row & 7)) << 4) : ((so_piece0 + nt) << 4))) =
               pack_half2(o[mt][nt][r * 2], o[mt][nt][r * 2 + 1]);
       } else if (qrow < n_q) {
         __half* orow = out_env + (int64_t)qrow * ldo + tig * 2;
@@ -462,9 +463,9 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
                          sk_pair = rows + (GD + hh * DH) * 2, sv_pair = rows + (2 * GD + hh * DH) * 2;
           __half* out_pair = p.out + (env * p.n_q + mt_own * 16) * (int64_t)p.ldo + (g * G + hh) * DH;
           const int n_q = p.n_q - mt_own * 16;      // query rows left from this warp's first one
-          uint8_t* so_tile = (G == 2 && p.out_tma) ? sO_g : nullptr;
-          if (G == 2 && n_q > 16) attend_pair<2, DH, LDQ, G == 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * kT + mt_own * 16, hh * (DH / 8) TRACE_ARGS);
-          else if (n_q > 0) attend_pair<1, DH, LDQ, G == 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * kT + mt_own * 16, hh * (DH / 8) TRACE_ARGS);
+          uint8_t* so_tile = p.out_tma ? sO_g : nullptr;
+          if (G == 2 && n_q > 16) attend_pair<2, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * kT + mt_own * 16, hh * (DH / 8) TRACE_ARGS);
+          else if (n_q > 0) attend_pair<1, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * kT + mt_own * 16, hh * (DH / 8) TRACE_ARGS);
         }
         TRACE(230 + g);
         __syncwarp();
@@ -516,10 +517,10 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
   CUtensorMap tm_h, tm_w;
   if (!make_tmap_f16(&tm_h, a.h, a.n_envs * kT, a.d, a.ldh, BM)) return BSRL_ERR_CUDA;
   if (!make_tmap_f16(&tm_w, a.wg, 3 * a.d, a.d, a.d, dh == 32 ? Shape<32, 2>::NG : Shape<48, 1>::NG)) return BSRL_ERR_CUDA;
-  // all 29 query rows of two heads of 32: a group's output is 116 contiguous rows x 128 bytes = one TMA store
-  const bool out_tma = dh == 32 && a.q_first == 0 && a.n_q == kT && a.n_envs * kT <= 0x7fffff00;
+  // all 29 query rows: a group's output is 116 contiguous rows x 128 (two heads of 32) or 96 bytes (one of 48) = one TMA store
+  const bool out_tma = a.q_first == 0 && a.n_q == kT && a.n_envs * kT <= 0x7fffff00;
   CUtensorMap tm_o = tm_h;
-  if (out_tma && !make_tmap_rows(&tm_o, a.out, 2, a.n_envs * kT, a.d, a.ldo, ROWS, 128)) return BSRL_ERR_CUDA;
+  if (out_tma && !make_tmap_rows(&tm_o, a.out, 2, a.n_envs * kT, a.d, a.ldo, ROWS, dh == 32 ? 128 : 96)) return BSRL_ERR_CUDA;
   static bool attr_set[64] = {};
   int dev = 0;
   BSRL_CUDA_OK(cudaGetDevice(&dev));

@@ -260,7 +260,7 @@ bool make_tmap_f16(CUtensorMap* map, const void* base, int64_t rows, int64_t col
 // 16-byte piece p of row r at r * 64 + ((p ^ ((r >> 1) & 3)) << 4)).
 bool make_tmap_rows64(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows, int64_t cols,
                       int64_t ld_elems, int box_rows);
-// The same with rows of row_bytes = 64 or 128 bytes (64- / 128-byte swizzle).
+// The same with rows of row_bytes = 64 or 128 bytes (64- / 128-byte swizzle), or any other multiple of 16 (dense rows, no swizzle).
 bool make_tmap_rows(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows, int64_t cols,
                     int64_t ld_elems, int box_rows, int row_bytes);
 
