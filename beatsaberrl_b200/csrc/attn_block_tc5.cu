@@ -17,8 +17,8 @@
 //
 // HBM traffic per token: read h (2d B), write att (2d B).  Replaces fp16_packed_linear + attn29 /
 // packed_sdpa (python/policy.py:586-600, :645-692; python/beat_arena_env/csrc/small_attn.cu).
-// With all 29 query rows and two heads of 32 per group, the group's output (116 rows x 128 bytes) is staged
-// in shared memory and leaves as one TMA store.  All waits are bounded (tc5.cuh).
+// With all 29 query rows, the group's output (116 rows x 128 bytes for two heads of 32, x 96 bytes for one
+// head of 48) is staged in shared memory and leaves as one TMA store.  All waits are bounded (tc5.cuh).
 #include "kernels.cuh"
 #include "tc5.cuh"
 
