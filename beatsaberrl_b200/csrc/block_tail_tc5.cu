@@ -11,15 +11,17 @@
 // (2d B each) -- against 18 d^2 FLOP, i.e. tensor-bound.
 //
 // Layout of one CTA (persistent, one per SM, 352 threads):
-//   warp 0       TMA producer: att tile -> sA (d/64 chunks of [128 x 64], 128B swizzle);
-//                weight tiles -> a 3-stage ring of 32 KB stages, in the MMA's consumption order
-//   warp 10      TMA producer of the attention tiles (sA is freed before the tile ends); pulls the
-//                next tile's residual rows into L2
+//   warp 0       TMA producer of the weight tiles: a 3-stage ring of 32 KB stages, in the MMA's
+//                consumption order
+//   warp 10      TMA producer of the attention tiles (att tile -> sA, d/64 chunks of [128 x 64], 128B
+//                swizzle; sA is freed before the tile ends); pulls the next tile's residual rows into L2
 //   warp 1       MMA issuer (one thread): tcgen05.mma, M = 128, K = 16
-//   warps 2..9   epilogue (two groups of four warps, each group owns half of the columns), thread = row: LayerNorm on TMEM rows -> h2 into sA; bias + ReLU of
-//                each 128-wide hidden chunk -> sH; final drain and LayerNorm outputs; all global
-//                traffic goes through a per-warp transposition buffer so that it is coalesced;
-//                the per-column parameters live in shared memory
+//   warps 2..9   epilogue (two groups of four warps, each group owns half of the columns), thread = row:
+//                LayerNorm on TMEM rows -> h2 into sA; bias + ReLU of each 128-wide hidden chunk -> sH;
+//                final drain and LayerNorm outputs.  Global traffic moves as per-warp TMA boxes (32 rows
+//                x 64 bytes) through three 2 KB swizzled buffers per warp -- residual rows in, fp32 and
+//                fp16 rows out; rows gathered through a row map fall back to coalesced loads through
+//                the staging buffer.  The per-column parameters live in shared memory.
 // TMEM (512 columns): region X (d columns) accumulates x1 and then xo in place -- x is
 // pre-stored there by the epilogue warps, so the out-projection and the FFN-down MMAs simply
 // accumulate onto it; the other 256 columns are two 128-column buffers for hidden chunks.  The

@@ -7,8 +7,9 @@
 //               shared-memory descriptors, accumulating in TMEM; two accumulator buffers of BN
 //               fp32 columns let tile t+1's MMAs overlap tile t's epilogue;
 //   warps 2..9  epilogue: tcgen05.ld the accumulator (thread = output row), add bias, ReLU,
-//               transpose through shared memory so stores (and the residual read) cover full
-//               128-byte lines; rows may be remapped on the way out.
+//               transpose through a per-warp swizzled staging block; dense residual-free outputs
+//               leave as one TMA store per block, remapped rows and residual adds as 16-byte
+//               stores that cover full 128-byte lines (residual pieces requested ahead).
 // All waits are bounded: a wait that runs out sets the library's device status word, raises
 // the CTA-wide abort flag, and every role falls through to the common teardown that frees TMEM.
 //
