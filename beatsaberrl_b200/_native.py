@@ -90,6 +90,13 @@ _sig = {
     "bsrl_profile_stage": (C.c_int, [C.c_int32, C.POINTER(C.c_double), C.POINTER(C.c_int64),
                                      C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "bsrl_embed": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, _P, _P, C.c_int64, _P]),
+    "bsrl_trunk_heads": (C.c_int, [_CFG, _P, _P, C.c_int64, _P, _P, _P, C.c_int64, _P]),
+    "bsrl_head_tail": (C.c_int, [_CFG, _P, _P, C.c_int64, _P, C.c_int32, _P, _P, _P, _P, _P, _P]),
+    "bsrl_head_layout": (C.c_int, [_CFG, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "bsrl_workspace_region": (C.c_int, [_CFG, C.c_int64, C.c_char_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64),
+                                        C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int32)]),
+    "bsrl_standin_env_step": (C.c_int, [_P, C.c_int64, _P, _P, _P, _P, _P]),
+    "bsrl_selftest_wait_timeout": (C.c_int, [C.c_int32, _P]),
     "bsrl_layernorm": (C.c_int, [_P, _P, _P, C.c_float, C.c_int64, C.c_int32, _P, C.c_int64, _P]),
     "bsrl_linear": (C.c_int, [_P, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
                               C.c_int32, _P]),
@@ -106,8 +113,6 @@ for _name, (_res, _args) in _sig.items():
 import os as _os
 if _os.environ.get("BSRL_ENGINE", "") == "mma":      # cross-check runs: warp-MMA kernels only
     lib.bsrl_set_engine(1)
-elif _os.environ.get("BSRL_ENGINE", "") == "pair":    # fused block tail on two-CTA clusters
-    lib.bsrl_set_engine(2)
 
 
 def last_error() -> str:

@@ -6,6 +6,7 @@
 // in a CUDA graph next to the simulator's step kernel (python/rollout_graph.py:45-74).
 #include <string.h>
 
+#include <atomic>
 #include <vector>
 
 #include "kernels.cuh"
@@ -52,8 +53,10 @@ struct Profiler {
   }
   void reset() { recs.clear(); used = 0; }
 };
-Profiler g_prof;
-int g_stage = kStGather;   // stage label of the launches that follow
+// Per host thread: each thread that enables the profiler times its own forwards, and forwards
+// running on other threads are not affected.
+thread_local Profiler g_prof;
+thread_local int g_stage = kStGather;   // stage label of the launches that follow
 
 double linear_bytes(const LinearArgs& p) {
   double b = (double)p.M * p.K * 2 + (double)p.N * p.K * 2 + (double)p.M * p.N * (p.out_f32 ? 4 : 2);
@@ -74,11 +77,13 @@ int timed(cudaStream_t st, double flops, double bytes, Fn&& fn) {
 }
 
 // engine choice for one linear layer: tcgen05 where the shape fits, warp-MMA otherwise
-int g_engine = 0;   // 0 = automatic, 1 = warp-MMA kernel only (cross-check runs)
-int g_pair = 0;     // fused block tail on two-CTA clusters (cta_group::2): validated, measured slower, off by default
+// 0 = automatic, 1 = warp-MMA kernel only (cross-check runs).  Process-wide test knob: set it before
+// the first forward; each forward reads it once (Ctx::engine), so a change never splits a forward.
+std::atomic<int> g_engine{0};
+thread_local int g_call_engine = 0;   // the engine of the forward running on this thread
 int linear(const LinearArgs& p, cudaStream_t st) {
   return timed(st, 2.0 * p.M * p.N * p.K, linear_bytes(p), [&] {
-    if (g_engine == 0 && p.M >= 128 && linear_tc5_ok(p)) return linear_tc5(p, st);
+    if (g_call_engine == 0 && p.M >= 128 && linear_tc5_ok(p)) return linear_tc5(p, st);
     return linear_mma(p, st);
   });
 }
@@ -125,6 +130,7 @@ int fused_attn(const AttnBlockArgs& a, cudaStream_t st) {
 struct Ctx {
   const bsrl_config* cfg;
   Layout l;
+  Paths paths;
   Workspace w;
   const void* arena;
   void* ws;
@@ -187,6 +193,51 @@ int run_embed(const Ctx& c, const void* obs, int obs_dtype, float* x, float* key
   return BSRL_OK;
 }
 
+// head sizes, packed-column offsets and value bins of the configuration
+void head_shape(const bsrl_config& cfg, const Layout& l, HeadTailArgs& t) {
+  t.bins = l.bins; t.vmax = cfg.value_vmax; t.k_max = l.k_max;
+  for (int j = 0; j < kActHeads; ++j) {
+    t.gears[j] = cfg.head_gears[j];
+    t.first[j] = l.head_first[j];
+  }
+}
+
+// readout (B, 5d) f16 -> SimBa / SimBaV2 trunk -> h (f16, in z[:, d:]) -> packed head outputs raw (B, head_cols_pad) f32
+// (NotePolicy._trunk + the packed head GEMM, python/policy.py:1107-1155, :1311-1335)
+int run_trunk(const Ctx& c, const __half* lead16, float* raw) {
+  const Layout& l = c.l;
+  const Workspace& w = c.w;
+  const int d = l.d, D = l.D;
+  const int64_t B = c.B;
+  const float eps = c.cfg->eps;
+  const RowMap ident = identity_map();
+  float* xt = at<float>(c.ws, w.xt);
+  __half* u = at<__half>(c.ws, w.u);
+  __half* r = at<__half>(c.ws, w.r);
+  __half* z = at<__half>(c.ws, w.z);
+  const int ldz = d + D;
+  g_stage = kStTrunk;
+  BSRL_TRY(linear(linear_args(lead16, kLead * d, c.W(l.trunk_proj), kLead * d, c.Bv(l.trunk_proj), xt, D, 1, 0, B, D, kLead * d), c.st));
+  if (l.trunk_v2) {
+    // SimBaV2 (python/policy.py:1140-1155): x = l2n(s_in W_in z); y = l2n(W2 relu(s_1 W1 x));
+    // x = l2n(x + alpha (y - x)); h = sqrt(D) x.  GEMMs on fp16 operands, everything else fp32.
+    float* t32 = at<float>(c.ws, w.t32);
+    BSRL_TRY(simba2_rows(0, xt, xt, at<float>(c.arena, l.v2_s_in), 0.f, B, D, u, D, c.st));
+    BSRL_TRY(linear(linear_args(u, D, c.W(l.trunk_fc1), D, c.Bv(l.trunk_fc1), t32, l.Hh, 1, 0, B, l.Hh, D), c.st));
+    BSRL_TRY(scale_relu_rows(t32, at<float>(c.arena, l.v2_s_1), B, l.Hh, r, c.st));
+    BSRL_TRY(linear(linear_args(r, l.Hh, c.W(l.trunk_fc2), l.Hh, c.Bv(l.trunk_fc2), t32, D, 1, 0, B, D, l.Hh), c.st));
+    BSRL_TRY(simba2_rows(1, t32, xt, at<float>(c.arena, l.v2_alpha), 0.5f * sqrtf((float)D), B, D, z + d, ldz, c.st));
+  } else {
+    BSRL_TRY(layernorm(xt, D, ident, c.G(l.trunk_ln1), c.Be(l.trunk_ln1), eps, B, D, u, D, c.st));
+    BSRL_TRY(linear(linear_args(u, D, c.W(l.trunk_fc1), D, c.Bv(l.trunk_fc1), r, l.Hh, 0, 1, B, l.Hh, D), c.st));
+    LinearArgs p2 = linear_args(r, l.Hh, c.W(l.trunk_fc2), l.Hh, c.Bv(l.trunk_fc2), xt, D, 1, 0, B, D, l.Hh);
+    p2.R = xt; p2.ldr = D;
+    BSRL_TRY(linear(p2, c.st));
+    BSRL_TRY(layernorm(xt, D, ident, c.G(l.trunk_ln2), c.Be(l.trunk_ln2), eps, B, D, z + d, ldz, c.st));
+  }
+  return linear(linear_args(z + d, ldz, c.W(l.heads), D, c.Bv(l.heads), raw, l.head_cols_pad, 1, 0, B, l.head_cols_pad, D), c.st);
+}
+
 int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs& tail_in) {
   const Layout& l = c.l;
   const Workspace& w = c.w;
@@ -196,9 +247,9 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   float* x = at<float>(c.ws, w.x);
   float* key_bias = at<float>(c.ws, w.key_bias);
   __half* h = at<__half>(c.ws, w.h);
-  __half* qkv = at<__half>(c.ws, w.qkv);
+  __half* qkv = w.qkv >= 0 ? at<__half>(c.ws, w.qkv) : nullptr;   // unfused attention path only
   __half* att = at<__half>(c.ws, w.att);
-  __half* hid = at<__half>(c.ws, w.hid);
+  __half* hid = w.hid >= 0 ? at<__half>(c.ws, w.hid) : nullptr;   // unfused FFN path only
   const RowMap lead_rows{kLead, kT, 0};
   const RowMap ident = identity_map();
 
@@ -218,13 +269,12 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     a.w0 = c.W(b.up); a.b0 = c.Bv(b.up);
     a.w2 = c.W(b.down); a.b2 = c.Bv(b.down);
     a.eps = eps;
-    a.pair = g_pair;
     return a;
   };
-  bool fused = false;
-  {
-    BlockTailArgs probe = tail_args(l.blocks[0], R);
-    fused = g_engine == 0 && block_tail_ok(probe);
+  const bool fused = c.paths.tail_fused;
+  if (fused && !block_tail_ok(tail_args(l.blocks[0], R))) {
+    set_error("forward: the fused block-tail kernel does not take this shape (d=%d, F=%d)", d, F);
+    return BSRL_ERR_UNSUPPORTED;
   }
   // Fused q|k|v projection + attention where head_dim is 32 (weights regrouped per head pair).
   auto attn_args = [&](const __half* rows, const Mat& wg, int q_first, int n_q, __half* out) {
@@ -236,7 +286,11 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     a.out = out; a.ldo = d;
     return a;
   };
-  const bool fused_qkv = g_engine == 0 && l.attn_G > 0 && attn_block_ok(attn_args(h, l.blocks[0].qkv_g, 0, kT, att));
+  const bool fused_qkv = c.paths.attn_fused;
+  if (fused_qkv && !attn_block_ok(attn_args(h, l.blocks[0].qkv_g, 0, kT, att))) {
+    set_error("forward: the fused attention kernel does not take this shape (d=%d, heads=%d)", d, l.H);
+    return BSRL_ERR_UNSUPPORTED;
+  }
   __half* hv = at<__half>(c.ws, w.enc_hid);   // critic LayerNorm rows (encoder scratch is free by now)
   bool have_h = false, have_hv = false;
   // value residual (python/policy.py:1263-1275): block 0 hands its attention values to every later block
@@ -338,33 +392,11 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     }
   }
 
-  // SimBa trunk on the (B, 5d) readout; its output h lands in z[:, d:]
-  float* xt = at<float>(c.ws, w.xt);
-  __half* u = at<__half>(c.ws, w.u);
-  __half* r = at<__half>(c.ws, w.r);
+  // SimBa trunk on the (B, 5d) readout; its output h lands in z[:, d:]; then the packed heads
   __half* z = at<__half>(c.ws, w.z);
   const int ldz = d + D;
-  g_stage = kStTrunk;
-  BSRL_TRY(linear(linear_args(lead16, kLead * d, c.W(l.trunk_proj), kLead * d, c.Bv(l.trunk_proj), xt, D, 1, 0, B, D, kLead * d), c.st));
-  if (l.trunk_v2) {
-    // SimBaV2 (python/policy.py:1140-1155): x = l2n(s_in W_in z); y = l2n(W2 relu(s_1 W1 x));
-    // x = l2n(x + alpha (y - x)); h = sqrt(D) x.  GEMMs on fp16 operands, everything else fp32.
-    float* t32 = at<float>(c.ws, w.t32);
-    BSRL_TRY(simba2_rows(0, xt, xt, at<float>(c.arena, l.v2_s_in), 0.f, B, D, u, D, c.st));
-    BSRL_TRY(linear(linear_args(u, D, c.W(l.trunk_fc1), D, c.Bv(l.trunk_fc1), t32, l.Hh, 1, 0, B, l.Hh, D), c.st));
-    BSRL_TRY(scale_relu_rows(t32, at<float>(c.arena, l.v2_s_1), B, l.Hh, r, c.st));
-    BSRL_TRY(linear(linear_args(r, l.Hh, c.W(l.trunk_fc2), l.Hh, c.Bv(l.trunk_fc2), t32, D, 1, 0, B, D, l.Hh), c.st));
-    BSRL_TRY(simba2_rows(1, t32, xt, at<float>(c.arena, l.v2_alpha), 0.5f * sqrtf((float)D), B, D, z + d, ldz, c.st));
-  } else {
-    BSRL_TRY(layernorm(xt, D, ident, c.G(l.trunk_ln1), c.Be(l.trunk_ln1), eps, B, D, u, D, c.st));
-    BSRL_TRY(linear(linear_args(u, D, c.W(l.trunk_fc1), D, c.Bv(l.trunk_fc1), r, l.Hh, 0, 1, B, l.Hh, D), c.st));
-    LinearArgs p2 = linear_args(r, l.Hh, c.W(l.trunk_fc2), l.Hh, c.Bv(l.trunk_fc2), xt, D, 1, 0, B, D, l.Hh);
-    p2.R = xt; p2.ldr = D;
-    BSRL_TRY(linear(p2, c.st));
-    BSRL_TRY(layernorm(xt, D, ident, c.G(l.trunk_ln2), c.Be(l.trunk_ln2), eps, B, D, z + d, ldz, c.st));
-  }
   float* raw = at<float>(c.ws, w.raw);
-  BSRL_TRY(linear(linear_args(z + d, ldz, c.W(l.heads), D, c.Bv(l.heads), raw, l.head_cols_pad, 1, 0, B, l.head_cols_pad, D), c.st));
+  BSRL_TRY(run_trunk(c, lead16, raw));
 
   // adapool critic over the resolved stream entering the final block (still in x)
   __half* att_c = at<__half>(c.ws, w.att_c);
@@ -395,11 +427,7 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   HeadTailArgs t = tail_in;
   t.raw = raw; t.ld_raw = l.head_cols_pad;
   t.vraw = vraw; t.ld_v = l.bins_pad;
-  t.bins = l.bins; t.vmax = c.cfg->value_vmax; t.k_max = l.k_max;
-  for (int j = 0; j < kActHeads; ++j) {
-    t.gears[j] = c.cfg->head_gears[j];
-    t.first[j] = l.head_first[j];
-  }
+  head_shape(*c.cfg, l, t);
   t.n_envs = B;
   g_stage = kStHeadTail;
   return timed(c.st, 0.0, (double)B * 4 * (l.head_cols_pad + l.bins_pad + kActHeads * l.k_max + 1),
@@ -423,7 +451,9 @@ int make_ctx(Ctx& c, const bsrl_config* cfg, const void* arena, int64_t n_envs, 
   }
   c.cfg = cfg;
   c.l = make_layout(*cfg);
-  c.w = make_workspace(c.l, n_envs);
+  g_call_engine = g_engine.load(std::memory_order_relaxed);
+  c.paths = plan_paths(c.l, g_call_engine);
+  c.w = make_workspace(c.l, n_envs, c.paths);
   if (ws_bytes < c.w.bytes) {
     set_error("forward: workspace %lld bytes < required %lld", (long long)ws_bytes, (long long)c.w.bytes);
     return BSRL_ERR_WORKSPACE;
@@ -538,7 +568,7 @@ int64_t bsrl_workspace_bytes(const bsrl_config* cfg, int64_t n_envs) {
   if (validate_config(cfg) != BSRL_OK) return -1;
   if (n_envs < 0) return -1;
   Layout l = make_layout(*cfg);
-  return make_workspace(l, n_envs).bytes;
+  return make_workspace(l, n_envs, plan_paths(l, g_engine.load(std::memory_order_relaxed))).bytes;
 }
 
 int bsrl_forward(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype,
@@ -653,18 +683,19 @@ int32_t bsrl_token_lane(int32_t tok, int32_t k) { return token_lane_host(tok, k)
 static __device__ __align__(256) unsigned char g_fixed_scratch[BSRL_FIXED_SCRATCH_BYTES];
 
 static int fixed_scratch_ptr(void** out) {
-  static void* cached[64] = {};
+  static DeviceOnce once;
+  static void* cached[kMaxDevices] = {};
+  BSRL_TRY(once.run("forward_fixed: scratch address", [] {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_fixed_scratch);   // address on the CURRENT device
+    if (e == cudaSuccess) cached[dev] = ptr;
+    return e;
+  }));
   int dev = 0;
   BSRL_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) {
-    set_error("forward_fixed: device ordinal %d not supported", dev);
-    return BSRL_ERR_UNSUPPORTED;
-  }
-  if (!cached[dev]) {
-    void* ptr = nullptr;
-    BSRL_CUDA_OK(cudaGetSymbolAddress(&ptr, g_fixed_scratch));   // address on the CURRENT device
-    cached[dev] = ptr;
-  }
   *out = cached[dev];
   return BSRL_OK;
 }
@@ -678,7 +709,7 @@ int bsrl_forward_fixed(const bsrl_config* cfg, const void* arena, const void* ob
     set_error("forward_fixed: n_envs %lld is negative", (long long)n_envs);
     return BSRL_ERR_SHAPE;
   }
-  const int64_t need = make_workspace(make_layout(*cfg), n_envs).bytes;
+  const int64_t need = bsrl_workspace_bytes(cfg, n_envs);
   if (need > BSRL_FIXED_SCRATCH_BYTES) {
     set_error("forward_fixed: %lld envs need %lld bytes of scratch, the built-in scratch holds %lld; "
               "use bsrl_forward with a caller workspace for larger batches",
@@ -694,12 +725,11 @@ int bsrl_forward_fixed(const bsrl_config* cfg, const void* arena, const void* ob
 }
 
 int bsrl_set_engine(int32_t engine) {
-  if (engine < 0 || engine > 2) {
-    set_error("set_engine: 0 (automatic), 1 (warp-MMA only) or 2 (automatic, block tail on CTA pairs)");
+  if (engine < 0 || engine > 1) {
+    set_error("set_engine: 0 (automatic) or 1 (warp-MMA only)");
     return BSRL_ERR_UNSUPPORTED;
   }
-  g_engine = engine == 1 ? 1 : 0;
-  g_pair = engine == 2 ? 1 : 0;
+  g_engine.store(engine, std::memory_order_relaxed);
   return BSRL_OK;
 }
 
@@ -762,6 +792,104 @@ int bsrl_embed(const bsrl_config* cfg, const void* arena, const void* obs, int32
   return run_embed(c, obs, obs_dtype, x, key_bias);
 }
 
+int bsrl_trunk_heads(const bsrl_config* cfg, const void* arena, const void* readout_f16, int64_t n_envs,
+                     float* head_out, void* trunk_h_f16, void* workspace, int64_t workspace_bytes, void* stream) {
+  Ctx c;
+  BSRL_TRY(make_ctx(c, cfg, arena, n_envs, workspace, workspace_bytes, stream));
+  if (!readout_f16 || !head_out) {
+    set_error("trunk_heads: NULL readout / head_out");
+    return BSRL_ERR_NULL;
+  }
+  if (!aligned16(readout_f16) || !aligned16(head_out) || (trunk_h_f16 && !aligned16(trunk_h_f16))) {
+    set_error("trunk_heads: readout, head_out and trunk_h must be 16-byte aligned");
+    return BSRL_ERR_ALIGN;
+  }
+  if (n_envs == 0) return BSRL_OK;
+  BSRL_TRY(run_trunk(c, static_cast<const __half*>(readout_f16), head_out));
+  if (trunk_h_f16) {   // h sits in the workspace as the right-hand columns of the critic MLP's input rows
+    const int d = c.l.d, D = c.l.D;
+    BSRL_CUDA_OK(cudaMemcpy2DAsync(trunk_h_f16, (size_t)D * 2, at<__half>(c.ws, c.w.z) + d, (size_t)(d + D) * 2,
+                                   (size_t)D * 2, (size_t)n_envs, cudaMemcpyDeviceToDevice, c.st));
+  }
+  return BSRL_OK;
+}
+
+int bsrl_head_tail(const bsrl_config* cfg, const float* head_out, const float* value_bin_logits, int64_t n_envs,
+                   const void* actions, int32_t act_dtype, float* logits, float* logprob, float* entropy,
+                   float* ent_head, float* value, void* stream) {
+  BSRL_TRY(validate_config(cfg));
+  if (!head_out || !value_bin_logits || !value) {
+    set_error("head_tail: NULL head_out / value_bin_logits / value");
+    return BSRL_ERR_NULL;
+  }
+  if (n_envs < 0) {
+    set_error("head_tail: n_envs %lld is negative", (long long)n_envs);
+    return BSRL_ERR_SHAPE;
+  }
+  Layout l = make_layout(*cfg);
+  HeadTailArgs t;
+  memset(&t, 0, sizeof(t));
+  t.raw = head_out; t.ld_raw = l.head_cols_pad;
+  t.vraw = value_bin_logits; t.ld_v = l.bins_pad;
+  head_shape(*cfg, l, t);
+  t.actions = actions; t.act_dtype = act_dtype;
+  t.logits = logits; t.logprob = logprob; t.entropy = entropy; t.ent_head = ent_head; t.value = value;
+  t.n_envs = n_envs;
+  return head_tail(t, as_stream(stream));
+}
+
+int bsrl_head_layout(const bsrl_config* cfg, int32_t* head_cols_pad, int32_t* bins_pad, int32_t* head_first) {
+  BSRL_TRY(validate_config(cfg));
+  Layout l = make_layout(*cfg);
+  if (head_cols_pad) *head_cols_pad = l.head_cols_pad;
+  if (bins_pad) *bins_pad = l.bins_pad;
+  if (head_first)
+    for (int j = 0; j < kActHeads; ++j) head_first[j] = l.head_first[j];
+  return BSRL_OK;
+}
+
+int bsrl_workspace_region(const bsrl_config* cfg, int64_t n_envs, const char* name, int64_t* byte_offset,
+                          int64_t* rows, int64_t* cols, int64_t* ld_elems, int32_t* dtype) {
+  BSRL_TRY(validate_config(cfg));
+  if (!name || n_envs < 0) {
+    set_error("workspace_region: NULL name or negative n_envs");
+    return BSRL_ERR_NULL;
+  }
+  Layout l = make_layout(*cfg);
+  Workspace w = make_workspace(l, n_envs, plan_paths(l, g_engine.load(std::memory_order_relaxed)));
+  int64_t off = -1, r = 0, cc = 0, ld = 0;
+  int32_t dt = BSRL_F16;
+  if (!strcmp(name, "trunk_h")) { off = w.z + (int64_t)l.d * 2; r = n_envs; cc = l.D; ld = l.d + l.D; }
+  else if (!strcmp(name, "x_resolved")) { off = w.x; r = n_envs * kT; cc = l.d; ld = l.d; dt = BSRL_F32; }
+  else if (!strcmp(name, "key_bias")) { off = w.key_bias; r = n_envs; cc = kT; ld = kT; dt = BSRL_F32; }
+  else if (!strcmp(name, "readout")) { off = w.lead16; r = n_envs; cc = kLead * l.d; ld = kLead * l.d; }
+  else if (!strcmp(name, "head_out")) { off = w.raw; r = n_envs; cc = l.head_cols_pad; ld = l.head_cols_pad; dt = BSRL_F32; }
+  else {
+    set_error("workspace_region: unknown region '%s' (trunk_h, x_resolved, key_bias, readout, head_out)", name);
+    return BSRL_ERR_UNSUPPORTED;
+  }
+  if (byte_offset) *byte_offset = off;
+  if (rows) *rows = r;
+  if (cols) *cols = cc;
+  if (ld_elems) *ld_elems = ld;
+  if (dtype) *dtype = dt;
+  return BSRL_OK;
+}
+
+int bsrl_selftest_wait_timeout(int32_t polls, void* stream) {
+  if (polls < 1 || polls > (1 << 20)) {
+    set_error("selftest_wait_timeout: polls must be in [1, 2^20]");
+    return BSRL_ERR_SHAPE;
+  }
+  return wait_selftest((uint32_t)polls, as_stream(stream));
+}
+
+int bsrl_standin_env_step(const int64_t* actions, int64_t n_envs, uint32_t* state, float* obs, float* reward,
+                          uint8_t* done, void* stream) {
+  return standin_env_step(reinterpret_cast<const long long*>(actions), n_envs, state, obs, reward, done,
+                          as_stream(stream));
+}
+
 int bsrl_layernorm(const float* x, const float* gamma, const float* beta, float eps, int64_t rows,
                    int32_t d, void* y_f16, int64_t ldy, void* stream) {
   return layernorm_rows(x, d, identity_map(), gamma, beta, eps, rows, d, static_cast<__half*>(y_f16), ldy,
@@ -802,7 +930,6 @@ int bsrl_block_tail(const void* att_f16, const float* x, const void* wo_f16, con
   a.eps = eps;
   a.x_out = x_out;
   a.out16[0] = static_cast<__half*>(ln_out_f16); a.ld16[0] = d; a.g16[0] = out_g; a.b16[0] = out_b;
-  a.pair = g_pair;
   return block_tail(a, as_stream(stream));
 }
 

@@ -158,13 +158,11 @@ template <int DH>
 int launch(const __half* qkv, int ld, const float* key_bias, int64_t n_envs, int d, int n_heads,
            int q_first, int n_q, __half* out, int ldo, cudaStream_t stream) {
   constexpr int smem = kWarps * 3 * kRows * (DH + 8) * 2;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  BSRL_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_set[dev]) {
-    BSRL_CUDA_OK(cudaFuncSetAttribute(attn29_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set[dev] = true;
-  }
+  static DeviceOnce once;
+  int rc = once.run("attn29_kernel set-up", [] {
+    return cudaFuncSetAttribute(attn29_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  });
+  if (rc != BSRL_OK) return rc;
   int64_t pairs = n_envs * n_heads;
   int64_t blocks = (pairs + kWarps - 1) / kWarps;
   int64_t cap = (int64_t)sm_count() * 8;

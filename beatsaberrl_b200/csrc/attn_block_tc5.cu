@@ -70,30 +70,6 @@ struct Params {
   int* status;
 };
 
-#ifdef BSRL_TRACE
-// Timeline instrumentation (debug builds only): per-thread slots of (tag, clock) records, plain stores.
-constexpr int TRACE_SLOTS = 10, TRACE_CAP = 2048;
-__device__ long long g_trace[TRACE_SLOTS * TRACE_CAP * 2];
-__device__ int g_trace_cnt[TRACE_SLOTS];
-__device__ __forceinline__ void trace(int slot, uint32_t& n, int tag) {
-  if (blockIdx.x != 0 || slot < 0 || n >= (uint32_t)TRACE_CAP) return;
-  long long* e = g_trace + ((size_t)slot * TRACE_CAP + n) * 2;
-  e[0] = tag;
-  e[1] = clock64();
-  ++n;
-  g_trace_cnt[slot] = (int)n;
-}
-#define TRACE_INIT(slot) const int tr_slot = (slot); uint32_t tr_n = 0;
-#define TRACE(tag) trace(tr_slot, tr_n, tag)
-#define TRACE_PARAMS , int tr_slot, uint32_t& tr_n
-#define TRACE_ARGS , tr_slot, tr_n
-#else
-#define TRACE_PARAMS
-#define TRACE_ARGS
-#define TRACE_INIT(slot)
-#define TRACE(tag)
-#endif
-
 __device__ __forceinline__ void give_up(Shared* sh, int* status, int role) {
   atomicCAS(status, 0, KERNEL_ID * 16 + role);
   sh->abort = 1;
@@ -117,7 +93,7 @@ __device__ __forceinline__ float rcp_approx(float x) {
 // OB: bytes per row of the staged group output (128: two heads of 32, swizzled; 96: one head of 48, dense)
 template <int MT, int DH, int LDQ, int OB>
 __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t sv, const float (&kb)[4][2],
-                                            int n_q, __half* out_env, int ldo, int lane, uint8_t* so, int so_row0, int so_piece0 TRACE_PARAMS) {
+                                            int n_q, __half* out_env, int ldo, int lane, uint8_t* so, int so_row0, int so_piece0) {
   const int g = lane >> 2, tig = lane & 3;
   const float scale = rsqrtf((float)DH) * 1.4426950408889634f;   // 1/sqrt(dh) * log2(e)
   float s[MT][4][4];
@@ -145,7 +121,6 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
       }
     }
   }
-  TRACE(251);
   uint32_t pa[MT][2][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
@@ -184,7 +159,6 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
       pa[mt][ks][3] = pack_half2(s[mt][2 * ks + 1][2] * sum[1], s[mt][2 * ks + 1][3] * sum[1]);
     }
   }
-  TRACE(252);
   float o[MT][DH / 8][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
@@ -206,7 +180,6 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
       }
     }
   }
-  TRACE(253);
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -327,7 +300,6 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
       uint32_t it = 0, tile_i = 0, gi = 0;
       bool ok = true;
       const uint32_t idesc = idesc_f16(BM, NG);
-      TRACE_INIT(0);
       for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_i) {
         for (int g = 0; g < n_groups && ok; ++g, ++gi) {
           const int buf = gi & 1;
@@ -337,7 +309,6 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
           // over, so that it runs while the workers drain the previous group instead.
           if (gi >= 2 && !mbar_wait(smem_u32(&sh->attn_done[buf]), ((gi - 2) >> 1) & 1, abort)) { give_up(sh, p.status, 10); ok = false; break; }
           tc_fence_after();
-          TRACE(100 + g);
           const uint32_t d_tmem = tmem_base + buf * 256;
           for (int kb = 0; kb < KB; ++kb, ++it) {
             if (g == 0 && !mbar_wait(smem_u32(&sh->a_full[kb]), tile_i & 1, abort)) { give_up(sh, p.status, 6); ok = false; break; }
@@ -351,7 +322,6 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
             if (g == n_groups - 1) tc_commit(smem_u32(&sh->a_free[kb]));
           }
           if (ok) tc_commit(smem_u32(&sh->acc_full[buf]));
-          TRACE(110 + g);
         }
       }
       tc_commit(smem_u32(&sh->mma_done));
@@ -373,7 +343,6 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
     uint32_t gi = 0;
     bool ok = true;
     const float vres_a = (VRES && p.vres) ? p.vres[0] : 1.f, vres_b = (VRES && p.vres) ? p.vres[1] : 0.f;
-    TRACE_INIT(lane == 0 ? wi + 1 : -1);
     for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
       const int64_t env = (int64_t)t * EPT + env_l;
       // this lane's key-bias values (keys nt * 8 + tig * 2 + e of the m16n8 accumulator layout, times
@@ -393,7 +362,6 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
         // the abort flag ahead of a barrier.
         if (!mbar_wait_warp(smem_u32(&sh->acc_full[buf]), (gi >> 1) & 1, abort) && lane == 0) give_up(sh, p.status, 9);
         tc_fence_after();
-        TRACE(200 + g);
         {
           const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + u_first * 16;
           const float* bias_u = s_bias + g * NG + u_first * 16;
@@ -449,10 +417,8 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[buf]));     // the TMEM buffer may be refilled
         if (wi == 0 && lane == 0) sh->quit = *abort;
-        TRACE(210 + g);
         if (p.out_tma && wi == 0 && lane == 0) bulk_wait_read<0>();     // the previous group's output store has read sO
         asm volatile("bar.sync 1, %0;" ::"n"(WORKERS * 32) : "memory");  // q|k|v tile complete
-        TRACE(220 + g);
         if (*reinterpret_cast<volatile int*>(&sh->quit)) {
           ok = false;
           break;
@@ -464,10 +430,9 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
           __half* out_pair = p.out + (env * p.n_q + mt_own * 16) * (int64_t)p.ldo + (g * G + hh) * DH;
           const int n_q = p.n_q - mt_own * 16;      // query rows left from this warp's first one
           uint8_t* so_tile = p.out_tma ? sO_g : nullptr;
-          if (G == 2 && n_q > 16) attend_pair<2, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * kT + mt_own * 16, hh * (DH / 8) TRACE_ARGS);
-          else if (n_q > 0) attend_pair<1, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * kT + mt_own * 16, hh * (DH / 8) TRACE_ARGS);
+          if (G == 2 && n_q > 16) attend_pair<2, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * kT + mt_own * 16, hh * (DH / 8));
+          else if (n_q > 0) attend_pair<1, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * kT + mt_own * 16, hh * (DH / 8));
         }
-        TRACE(230 + g);
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh->attn_done[buf]));
         if (p.out_tma) fence_proxy_async_smem();                         // this thread's sO writes -> the TMA engine
@@ -476,7 +441,6 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
           tma_store_2d(&tm_o, g * GD, t * ROWS, sO);
           bulk_commit();
         }
-        TRACE(240 + g);
       }
     }
     if (p.out_tma && wi == 0 && lane == 0) bulk_wait_all();   // the output stores are complete before the CTA exits
@@ -521,16 +485,16 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
   const bool out_tma = a.q_first == 0 && a.n_q == kT && a.n_envs * kT <= 0x7fffff00;
   CUtensorMap tm_o = tm_h;
   if (out_tma && !make_tmap_rows(&tm_o, a.out, 2, a.n_envs * kT, a.d, a.ldo, ROWS, dh == 32 ? 128 : 96)) return BSRL_ERR_CUDA;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  BSRL_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_set[dev]) {
-    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel<32, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<32, 2>::SMEM_BYTES));
-    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel<32, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<32, 2>::SMEM_BYTES));
-    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel<48, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<48, 1>::SMEM_BYTES));
-    BSRL_CUDA_OK(cudaFuncSetAttribute(attn_block_kernel<48, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<48, 1>::SMEM_BYTES));
-    attr_set[dev] = true;
-  }
+  static DeviceOnce once;
+  int rc = once.run("attn_block_kernel set-up", [] {
+    const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
+    cudaError_t e = cudaFuncSetAttribute(attn_block_kernel<32, 2, false>, at, Shape<32, 2>::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_block_kernel<32, 2, true>, at, Shape<32, 2>::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_block_kernel<48, 1, false>, at, Shape<48, 1>::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_block_kernel<48, 1, true>, at, Shape<48, 1>::SMEM_BYTES);
+    return e;
+  });
+  if (rc != BSRL_OK) return rc;
   Params p;
   p.d = a.d; p.n_heads = a.n_heads; p.q_first = a.q_first; p.n_q = a.n_q;
   p.n_envs = a.n_envs;
@@ -549,22 +513,5 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
   return BSRL_OK;
 }
 
-#ifdef BSRL_TRACE
-extern "C" int bsrl_trace_read_attn(long long* out, int cap) {
-  static long long host[TRACE_SLOTS * TRACE_CAP * 2];
-  int cnt[TRACE_SLOTS];
-  cudaMemcpyFromSymbol(cnt, g_trace_cnt, sizeof(cnt));
-  cudaMemcpyFromSymbol(host, g_trace, sizeof(host));
-  int n = 0;
-  for (int s = 0; s < TRACE_SLOTS; ++s)
-    for (int i = 0; i < cnt[s] && i < TRACE_CAP && n < cap; ++i, ++n) {
-      out[2 * n] = host[((size_t)s * TRACE_CAP + i) * 2] + 10000LL * s;
-      out[2 * n + 1] = host[((size_t)s * TRACE_CAP + i) * 2 + 1];
-    }
-  int zero[TRACE_SLOTS] = {};
-  cudaMemcpyToSymbol(g_trace_cnt, zero, sizeof(zero));
-  return n;
-}
-#endif
 
 }  // namespace bsrl

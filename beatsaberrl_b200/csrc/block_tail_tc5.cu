@@ -39,8 +39,8 @@ using namespace tc5;
 
 constexpr int BM = 128;          // rows per tile
 constexpr int HC = 128;          // hidden chunk width
-constexpr int RING_BYTES = 3 * 32768;      // weight ring: 3 stages of 32 KB (one CTA) or 6 of 16 KB (CTA pair)
-constexpr int MAX_STAGES = 6;
+constexpr int STAGES = 3, STAGE_BYTES = 32768;   // weight ring
+constexpr int RING_BYTES = STAGES * STAGE_BYTES;
 constexpr int CHUNK_BYTES = BM * 64 * 2;   // one [128 x 64] fp16 swizzled chunk
 constexpr int SA_BYTES = 4 * CHUNK_BYTES;  // d <= 256
 constexpr int SH_BYTES = 2 * CHUNK_BYTES;  // one 128 x 128 hidden chunk
@@ -55,7 +55,7 @@ constexpr int SMEM_BYTES = SA_BYTES + SH_BYTES + RING_BYTES + EPI_WARPS * STG_BY
 constexpr int KERNEL_ID = 2;
 
 struct Shared {
-  uint64_t w_full[MAX_STAGES], w_empty[MAX_STAGES];
+  uint64_t w_full[STAGES], w_empty[STAGES];
   uint64_t a_full, a_free, x_ready, o_done, h2_ready, x_done, mma_done;
   uint64_t acc1_full[2], hid_ready[2], hid_free[2];   // hid_*: per 64-column half of the hidden chunk
   uint64_t io_full[EPI_WARPS][3];                     // per epilogue warp: residual blocks landed in its buffers
@@ -86,27 +86,6 @@ struct TailParams {
   int* status;
 };
 
-#ifdef BSRL_TRACE
-// Timeline instrumentation (debug builds only): each traced thread appends (tag, clock) records to a
-// slot of its own with plain stores -- no atomics, so a record costs a few cycles, not a round trip.
-constexpr int TRACE_SLOTS = 10, TRACE_CAP = 2048;
-__device__ long long g_trace[TRACE_SLOTS * TRACE_CAP * 2];
-__device__ int g_trace_cnt[TRACE_SLOTS];
-__device__ __forceinline__ void trace(int slot, uint32_t& n, int tag, long long val = -1) {
-  if (blockIdx.x != 0 || slot < 0 || n >= (uint32_t)TRACE_CAP) return;
-  long long* e = g_trace + ((size_t)slot * TRACE_CAP + n) * 2;
-  e[0] = tag;
-  e[1] = val >= 0 ? val : clock64();
-  ++n;
-  g_trace_cnt[slot] = (int)n;
-}
-#define TRACE_INIT(slot) const int tr_slot = (slot); uint32_t tr_n = 0;
-#define TRACE(...) trace(tr_slot, tr_n, __VA_ARGS__)
-#else
-#define TRACE_INIT(slot)
-#define TRACE(...)
-#endif
-
 __device__ __forceinline__ void give_up(Shared* sh, int* status, int role) {
   atomicCAS(status, 0, KERNEL_ID * 16 + role);
   sh->abort = 1;
@@ -127,14 +106,12 @@ __device__ __forceinline__ void give_up(Shared* sh, int* status, int role) {
   }
 
 // four MMAs (K = 64) of one k-block: A chunk and B tile both [rows x 64] swizzled
-template <bool PAIR>
 __device__ __forceinline__ void mma_kblock(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc,
                                            bool acc_first) {
   const uint64_t ad = smem_desc_sw128(a_addr), bd = smem_desc_sw128(b_addr);
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    if (PAIR) mma_f16_ss_pair(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (acc_first || k) ? 1u : 0u);
-    else mma_f16_ss(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (acc_first || k) ? 1u : 0u);
+    mma_f16_ss(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (acc_first || k) ? 1u : 0u);
   }
 }
 
@@ -150,9 +127,6 @@ __device__ __forceinline__ void store_h32(uint8_t* chunks, int row, int col, con
   }
 }
 
-// CTAS = 1: one CTA per tile.  CTAS = 2: a cluster of two CTAs on two tiles; the leader's MMA thread
-// issues cta_group::2 MMAs (M = 256) for both, each CTA loads only its half of every weight tile.
-template <int CTAS>
 __global__ void __launch_bounds__(THREADS, 1)
 block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_constant__ CUtensorMap tm_wo,
                   const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w2,
@@ -163,17 +137,12 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw);
-  constexpr bool PAIR = CTAS == 2;
-  constexpr int STAGES = PAIR ? 6 : 3, STAGE_BYTES = RING_BYTES / STAGES;
-  const uint32_t rank = PAIR ? cluster_rank() : 0u;
-  const bool leader = rank == 0;
-  // tiles of this CTA: tile0, tile0 + tstep, ... < t_end (both CTAs of a pair make the same number of trips;
-  // a trailing odd tile is paired with an empty one whose rows are all >= M)
-  // (kept as expressions of the unsigned special registers rather than int variables: the single-CTA
+  // tiles of this CTA: tile0, tile0 + tstep, ... < t_end
+  // (kept as expressions of the unsigned special registers rather than int variables: the
   // kernel measured 11 % slower with them held in signed locals)
-#define tile0 (PAIR ? (int)(blockIdx.x & ~1u) + (int)rank : (int)blockIdx.x)
+#define tile0 ((int)blockIdx.x)
 #define tstep (gridDim.x)
-#define t_end (PAIR ? ((p.n_tiles + 1) & ~1) : p.n_tiles)
+#define t_end (p.n_tiles)
   const uint32_t sA = base, sH = base + SA_BYTES, ring = sH + SH_BYTES;
   uint8_t* sA_g = gen;
   uint8_t* sH_g = gen + SA_BYTES;
@@ -192,14 +161,14 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     }
     mbar_init(smem_u32(&sh->a_full), 1);
     mbar_init(smem_u32(&sh->a_free), 1);
-    mbar_init(smem_u32(&sh->x_ready), EPI_WARPS * CTAS);
+    mbar_init(smem_u32(&sh->x_ready), EPI_WARPS);
     mbar_init(smem_u32(&sh->o_done), 1);
-    mbar_init(smem_u32(&sh->h2_ready), EPI_WARPS * CTAS);
+    mbar_init(smem_u32(&sh->h2_ready), EPI_WARPS);
     mbar_init(smem_u32(&sh->x_done), 1);
     mbar_init(smem_u32(&sh->mma_done), 1);
     for (int b = 0; b < 2; ++b) mbar_init(smem_u32(&sh->acc1_full[b]), 1);
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&sh->hid_ready[b]), 4 * CTAS);
+      mbar_init(smem_u32(&sh->hid_ready[b]), 4);
       mbar_init(smem_u32(&sh->hid_free[b]), 1);
     }
     for (int w = 0; w < EPI_WARPS; ++w)
@@ -216,13 +185,8 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     tma_prefetch_desc(&tm_o1);
   }
   if (warp == 1) {
-    if (PAIR) {
-      tmem_alloc_pair(smem_u32(&sh->tmem_base), 512);
-      tmem_relinquish_pair();
-    } else {
-      tmem_alloc(smem_u32(&sh->tmem_base), 512);
-      tmem_relinquish();
-    }
+    tmem_alloc(smem_u32(&sh->tmem_base), 512);
+    tmem_relinquish();
   }
   // per-column parameters into shared memory: [bo | ln_g | ln_b | b2 | g16_0 | b16_0 | g16_1 | b16_1] (256
   // floats each) then b0 (F floats); absent vectors read as gamma = 1, beta = 0
@@ -239,24 +203,10 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
   for (int i = threadIdx.x; i < p.F; i += THREADS) prm[8 * 256 + i] = p.b0[i];
   tc_fence_before();
   __syncthreads();
-  if (PAIR) cluster_sync_all();     // the peer's barriers exist before anything is signalled across
   tc_fence_after();
-#ifdef BSRL_SKEW
-  {   // experiment: start groups of CTAs out of phase
-    const long long wait = (long long)BSRL_SKEW * (blockIdx.x % BSRL_SKEW_GROUPS);
-    const long long t0 = clock64();
-    while (clock64() - t0 < wait) {}
-  }
-#endif
   const uint32_t tmem_base = sh->tmem_base;
-  // completion of this CTA's TMA loads is counted on the leader's barriers
-  auto lead_bar = [&](uint64_t* bar) -> uint32_t { return PAIR ? map_to_cta(smem_u32(bar), 0) : smem_u32(bar); };
-  auto tma = [&](uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    if (PAIR) tma_load_2d_pair(dst, map, x, y, bar);
-    else tma_load_2d(dst, map, x, y, bar);
-  };
-  const int rows_d = PAIR ? d >> 1 : d;          // weight rows of an N = d tile held by this CTA
-  const int rows_h = PAIR ? HC >> 1 : HC;        // ... of an N = 128 tile
+  const int rows_d = d;          // weight rows of an N = d tile
+  const int rows_h = HC;         // ... of an N = 128 tile
 
   if (warp == 0) {
     // ------------------------------------------------------------ weight producer
@@ -268,31 +218,30 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
         if (!mbar_wait(smem_u32(&sh->w_empty[s]), ph ^ 1, abort)) { give_up(sh, p.status, 1); return false; }
-        if (leader) mbar_expect_tx(smem_u32(&sh->w_full[s]), bytes_each * n_loads * CTAS);
-        const uint32_t bar = lead_bar(&sh->w_full[s]);
+        const uint32_t bar = smem_u32(&sh->w_full[s]);
+        mbar_expect_tx(bar, bytes_each * n_loads);
         for (int i = 0; i < n_loads; ++i)
-          tma(ring + s * STAGE_BYTES + i * bytes_each, map, x0 + i * 64, y0, bar);
+          tma_load_2d(ring + s * STAGE_BYTES + i * bytes_each, map, x0 + i * 64, y0, bar);
         ++it;
         return true;
       };
       auto g1 = [&](int j) -> bool {   // W0 rows [128 j, +128), two k-blocks per stage
         for (int i = 0; i < S1; ++i) {
           const int n = (2 * i + 1 < KB) ? 2 : 1;
-          if (!stage(&tm_w0, 128 * i, HC * j + (int)rank * rows_h, n, rows_h * 128)) return false;
+          if (!stage(&tm_w0, 128 * i, HC * j, n, rows_h * 128)) return false;
         }
         return true;
       };
       for (int t = tile0; t < t_end && ok; t += tstep) {
-        for (int kb = 0; kb < KB && ok; ++kb) ok = stage(&tm_wo, 64 * kb, (int)rank * rows_d, 1, rows_d * 128);
+        for (int kb = 0; kb < KB && ok; ++kb) ok = stage(&tm_wo, 64 * kb, 0, 1, rows_d * 128);
         ok = ok && g1(0) && g1(1);
         for (int j = 0; j < NC && ok; ++j) {
-          for (int kc = 0; kc < 2 && ok; ++kc) ok = stage(&tm_w2, HC * j + 64 * kc, (int)rank * rows_d, 1, rows_d * 128);
+          for (int kc = 0; kc < 2 && ok; ++kc) ok = stage(&tm_w2, HC * j + 64 * kc, 0, 1, rows_d * 128);
           if (ok && j + 2 < NC) ok = g1(j + 2);
         }
       }
-      // loads in flight must land before the CTA exits (bounded, ignoring abort); in a pair both
-      // CTAs' loads are counted on the leader's barriers, and the peer stays until the final cluster sync
-      for (uint32_t j = it > STAGES ? it - STAGES : 0; leader && j < it; ++j) {
+      // loads in flight must land before the CTA exits (bounded, ignoring abort)
+      for (uint32_t j = it > STAGES ? it - STAGES : 0; j < it; ++j) {
         uint32_t spins = 0;
         while (!mbar_try_wait(smem_u32(&sh->w_full[j % STAGES]), (j / STAGES) & 1) && ++spins < kSpinLimit) {}
         if (spins >= kSpinLimit) give_up(sh, p.status, 2);
@@ -312,9 +261,9 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         break;
       }
       if (lane == 0) {
-        if (leader) mbar_expect_tx(smem_u32(&sh->a_full), KB * CHUNK_BYTES * CTAS);
-        const uint32_t bar = lead_bar(&sh->a_full);
-        for (int c = 0; c < KB; ++c) tma(sA + c * CHUNK_BYTES, &tm_att, 64 * c, t * BM, bar);
+        const uint32_t bar = smem_u32(&sh->a_full);
+        mbar_expect_tx(bar, KB * CHUNK_BYTES);
+        for (int c = 0; c < KB; ++c) tma_load_2d(sA + c * CHUNK_BYTES, &tm_att, 64 * c, t * BM, bar);
       }
       const int tn = t + tstep;
       if (tn < t_end) {
@@ -327,34 +276,24 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         }
       }
     }
-    if (lane == 0 && leader && tile_i > 0) {
+    if (lane == 0 && tile_i > 0) {
       uint32_t spins = 0;
       while (!mbar_try_wait(smem_u32(&sh->a_full), (tile_i - 1) & 1) && ++spins < kSpinLimit) {}
       if (spins >= kSpinLimit) give_up(sh, p.status, 4);
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (the leader's, in a pair)
-    if (lane == 0 && leader) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
       uint32_t it = 0, tile_i = 0, n_hid = 0;
       bool ok = true;
-      TRACE_INIT(0);
-      const uint32_t idesc_d = idesc_f16(BM * CTAS, d), idesc_h = idesc_f16(BM * CTAS, HC);
-      // completion of the MMAs issued so far -> the barrier (of both CTAs, in a pair)
-      auto commit = [&](uint64_t* bar) {
-        if (PAIR) tc_commit_pair(smem_u32(bar));
-        else tc_commit(smem_u32(bar));
-      };
+      const uint32_t idesc_d = idesc_f16(BM, d), idesc_h = idesc_f16(BM, HC);
+      // completion of the MMAs issued so far -> the barrier
+      auto commit = [&](uint64_t* bar) { tc_commit(smem_u32(bar)); };
       // consume one ring stage: wait, run `body(stage address)`, release the stage
       auto with_stage = [&](auto&& body) -> bool {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
-#ifdef BSRL_TRACE
-        long long t0 = clock64();
-#endif
         if (!mbar_wait(smem_u32(&sh->w_full[s]), ph, abort)) { give_up(sh, p.status, 5); return false; }
-#ifdef BSRL_TRACE
-        TRACE(160, clock64() - t0);
-#endif
         tc_fence_after();
         body(ring + s * STAGE_BYTES);
         commit(&sh->w_empty[s]);
@@ -369,8 +308,8 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
           const uint32_t dst = acol + (j & 1) * HC;
           for (int i = 0; i < S1; ++i) {
             if (!with_stage([&](uint32_t st) {
-                  mma_kblock<PAIR>(dst, sA + (2 * i) * CHUNK_BYTES, st, idesc_h, i != 0);
-                  if (2 * i + 1 < KB) mma_kblock<PAIR>(dst, sA + (2 * i + 1) * CHUNK_BYTES, st + rows_h * 128, idesc_h, true);
+                  mma_kblock(dst, sA + (2 * i) * CHUNK_BYTES, st, idesc_h, i != 0);
+                  if (2 * i + 1 < KB) mma_kblock(dst, sA + (2 * i + 1) * CHUNK_BYTES, st + rows_h * 128, idesc_h, true);
                 }))
               return false;
           }
@@ -380,35 +319,28 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         TAIL_WAIT(&sh->a_full, par, 6);
         TAIL_WAIT(&sh->x_ready, par, 7);
         tc_fence_after();
-        TRACE(100);
         for (int kb = 0; kb < KB && ok; ++kb)       // x1 = x (pre-stored) + att Wo^T
-          ok = with_stage([&](uint32_t st) { mma_kblock<PAIR>(xcol, sA + kb * CHUNK_BYTES, st, idesc_d, true); });
+          ok = with_stage([&](uint32_t st) { mma_kblock(xcol, sA + kb * CHUNK_BYTES, st, idesc_d, true); });
         if (!ok) break;
         commit(&sh->o_done);
-        TRACE(101);
         TAIL_WAIT(&sh->h2_ready, par, 8);
         tc_fence_after();
-        TRACE(102);
         ok = g1(0) && g1(1);
         if (NC == 2 && ok) commit(&sh->a_free);
         for (int j = 0; j < NC && ok; ++j) {
           for (int kc = 0; kc < 2 && ok; ++kc) {    // xo += hidden chunk j * W2[:, chunk j]^T, one 64-column half at a time
             if (!mbar_wait(smem_u32(&sh->hid_ready[kc]), n_hid & 1, abort)) { give_up(sh, p.status, 9); ok = false; break; }
             tc_fence_after();
-            TRACE(140 + 2 * j + kc);
-            ok = with_stage([&](uint32_t st) { mma_kblock<PAIR>(xcol, sH + kc * CHUNK_BYTES, st, idesc_d, true); });
+            ok = with_stage([&](uint32_t st) { mma_kblock(xcol, sH + kc * CHUNK_BYTES, st, idesc_d, true); });
             if (ok) commit(&sh->hid_free[kc]);   // this half of sH may be overwritten once retired
           }
           ++n_hid;
-          TRACE(130 + j);
           if (ok && j + 2 < NC) {
             ok = g1(j + 2);
-            TRACE(170 + j);
             if (ok && j + 3 == NC) commit(&sh->a_free);   // last reader of h2 issued
           }
         }
         if (ok) commit(&sh->x_done);
-        TRACE(150);
       }
       commit(&sh->mma_done);
       uint32_t spins = 0;
@@ -423,7 +355,6 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     // 4 lanes cover 64 contiguous bytes of one row (lane = (row sub8 + 8 i, 16-byte piece)).
     const int grp = (warp - 2) >> 2;
     const int q = warp & 3;
-    TRACE_INIT(lane == 0 ? warp - 1 : -1);
     const int trow = q * 32 + lane;                         // row inside the tile
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     uint8_t* stg = stg_all + (warp - 2) * STG_BYTES;
@@ -449,17 +380,13 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
     auto stg_read = [&](int row, int pc) -> uint4 { return buf_read(stg, row, pc); };
     uint32_t n_io = 0;                                      // residual blocks this warp has consumed so far
     auto group_sync = [&]() { asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory"); };
-    auto signal = [&](uint64_t* bar) {   // one arrival per warp (on the leader's barrier), after everyone's writes
+    auto signal = [&](uint64_t* bar) {   // one arrival per warp, after everyone's writes
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        if (PAIR) mbar_arrive_cluster(map_to_cta(smem_u32(bar), 0));
-        else mbar_arrive(smem_u32(bar));
-      }
+      if (lane == 0) mbar_arrive(smem_u32(bar));
     };
-    // shared-memory writes of this thread -> visible to the tensor core (the leader's too, in a pair:
-    // the all-state-space form of the fence measured ~2,000 cycles per use and is not needed for
-    // this CTA's own shared memory)
+    // shared-memory writes of this thread -> visible to the tensor core (the all-state-space form of
+    // the fence measured ~2,000 cycles per use and is not needed for this CTA's own shared memory)
     auto publish_smem = [&]() { fence_proxy_async_smem(); };
     // row statistics of the whole row from this group's partial sums and the other group's
     auto row_stats = [&](int phase, float sum, float sq, float& mean, float& rstd) {
@@ -570,7 +497,6 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       // ---- E1: h2 = LN_ffn(x1) -> sA   (X already holds x + bo + att Wo^T)
       TAIL_WAIT_WARP(&sh->o_done, par, 11);
       tc_fence_after();
-      TRACE(200);
       {
         float sum = 0.f, sq = 0.f;
         for (int c = c_lo; c < c_lo + dh2; c += 32) {
@@ -605,7 +531,6 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
       }
       publish_smem();
       signal(&sh->h2_ready);
-      TRACE(201);
       // ---- hidden chunks: relu(acc + b0) -> sH; this group handles 64 of the chunk's 128 columns
       for (int j = 0; j < NC && ok; ++j) {
         const int b = j & 1;
@@ -616,7 +541,6 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         }
         ++n_acc[b];
         tc_fence_after();
-        TRACE(210 + j);
         uint32_t hp[32];                                    // 64 fp16 values of this row
 #pragma unroll
         for (int c = 0; c < 64; c += 32) {
@@ -639,7 +563,6 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
           break;
         }
         ++n_free;
-        TRACE(220 + j);
         {
           uint8_t* rowp = sH_g + grp * CHUNK_BYTES + (trow >> 3) * 1024 + (trow & 7) * 128;
 #pragma unroll
@@ -649,18 +572,14 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         }
         publish_smem();
         signal(&sh->hid_ready[grp]);
-        TRACE(230 + j);
       }
       if (!ok) break;
       // ---- all MMAs of the tile have retired: X holds x1 + FFN, sH and both hidden buffers are free
       TAIL_WAIT_WARP(&sh->x_done, par, 13);
       tc_fence_after();
-      TRACE(250);
       // pre-store the next tile's x over the hidden buffers; its out-projection then runs under the drain
       if (t_next < t_end) {
-        TRACE(261);
         ok = prestore(t_next, acol);
-        TRACE(262);
         signal(&sh->x_ready);
         if (!ok) break;
       }
@@ -712,9 +631,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
           }
         }
         float mean = 0.f, rstd = 1.f;
-        TRACE(252);
         if (want_stats) row_stats(1, sum, sq, mean, rstd);
-        TRACE(253);
 #pragma unroll 1
         for (int o = 0; o < 2; ++o) {
           if (!p.out16[o]) continue;
@@ -750,7 +667,6 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         __syncwarp();
       }
       tc_fence_before();
-      TRACE(251);
     }
     if (lane == 0) bulk_wait_all();                         // the stores are complete before the CTA exits
   }
@@ -758,11 +674,9 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
-  if (PAIR) cluster_sync_all();     // the leader's MMAs read the peer's shared memory until they retire
   if (warp == 1) {
     tc_fence_after();
-    if (PAIR) tmem_dealloc_pair(tmem_base, 512);
-    else tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, 512);
   }
 }
 #undef tile0
@@ -793,13 +707,11 @@ int block_tail(const BlockTailArgs& a, cudaStream_t stream) {
   int* status = device_status_ptr();
   if (!status) return BSRL_ERR_CUDA;
   const int n_tiles = (int)((a.M + BM - 1) / BM);
-  // CTA pairs (cta_group::2): each CTA fetches half of every weight tile; needs two tiles at least
-  const bool pair = a.pair && n_tiles >= 2;
   CUtensorMap tm_att, tm_wo, tm_w0, tm_w2;
   if (!make_tmap_f16(&tm_att, a.att, a.M, a.d, a.ld_att, BM)) return BSRL_ERR_CUDA;
-  if (!make_tmap_f16(&tm_wo, a.wo, a.d, a.d, a.d, pair ? a.d / 2 : a.d)) return BSRL_ERR_CUDA;
-  if (!make_tmap_f16(&tm_w0, a.w0, a.F, a.d, a.d, pair ? HC / 2 : HC)) return BSRL_ERR_CUDA;
-  if (!make_tmap_f16(&tm_w2, a.w2, a.d, a.F, a.F, pair ? a.d / 2 : a.d)) return BSRL_ERR_CUDA;
+  if (!make_tmap_f16(&tm_wo, a.wo, a.d, a.d, a.d, a.d)) return BSRL_ERR_CUDA;
+  if (!make_tmap_f16(&tm_w0, a.w0, a.F, a.d, a.d, HC)) return BSRL_ERR_CUDA;
+  if (!make_tmap_f16(&tm_w2, a.w2, a.d, a.F, a.F, a.d)) return BSRL_ERR_CUDA;
   // residual rows in and the outputs move as 32-row x 64-byte TMA boxes; a map that is not needed
   // aliases the attention tile's (the kernel only prefetches its descriptor)
   const bool x_tma = a.xmap.group == 0x7fffffff && a.xmap.stride == 0 && a.xmap.first == 0;
@@ -808,31 +720,11 @@ int block_tail(const BlockTailArgs& a, cudaStream_t stream) {
   if (a.x_out && !make_tmap_rows64(&tm_xo, a.x_out, 4, a.M, a.d, a.d, 32)) return BSRL_ERR_CUDA;
   for (int o = 0; o < 2; ++o)
     if (a.out16[o] && !make_tmap_rows64(&tm_o[o], a.out16[o], 2, a.M, a.d, a.ld16[o], 32)) return BSRL_ERR_CUDA;
-  static bool attr_set[64] = {};
-  static int max_pairs[64] = {};
-  int dev = 0;
-  BSRL_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_set[dev]) {
-    BSRL_CUDA_OK(cudaFuncSetAttribute(block_tail_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    BSRL_CUDA_OK(cudaFuncSetAttribute(block_tail_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    // how many two-CTA clusters the device can hold at once (SMs pair up inside a GPC)
-    cudaLaunchConfig_t q = {};
-    q.gridDim = dim3(2 * (sm_count() / 2));
-    q.blockDim = dim3(THREADS);
-    q.dynamicSmemBytes = SMEM_BYTES;
-    cudaLaunchAttribute qa;
-    qa.id = cudaLaunchAttributeClusterDimension;
-    qa.val.clusterDim.x = 2; qa.val.clusterDim.y = 1; qa.val.clusterDim.z = 1;
-    q.attrs = &qa;
-    q.numAttrs = 1;
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, block_tail_kernel<2>, &q) != cudaSuccess || n < 1) {
-      cudaGetLastError();
-      n = 0;
-    }
-    max_pairs[dev] = n;
-    attr_set[dev] = true;
-  }
+  static DeviceOnce once;
+  int rc = once.run("block_tail_kernel set-up", [] {
+    return cudaFuncSetAttribute(block_tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  });
+  if (rc != BSRL_OK) return rc;
   TailParams p;
   p.d = a.d; p.F = a.F; p.M = a.M;
   p.x = a.x; p.ldx = a.ldx; p.xmap = a.xmap;
@@ -844,50 +736,11 @@ int block_tail(const BlockTailArgs& a, cudaStream_t stream) {
   p.n_tiles = n_tiles;
   p.x_tma = x_tma ? 1 : 0;
   p.status = status;
-  if (pair && dev < 64 && max_pairs[dev] > 0) {
-    const int n_pairs = (n_tiles + 1) / 2;
-    const int clusters = n_pairs < max_pairs[dev] ? n_pairs : max_pairs[dev];
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * clusters);
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = SMEM_BYTES;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    BSRL_CUDA_OK(cudaLaunchKernelEx(&cfg, block_tail_kernel<2>, tm_att, tm_wo, tm_w0, tm_w2, tm_x, tm_xo, tm_o[0], tm_o[1], p));
-    return BSRL_OK;
-  }
-  if (pair) {   // no room for clusters on this device: one CTA per tile, full-size weight boxes
-    if (!make_tmap_f16(&tm_wo, a.wo, a.d, a.d, a.d, a.d)) return BSRL_ERR_CUDA;
-    if (!make_tmap_f16(&tm_w0, a.w0, a.F, a.d, a.d, HC)) return BSRL_ERR_CUDA;
-    if (!make_tmap_f16(&tm_w2, a.w2, a.d, a.F, a.F, a.d)) return BSRL_ERR_CUDA;
-  }
   int grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
-  block_tail_kernel<1><<<grid, THREADS, SMEM_BYTES, stream>>>(tm_att, tm_wo, tm_w0, tm_w2, tm_x, tm_xo, tm_o[0], tm_o[1], p);
+  block_tail_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_att, tm_wo, tm_w0, tm_w2, tm_x, tm_xo, tm_o[0], tm_o[1], p);
   BSRL_LAUNCH_OK("block_tail_kernel");
   return BSRL_OK;
 }
 
-#ifdef BSRL_TRACE
-// (tag + 10000 * slot, clock) pairs of all slots; resets the counters
-extern "C" int bsrl_trace_read(long long* out, int cap) {
-  static long long host[TRACE_SLOTS * TRACE_CAP * 2];
-  int cnt[TRACE_SLOTS];
-  cudaMemcpyFromSymbol(cnt, g_trace_cnt, sizeof(cnt));
-  cudaMemcpyFromSymbol(host, g_trace, sizeof(host));
-  int n = 0;
-  for (int s = 0; s < TRACE_SLOTS; ++s)
-    for (int i = 0; i < cnt[s] && i < TRACE_CAP && n < cap; ++i, ++n) {
-      out[2 * n] = host[((size_t)s * TRACE_CAP + i) * 2] + 10000LL * s;
-      out[2 * n + 1] = host[((size_t)s * TRACE_CAP + i) * 2 + 1];
-    }
-  int zero[TRACE_SLOTS] = {};
-  cudaMemcpyToSymbol(g_trace_cnt, zero, sizeof(zero));
-  return n;
-}
-#endif
 
 }  // namespace bsrl

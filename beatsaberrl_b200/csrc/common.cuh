@@ -5,6 +5,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "../../include/bsrl.h"
 
 namespace bsrl {
@@ -49,6 +51,32 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
 int sm_count();  // multiprocessors of the current device (cached per device)
+
+// One-time set-up per device (raising a kernel's dynamic shared-memory limit, resolving a device
+// symbol): run(what, fn) calls fn() -> cudaError_t once for the CURRENT device, whichever host
+// thread gets there first, and returns BSRL_OK or the failure of that first run.  The cached result
+// belongs to the device's primary context: it does not survive cudaDeviceReset.
+constexpr int kMaxDevices = 64;
+class DeviceOnce {
+ public:
+  template <typename Fn>
+  int run(const char* what, Fn&& fn) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) {
+      set_error("%s: device ordinal %d not supported (at most %d devices)", what, dev, kMaxDevices);
+      return BSRL_ERR_UNSUPPORTED;
+    }
+    std::call_once(flag_[dev], [&] { err_[dev] = fn(); });
+    if (err_[dev] != cudaSuccess) return cuda_fail(err_[dev], what);
+    return BSRL_OK;
+  }
+
+ private:
+  std::once_flag flag_[kMaxDevices];
+  cudaError_t err_[kMaxDevices] = {};
+};
 
 // ----------------------------------------------------------------------------- device
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

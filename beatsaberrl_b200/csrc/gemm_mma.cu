@@ -159,14 +159,11 @@ int linear_mma(const LinearArgs& p, cudaStream_t stream) {
     return BSRL_ERR_ALIGN;
   }
   if (p.M == 0) return BSRL_OK;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  BSRL_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_set[dev]) {
-    BSRL_CUDA_OK(cudaFuncSetAttribute(linear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      STAGES * STAGE_BYTES));
-    attr_set[dev] = true;
-  }
+  static DeviceOnce once;
+  int rc = once.run("linear_mma_kernel set-up", [] {
+    return cudaFuncSetAttribute(linear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, STAGES * STAGE_BYTES);
+  });
+  if (rc != BSRL_OK) return rc;
   int64_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   if (tiles > 0x7fffffffLL) {
     set_error("linear: too many tiles");

@@ -391,14 +391,13 @@ int linear_tc5(const LinearArgs& p, cudaStream_t stream) {
                      p.M <= 0x7fffff00;
   CUtensorMap tm_c = tm_a;
   if (tma_c && !make_tmap_rows(&tm_c, p.C, p.out_f32 ? 4 : 2, p.M, p.N, p.ldc, 32, 128)) return BSRL_ERR_CUDA;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  BSRL_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_set[dev]) {
-    BSRL_CUDA_OK(cudaFuncSetAttribute(linear_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    BSRL_CUDA_OK(cudaFuncSetAttribute(linear_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    attr_set[dev] = true;
-  }
+  static DeviceOnce once;
+  int rc = once.run("linear_tc5_kernel set-up", [] {
+    cudaError_t e = cudaFuncSetAttribute(linear_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(linear_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  });
+  if (rc != BSRL_OK) return rc;
   const int64_t m_tiles = (p.M + BM - 1) / BM;
   const int n_tiles = (p.N + BN - 1) / BN;
   if (m_tiles > 0x7fffffff / n_tiles) {
@@ -417,22 +416,43 @@ int linear_tc5(const LinearArgs& p, cudaStream_t stream) {
 }
 
 int* device_status_ptr() {
-  static int* cached[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
-    set_error("device_status_ptr: no current device");
-    return nullptr;
-  }
-  if (!cached[dev]) {
+  static DeviceOnce once;
+  static int* cached[kMaxDevices] = {};
+  int rc = once.run("device status word", [] {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
     void* p = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&p, g_device_status);
-    if (e != cudaSuccess) {
-      cuda_fail(e, "cudaGetSymbolAddress(g_device_status)");
-      return nullptr;
-    }
-    cached[dev] = static_cast<int*>(p);
-  }
+    e = cudaGetSymbolAddress(&p, g_device_status);     // address on the CURRENT device
+    if (e == cudaSuccess) cached[dev] = static_cast<int*>(p);
+    return e;
+  });
+  if (rc != BSRL_OK) return nullptr;
+  int dev = 0;
+  cudaGetDevice(&dev);
   return cached[dev];
+}
+
+namespace {
+__global__ void wait_selftest_kernel(int* status, uint32_t polls) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_barrier_init();
+    // phase 0 of this barrier never completes: no thread arrives and no copy is counted on it
+    if (!mbar_wait_limit(smem_u32(&bar), 0, &abort_flag, polls)) atomicCAS(status, 0, kSelfTestKernel * 16 + 1);
+  }
+}
+}  // namespace
+
+int wait_selftest(uint32_t polls, cudaStream_t stream) {
+  int* status = device_status_ptr();
+  if (!status) return BSRL_ERR_CUDA;
+  wait_selftest_kernel<<<1, 32, 0, stream>>>(status, polls);
+  BSRL_LAUNCH_OK("wait_selftest_kernel");
+  return BSRL_OK;
 }
 
 int device_status_take() {

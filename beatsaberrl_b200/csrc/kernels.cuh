@@ -53,7 +53,6 @@ struct BlockTailArgs {
   int64_t ld16[2];
   const float* g16[2];
   const float* b16[2];
-  int pair;            // 1 = run on two-CTA clusters (cta_group::2) when there are at least two tiles
 };
 bool block_tail_ok(const BlockTailArgs& a);
 int block_tail(const BlockTailArgs& a, cudaStream_t stream);
@@ -141,6 +140,11 @@ struct HeadTailArgs {
   int64_t n_envs;
 };
 int head_tail(const HeadTailArgs& a, cudaStream_t stream);
+
+// Stand-in for the simulator's step kernel (graph tests / tick benchmarks): actions in, the env's obs row,
+// reward and done flag rewritten in place.
+int standin_env_step(const long long* actions, int64_t n_envs, uint32_t* state, float* obs, float* reward,
+                     unsigned char* done, cudaStream_t stream);
 
 // f32 -> f16 cast with row pitch (weight packing), and plain f32 copy.
 int pack_cast(const float* src, int64_t rows, int64_t cols, __half* dst, int64_t dst_pitch,

@@ -4,6 +4,8 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "kernels.cuh"
 
 namespace bsrl {
@@ -25,15 +27,15 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 int sm_count() {
-  static int cached[64] = {};
+  static std::atomic<int> cached[kMaxDevices];     // 0 = not read yet; racing first readers store the same value
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
 }
 
 LinearArgs linear_args(const __half* A, int lda, const __half* W, int ldw, const float* bias,
@@ -304,7 +306,15 @@ std::vector<CopySlot> make_copy_slots(const bsrl_config& c, const Layout& l, con
 }
 
 // ------------------------------------------------------------------ workspace
-Workspace make_workspace(const Layout& l, int64_t B) {
+Paths plan_paths(const Layout& l, int engine) {
+  Paths p;
+  const bool widths = engine == 0 && l.d % 64 == 0 && l.d >= 64 && l.d <= 256;
+  p.attn_fused = widths && l.attn_G > 0;
+  p.tail_fused = widths && l.F % 256 == 0 && l.F >= 256 && l.F <= 1024;
+  return p;
+}
+
+Workspace make_workspace(const Layout& l, int64_t B, const Paths& paths) {
   Workspace w;
   Carver cv;
   const int64_t R = B * kT, Rl = B * kLead;
@@ -317,9 +327,9 @@ Workspace make_workspace(const Layout& l, int64_t B) {
   w.enc_hid = cv.take(R * d * 2);
   w.x = cv.take(R * d * 4);
   w.h = cv.take(R * d * 2);
-  w.qkv = cv.take(R * 3 * d * 2);
+  w.qkv = paths.attn_fused ? -1 : cv.take(R * 3 * d * 2);
   w.att = cv.take(R * d * 2);
-  w.hid = cv.take(R * (int64_t)l.F * 2);
+  w.hid = paths.tail_fused ? -1 : cv.take(R * (int64_t)l.F * 2);
   w.x_lead = cv.take(Rl * d * 4);
   w.h_lead = cv.take(Rl * d * 2);
   w.lead16 = cv.take(Rl * d * 2);

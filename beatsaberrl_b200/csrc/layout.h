@@ -71,7 +71,16 @@ Layout make_layout(const bsrl_config& c);
 std::vector<ParamSlot> make_param_slots(const bsrl_config& c, const Layout& l);
 std::vector<CopySlot> make_copy_slots(const bsrl_config& c, const Layout& l, const std::vector<ParamSlot>& params);
 
-// Workspace carve-up for a batch of n_envs.
+// Which kernels a forward of this shape runs: the fused tcgen05 kernels where the widths fit them
+// (and the engine override allows), separate GEMM / LayerNorm / attention kernels otherwise.  The
+// workspace only holds the intermediates of the path taken.
+struct Paths {
+  bool attn_fused;   // q|k|v projection + attention in one kernel (no (rows, 3d) buffer)
+  bool tail_fused;   // out-projection + LayerNorm + FFN in one kernel (no (rows, 4d) hidden buffer)
+};
+Paths plan_paths(const Layout& l, int engine);
+
+// Workspace carve-up for a batch of n_envs (offsets of buffers the path does not use are -1).
 struct Workspace {
   int64_t key_bias, f_saber, f_torso, f_leg, f_note, enc_hid, x, h, qkv, att, hid;
   int64_t x_lead, h_lead, lead16, xt, u, r, z, m1, m2, raw, vraw, att_c;
@@ -79,6 +88,6 @@ struct Workspace {
   int64_t t32;  // SimBaV2 trunk: fp32 GEMM outputs (B, max(D, Hh))
   int64_t bytes;
 };
-Workspace make_workspace(const Layout& l, int64_t n_envs);
+Workspace make_workspace(const Layout& l, int64_t n_envs, const Paths& paths);
 
 }  // namespace bsrl

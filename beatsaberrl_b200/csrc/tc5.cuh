@@ -41,13 +41,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the limit ran out or another role already gave up (*abort != 0).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+// Bounded wait: false when `limit` polls ran out or another role already gave up (*abort != 0).
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;   // the hardware parks the thread inside try_wait
     if ((i & 1023u) == 1023u && *abort) return false;
   }
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
+  return mbar_wait_limit(bar, parity, abort, kSpinLimit);
 }
 
 // Whole-warp bounded wait: only lane 0 polls the barrier (32 lanes polling the same word would
@@ -168,62 +171,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
-// ---- CTA pairs (cluster of two CTAs on neighbouring SMs, tcgen05 cta_group::2) ---------------
-// One thread of the leader CTA (cluster rank 0) issues MMAs with M = 256: each CTA supplies its own
-// 128 rows of A and HALF of the B tile's rows (at the same shared-memory offset in both CTAs) and
-// receives its own 128 x N accumulator rows in its own TMEM.  No load is multicast: each CTA
-// fetches its half of B itself, and its TMA signals the leader's barrier.
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
-// TMA tile load into THIS CTA's shared memory, completion bytes counted on a barrier of the pair's
-// leader (bar_cluster_addr = map_to_cta(barrier, 0))
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
-                                                 uint32_t bar_cluster_addr) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-// arrive on the barrier at this shared-memory offset in BOTH CTAs once the pair's MMAs have retired
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(bar), "h"((uint16_t)3) : "memory");
-}
-__device__ __forceinline__ void mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 // Shared-memory matrix descriptor of a K-major operand tile stored as [rows][64 fp16] with the
 // 128-byte swizzle (what a TMA load with CU_TENSOR_MAP_SWIZZLE_128B writes): 8-row groups are
 // 1024 bytes apart; the tile base is 1024-byte aligned; a 16-element K step advances the start
@@ -268,5 +215,10 @@ bool make_tmap_rows(CUtensorMap* map, const void* base, int elem_bytes, int64_t 
 int* device_status_ptr();
 // Reads and clears the current device's status word (synchronises the device); -1 on failure.
 int device_status_take();
+// Launches a one-CTA kernel whose only thread waits, with a limit of `polls` polls, on an mbarrier
+// that nothing ever arrives on: the wait runs out, the kernel records kSelfTestKernel * 16 + 1 in
+// the status word and returns.  Exercises the give-up path without hanging or trapping anything.
+constexpr int kSelfTestKernel = 15;
+int wait_selftest(uint32_t polls, cudaStream_t stream);
 
 }  // namespace bsrl

@@ -223,18 +223,66 @@ class NotePolicy(nn.Module):
         """Build the packed fp16 arena now (call once before CUDA-graph capture)."""
         self._pack(force=True)
 
-    def refresh_fp16_caches(self) -> None:
+    def refresh_fp16_caches(self, check: bool = False) -> None:
         """Repack the arena in place from the current fp32 masters (after optimizer steps;
-        a captured graph keeps reading the same storage)."""
+        a captured graph keeps reading the same storage).  ``check=True`` also runs
+        ``check_device()`` (a device synchronisation) first."""
+        if check:
+            self.check_device()
         self._pack(force=True)
 
+    _MAX_IDLE_WORKSPACES = 2    # workspaces of batch sizes no captured graph uses, kept for reuse
+
     def _workspace(self, B: int, dev):
-        ws = self._workspaces.get((B, dev))
-        if ws is None:
+        """The forward's intermediates for a batch of B on ``dev``.
+
+        A CUDA graph captured around a forward holds this buffer's raw address, so a workspace
+        that was used while a stream was capturing is kept for the module's lifetime: a later
+        call with another batch size (the PPO recompute on minibatches, after the rollout graph
+        was captured at n_envs) gets a workspace of its own instead of replacing it.  Other
+        workspaces are kept for reuse, the least recently used dropped beyond a small limit."""
+        key = (B, dev)
+        capturing = torch.cuda.is_current_stream_capturing()
+        ent = self._workspaces.pop(key, None)
+        if ent is None:
             n = nat.lib.bsrl_workspace_bytes(C.byref(self._cfg), B)
-            ws = torch.empty(max(n, 256), dtype=torch.uint8, device=dev)
-            self._workspaces = {(B, dev): ws}      # keep one batch size resident
-        return ws
+            if n < 0:
+                raise nat.BsrlError(int(n), nat.last_error())
+            ent = [torch.empty(max(n, 256), dtype=torch.uint8, device=dev), False]
+        ent[1] = ent[1] or capturing
+        self._workspaces[key] = ent                 # most recently used last
+        if not capturing:
+            # kernels of an earlier call may still be reading a workspace on another stream when the
+            # allocator hands its memory out again: tie the buffer to every stream that uses it
+            ent[0].record_stream(torch.cuda.current_stream(dev))
+            idle = [k for k, (_, pinned) in self._workspaces.items() if not pinned and k != key]
+            for k in idle[:max(0, len(idle) - (self._MAX_IDLE_WORKSPACES - 1))]:
+                del self._workspaces[k]
+        return ent[0]
+
+    def check_device(self) -> None:
+        """Raise if a bounded wait inside one of the kernels ran out since the last check.
+
+        The kernels never spin without a limit: a wait that runs out makes the kernel set a status
+        word and return, and that launch's outputs are garbage.  This synchronises the device, reads
+        and clears the word (``bsrl_device_status``) and raises ``BsrlError`` (status -7) if it was
+        set.  Call it where the host synchronises anyway -- the end of a rollout, before an update
+        consumes the rollout's outputs; ``refresh_fp16_caches`` does."""
+        dev = self.critic_q.weight.device
+        if dev.type != "cuda":
+            return
+        with torch.cuda.device(dev):
+            nat.check(nat.lib.bsrl_device_status())
+
+    def _stash_diag(self, B: int, dev) -> None:
+        """``_diag_stash`` of the reference (python/policy.py:1068-1073, :1309-1310): keep the trunk
+        output h (B, trunk_dim) of the forward that just ran, copied out of the workspace."""
+        off, rows, cols, ld, dt = (C.c_int64(), C.c_int64(), C.c_int64(), C.c_int64(), C.c_int32())
+        nat.check(nat.lib.bsrl_workspace_region(C.byref(self._cfg), B, b"trunk_h", C.byref(off), C.byref(rows),
+                                                C.byref(cols), C.byref(ld), C.byref(dt)))
+        ws = self._workspaces[(B, dev)][0]
+        flat = ws[off.value: off.value + (rows.value - 1) * ld.value * 2 + cols.value * 2].view(torch.float16)
+        self._diag_h = torch.as_strided(flat, (rows.value, cols.value), (ld.value, 1)).clone()
 
     @staticmethod
     def _obs_dtype(obs):
@@ -269,6 +317,8 @@ class NotePolicy(nn.Module):
                 logits.data_ptr(), value.data_ptr(), vl.data_ptr() if vl is not None else None,
                 ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream))
         self._value_logits = vl
+        if self._diag_stash:
+            self._stash_diag(B, dev)
         return logits, value
 
     def forward(self, obs: torch.Tensor):
@@ -308,13 +358,19 @@ class NotePolicy(nn.Module):
         if need_entropy:
             self._ent_h = ent_h
         self._value_logits = vl
+        if self._diag_stash:
+            self._stash_diag(B, dev)
         return action, logprob, entropy, value
 
     def seed_sampler(self, seed: int) -> None:
         """(Re)start the action-sampling stream: [seed, call counter] in a device tensor that the
         head kernel reads, so a captured CUDA graph draws fresh numbers on every replay."""
         dev = self.critic_q.weight.device
-        self._rng_state = torch.tensor([seed & 0x7FFFFFFFFFFFFFFF, 0], dtype=torch.int64, device=dev)
+        vals = torch.tensor([seed & 0x7FFFFFFFFFFFFFFF, 0], dtype=torch.int64)
+        if self._rng_state is not None and self._rng_state.device == dev:
+            self._rng_state.copy_(vals)      # in place: a captured graph keeps reading this tensor
+        else:
+            self._rng_state = vals.to(dev)
 
     @torch.no_grad()
     def _sample(self, obs, need_entropy):

@@ -3,9 +3,13 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
 
 One step = one ``forward_stacked`` over one batch of synthetic observations (65,536 envs per GPU
-for the default ``cfg2`` workload: d=256, 4 blocks, 8 heads, Xavier init seed 1).  Under torchrun
-every rank runs the same per-GPU batch (weak scaling, no collective on the path); timing is
-CUDA events bracketed by barrier + synchronize, max over ranks.  Rank 0 prints ONE JSON line.
+for the default ``cfg2`` workload: d=256, 4 blocks, 8 heads, Xavier init seed 1), replayed from a
+CUDA graph captured after the warm-up, stage profiler off.  Under torchrun every rank runs the same
+per-GPU batch (weak scaling, no collective on the path); timing is CUDA events bracketed by barrier
++ synchronize, max over ranks.  Rank 0 prints ONE JSON line, which also carries: the eager time of
+the same step; per-stage times from a separate pass; ``e2e`` with host buffers; ``cfg5_recompute``
+(131,072 envs per GPU through ``get_action_and_value(obs, int32 actions)``); the CPU baseline and,
+on one GPU, ``reference_gpu`` (the reference's own fp16 GPU stream, if staged under ``baseline/_ref``).
 
 ``--impl reference`` times the reference algorithm's CPU implementation (the oracle port of
 python/policy.py) on the host cores over a bounded sample of the same workload.
@@ -151,6 +155,26 @@ def describe(cfg):
             f"trunk={cfg.trunk_dim} T=29 lead=5 gears={cfg.n_gears}")
 
 
+def reference_gpu_leg(workload, timeout_s=420):
+    """The reference's own fp16 GPU stream on this GPU, in a process of its own (none of this library's
+    kernels loaded there): ``baseline/ref_gpu_bench.py`` on the tree ``baseline/setup_ref.py`` staged."""
+    script = ROOT / "baseline" / "ref_gpu_bench.py"
+    if not (ROOT / "baseline" / "_ref" / "python" / "policy.py").exists():
+        return {"unavailable": "baseline/_ref is not staged on this machine"}
+    try:
+        r = subprocess.run([sys.executable, str(script), "--workload", workload], capture_output=True, text=True,
+                           timeout=timeout_s, env=dict(os.environ, PYTHONDONTWRITEBYTECODE="1"))
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"reference GPU stream did not finish within {timeout_s} s"}
+    for line in reversed(r.stdout.splitlines()):
+        if line.startswith("{"):
+            try:
+                return json.loads(line)
+            except ValueError:
+                break
+    return {"unavailable": ("no result line; stderr tail: " + r.stderr[-300:]).replace("\n", " ")}
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from beatsaberrl_b200 import _native as nat
@@ -187,24 +211,52 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- device-resident throughput (value) ------------------------------------------
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed_ms(step, n):
+        """n calls of step() between two events, barrier + synchronize on both sides, max over ranks."""
+        barrier()
+        e0.record()
+        for _ in range(n):
+            step()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
+    # ---- device-resident throughput (value): CUDA-graph replays, stage profiler OFF -------------
+    # Protocol of the reference's forward bench (python/bench_policy_forward.py:72-83): warm up, capture
+    # the forward once, time the replays.  The same forward is also timed eagerly.
     for _ in range(args.warmup):
         policy.forward_stacked(obs)
+    torch.cuda.synchronize()
+    graph, timing = None, "eager launches"
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                g_out = policy.forward_stacked(obs)
+            timing = "CUDA-graph replays of one captured forward"
+        except Exception as e:              # noqa: BLE001 -- report and fall back to eager launches
+            graph, timing = None, f"eager launches (capture failed: {type(e).__name__})"
+            torch.cuda.synchronize()
+    step = graph.replay if graph is not None else (lambda: policy.forward_stacked(obs))
+    for _ in range(max(3, args.warmup)):
+        step()
     sampler = ClockSampler(local_rank)
     barrier()
     sampler.start()
-    nat.check(nat.lib.bsrl_profile_enable(1))
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        policy.forward_stacked(obs)
-    e1.record()
-    barrier()
-    ms = max_over_ranks(e0.elapsed_time(e1))
-    stages = nat.profile_read()
-    nat.check(nat.lib.bsrl_profile_enable(0))
+    ms = timed_ms(step, args.steps)
     clocks = sampler.stop()
     value = world * envs * args.steps / (ms * 1e-3)
+    ms_eager = timed_ms(lambda: policy.forward_stacked(obs), args.steps)
+
+    # ---- stage times: a separate pass with the library's per-launch events switched on ----------
+    stage_steps = min(args.steps, 5)
+    nat.check(nat.lib.bsrl_profile_enable(1))
+    timed_ms(lambda: policy.forward_stacked(obs), stage_steps)
+    stages = nat.profile_read()
+    nat.check(nat.lib.bsrl_profile_enable(0))
+    launches_per_step = int(sum(v["launches"] for v in stages.values())) // stage_steps
 
     # ---- end to end through the public API, host buffers (e2e) -----------------------
     # Every step copies its obs from pinned host memory, runs the forward and reads logits + value
@@ -249,6 +301,24 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     ms_e2e = max_over_ranks(e0.elapsed_time(e1))
     e2e_value = world * envs * args.steps / (ms_e2e * 1e-3)
+    del obs_dev, keep, logits_host
+
+    # ---- the PPO-recompute call at the sharded-rollout size: 131,072 envs per GPU through
+    # get_action_and_value(obs, int32 actions) -- forward + fused log-softmax / log-prob / entropy ----
+    recompute = None
+    if args.workload == "cfg2" and not args.envs and not args.no_recompute:
+        envs5 = WORKLOADS["cfg5"][1]
+        obs5 = po.make_obs(envs5, oseed + 1000 * rank + 7).to(dev)
+        act5 = po.make_actions(envs5, cfg, 4 + rank).to(torch.int32).to(dev)
+        call = lambda: policy.get_action_and_value(obs5, act5)
+        for _ in range(max(3, args.warmup)):
+            call()
+        ms5 = timed_ms(call, args.steps)
+        recompute = {"workload": f"cfg5: {describe(cfg)}, {envs5} envs per GPU, get_action_and_value(obs, int32 actions)",
+                     "value": world * envs5 * args.steps / (ms5 * 1e-3), "unit": UNIT,
+                     "ms_per_step": ms5 / args.steps, "envs_per_gpu": envs5, "timing": "eager launches",
+                     "outputs": "logprob, entropy, per-head entropy, value"}
+        del obs5, act5
 
     if rank != 0:
         if world > 1:
@@ -259,28 +329,44 @@ def run_ours(args, rank, world, local_rank):
     fwd_tflops = 2.0 * mac * (value / world) / 1e12          # per GPU
     gemm = {k: v for k, v in stages.items() if v["flops"] > 0 and k != "attention"}
     top_name = max(gemm, key=lambda k: gemm[k]["ms"]) if gemm else None
+    traffic = read_traffic_ratios()
+    sm_mhz = clocks.get("sm_mhz")
     roofline = None
     if top_name:
         t = gemm[top_name]
         achieved = t["flops"] / (t["ms"] * 1e-3) / 1e12
+        ms_launch = t["ms"] / t["launches"]
+        tr = traffic.get(top_name)
         roofline = {"bound": "tensor", "kernel": top_name, "achieved": achieved,
-                    "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
-                    "frac": achieved / peaks["tflops_sustained"],
-                    "traffic": (TRAFFIC_RATIO[top_name] * t["bytes"] / t["launches"] if top_name in TRAFFIC_RATIO else None),
-                    "traffic_source": "ncu dram bytes of a 237,568-row launch scaled by rows (profiles/)",
-                    "peak_source": peaks["source"] + " (sustained bf16 GEMM; burst %.1f)" % peaks["tflops_burst"],
-                    "launches": t["launches"], "ms_per_launch": t["ms"] / t["launches"],
+                    "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["tflops_burst"],
+                    "peak_source": peaks["source"] + " (bf16 GEMM burst; the timed region is well under a second)",
+                    "frac_of_sustained": achieved / peaks["tflops_sustained"], "peak_sustained": peaks["tflops_sustained"],
+                    # clock-normalised: FLOP per SM per cycle at the SM clock sampled during the run, against
+                    # the 8192 of one 128x256x16 f16 MMA every 128 cycles
+                    "flop_per_sm_cycle": (t["flops"] / t["launches"]) / (ms_launch * 1e-3 * sm_mhz * 1e6 * 148) if sm_mhz else None,
+                    "flop_per_sm_cycle_peak": 8192,
+                    "traffic": (tr["ratio"] * t["bytes"] / t["launches"] if tr else None),
+                    "traffic_source": (tr["source"] if tr else None),
+                    "launches": t["launches"], "ms_per_launch": ms_launch,
                     "algorithmic_bytes_per_launch": t["bytes"] / t["launches"],
                     "forward_tflops": fwd_tflops,
                     "forward_frac_of_burst": fwd_tflops / peaks["tflops_burst"],
+                    "forward_frac_of_sustained": fwd_tflops / peaks["tflops_sustained"],
                     "forward_frac_of_datasheet_2250": fwd_tflops / 2250.0,
-                    "stage_ms_per_step": {k: round(v["ms"] / args.steps, 4) for k, v in stages.items()}}
+                    "stage_ms_per_step": {k: round(v["ms"] / stage_steps, 4) for k, v in stages.items()},
+                    "stage_pass": f"{stage_steps} eager steps with per-launch events, separate from the timed region"}
     cpu_baseline = None
+    reference_gpu = None
     if world == 1:
         sample = args.cpu_sample or max(64, min(envs, int(6.0e11 / (2 * mac))))
         rate, times = cpu_forward_rate(cfg, sd, sample, oseed, padded, reps=3, warm=1)
         cpu_baseline = {"value": rate, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                         "sample": f"{sample} envs, best of 3 after 1 warm-up, torch fp32 on all host threads"}
+        if not args.no_ref_gpu:
+            del policy, obs
+            torch.cuda.empty_cache()
+            reference_gpu = reference_gpu_leg(args.workload if args.workload in ("cfg1", "cfg2", "cfg4", "recipe") else "cfg2")
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -290,17 +376,33 @@ def run_ours(args, rank, world, local_rank):
                                f"{'Xavier' if xavier else 'default'} init seed {wseed}",
                    "l2": "inputs and activations larger than L2 (obs %.0f MB, token stream %.1f GB)"
                          % (envs * 630 * 4 / 1e6, envs * 29 * cfg.embed * 4 / 1e9),
-                   "mac_per_env": mac},
+                   "timing": timing, "mac_per_env": mac},
+        "eager_ms_per_step": ms_eager / args.steps,
         "roofline": roofline, "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": obs_host.numel() * 4,
-                "d2h_bytes_per_step": (logits_host[0].numel() + value_host[0].numel()) * 4},
-        "gpu_launches": int(sum(v["launches"] for v in stages.values())),
+                "d2h_bytes_per_step": (envs * 29 * cfg.k_max + envs) * 4},
+        "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
+    if recompute:
+        line["cfg5_recompute"] = recompute
+    if reference_gpu is not None:
+        line["reference_gpu"] = reference_gpu
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def read_traffic_ratios():
+    """{stage: {"ratio": measured DRAM bytes / algorithmic bytes, "source": ...}} written next to the ncu
+    summaries when a kernel is profiled; traffic grows in proportion to the rows of a launch, so a
+    full-size launch's traffic is the ratio times its algorithmic bytes."""
+    p = ROOT / "profiles" / "traffic_ratios.json"
+    try:
+        return json.loads(p.read_text())
+    except (OSError, ValueError):
+        return {}
 
 
 def run_kernel(args):
@@ -358,12 +460,6 @@ def run_kernel(args):
                       "tflops": flops / ms / 1e9, "algorithmic_gbs": nbytes / ms / 1e6}), flush=True)
 
 
-# Measured DRAM traffic / algorithmic bytes of each stage's kernel, from the committed ncu captures
-# (profiles/*_rows237568_d256.md, taken on 237,568-row cases; traffic grows in proportion to the
-# rows, so a full-size launch's traffic is this ratio times its algorithmic bytes).
-TRAFFIC_RATIO = {"block_tail": 0.97, "attn_block": 0.82}
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -373,6 +469,9 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--envs", type=int, default=0, help="envs per GPU (default: the workload's)")
     ap.add_argument("--cpu-sample", type=int, default=0, help="envs in the CPU sample")
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replays")
+    ap.add_argument("--no-recompute", action="store_true", help="skip the cfg5 PPO-recompute sub-record")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="skip the reference's GPU stream (1-GPU runs)")
     ap.add_argument("--kernel", default="", choices=("", "block_tail", "attn_block", "linear"),
                     help="time one kernel alone on --rows token rows instead of the whole forward")
     ap.add_argument("--rows", type=int, default=237568)

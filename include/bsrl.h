@@ -8,6 +8,11 @@
  * negative bsrl_status otherwise, with a thread-local message behind bsrl_last_error().
  * All argument checks happen on the host before the first launch.
  *
+ * Threads and devices: entry points may be called from several host threads, each on its own
+ * stream / device; the stage profiler is per host thread; per-device set-up (kernel attributes,
+ * device-symbol addresses) is done once per device under a lock and belongs to the device's
+ * primary context, so do not call cudaDeviceReset between calls.
+ *
  * The entry points replace, for the policy-forward path, what the reference binds through
  * its two pybind11 torch extensions and the torch library calls around them:
  *   layer_norm_cuda {ln_fwd, ln_fwd_add}   python/beat_arena_env/csrc/layer_norm.cu:733-749
@@ -25,7 +30,7 @@
 extern "C" {
 #endif
 
-#define BSRL_ABI_VERSION 2
+#define BSRL_ABI_VERSION 3
 #define BSRL_OBS_DIM 630
 #define BSRL_N_TOKENS 29
 #define BSRL_N_LEAD 5
@@ -230,13 +235,54 @@ int bsrl_block_tail(const void* att_f16, const float* x, const void* wo_f16, con
                     const void* w2_f16, const float* b2, float eps, int64_t m, int32_t d, int32_t f,
                     float* x_out, void* ln_out_f16, const float* out_g, const float* out_b, void* stream);
 
+/* Readout trunk + packed action heads alone (NotePolicy._trunk and the packed head GEMM,
+ * python/policy.py:1107-1155, :1311-1335): readout (n_envs, 5 * embed) f16 = the lead rows leaving the
+ * last block -> head_out (n_envs, head_cols_pad) f32, the 29 heads' outputs side by side (bias
+ * included, before the masked-lane fill; bsrl_head_layout gives the pitch and each head's first
+ * column).  trunk_h (n_envs, trunk_dim) f16 is optional: the trunk output the reference stashes as
+ * NotePolicy._diag_h (python/policy.py:1309-1310).  Uses the forward's workspace. */
+int bsrl_trunk_heads(const bsrl_config* cfg, const void* arena, const void* readout_f16, int64_t n_envs,
+                     float* head_out, void* trunk_h_f16, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Head tail alone: masked-lane fill, log-softmax, summed log-prob of the given actions, entropy,
+ * HL-Gauss value (python/policy.py:1337-1344, :1399-1403, :1473-1516).  head_out (n_envs,
+ * head_cols_pad) f32 and value_bin_logits (n_envs, bins_pad) f32 as the forward's GEMMs leave them;
+ * actions, logits, logprob, entropy, ent_head may be NULL. */
+int bsrl_head_tail(const bsrl_config* cfg, const float* head_out, const float* value_bin_logits, int64_t n_envs,
+                   const void* actions, int32_t act_dtype, float* logits, float* logprob, float* entropy,
+                   float* ent_head, float* value, void* stream);
+/* Row pitches of head_out and value_bin_logits, and the first packed column of each of the 29 heads. */
+int bsrl_head_layout(const bsrl_config* cfg, int32_t* head_cols_pad, int32_t* bins_pad, int32_t* head_first);
+
+/* Where a named intermediate of the last forward sits in the caller's workspace (valid until the next
+ * call on that workspace): "trunk_h" (the reference's _diag_h), "x_resolved" (the residual stream
+ * entering the last block, the critic's input; python/policy.py:1302-1305), "key_bias", "readout",
+ * "head_out".  dtype is a bsrl_dtype; ld_elems the row pitch in elements. */
+int bsrl_workspace_region(const bsrl_config* cfg, int64_t n_envs, const char* name, int64_t* byte_offset,
+                          int64_t* rows, int64_t* cols, int64_t* ld_elems, int32_t* dtype);
+
+/* Stand-in for the simulator's per-tick step kernel (step_kernel,
+ * python/beat_arena_env/csrc/beat_arena_cuda.cu:6188-6245), for graph-capture tests and rollout-tick
+ * benchmarks only: it has the real kernel's memory behaviour -- reads actions (n_envs, 29) i64,
+ * rewrites obs (n_envs, 630) f32, reward (n_envs) f32 and done (n_envs) u8 IN PLACE, advances state
+ * (n_envs) u32 -- and none of its physics (the next obs is a hash of state and actions, clipped to
+ * +-5, slot-mask lanes 0 or 1).  reward and done may be NULL. */
+int bsrl_standin_env_step(const int64_t* actions, int64_t n_envs, uint32_t* state, float* obs, float* reward,
+                          uint8_t* done, void* stream);
+
+/* Self-test of the bounded waits: launches a one-CTA kernel whose only thread waits, for at most
+ * `polls` polls, on an mbarrier that nothing ever arrives on.  The wait runs out, the kernel sets the
+ * device status word (kernel 15, role 1) and returns; the next bsrl_device_status() therefore reports
+ * BSRL_ERR_TIMEOUT, and the GPU and the context stay usable.  Nothing traps or hangs.  No counterpart
+ * in the reference. */
+int bsrl_selftest_wait_timeout(int32_t polls, void* stream);
+
 /* Which GEMM kernel the forward's linear layers use: 0 (default) = the tcgen05/TMEM kernel
  * wherever the shape fits it (and the fused block-tail kernel), the warp-MMA kernel elsewhere;
- * 1 = the warp-MMA kernel and separate LayerNorm kernels everywhere; 2 = as 0 but the fused block
- * tail runs on two-CTA clusters (tcgen05 cta_group::2: each CTA fetches half of every weight tile;
- * correct, but measured slower than one CTA per tile, so it is not the default).
+ * 1 = the warp-MMA kernel and separate LayerNorm kernels everywhere.
  * Both are CUDA kernels of this library; 1 exists so tests can cross-check one against the
- * other.  No counterpart in the reference. */
+ * other.  The choice is process-wide: set it before the first forward and before asking for
+ * bsrl_workspace_bytes (the unfused kernels need more workspace).  No counterpart in the reference. */
 int bsrl_set_engine(int32_t engine);
 
 /* Synchronises the current device, then reads and clears its status word: BSRL_OK, or

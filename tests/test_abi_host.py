@@ -20,7 +20,7 @@ def test_every_declared_symbol_is_exported(native):
     assert len(names) >= 15
     for n in names:
         assert hasattr(native.lib, n), n
-    assert native.lib.bsrl_abi_version() == 2
+    assert native.lib.bsrl_abi_version() == 3
 
 
 def test_token_lanes_match_oracle(native):

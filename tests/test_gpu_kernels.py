@@ -183,3 +183,73 @@ def test_qkv_attention(native, B, d, H, q_first, n_q):
     q, k, v = qkv.split(d, -1)
     ref = po.attention(q[:, q_first:q_first + n_q], k, v, kb, H)
     torch.testing.assert_close(out.float().cpu().view(B, n_q, d), ref, atol=5e-3, rtol=3e-3)
+
+
+def _native_cfg(native, cfg):
+    return native.make_config(cfg.embed, cfg.n_heads, cfg.n_blocks, cfg.ffn_mult, cfg.trunk_dim,
+                              cfg.trunk_hidden, cfg.value_bins, cfg.note_geo, cfg.head_gears,
+                              cfg.z_asinh, cfg.value_vmax, cfg.eps, trunk_v2=(cfg.trunk_arch == "simbav2"))
+
+
+@pytest.mark.parametrize("case,B", [("tiny_plain", 200), ("tiny_geo_mixed", 77), ("tiny_simbav2", 130)])
+def test_trunk_heads_stage(native, case, B):
+    """Readout trunk + packed heads alone (bsrl_trunk_heads) against the oracle's trunk and head
+    Linears on the same fp16-rounded readout rows."""
+    cfg, sd = golden_case(case)
+    from helpers import cuda_policy
+    m = cuda_policy(cfg, sd)
+    m.flatten_fp16()
+    c = m._cfg
+    g = torch.Generator().manual_seed(B)
+    lead = (torch.randn(B, 5 * cfg.embed, generator=g)).half()
+    pad, bins_pad = C.c_int32(), C.c_int32()
+    first = (C.c_int32 * 29)()
+    native.check(native.lib.bsrl_head_layout(C.byref(c), C.byref(pad), C.byref(bins_pad), first))
+    ws_n = native.lib.bsrl_workspace_bytes(C.byref(c), B)
+    ws = torch.empty(ws_n, dtype=torch.uint8, device="cuda")
+    raw = torch.empty(B, pad.value, device="cuda")
+    h16 = torch.empty(B, cfg.trunk_dim, dtype=torch.float16, device="cuda")
+    lead_d = lead.cuda()
+    native.check(native.lib.bsrl_trunk_heads(C.byref(c), m._arena.data_ptr(), lead_d.data_ptr(), B, raw.data_ptr(),
+                                             h16.data_ptr(), ws.data_ptr(), ws_n, _stream()))
+    h_ref = po.trunk(sd, cfg, lead.float())
+    torch.testing.assert_close(h16.float().cpu(), h_ref, atol=3e-2, rtol=2e-2)
+    logits_ref = po.head_logits(sd, cfg, h_ref)                   # (B, 29, k_max) with -1e9 fill
+    raw = raw.cpu()
+    for j, k in enumerate(cfg.head_gears or (cfg.n_gears,) * 29):
+        torch.testing.assert_close(raw[:, first[j]:first[j] + k], logits_ref[:, j, :k], atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("case,B", [("tiny_plain", 300), ("tiny_geo_mixed", 65)])
+def test_head_tail_stage(native, case, B):
+    """Head tail alone (bsrl_head_tail): fill, log-softmax, log-prob, entropy and HL-Gauss value are fp32
+    arithmetic on given inputs, so they match the oracle to float rounding."""
+    cfg, sd = golden_case(case)
+    c = _native_cfg(native, cfg)
+    gears = cfg.head_gears or (cfg.n_gears,) * 29
+    pad, bins_pad = C.c_int32(), C.c_int32()
+    first = (C.c_int32 * 29)()
+    native.check(native.lib.bsrl_head_layout(C.byref(c), C.byref(pad), C.byref(bins_pad), first))
+    g = torch.Generator().manual_seed(B)
+    raw = torch.randn(B, pad.value, generator=g) * 2
+    vraw = torch.randn(B, bins_pad.value, generator=g) * 3
+    act = po.make_actions(B, cfg, 9)
+    k_max = max(gears)
+    out = dict(logits=torch.empty(B, 29, k_max), logprob=torch.empty(B), entropy=torch.empty(B),
+               ent_head=torch.empty(B, 29), value=torch.empty(B))
+    out = {k: v.cuda() for k, v in out.items()}
+    raw_d, vraw_d, act_d = raw.cuda(), vraw.cuda(), act.to(torch.int32).cuda()
+    native.check(native.lib.bsrl_head_tail(C.byref(c), raw_d.data_ptr(), vraw_d.data_ptr(), B, act_d.data_ptr(),
+                                           native.I32, out["logits"].data_ptr(), out["logprob"].data_ptr(),
+                                           out["entropy"].data_ptr(), out["ent_head"].data_ptr(),
+                                           out["value"].data_ptr(), _stream()))
+    ref_logits = torch.full((B, 29, k_max), -1e9)
+    for j, k in enumerate(gears):
+        ref_logits[:, j, :k] = raw[:, first[j]:first[j] + k]
+    assert torch.equal(out["logits"].cpu(), ref_logits)
+    lp, ent, ent_h = po.evaluate_actions(ref_logits, act)
+    torch.testing.assert_close(out["logprob"].cpu(), lp, atol=2e-4, rtol=1e-5)
+    torch.testing.assert_close(out["ent_head"].cpu(), ent_h, atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(out["entropy"].cpu(), ent, atol=2e-4, rtol=1e-5)
+    val = torch.softmax(vraw[:, :cfg.value_bins], -1) @ po.value_centers(cfg)
+    torch.testing.assert_close(out["value"].cpu(), val, atol=1e-5, rtol=1e-5)
