@@ -72,6 +72,9 @@ _sig = {
     "bsrl_param_desc": (C.c_int, [_CFG, C.c_int32, C.c_char_p, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "bsrl_weights_bytes": (C.c_int64, [_CFG]),
     "bsrl_pack_weights": (C.c_int, [_CFG, C.POINTER(_P), C.c_int32, _P, C.c_int64, _P]),
+    "bsrl_adam_step_pack": (C.c_int, [_CFG, C.POINTER(_P), C.POINTER(_P), C.POINTER(_P), C.POINTER(_P), C.c_int32,
+                                      C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_float, C.c_float, C.c_float,
+                                      C.c_int32, _P, _P, _P, C.c_int64, _P]),
     "bsrl_workspace_bytes": (C.c_int64, [_CFG, C.c_int64]),
     "bsrl_forward": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, _P, _P, _P, C.c_int64, _P]),
     "bsrl_fixed_scratch_bytes": (C.c_int64, []),

@@ -32,9 +32,9 @@ inline const T* at(const void* base, int64_t off) {
 // Optional CUDA-event timing of every launch of a forward, grouped by stage.  Off by default
 // (a captured graph must not contain it); the benchmark switches it on to time the dominant
 // kernel live, on the stream the kernels run on.
-enum Stage { kStGather = 0, kStEncoder, kStLayerNorm, kStQkv, kStAttention, kStOutProj, kStFfnUp,
+enum Stage { kStGather = 0, kStEncoder, kStEncoderFused, kStLayerNorm, kStQkv, kStAttention, kStOutProj, kStFfnUp,
              kStFfnDown, kStBlockTail, kStAttnBlock, kStTrunk, kStCritic, kStHeadTail, kStCount };
-const char* const kStageNames[kStCount] = {"embed_gather", "encoder_gemm", "layernorm", "qkv_gemm",
+const char* const kStageNames[kStCount] = {"embed_gather", "encoder_gemm", "encoder_fused", "layernorm", "qkv_gemm",
                                            "attention", "out_proj_gemm", "ffn_up_gemm", "ffn_down_gemm", "block_tail", "attn_block",
                                            "trunk", "critic", "head_tail"};
 struct Profiler {
@@ -149,8 +149,10 @@ struct Ctx {
     if (rc__ != BSRL_OK) return rc__; \
   } while (0)
 
-// obs -> x (B*29, d) f32 + key bias
-int run_embed(const Ctx& c, const void* obs, int obs_dtype, float* x, float* key_bias) {
+// obs -> x (B*29, d) f32 + key bias; with h_out (and the fused encoder kernel) also block 0's LayerNorm rows.
+// Returns through *have_h whether h_out was written.
+int run_embed(const Ctx& c, const void* obs, int obs_dtype, float* x, float* key_bias, __half* h_out = nullptr,
+              bool* have_h = nullptr) {
   const Layout& l = c.l;
   const Workspace& w = c.w;
   const int d = l.d;
@@ -166,6 +168,26 @@ int run_embed(const Ctx& c, const void* obs, int obs_dtype, float* x, float* key
   g_stage = kStGather;
   BSRL_TRY(timed(c.st, 0.0, (double)B * (kObs * 4 + (2 * kSaberK + kTorsoK + 2 * kLegK + kSlots * l.note_k) * 2 + kT * 4),
                  [&] { return embed_gather(obs, obs_dtype, B, c.cfg->note_geo, c.cfg->game_flux, c.cfg->z_asinh, eb, c.st); }));
+  if (have_h) *have_h = false;
+  if (c.paths.enc_fused) {
+    EncoderArgs ea;
+    ea.d = d; ea.n_envs = B; ea.feat = eb.saber;
+    const Encoder* encs[4] = {&l.saber, &l.torso, &l.leg, &l.note};
+    const int kpad[4] = {kSaberK, kTorsoK, kLegK, l.note_k};
+    for (int e = 0; e < 4; ++e) {
+      ea.w0[e] = c.W(encs[e]->l0); ea.b0[e] = c.Bv(encs[e]->l0); ea.k0[e] = kpad[e];
+      ea.w1[e] = c.W(encs[e]->l1); ea.b1[e] = c.Bv(encs[e]->l1);
+    }
+    const BlockW& b0 = l.blocks[0];
+    ea.ln_g = c.G(b0.ln_attn); ea.ln_b = c.Be(b0.ln_attn); ea.eps = c.cfg->eps;
+    ea.x = x; ea.h = h_out;
+    g_stage = kStEncoderFused;
+    const double rows = (double)B * kT;
+    BSRL_TRY(timed(c.st, 2.0 * rows * d * (64 + d), rows * (128 + 4.0 * d + (h_out ? 2.0 * d : 0.0)),
+                   [&] { return encoder_fused(ea, c.st); }));
+    if (have_h) *have_h = h_out != nullptr;
+    return BSRL_OK;
+  }
   g_stage = kStEncoder;
   __half* hid = at<__half>(c.ws, w.enc_hid);
   struct Part { const Encoder* e; const __half* f; int kpad; int64_t rows; int64_t row0; int group; int first; };
@@ -253,7 +275,8 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   const RowMap lead_rows{kLead, kT, 0};
   const RowMap ident = identity_map();
 
-  BSRL_TRY(run_embed(c, obs, obs_dtype, x, key_bias));
+  bool have_h = false, have_hv = false;
+  BSRL_TRY(run_embed(c, obs, obs_dtype, x, key_bias, h, &have_h));
 
   // Fused block tail (out-projection + LayerNorm + FFN in one tcgen05 kernel) where the widths fit;
   // it also emits the next block's LayerNorm rows (and the critic's), so the standalone LayerNorm
@@ -292,7 +315,6 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     return BSRL_ERR_UNSUPPORTED;
   }
   __half* hv = at<__half>(c.ws, w.enc_hid);   // critic LayerNorm rows (encoder scratch is free by now)
-  bool have_h = false, have_hv = false;
   // value residual (python/policy.py:1263-1275): block 0 hands its attention values to every later block
   __half* v0buf = l.value_residual ? at<__half>(c.ws, w.v0) : nullptr;
   auto vres_fused = [&](AttnBlockArgs a, int i) {
@@ -547,21 +569,45 @@ int bsrl_pack_weights(const bsrl_config* cfg, const float* const* params, int32_
   cudaStream_t st = as_stream(stream);
   // padding columns / rows of the stacked matrices must read as zero
   BSRL_CUDA_OK(cudaMemsetAsync(arena, 0, l.bytes, st));
-  for (int32_t i = 0; i < n_params; ++i) {
-    const ParamSlot& p = s[i];
-    if (p.half)
-      BSRL_TRY(pack_cast(params[i], p.rows, p.cols, at<__half>(arena, p.dst), p.dst_pitch, st));
-    else
-      BSRL_TRY(pack_copy(params[i], p.rows, at<float>(arena, p.dst), st));
+  return multi_pack(*cfg, l, const_cast<float* const*>(params), nullptr, nullptr, nullptr, nullptr, nullptr, 0.f, 0.f,
+                    0.f, 0, nullptr, nullptr, arena, st);
+}
+
+int bsrl_adam_step_pack(const bsrl_config* cfg, float* const* params, const float* const* grads,
+                        float* const* exp_avg, float* const* exp_avg_sq, int32_t n_params, const float* lr,
+                        const float* weight_decay, float beta1, float beta2, float eps, int32_t step,
+                        const float* inv_scale, const float* found_inf, void* arena, int64_t arena_bytes,
+                        void* stream) {
+  BSRL_TRY(validate_config(cfg));
+  Layout l = make_layout(*cfg);
+  const int32_t want = (int32_t)make_param_slots(*cfg, l).size();
+  if (!params || !grads || !exp_avg || !exp_avg_sq || !lr || !arena) {
+    set_error("adam_step_pack: NULL argument");
+    return BSRL_ERR_NULL;
   }
-  for (const CopySlot& cs : make_copy_slots(*cfg, l, s)) {
-    const float* src = params[cs.param] + cs.src_row0 * cs.cols;
-    if (cs.half)
-      BSRL_TRY(pack_cast(src, cs.n_rows, cs.cols, at<__half>(arena, cs.dst), cs.dst_pitch, st));
-    else
-      BSRL_TRY(pack_copy(src, cs.n_rows, at<float>(arena, cs.dst), st));
+  if (n_params != want) {
+    set_error("adam_step_pack: %d parameters given, %d expected", n_params, want);
+    return BSRL_ERR_SHAPE;
   }
-  return BSRL_OK;
+  if (arena_bytes < l.bytes) {
+    set_error("adam_step_pack: arena %lld bytes < required %lld", (long long)arena_bytes, (long long)l.bytes);
+    return BSRL_ERR_WORKSPACE;
+  }
+  if (reinterpret_cast<uintptr_t>(arena) & 255) {
+    set_error("adam_step_pack: arena must be 256-byte aligned");
+    return BSRL_ERR_ALIGN;
+  }
+  if (step < 1 || !(beta1 >= 0.f && beta1 < 1.f) || !(beta2 >= 0.f && beta2 < 1.f) || !(eps > 0.f)) {
+    set_error("adam_step_pack: step must be >= 1, betas in [0, 1), eps > 0");
+    return BSRL_ERR_SHAPE;
+  }
+  for (int32_t i = 0; i < n_params; ++i)
+    if (!params[i]) {
+      set_error("adam_step_pack: parameter %d is NULL", i);
+      return BSRL_ERR_NULL;
+    }
+  return multi_pack(*cfg, l, params, grads, exp_avg, exp_avg_sq, lr, weight_decay, beta1, beta2, eps, step, inv_scale,
+                    found_inf, arena, as_stream(stream));
 }
 
 int64_t bsrl_workspace_bytes(const bsrl_config* cfg, int64_t n_envs) {

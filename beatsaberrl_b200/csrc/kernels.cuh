@@ -108,6 +108,26 @@ int embed_gather(const void* obs, int obs_dtype, int64_t n_envs, int note_geo, i
                  const EmbedBuffers& out, cudaStream_t stream);
 int token_lane_host(int tok, int k);
 
+// Fused token encoders (both layers of the four MLPs + block 0's LayerNorm), one tcgen05 kernel.
+// Encoder order everywhere: saber, torso, leg, note.
+struct EncoderArgs {
+  int d;
+  int64_t n_envs;
+  const __half* feat;    // (29 n_envs, 64) f16: 2 n_envs saber rows, n_envs torso, 2 n_envs leg, 24 n_envs note rows
+  const __half* w0[4];   // (d, 64) first layers, K-padded
+  const float* b0[4];
+  int k0[4];             // padded input widths (all 64)
+  const __half* w1[4];   // (d, d) second layers
+  const float* b1[4];
+  const float* ln_g;     // block 0's ln_attn (used when h is given)
+  const float* ln_b;
+  float eps;
+  float* x;              // (29 n_envs, d) f32 token stream out
+  __half* h;             // (29 n_envs, d) f16 LayerNorm rows out, or nullptr
+};
+bool encoder_fused_ok(const EncoderArgs& a);
+int encoder_fused(const EncoderArgs& a, cudaStream_t stream);
+
 // Masked MHA over the 29 keys of each env.
 int attention29(const __half* qkv, int ld_qkv, const float* key_bias, int64_t n_envs, int d,
                 int n_heads, int q_first, int n_q, __half* out, int ldo, cudaStream_t stream);
@@ -146,9 +166,13 @@ int head_tail(const HeadTailArgs& a, cudaStream_t stream);
 int standin_env_step(const long long* actions, int64_t n_envs, uint32_t* state, float* obs, float* reward,
                      unsigned char* done, cudaStream_t stream);
 
-// f32 -> f16 cast with row pitch (weight packing), and plain f32 copy.
-int pack_cast(const float* src, int64_t rows, int64_t cols, __half* dst, int64_t dst_pitch,
-              cudaStream_t stream);
-int pack_copy(const float* src, int64_t n, float* dst, cudaStream_t stream);
+// Scatter of every fp32 master into the packed arena (a few launches), with an optional Adam / AdamW
+// step applied to the masters that come with a gradient first (optim.cu).  lr / wd: one value per
+// parameter (host arrays) or nullptr; step: 1-based step count for the bias corrections (0: none).
+struct Layout;
+int multi_pack(const bsrl_config& cfg, const Layout& l, float* const* params, const float* const* grads,
+               float* const* exp_avg, float* const* exp_avg_sq, const float* lr, const float* wd, float beta1,
+               float beta2, float eps, int step, const float* inv_scale, const float* found_inf, void* arena,
+               cudaStream_t stream);
 
 }  // namespace bsrl

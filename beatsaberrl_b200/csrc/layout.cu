@@ -311,6 +311,7 @@ Paths plan_paths(const Layout& l, int engine) {
   const bool widths = engine == 0 && l.d % 64 == 0 && l.d >= 64 && l.d <= 256;
   p.attn_fused = widths && l.attn_G > 0;
   p.tail_fused = widths && l.F % 256 == 0 && l.F >= 256 && l.F <= 1024;
+  p.enc_fused = widths && !l.emb_ln.width && l.note_k == 64;
   return p;
 }
 
@@ -320,10 +321,12 @@ Workspace make_workspace(const Layout& l, int64_t B, const Paths& paths) {
   const int64_t R = B * kT, Rl = B * kLead;
   const int d = l.d;
   w.key_bias = cv.take(R * 4);
-  w.f_saber = cv.take(B * 2 * kSaberK * 2);
-  w.f_torso = cv.take(B * kTorsoK * 2);
-  w.f_leg = cv.take(B * 2 * kLegK * 2);
-  w.f_note = cv.take(B * kSlots * l.note_k * 2);
+  // encoder input rows, all 64 wide, as ONE (29 B, 64) matrix: saber | torso | leg | note
+  static_assert(kSaberK == 64 && kTorsoK == 64 && kLegK == 64, "the feature matrix has one row width");
+  w.f_saber = cv.take(B * kT * 64 * 2);
+  w.f_torso = w.f_saber + B * 2 * 64 * 2;
+  w.f_leg = w.f_torso + B * 64 * 2;
+  w.f_note = w.f_leg + B * 2 * 64 * 2;
   w.enc_hid = cv.take(R * d * 2);
   w.x = cv.take(R * d * 4);
   w.h = cv.take(R * d * 2);
@@ -346,43 +349,6 @@ Workspace make_workspace(const Layout& l, int64_t B, const Paths& paths) {
   w.t32 = cv.take(l.trunk_v2 ? B * (int64_t)(l.D > l.Hh ? l.D : l.Hh) * 4 : 0);
   w.bytes = cv.off;
   return w;
-}
-
-// ------------------------------------------------------------------ pack kernels
-namespace {
-__global__ void cast_rows_kernel(const float* __restrict__ src, int64_t rows, int64_t cols,
-                                 __half* __restrict__ dst, int64_t pitch) {
-  int64_t n = rows * cols;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t r = i / cols, c = i % cols;
-    dst[r * pitch + c] = __float2half_rn(src[i]);
-  }
-}
-__global__ void copy_kernel(const float* __restrict__ src, int64_t n, float* __restrict__ dst) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-       i += (int64_t)gridDim.x * blockDim.x)
-    dst[i] = src[i];
-}
-}  // namespace
-
-int pack_cast(const float* src, int64_t rows, int64_t cols, __half* dst, int64_t dst_pitch,
-              cudaStream_t stream) {
-  int64_t n = rows * cols;
-  if (n == 0) return BSRL_OK;
-  int64_t blocks = (n + 255) / 256;
-  if (blocks > 1024) blocks = 1024;
-  cast_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(src, rows, cols, dst, dst_pitch);
-  BSRL_LAUNCH_OK("cast_rows_kernel");
-  return BSRL_OK;
-}
-int pack_copy(const float* src, int64_t n, float* dst, cudaStream_t stream) {
-  if (n == 0) return BSRL_OK;
-  int64_t blocks = (n + 255) / 256;
-  if (blocks > 1024) blocks = 1024;
-  copy_kernel<<<(unsigned)blocks, 256, 0, stream>>>(src, n, dst);
-  BSRL_LAUNCH_OK("copy_kernel");
-  return BSRL_OK;
 }
 
 }  // namespace bsrl

@@ -77,6 +77,7 @@ std::vector<CopySlot> make_copy_slots(const bsrl_config& c, const Layout& l, con
 struct Paths {
   bool attn_fused;   // q|k|v projection + attention in one kernel (no (rows, 3d) buffer)
   bool tail_fused;   // out-projection + LayerNorm + FFN in one kernel (no (rows, 4d) hidden buffer)
+  bool enc_fused;    // both encoder layers + block 0's LayerNorm in one kernel
 };
 Paths plan_paths(const Layout& l, int engine);
 

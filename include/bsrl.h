@@ -103,6 +103,25 @@ int64_t bsrl_weights_bytes(const bsrl_config* cfg);
 int bsrl_pack_weights(const bsrl_config* cfg, const float* const* params, int32_t n_params,
                       void* arena, int64_t arena_bytes, void* stream);
 
+/* Optimizer step and arena refresh in one pass: an Adam / AdamW update of every fp32 master that has
+ * a gradient, written straight into the master AND into its fp16 / fp32 places in the arena by the
+ * same kernel, so that no separate refresh follows opt.step().  Replaces the pair
+ * "fused Adam step, then bump_weights_version() + flat fp16 recast" of the reference trainer
+ * (python/train_batch.py:2847-2854, python/fp16_linear.py:236-246).  Arithmetic of torch.optim.AdamW:
+ *   g' = g * *inv_scale;  p *= 1 - lr wd;  m = b1 m + (1 - b1) g';  v = b2 v + (1 - b2) g'^2;
+ *   p -= lr / (1 - b1^step) * m / (sqrt(v) / sqrt(1 - b2^step) + eps)
+ * params / grads / exp_avg / exp_avg_sq: n_params DEVICE pointers each, in bsrl_param_desc order;
+ * grads[i] == NULL leaves master i unchanged and only re-scatters it (frozen parameters, or ones
+ * another optimizer owns).  lr and weight_decay: n_params HOST floats (weight_decay may be NULL = 0).
+ * inv_scale / found_inf: optional DEVICE scalars of a loss scaler (non-zero found_inf skips every
+ * update).  The arena must have been packed once by bsrl_pack_weights (which also zeroes its padding).
+ * A handful of launches for the whole model; nothing allocated. */
+int bsrl_adam_step_pack(const bsrl_config* cfg, float* const* params, const float* const* grads,
+                        float* const* exp_avg, float* const* exp_avg_sq, int32_t n_params, const float* lr,
+                        const float* weight_decay, float beta1, float beta2, float eps, int32_t step,
+                        const float* inv_scale, const float* found_inf, void* arena, int64_t arena_bytes,
+                        void* stream);
+
 /* --- forward -------------------------------------------------------------------- */
 int64_t bsrl_workspace_bytes(const bsrl_config* cfg, int64_t n_envs);
 
