@@ -9,24 +9,13 @@
 #include <atomic>
 #include <vector>
 
-#include "kernels.cuh"
-#include "layout.h"
+#include "api_internal.cuh"
 #include "tc5.cuh"
 
 namespace bsrl {
 const char* last_error();
 
-namespace {
-
-inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
-template <typename T>
-inline T* at(void* base, int64_t off) {
-  return reinterpret_cast<T*>(static_cast<uint8_t*>(base) + off);
-}
-template <typename T>
-inline const T* at(const void* base, int64_t off) {
-  return reinterpret_cast<const T*>(static_cast<const uint8_t*>(base) + off);
-}
+namespace fwd {
 
 // ---------------------------------------------------------------- stage profiler
 // Optional CUDA-event timing of every launch of a forward, grouped by stage.  Off by default
@@ -127,41 +116,20 @@ int fused_attn(const AttnBlockArgs& a, cudaStream_t st) {
   return rc;
 }
 
-struct Ctx {
-  const bsrl_config* cfg;
-  Layout l;
-  Paths paths;
-  Workspace w;
-  const void* arena;
-  void* ws;
-  int64_t B;
-  cudaStream_t st;
-  __half* obs16 = nullptr;   // optional fp16 copy of the obs rows, written by the tokenizer kernel
-  const __half* W(const Mat& m, int row0 = 0) const { return at<__half>(arena, m.w) + (int64_t)row0 * m.pitch; }
-  const float* Bv(const Mat& m, int row0 = 0) const { return at<float>(arena, m.b) + row0; }
-  const float* G(const Norm& n) const { return at<float>(arena, n.g); }
-  const float* Be(const Norm& n) const { return at<float>(arena, n.b); }
-};
-
-#define BSRL_TRY(expr)             \
-  do {                             \
-    int rc__ = (expr);             \
-    if (rc__ != BSRL_OK) return rc__; \
-  } while (0)
-
 // obs -> x (B*29, d) f32 + key bias; with h_out (and the fused encoder kernel) also block 0's LayerNorm rows.
 // Returns through *have_h whether h_out was written.
-int run_embed(const Ctx& c, const void* obs, int obs_dtype, float* x, float* key_bias, __half* h_out = nullptr,
-              bool* have_h = nullptr) {
+int run_embed(const Ctx& c, const void* obs, int obs_dtype, float* x, float* key_bias, __half* h_out,
+              bool* have_h) {
   const Layout& l = c.l;
   const Workspace& w = c.w;
   const int d = l.d;
   const int64_t B = c.B;
   EmbedBuffers eb;
-  eb.saber = at<__half>(c.ws, w.f_saber);
-  eb.torso = at<__half>(c.ws, w.f_torso);
-  eb.leg = at<__half>(c.ws, w.f_leg);
-  eb.note = at<__half>(c.ws, w.f_note);
+  // one (29 B, 64) feature matrix: saber | torso | leg | note rows (kept for the backward in a grad-mode forward)
+  eb.saber = c.train ? c.train->feat : at<__half>(c.ws, w.f_saber);
+  eb.torso = eb.saber + 2 * B * 64;
+  eb.leg = eb.torso + B * 64;
+  eb.note = eb.leg + 2 * B * 64;
   eb.key_bias = key_bias;
   eb.obs16 = c.obs16;
   eb.ks = kSaberK; eb.kt = kTorsoK; eb.kl = kLegK; eb.kn = l.note_k;
@@ -266,8 +234,10 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   const int d = l.d, F = l.F, D = l.D;
   const int64_t B = c.B, R = B * kT, Rl = B * kLead;
   const float eps = c.cfg->eps;
-  float* x = at<float>(c.ws, w.x);
-  float* key_bias = at<float>(c.ws, w.key_bias);
+  // the residual stream: one buffer updated in place, or -- in a grad-mode forward -- one buffer per
+  // block input, so that the backward can recompute every block from what entered it
+  float* x = c.train ? c.train->x[0] : at<float>(c.ws, w.x);
+  float* key_bias = c.train ? c.train->key_bias : at<float>(c.ws, w.key_bias);
   __half* h = at<__half>(c.ws, w.h);
   __half* qkv = w.qkv >= 0 ? at<__half>(c.ws, w.qkv) : nullptr;   // unfused attention path only
   __half* att = at<__half>(c.ws, w.att);
@@ -330,6 +300,7 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
 
   for (int i = 0; i + 1 < l.L; ++i) {
     const BlockW& b = l.blocks[i];
+    float* x_next = c.train ? c.train->x[i + 1] : x;
     if (!have_h) BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
     if (fused_qkv) {
       BSRL_TRY(fused_attn(vres_fused(attn_args(h, b.qkv_g, 0, kT, att), i), c.st));
@@ -342,7 +313,7 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
     if (fused) {
       const BlockW& nb = l.blocks[i + 1];
       BlockTailArgs a = tail_args(b, R);
-      a.x_out = x;
+      a.x_out = x_next;
       a.out16[0] = h; a.ld16[0] = d; a.g16[0] = c.G(nb.ln_attn); a.b16[0] = c.Be(nb.ln_attn);
       if (i + 2 == l.L) {
         a.out16[1] = hv; a.ld16[1] = d; a.g16[1] = c.G(l.critic_ln); a.b16[1] = c.Be(l.critic_ln);
@@ -350,12 +321,14 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
       }
       BSRL_TRY(fused_tail(a, c.st));
       have_h = true;
+      x = x_next;
       continue;
     }
-    LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x, d, 1, 0, R, d, d);
+    LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x_next, d, 1, 0, R, d, d);
     po.R = x; po.ldr = d;
     g_stage = kStOutProj;
     BSRL_TRY(linear(po, c.st));
+    x = x_next;
     BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, R, d, h, d, c.st));
     g_stage = kStFfnUp;
     BSRL_TRY(linear(linear_args(h, d, c.W(b.up), d, c.Bv(b.up), hid, F, 0, 1, R, F, d), c.st));
@@ -368,7 +341,7 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   // final block: keys/values over all 29 rows, everything else on the 5 lead rows
   float* x_lead = at<float>(c.ws, w.x_lead);
   __half* h_lead = at<__half>(c.ws, w.h_lead);
-  __half* lead16 = at<__half>(c.ws, w.lead16);
+  __half* lead16 = c.train ? c.train->lead16 : at<__half>(c.ws, w.lead16);
   {
     const BlockW& b = l.blocks[l.L - 1];
     if (!have_h) BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, c.st));
@@ -417,14 +390,14 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
   // SimBa trunk on the (B, 5d) readout; its output h lands in z[:, d:]; then the packed heads
   __half* z = at<__half>(c.ws, w.z);
   const int ldz = d + D;
-  float* raw = at<float>(c.ws, w.raw);
+  float* raw = c.train ? c.train->raw : at<float>(c.ws, w.raw);
   BSRL_TRY(run_trunk(c, lead16, raw));
 
   // adapool critic over the resolved stream entering the final block (still in x)
   __half* att_c = at<__half>(c.ws, w.att_c);
   __half* m1 = at<__half>(c.ws, w.m1);
   __half* m2 = at<__half>(c.ws, w.m2);
-  float* vraw = at<float>(c.ws, w.vraw);
+  float* vraw = c.train ? c.train->vraw : at<float>(c.ws, w.vraw);
   {
     const RowMap torso_rows{1, kT, 2};
     g_stage = kStCritic;
@@ -487,10 +460,11 @@ int make_ctx(Ctx& c, const bsrl_config* cfg, const void* arena, int64_t n_envs, 
   return BSRL_OK;
 }
 
-}  // namespace
+}  // namespace fwd
 }  // namespace bsrl
 
 using namespace bsrl;
+using namespace bsrl::fwd;
 
 extern "C" {
 

@@ -61,7 +61,10 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   Shared* sh = reinterpret_cast<Shared*>(staging + EPI_WARPS * STG_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_blocks = p.K / BK;
-  const int64_t n_work = (int64_t)m_tiles * n_tiles;
+  const int splits = p.k_splits > 1 ? p.k_splits : 1;
+  const int kps = (k_blocks + splits - 1) / splits;          // k-blocks per split
+  const int64_t n_tile_work = (int64_t)m_tiles * n_tiles;
+  const int64_t n_work = n_tile_work * splits;                // work item = (split, tile): split-major
   volatile int* abort = &sh->abort;
 
   if (threadIdx.x == 0) {
@@ -93,9 +96,11 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < n_work && ok; t += gridDim.x) {
+      for (int64_t w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const int64_t t = w % n_tile_work;
+        const int kb0 = (int)(w / n_tile_work) * kps, kb1 = min(k_blocks, kb0 + kps);
         const int m0 = (int)(t / n_tiles) * BM, n0 = (int)(t % n_tiles) * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(smem_u32(&sh->empty[s]), ph ^ 1, abort)) { give_up(sh, status, 1); ok = false; break; }
@@ -122,7 +127,9 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < n_work && ok; t += gridDim.x, ++tile_i) {
+      for (int64_t w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++tile_i) {
+        const int64_t t = w % n_tile_work;
+        const int kb0 = (int)(w / n_tile_work) * kps, kb1 = min(k_blocks, kb0 + kps);
         const int n0 = (int)(t % n_tiles) * BN;
         int n_cols = p.N - n0;
         if (n_cols > BN) n_cols = BN;
@@ -132,7 +139,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if (!mbar_wait(smem_u32(&sh->tmem_empty[buf]), acc_ph ^ 1, abort)) { give_up(sh, status, 3); ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(smem_u32(&sh->full[s]), ph, abort)) { give_up(sh, status, 4); ok = false; break; }
@@ -142,7 +149,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           const uint64_t w_desc = smem_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)   // +32 bytes (2 x 16-byte units) per K step of 16
-            mma_f16_ss(d_tmem, a_desc + 2 * k, w_desc + 2 * k, idesc, (kb | k) != 0);
+            mma_f16_ss(d_tmem, a_desc + 2 * k, w_desc + 2 * k, idesc, (kb != kb0 || k) ? 1u : 0u);
           tc_commit(smem_u32(&sh->empty[s]));
         }
         if (ok) tc_commit(smem_u32(&sh->tmem_full[buf]));
@@ -168,7 +175,9 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const int sub = lane >> 3, piece = lane & 7;   // transposed phase: row sub + 4 i, 16-byte piece
     uint32_t tile_i = 0;
     bool ok = true;
-    for (int64_t t = blockIdx.x; t < n_work && ok; t += gridDim.x, ++tile_i) {
+    for (int64_t w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++tile_i) {
+      const int64_t t = w % n_tile_work;
+      const bool first_split = w < n_tile_work;              // the piece that carries the bias
       const int64_t m0 = (t / n_tiles) * BM;
       const int n0 = (int)(t % n_tiles) * BN;
       const int buf = tile_i & 1;
@@ -212,7 +221,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (p.bias) {
+          if (p.bias && first_split) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               // columns past N read the zero padding of the accumulator; clamp the bias index
@@ -270,7 +279,10 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               if (HAS_R) {
                 f.x += rv[i].x; f.y += rv[i].y; f.z += rv[i].z; f.w += rv[i].w;
               }
-              if (p.out_f32)
+              if (splits > 1) {
+                float* dst = static_cast<float*>(p.C) + crow[i] + pcol;
+                atomicAdd(dst, f.x); atomicAdd(dst + 1, f.y); atomicAdd(dst + 2, f.z); atomicAdd(dst + 3, f.w);
+              } else if (p.out_f32)
                 *reinterpret_cast<float4*>(static_cast<float*>(p.C) + crow[i] + pcol) = f;
               else
                 *reinterpret_cast<uint2*>(static_cast<__half*>(p.C) + crow[i] + pcol) =
@@ -373,10 +385,20 @@ bool linear_tc5_ok(const LinearArgs& p) {
   if (p.ldc % (p.out_f32 ? 4 : 8)) return false;
   if (p.bias && !aligned16(p.bias)) return false;
   if (p.R && (!aligned16(p.R) || (p.ldr % 4))) return false;
+  if (p.k_splits > 1 && (!p.out_f32 || p.relu || p.R)) return false;   // split-K adds raw fp32 partial products
   return true;
 }
 
-int linear_tc5(const LinearArgs& p, cudaStream_t stream) {
+int linear_tc5(const LinearArgs& p_in, cudaStream_t stream) {
+  LinearArgs p = p_in;
+  if (p.k_splits > 1) {   // no piece may be empty: an empty piece would add an unwritten accumulator
+    const int k_blocks = p.K / BK;
+    if (p.k_splits > k_blocks) p.k_splits = k_blocks;
+    if (p.k_splits > 1) {
+      const int kps = (k_blocks + p.k_splits - 1) / p.k_splits;
+      p.k_splits = (k_blocks + kps - 1) / kps;
+    }
+  }
   if (!linear_tc5_ok(p)) {
     set_error("linear: shape m=%lld n=%d k=%d does not fit the tcgen05 engine", (long long)p.M, p.N, p.K);
     return BSRL_ERR_UNSUPPORTED;
@@ -387,7 +409,7 @@ int linear_tc5(const LinearArgs& p, cudaStream_t stream) {
   if (!make_tmap_f16(&tm_a, p.A, p.M, p.K, p.lda, BM)) return BSRL_ERR_CUDA;
   if (!make_tmap_f16(&tm_w, p.W, p.N, p.K, p.ldw, BN)) return BSRL_ERR_CUDA;
   // dense output rows without a residual leave as TMA stores of the epilogue's 32 x 128-byte staging blocks
-  const bool tma_c = !p.R && p.cmap.group == 0x7fffffff && p.cmap.stride == 0 && p.cmap.first == 0 &&
+  const bool tma_c = !p.R && p.k_splits <= 1 && p.cmap.group == 0x7fffffff && p.cmap.stride == 0 && p.cmap.first == 0 &&
                      p.M <= 0x7fffff00;
   CUtensorMap tm_c = tm_a;
   if (tma_c && !make_tmap_rows(&tm_c, p.C, p.out_f32 ? 4 : 2, p.M, p.N, p.ldc, 32, 128)) return BSRL_ERR_CUDA;
@@ -404,7 +426,7 @@ int linear_tc5(const LinearArgs& p, cudaStream_t stream) {
     set_error("linear: too many tiles");
     return BSRL_ERR_SHAPE;
   }
-  int64_t grid = m_tiles * n_tiles;
+  int64_t grid = m_tiles * n_tiles * (p.k_splits > 1 ? p.k_splits : 1);
   if (grid > sm_count()) grid = sm_count();
   if (p.R)
     linear_tc5_kernel<true><<<(unsigned)grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_w, tm_c, 0, p, (int)m_tiles, n_tiles, status);

@@ -22,6 +22,10 @@ struct LinearArgs {
   int relu;
   int64_t M;
   int N, K;
+  // Split-K (weight gradients: few output tiles, a very long K): the K range is cut into k_splits
+  // pieces that run as separate work items and ADD their partial products into the fp32 output with
+  // atomics (the caller zeroes C first; bias goes in with the first piece).  0 or 1 = off.
+  int k_splits = 0;
 };
 LinearArgs linear_args(const __half* A, int lda, const __half* W, int ldw, const float* bias,
                        void* C, int ldc, int out_f32, int relu, int64_t M, int N, int K);
