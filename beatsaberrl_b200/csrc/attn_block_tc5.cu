@@ -4,11 +4,14 @@
 //   qkv = h [Wq;Wk;Wv]^T + b          (h = LayerNorm rows, fp16)
 //   att = softmax(q k^T / sqrt(dh) + key_bias) v, heads concatenated
 //
-// One tile = 4 environments = 116 token rows (padded to the 128-row MMA).  The projection runs per
-// HEAD GROUP (two heads: 64 q + 64 k + 64 v = 192 output columns, the weight rows regrouped at
-// pack time), so that a group's q, k, v fit in one 50 KB shared-memory tile; the attention of the
-// group's 8 (env, head) pairs then runs on 8 warps from that tile (m16n8k16 MMAs, fp32 softmax in
-// registers) while the tensor core already projects the next group into the other TMEM buffer.
+// One tile = 4 environments, each padded from 29 to 32 token rows (a 3-D TMA load zero-fills rows
+// 29..31), so that env e of the tile is exactly rows [32 e, 32 e + 32) = TMEM lane quadrant e of the
+// 128-row MMA.  The projection runs per HEAD GROUP (two heads: 64 q + 64 k + 64 v = 192 output
+// columns, the weight rows regrouped at pack time), so that a group's q, k, v fit in one 50 KB
+// shared-memory tile.  The two warps that own a lane quadrant drain THEIR env's rows (half of the
+// columns each) and then attend that env's two heads (m16n8k16 MMAs, fp32 softmax in registers): an env
+// only ever waits for its own pair of warps (a 64-thread named barrier), never for the whole CTA, while
+// the tensor core already projects the next group into the other TMEM buffer.
 //
 //   warp 0      TMA producer: the h tile (d/64 swizzled chunks, loaded once per tile) and the
 //               regrouped weight tiles (192 x 64 or 144 x 64 per stage, 3- or 4-stage ring)
@@ -17,8 +20,9 @@
 //
 // HBM traffic per token: read h (2d B), write att (2d B).  Replaces fp16_packed_linear + attn29 /
 // packed_sdpa (python/policy.py:586-600, :645-692; python/beat_arena_env/csrc/small_attn.cu).
-// With all 29 query rows, the group's output (116 rows x 128 bytes for two heads of 32, x 96 bytes for one
-// head of 48) is staged in shared memory and leaves as one TMA store.  All waits are bounded (tc5.cuh).
+// With all 29 query rows, an env's output for the group (29 rows x 128 bytes for two heads of 32, x 96 bytes
+// for one head of 48) is staged in shared memory and leaves as one TMA store per env.  All waits are
+// bounded (tc5.cuh).
 #include "kernels.cuh"
 #include "tc5.cuh"
 
@@ -27,8 +31,8 @@ namespace {
 using namespace tc5;
 
 constexpr int EPT = 4;                  // envs per tile
-constexpr int ROWS = EPT * kT;          // 116 live rows
-constexpr int BM = 128;
+constexpr int EROWS = 32;               // tile rows per env: 29 tokens + 3 zero rows
+constexpr int BM = EPT * EROWS;
 constexpr int MAX_STAGES = 4;           // weight ring: 3 stages of 24 KB (head_dim 32) or 4 of 18 KB (head_dim 48), as measured
 constexpr int CHUNK_BYTES = BM * 128;   // 16 KB: 128 rows x 64 k-columns
 constexpr int WORKERS = 8;
@@ -52,7 +56,7 @@ struct Shared {
   uint64_t w_full[MAX_STAGES], w_empty[MAX_STAGES], a_full[4], a_free[4], acc_full[2], acc_empty[2], attn_done[2], mma_done;
   uint32_t tmem_base;
   int abort;
-  int quit;   // abort flag as sampled by one thread before a CTA-level barrier, so all workers leave together
+  int quit[EPT];   // abort flag as sampled by one thread of an env's warp pair before their barrier, so both leave together
 };
 
 struct Params {
@@ -239,7 +243,7 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
     }
     mbar_init(smem_u32(&sh->mma_done), 1);
     sh->abort = 0;
-    sh->quit = 0;
+    for (int e = 0; e < EPT; ++e) sh->quit[e] = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_h);
     tma_prefetch_desc(&tm_w);
@@ -275,7 +279,7 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
           if (!mbar_wait(smem_u32(&sh->a_free[kb]), (tile_i & 1) ^ 1, abort)) { give_up(sh, p.status, 2); ok = false; break; }
           const uint32_t bar = smem_u32(&sh->a_full[kb]);
           mbar_expect_tx(bar, CHUNK_BYTES);
-          tma_load_2d(sA + kb * CHUNK_BYTES, &tm_h, 64 * kb, t * ROWS, bar);
+          tma_load_3d(sA + kb * CHUNK_BYTES, &tm_h, 64 * kb, 0, t * EPT, bar);
           ok = w_stage(0, kb);
         }
         for (int g = 1; g < n_groups && ok; ++g)
@@ -306,7 +310,8 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
           if (!mbar_wait(smem_u32(&sh->acc_empty[buf]), ((gi >> 1) & 1) ^ 1, abort)) { give_up(sh, p.status, 5); ok = false; break; }
           // The workers' attention runs on warp-level MMAs, which queue behind tcgen05 MMAs on the same
           // tensor cores: this group's projection is held back until the attention of two groups ago is
-          // over, so that it runs while the workers drain the previous group instead.
+          // over, so that it runs while the workers drain the previous group instead (without the wait the
+          // kernel measured 3 % slower).
           if (gi >= 2 && !mbar_wait(smem_u32(&sh->attn_done[buf]), ((gi - 2) >> 1) & 1, abort)) { give_up(sh, p.status, 10); ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * 256;
@@ -332,14 +337,15 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
   } else {
     // ------------------------------------------------------------ workers: drain, then attend
     const int wi = warp - 2;
-    const int q = warp & 3, half = wi >> 2;           // TMEM lane quadrant, column half
-    const int trow = q * 32 + lane;
+    const int q = warp & 3, half = wi >> 2;           // TMEM lane quadrant = env of the tile, column half
+    const int trow = q * EROWS + lane;                // tile row: token `lane` of env q (29..31: zero rows)
     // drain: the group's NG columns in 16-column units, split between the two halves (6 + 6 or 5 + 4)
     constexpr int UNITS = NG / 16, U0 = (UNITS + 1) / 2;
     const int u_first = half ? U0 : 0, u_count = half ? UNITS - U0 : U0;
-    // attention: G = 2: one (env, head) pair per warp, both 16-row query tiles; G = 1: one env per two
-    // warps, one query tile each
-    const int env_l = wi >> 1, hh = G == 2 ? (wi & 1) : 0, mt_own = G == 2 ? 0 : (wi & 1);
+    // attention of the env this warp drained: G = 2: one head per warp of the pair, both 16-row query tiles;
+    // G = 1: one query tile each
+    const int env_l = q, hh = G == 2 ? half : 0, mt_own = G == 2 ? 0 : half;
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); };
     uint32_t gi = 0;
     bool ok = true;
     const float vres_a = (VRES && p.vres) ? p.vres[0] : 1.f, vres_b = (VRES && p.vres) ? p.vres[1] : 0.f;
@@ -372,8 +378,8 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
             // value residual (python/policy.py:604-615): the group's v columns are written out as
             // this block's own values and / or mixed with block 0's before the attention reads them
             const int vcol = (u_first + u) * 16 - 2 * GD;           // column inside the group's v section
-            const bool vres_rows = VRES && vcol >= 0 && trow < ROWS && (int64_t)t * EPT + trow / kT < p.n_envs;
-            const int64_t goff = ((int64_t)t * ROWS + trow) * d + g * GD + vcol;
+            const bool vres_rows = VRES && vcol >= 0 && lane < kT && env < p.n_envs;
+            const int64_t goff = (env * kT + lane) * d + g * GD + vcol;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
               const float4 b0 = b4[2 * j], b1 = b4[2 * j + 1];
@@ -416,34 +422,36 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[buf]));     // the TMEM buffer may be refilled
-        if (wi == 0 && lane == 0) sh->quit = *abort;
-        if (p.out_tma && wi == 0 && lane == 0) bulk_wait_read<0>();     // the previous group's output store has read sO
-        asm volatile("bar.sync 1, %0;" ::"n"(WORKERS * 32) : "memory");  // q|k|v tile complete
-        if (*reinterpret_cast<volatile int*>(&sh->quit)) {
+        if (half == 0 && lane == 0) {
+          sh->quit[q] = *abort;
+          if (p.out_tma) bulk_wait_read<0>();           // this env's previous output store has read its sO rows
+        }
+        pair_sync();                                    // the env's q|k|v rows are complete
+        if (*reinterpret_cast<volatile int*>(&sh->quit[q])) {
           ok = false;
           break;
         }
         if (env < p.n_envs) {
-          const uint32_t rows = sQ + (env_l * kT) * LDQ;
+          const uint32_t rows = sQ + (env_l * EROWS) * LDQ;
           const uint32_t sq_pair = rows + (p.q_first + mt_own * 16) * LDQ + (hh * DH) * 2,
                          sk_pair = rows + (GD + hh * DH) * 2, sv_pair = rows + (2 * GD + hh * DH) * 2;
           __half* out_pair = p.out + (env * p.n_q + mt_own * 16) * (int64_t)p.ldo + (g * G + hh) * DH;
           const int n_q = p.n_q - mt_own * 16;      // query rows left from this warp's first one
           uint8_t* so_tile = p.out_tma ? sO_g : nullptr;
-          if (G == 2 && n_q > 16) attend_pair<2, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * kT + mt_own * 16, hh * (DH / 8));
-          else if (n_q > 0) attend_pair<1, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * kT + mt_own * 16, hh * (DH / 8));
+          if (G == 2 && n_q > 16) attend_pair<2, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * EROWS + mt_own * 16, hh * (DH / 8));
+          else if (n_q > 0) attend_pair<1, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * EROWS + mt_own * 16, hh * (DH / 8));
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh->attn_done[buf]));
         if (p.out_tma) fence_proxy_async_smem();                         // this thread's sO writes -> the TMA engine
-        asm volatile("bar.sync 1, %0;" ::"n"(WORKERS * 32) : "memory");  // tile may be overwritten
-        if (p.out_tma && wi == 0 && lane == 0) {                         // rows past the last env are clipped
-          tma_store_2d(&tm_o, g * GD, t * ROWS, sO);
+        pair_sync();                                                     // the env's rows may be overwritten
+        if (p.out_tma && half == 0 && lane == 0 && env < p.n_envs) {     // token rows 29..31 of the box are clipped
+          tma_store_3d(&tm_o, g * GD, 0, (int)env, sO + (uint32_t)(q * EROWS) * (uint32_t)(GD * 2));
           bulk_commit();
         }
       }
     }
-    if (p.out_tma && wi == 0 && lane == 0) bulk_wait_all();   // the output stores are complete before the CTA exits
+    if (p.out_tma && half == 0 && lane == 0) bulk_wait_all();   // the output stores are complete before the CTA exits
   }
 
   // ------------------------------------------------------------------ teardown
@@ -460,7 +468,7 @@ bool attn_block_ok(const AttnBlockArgs& a) {
   if (a.d % 64 != 0 || a.d < 64 || a.d > 256 || a.n_heads < 1 || a.d % a.n_heads != 0) return false;
   const int dh = a.d / a.n_heads;
   if (!((dh == 32 && a.n_heads % 2 == 0) || dh == 48)) return false;
-  if (a.n_envs < 1 || a.n_envs > 0x7fffffffLL / (ROWS * 2)) return false;
+  if (a.n_envs < 1 || a.n_envs > 0x7fffffffLL / (BM * 2)) return false;
   if (a.q_first < 0 || a.n_q < 1 || a.q_first + a.n_q > kT) return false;
   if (!aligned16(a.h) || !aligned16(a.wg) || !aligned16(a.bg) || !aligned16(a.out) || (a.ldh % 8) || (a.ldo % 8)) return false;
   return true;
@@ -479,12 +487,12 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
   if (!status) return BSRL_ERR_CUDA;
   const int dh = a.d / a.n_heads;
   CUtensorMap tm_h, tm_w;
-  if (!make_tmap_f16(&tm_h, a.h, a.n_envs * kT, a.d, a.ldh, BM)) return BSRL_ERR_CUDA;
+  if (!make_tmap_env3d(&tm_h, a.h, a.n_envs, kT, a.d, a.ldh, 64, EROWS, EPT)) return BSRL_ERR_CUDA;
   if (!make_tmap_f16(&tm_w, a.wg, 3 * a.d, a.d, a.d, dh == 32 ? Shape<32, 2>::NG : Shape<48, 1>::NG)) return BSRL_ERR_CUDA;
-  // all 29 query rows: a group's output is 116 contiguous rows x 128 (two heads of 32) or 96 bytes (one of 48) = one TMA store
-  const bool out_tma = a.q_first == 0 && a.n_q == kT && a.n_envs * kT <= 0x7fffff00;
+  // all 29 query rows: an env's output for a group is 29 contiguous rows x 128 (two heads of 32) or 96 bytes (one of 48) = one TMA store
+  const bool out_tma = a.q_first == 0 && a.n_q == kT;
   CUtensorMap tm_o = tm_h;
-  if (out_tma && !make_tmap_rows(&tm_o, a.out, 2, a.n_envs * kT, a.d, a.ldo, ROWS, dh == 32 ? 128 : 96)) return BSRL_ERR_CUDA;
+  if (out_tma && !make_tmap_env3d(&tm_o, a.out, a.n_envs, kT, a.d, a.ldo, dh == 32 ? 64 : 48, EROWS, 1)) return BSRL_ERR_CUDA;
   static DeviceOnce once;
   int rc = once.run("attn_block_kernel set-up", [] {
     const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;

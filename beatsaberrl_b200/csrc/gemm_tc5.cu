@@ -377,6 +377,30 @@ bool make_tmap_rows(CUtensorMap* map, const void* base, int elem_bytes, int64_t 
   return true;
 }
 
+bool make_tmap_env3d(CUtensorMap* map, const void* base, int64_t n_envs, int tokens_per_env, int64_t cols,
+                     int64_t ld_elems, int box_cols, int box_tokens, int box_envs) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return false;
+  }
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)tokens_per_env, (cuuint64_t)n_envs};
+  cuuint64_t strides[2] = {(cuuint64_t)ld_elems * 2, (cuuint64_t)ld_elems * 2 * (cuuint64_t)tokens_per_env};
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_tokens, (cuuint32_t)box_envs};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const int row_bytes = box_cols * 2;
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed (%d) for a (%lld envs x %d tokens x %lld) fp16 view, ld %lld", (int)r,
+              (long long)n_envs, tokens_per_env, (long long)cols, (long long)ld_elems);
+    return false;
+  }
+  return true;
+}
+
 bool linear_tc5_ok(const LinearArgs& p) {
   if (!p.A || !p.W || !p.C || p.M < 1) return false;
   if (p.K % BK != 0 || p.N % 16 != 0 || p.N < 16) return false;

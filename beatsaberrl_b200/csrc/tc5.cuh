@@ -77,6 +77,20 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
                "r"(src), "r"(x), "r"(y)
                : "memory");
 }
+// 3-D forms (x = column, y = token of the env, z = env): rows past a dimension's extent are zero-filled
+// by the load and clipped by the store
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int x, int y, int z, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // waits until at most N of this thread's bulk groups still have to READ their shared-memory source
 template <int N>
@@ -210,6 +224,14 @@ bool make_tmap_rows64(CUtensorMap* map, const void* base, int elem_bytes, int64_
 // The same with rows of row_bytes = 64 or 128 bytes (64- / 128-byte swizzle), or any other multiple of 16 (dense rows, no swizzle).
 bool make_tmap_rows(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows, int64_t cols,
                     int64_t ld_elems, int box_rows, int row_bytes);
+
+// Encodes a 3-D fp16 view (cols, tokens_per_env, n_envs) of a token-row matrix whose env e owns rows
+// [e * tokens_per_env, (e + 1) * tokens_per_env): box = (box_cols, box_tokens, box_envs).  box_tokens may
+// exceed tokens_per_env (29 -> 32): a load then fills the extra rows with zeros and a store skips them, so
+// that every env starts on a 32-row boundary of the shared-memory tile.  row_bytes = box_cols * 2 selects the
+// swizzle as in make_tmap_rows (128: 128-byte swizzle, 64: 64-byte, otherwise none).
+bool make_tmap_env3d(CUtensorMap* map, const void* base, int64_t n_envs, int tokens_per_env, int64_t cols,
+                     int64_t ld_elems, int box_cols, int box_tokens, int box_envs);
 
 // Address of the current device's status word (nullptr with the error message set on failure).
 int* device_status_ptr();
