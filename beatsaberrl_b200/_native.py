@@ -77,6 +77,19 @@ _sig = {
                                       C.c_int32, _P, _P, _P, C.c_int64, _P]),
     "bsrl_workspace_bytes": (C.c_int64, [_CFG, C.c_int64]),
     "bsrl_forward": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, _P, _P, _P, C.c_int64, _P]),
+    "bsrl_train_save_bytes": (C.c_int64, [_CFG, C.c_int64]),
+    "bsrl_backward_workspace_bytes": (C.c_int64, [_CFG, C.c_int64]),
+    "bsrl_grad_floats": (C.c_int64, [_CFG, C.POINTER(C.c_int64), C.c_int32]),
+    "bsrl_forward_train": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, C.c_int32, _P, _P, _P, _P, _P, _P,
+                                     _P, C.c_int64, _P, C.c_int64, _P]),
+    "bsrl_backward": (C.c_int, [_CFG, _P, C.c_int64, _P, C.c_int32, _P, C.c_int64, _P, _P, _P, _P, _P, C.c_float,
+                                _P, C.c_int64, _P, C.c_int64, _P]),
+    "bsrl_layernorm_bwd": (C.c_int, [_P, _P, C.c_float, _P, _P, C.c_int64, C.c_int32, _P, _P, _P, _P]),
+    "bsrl_attention_bwd": (C.c_int, [_P, _P, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P]),
+    "bsrl_head_tail_bwd": (C.c_int, [_CFG, _P, _P, C.c_int64, _P, C.c_int32, _P, _P, _P, _P, _P, C.c_float, _P, C.c_int32,
+                                     _P, C.c_int32, _P]),
+    "bsrl_linear_bwd_scratch_bytes": (C.c_int64, [C.c_int64, C.c_int32, C.c_int32]),
+    "bsrl_linear_bwd": (C.c_int, [_P, _P, _P, C.c_int64, C.c_int32, C.c_int32, _P, _P, _P, C.c_int32, _P, C.c_int64, _P]),
     "bsrl_fixed_scratch_bytes": (C.c_int64, []),
     "bsrl_forward_fixed": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, _P, _P]),
     "bsrl_forward_act": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, C.c_int32, _P, _P, _P, _P, _P, _P,

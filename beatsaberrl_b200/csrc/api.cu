@@ -70,6 +70,7 @@ int timed(cudaStream_t st, double flops, double bytes, Fn&& fn) {
 // the first forward; each forward reads it once (Ctx::engine), so a change never splits a forward.
 std::atomic<int> g_engine{0};
 thread_local int g_call_engine = 0;   // the engine of the forward running on this thread
+void use_process_engine() { g_call_engine = g_engine.load(std::memory_order_relaxed); }
 int linear(const LinearArgs& p, cudaStream_t st) {
   return timed(st, 2.0 * p.M * p.N * p.K, linear_bytes(p), [&] {
     if (g_call_engine == 0 && p.M >= 128 && linear_tc5_ok(p)) return linear_tc5(p, st);
@@ -446,7 +447,7 @@ int make_ctx(Ctx& c, const bsrl_config* cfg, const void* arena, int64_t n_envs, 
   }
   c.cfg = cfg;
   c.l = make_layout(*cfg);
-  g_call_engine = g_engine.load(std::memory_order_relaxed);
+  use_process_engine();
   c.paths = plan_paths(c.l, g_call_engine);
   c.w = make_workspace(c.l, n_envs, c.paths);
   if (ws_bytes < c.w.bytes) {

@@ -61,6 +61,9 @@ int run_embed(const Ctx& c, const void* obs, int obs_dtype, float* x, float* key
 int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs& tail_in);
 void head_shape(const bsrl_config& cfg, const Layout& l, HeadTailArgs& t);
 
+// makes the calling thread's launch wrappers follow the process-wide engine choice (bsrl_set_engine)
+void use_process_engine();
+
 // stage-labelled launch wrappers (timed when the calling thread has the profiler on)
 int linear(const LinearArgs& p, cudaStream_t st);
 int layernorm(const float* x, int64_t ldx, RowMap xmap, const float* g, const float* b, float eps, int64_t rows, int d,

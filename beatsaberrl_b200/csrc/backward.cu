@@ -209,12 +209,13 @@ __device__ __forceinline__ int load_action(const void* a, int dtype, int64_t idx
 __global__ void __launch_bounds__(256) head_tail_bwd_kernel(HeadTailArgs p, const float* __restrict__ g_logprob,
                                                             const float* __restrict__ g_entropy, const float* __restrict__ g_value,
                                                             const float* __restrict__ g_vlogits, const float* __restrict__ g_logits,
-                                                            float scale, __half* __restrict__ g_raw, __half* __restrict__ g_vraw) {
+                                                            float scale, __half* __restrict__ g_raw, int ldg_raw,
+                                                            __half* __restrict__ g_vraw, int ldg_v) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   for (int64_t env = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); env < p.n_envs; env += warps) {
-    for (int c = lane + p.first[kActHeads - 1] + p.gears[kActHeads - 1]; c < p.ld_raw; c += 32)
-      g_raw[env * p.ld_raw + c] = __float2half_rn(0.f);           // padding columns of the packed head matrix
+    for (int c = lane + p.first[kActHeads - 1] + p.gears[kActHeads - 1]; c < ldg_raw; c += 32)
+      g_raw[env * (int64_t)ldg_raw + c] = __float2half_rn(0.f);   // padding columns of the packed head matrix
     if (lane < kActHeads) {
       const int k = p.gears[lane];
       const float* src = p.raw + env * p.ld_raw + p.first[lane];
@@ -244,7 +245,7 @@ __global__ void __launch_bounds__(256) head_tail_bwd_kernel(HeadTailArgs p, cons
           const float ls = v[i] - lse, pi = expf(ls);
           float g = glp * ((i == a ? 1.f : 0.f) - pi) - gen * pi * (ls + ent);
           if (g_logits) g += g_logits[(env * kActHeads + lane) * p.k_max + i];
-          g_raw[env * p.ld_raw + p.first[lane] + i] = __float2half_rn(g * scale);
+          g_raw[env * (int64_t)ldg_raw + p.first[lane] + i] = __float2half_rn(g * scale);
         }
     }
     const float* vr = p.vraw + env * p.ld_v;
@@ -262,14 +263,14 @@ __global__ void __launch_bounds__(256) head_tail_bwd_kernel(HeadTailArgs p, cons
     se = warp_sum(se);
     sc = warp_sum(sc);
     const float val = sc / se, gv = g_value ? g_value[env] : 0.f;
-    for (int i = lane; i < p.ld_v; i += 32) {
+    for (int i = lane; i < ldg_v; i += 32) {
       float g = 0.f;
       if (i < p.bins) {
         const float c = i < p.bins / 2 ? -p.vmax + step * i : p.vmax - step * (p.bins - 1 - i);
         g = gv * (expf(vr[i] - mx) / se) * (c - val);
         if (g_vlogits) g += g_vlogits[env * p.bins + i];
       }
-      g_vraw[env * p.ld_v + i] = __float2half_rn(g * scale);
+      g_vraw[env * (int64_t)ldg_v + i] = __float2half_rn(g * scale);
     }
   }
 }
@@ -307,7 +308,7 @@ int layernorm_bwd(const float* x, int64_t ldx, RowMap xmap, const float* gamma, 
 }
 
 int colsum16(const __half* in, int64_t ld, int64_t rows, int n, float* out, cudaStream_t stream) {
-  if (rows == 0 || n == 0) return BSRL_OK;
+  if (rows == 0 || n == 0 || !out) return BSRL_OK;
   int64_t chunks = (rows + 511) / 512;
   if (chunks > 1024) chunks = 1024;
   colsum_kernel<<<dim3((n + 255) / 256, (unsigned)chunks), 256, 0, stream>>>(in, ld, rows, n, out);
@@ -352,15 +353,15 @@ int transpose16(const __half* in, int64_t ldi, RowMap imap, int64_t rows, int co
 }
 
 int head_tail_bwd(const HeadTailArgs& a, const float* g_logprob, const float* g_entropy, const float* g_value,
-                  const float* g_vlogits, const float* g_logits, float scale, __half* g_raw, __half* g_vraw,
-                  cudaStream_t stream) {
+                  const float* g_vlogits, const float* g_logits, float scale, __half* g_raw, int ldg_raw, __half* g_vraw,
+                  int ldg_v, cudaStream_t stream) {
   if (!a.raw || !a.vraw || !g_raw || !g_vraw) {
     set_error("head_tail_bwd: NULL operand");
     return BSRL_ERR_NULL;
   }
   if (a.n_envs == 0) return BSRL_OK;
   head_tail_bwd_kernel<<<(unsigned)grid_for(a.n_envs, 8), 256, 0, stream>>>(a, g_logprob, g_entropy, g_value, g_vlogits,
-                                                                            g_logits, scale, g_raw, g_vraw);
+                                                                            g_logits, scale, g_raw, ldg_raw, g_vraw, ldg_v);
   BSRL_LAUNCH_OK("head_tail_bwd_kernel");
   return BSRL_OK;
 }

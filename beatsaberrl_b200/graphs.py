@@ -86,7 +86,8 @@ class GraphedForward(Graphed):
         policy.flatten_fp16()
 
     def _compute(self):
-        return self.policy.forward_stacked(self.obs)
+        with torch.no_grad():
+            return self.policy.forward_stacked(self.obs)
 
     def __call__(self, obs):
         self._copy_static(self.obs, obs, non_blocking=True)

@@ -81,6 +81,71 @@ class _Block(nn.Module):
 _ACT_DTYPES = {torch.uint8: nat.U8, torch.int32: nat.I32, torch.int64: nat.I64}
 
 
+class _RecomputeFn(torch.autograd.Function):
+    """The policy forward as ONE autograd node: ``bsrl_forward_train`` going forward (the rollout's own
+    kernels, so log-probs match the rollout bit for bit, plus a save buffer), ``bsrl_backward`` coming
+    back.  Stands in for the chain of autograd.Functions of the reference's fp16 stream
+    (python/fp16_linear.py:461-767, :931-1064, :1197-1251; python/fused_ln.py:58-107)."""
+
+    @staticmethod
+    def forward(ctx, policy, obs, action, *params):
+        B, dev = obs.shape[0], obs.device
+        cfg = policy._cfg
+        f32 = dict(dtype=torch.float32, device=dev)
+        logits = torch.empty(B, N_ACTION_HEADS, policy.k_max, **f32)
+        logprob, entropy, value = torch.empty(B, **f32), torch.empty(B, **f32), torch.empty(B, **f32)
+        ent_h = torch.empty(B, N_ACTION_HEADS, **f32)
+        vlogits = torch.empty(B, policy.value_bins, **f32)
+        n_save = nat.lib.bsrl_train_save_bytes(C.byref(cfg), B)
+        if n_save < 0:
+            raise nat.BsrlError(int(n_save), nat.last_error())
+        save = torch.empty(max(n_save, 256), dtype=torch.uint8, device=dev)
+        ws = policy._workspace(B, dev)
+        with torch.cuda.device(dev):
+            nat.check(nat.lib.bsrl_forward_train(
+                C.byref(cfg), policy._arena.data_ptr(), obs.data_ptr(), policy._obs_dtype(obs), B,
+                action.data_ptr(), _ACT_DTYPES[action.dtype], logits.data_ptr(), logprob.data_ptr(),
+                entropy.data_ptr(), ent_h.data_ptr(), value.data_ptr(), vlogits.data_ptr(), save.data_ptr(),
+                save.numel(), ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream))
+        ctx.policy, ctx.save, ctx.action, ctx.B = policy, save, action, B
+        ctx.needs = [p.requires_grad for p in params]
+        ctx.mark_non_differentiable(ent_h)
+        return logits, logprob, entropy, value, vlogits, ent_h
+
+    @staticmethod
+    def backward(ctx, g_logits, g_logprob, g_entropy, g_value, g_vlogits, _g_ent_h):
+        policy, B = ctx.policy, ctx.B
+        cfg, dev = policy._cfg, ctx.save.device
+        n = len(policy._param_table)
+        offs = (C.c_int64 * n)()
+        total = nat.lib.bsrl_grad_floats(C.byref(cfg), offs, n)
+        if total < 0:
+            raise nat.BsrlError(int(total), nat.last_error())
+        flat = torch.empty(total, dtype=torch.float32, device=dev)
+        n_ws = nat.lib.bsrl_backward_workspace_bytes(C.byref(cfg), B)
+        ws = torch.empty(max(n_ws, 256), dtype=torch.uint8, device=dev)
+        scale = float(policy.grad_scale)
+
+        def up(g):
+            return None if g is None else g.contiguous().float()
+        ups = [up(g) for g in (g_logprob, g_entropy, g_value, g_vlogits, g_logits)]
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        with torch.cuda.device(dev):
+            nat.check(nat.lib.bsrl_backward(
+                C.byref(cfg), policy._arena.data_ptr(), B, ctx.action.data_ptr(), _ACT_DTYPES[ctx.action.dtype],
+                ctx.save.data_ptr(), ctx.save.numel(), ptr(ups[0]), ptr(ups[1]), ptr(ups[2]), ptr(ups[3]), ptr(ups[4]),
+                scale, flat.data_ptr(), total, ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream))
+        flat.mul_(1.0 / scale)
+        grads = []
+        for i, (_, rows, cols) in enumerate(policy._param_table):
+            if not ctx.needs[i]:
+                grads.append(None)
+                continue
+            grads.append(flat[offs[i]: offs[i] + rows * cols])
+        ctx.save = None
+        return (None, None, None, *grads)
+
+
 class NotePolicy(nn.Module):
     def __init__(self, embed: int = 128, trunk_dim: int = 256, encoder: str = "transformer",
                  n_blocks: int = 3, n_heads: int = 4, n_gears: int = 3, ffn_mult: int = 4,
@@ -181,6 +246,9 @@ class NotePolicy(nn.Module):
         self._ent_h = None
         self._value_logits = None
         self.keep_value_logits = False   # set True to have forwards fill _value_logits
+        # loss scale of the backward's fp16 activation gradients (gradients come back unscaled); raise it if
+        # tiny upstream gradients underflow, lower it if large ones overflow
+        self.grad_scale = 4096.0
         self._cfg = nat.make_config(embed, n_heads, n_blocks, ffn_mult, trunk_dim, H, self.value_bins,
                                     note_geo, head_gears, float(z_asinh), float(value_vmax),
                                     float(self.blocks[0].ln_attn.eps), emb_ln=emb_ln, final_ln=final_ln,
@@ -300,9 +368,32 @@ class NotePolicy(nn.Module):
         return obs.contiguous()
 
     # ------------------------------------------------------------------ forward
-    @torch.no_grad()
+    def _wants_grad(self) -> bool:
+        return torch.is_grad_enabled() and any(p.requires_grad for p in self.parameters())
+
+    def _recompute(self, obs, action):
+        """Grad-mode forward: one autograd node over all parameters (see ``_RecomputeFn``)."""
+        obs = self._check_obs(obs)
+        self._pack()
+        named = dict(self.named_parameters())
+        params = [named[n] for n, _, _ in self._param_table]
+        shapes = [p.shape for p in params]
+        flat_params = [p.reshape(-1) if p.dim() != 1 else p for p in params]   # the node hands back flat gradients
+        del shapes
+        return _RecomputeFn.apply(self, obs, action, *flat_params)
+
     def forward_stacked(self, obs: torch.Tensor):
-        """obs (B, 630) -> stacked logits (B, 29, k_max) fp32 + the critic's value (B,) fp32."""
+        """obs (B, 630) -> stacked logits (B, 29, k_max) fp32 + the critic's value (B,) fp32.  In grad mode
+        the outputs carry gradients to every parameter (``_value_logits`` too)."""
+        if self._wants_grad():
+            dummy = torch.zeros(obs.shape[0], N_ACTION_HEADS, dtype=torch.uint8, device=obs.device)
+            logits, _, _, value, vl, _ = self._recompute(obs, dummy)
+            self._value_logits = vl
+            return logits, value
+        with torch.no_grad():
+            return self._forward_stacked_nograd(obs)
+
+    def _forward_stacked_nograd(self, obs: torch.Tensor):
         obs = self._check_obs(obs)
         self._pack()
         B, dev = obs.shape[0], obs.device
@@ -325,15 +416,30 @@ class NotePolicy(nn.Module):
         logits, value = self.forward_stacked(obs)
         return list(logits.unbind(1)), value
 
-    @torch.no_grad()
     def get_action_and_value(self, obs, action=None, need_entropy=True):
         """With ``action`` given (the PPO recompute call) the log-softmax, the summed log-prob
-        and the entropy come out of the fused head kernel.  With ``action=None`` the actions are
-        drawn inside the head kernel by Gumbel-max on the log-softmax, as the reference does
-        (python/policy.py:1475-1490), from a Philox stream keyed by ``self.seed_sampler(seed)``
+        and the entropy come out of the fused head kernel; in grad mode they (and ``_value_logits``)
+        carry gradients to every parameter, computed by the library's backward.  With ``action=None``
+        the actions are drawn inside the head kernel by Gumbel-max on the log-softmax, as the reference
+        does (python/policy.py:1475-1490), from a Philox stream keyed by ``self.seed_sampler(seed)``
         (default: seeded from torch's generator at first use)."""
         if action is None:
             return self._sample(obs, need_entropy)
+        if self._wants_grad():
+            B, dev = obs.shape[0], obs.device
+            if action.dtype not in _ACT_DTYPES:
+                action = action.long()
+            action = action.contiguous()
+            if tuple(action.shape) != (B, N_ACTION_HEADS) or action.device != dev:
+                raise ValueError(f"action must be ({B}, {N_ACTION_HEADS}) on {dev}")
+            _, logprob, entropy, value, vl, ent_h = self._recompute(obs, action)
+            self._ent_h = ent_h if need_entropy else None
+            self._value_logits = vl
+            return action, logprob, (entropy if need_entropy else None), value
+        with torch.no_grad():
+            return self._evaluate_nograd(obs, action, need_entropy)
+
+    def _evaluate_nograd(self, obs, action, need_entropy):
         obs = self._check_obs(obs)
         self._pack()
         B, dev = obs.shape[0], obs.device

@@ -486,10 +486,11 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the policy forward has no CPU path)")
-    if args.kernel:
-        run_kernel(args)
-        return
-    run_ours(args, rank, world, local_rank)
+    with torch.no_grad():          # the rollout / evaluation forward, as the reference's callers run it
+        if args.kernel:
+            run_kernel(args)
+            return
+        run_ours(args, rank, world, local_rank)
 
 
 if __name__ == "__main__":

@@ -198,6 +198,64 @@ int bsrl_forward_rollout(const bsrl_config* cfg, const void* arena, const void* 
                          const float* ret_sigma, const float* ret_mu, void* obs16, void* workspace,
                          int64_t workspace_bytes, void* stream);
 
+/* --- training: grad-mode forward and backward --------------------------------------- *
+ * The PPO update's recompute (python/train_batch.py:2669-2741): get_action_and_value(obs, action) in
+ * grad mode, then loss.backward().  The reference gets its backward from autograd over its
+ * autograd.Functions (python/fp16_linear.py:461-767, :931-1064, :1197-1251; python/fused_ln.py:58-107)
+ * and their kernels (ln_bwd*, attn29_bwd, wgrad / wgrad_bgrad / dgrad_drelu / relu_bwd); here the two
+ * halves are two calls.  Not built for emb_ln / final_ln / value_residual / trunk_v2 (BSRL_ERR_UNSUPPORTED).
+ *
+ * bsrl_forward_train: same arguments and outputs as bsrl_forward_act, computed by the same kernels
+ * (outputs are bit-identical to bsrl_forward_act's), plus a caller-owned `save` buffer of
+ * bsrl_train_save_bytes() that receives what the backward needs: the tokenizer's feature rows, the key
+ * bias, the residual stream entering every block, the readout rows, the head outputs. */
+int64_t bsrl_train_save_bytes(const bsrl_config* cfg, int64_t n_envs);
+int bsrl_forward_train(const bsrl_config* cfg, const void* arena, const void* obs, int32_t obs_dtype, int64_t n_envs,
+                       const void* actions, int32_t act_dtype, float* logits, float* logprob, float* entropy,
+                       float* ent_head, float* value, float* value_logits, void* save, int64_t save_bytes,
+                       void* workspace, int64_t workspace_bytes, void* stream);
+
+/* bsrl_backward: gradients of every parameter given the upstream gradients (DEVICE fp32, any may be
+ * NULL = zero) of logprob (n_envs), entropy (n_envs), value (n_envs), value_logits (n_envs, value_bins)
+ * and logits (n_envs, 29, k_max).  grads: ONE flat fp32 buffer of bsrl_grad_floats() floats; parameter i
+ * (bsrl_param_desc order, master shape) starts at offsets[i] (every slot 16-byte aligned); the call
+ * zeroes it first.  Each block's intermediates are recomputed from the saved block input; matrix
+ * products run on the tcgen05 GEMM (weight gradients as split-K products over the token rows).
+ * Activation gradients travel as fp16 multiplied by loss_scale, and the parameter gradients come out
+ * multiplied by loss_scale too: divide by it (pick it so that loss_scale * |upstream| stays well inside
+ * fp16 range; 1024-65536 for mean-reduced PPO losses).  workspace: bsrl_backward_workspace_bytes(). */
+int64_t bsrl_backward_workspace_bytes(const bsrl_config* cfg, int64_t n_envs);
+int64_t bsrl_grad_floats(const bsrl_config* cfg, int64_t* offsets, int32_t n_offsets);
+int bsrl_backward(const bsrl_config* cfg, const void* arena, int64_t n_envs, const void* actions, int32_t act_dtype,
+                  const void* save, int64_t save_bytes, const float* g_logprob, const float* g_entropy,
+                  const float* g_value, const float* g_value_logits, const float* g_logits, float loss_scale,
+                  float* grads, int64_t grad_floats, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Single stages of the backward, for unit tests.
+ * bsrl_layernorm_bwd: gx = (g_residual ? g_residual : 0) + dLayerNorm(gy; x, gamma), g_gamma / g_beta
+ *   ACCUMULATE (zero them first); all fp32, rows x d (ln_bwd with the fused residual gradient,
+ *   python/beat_arena_env/csrc/layer_norm.cu:289-519).
+ * bsrl_attention_bwd: gradients of the packed projection for g_out (n_envs*n_q, d) f16: gq (n_envs*n_q, d),
+ *   gkv (n_envs*29, 2d) = [gk | gv], fp16 (attn29_bwd, python/beat_arena_env/csrc/small_attn.cu:345-463).
+ * bsrl_head_tail_bwd: gradients (fp16, times `scale`) of the packed head outputs and value-bin logits from
+ *   the upstream gradients of logprob / entropy / value / value_logits / logits (any may be NULL).
+ * bsrl_linear_bwd: for y = x w^T + b with x (m, k), w (n, k), g = dL/dy (m, n) fp16: g_weight (n, k) f32 +=
+ *   g^T x (split-K tcgen05 product over the m rows; zero it first), g_bias (n) += column sums, g_x (m, k) =
+ *   g w (fp16 or fp32); any output may be NULL (wgrad / wgrad_bgrad / dgrad of
+ *   python/beat_arena_env/csrc/fp16_gemm.cu:252-373, :499-518). */
+int bsrl_layernorm_bwd(const float* x, const float* gamma, float eps, const float* gy, const float* g_residual,
+                       int64_t rows, int32_t d, float* gx, float* g_gamma, float* g_beta, void* stream);
+int bsrl_attention_bwd(const void* qkv_f16, const float* key_bias, int64_t n_envs, int32_t d, int32_t n_heads,
+                       int32_t q_first, int32_t n_q, const void* g_out_f16, void* gq_f16, void* gkv_f16, void* stream);
+int bsrl_head_tail_bwd(const bsrl_config* cfg, const float* head_out, const float* value_bin_logits, int64_t n_envs,
+                       const void* actions, int32_t act_dtype, const float* g_logprob, const float* g_entropy,
+                       const float* g_value, const float* g_value_logits, const float* g_logits, float scale,
+                       void* g_head_out_f16, int32_t ld_g_head, void* g_value_bins_f16, int32_t ld_g_bins, void* stream);
+int64_t bsrl_linear_bwd_scratch_bytes(int64_t m, int32_t n, int32_t k);
+int bsrl_linear_bwd(const void* g_f16, const void* x_f16, const void* w_f16, int64_t m, int32_t n, int32_t k,
+                    float* g_weight, float* g_bias, void* g_x, int32_t g_x_f32, void* scratch, int64_t scratch_bytes,
+                    void* stream);
+
 /* --- single stages (unit tests and profiling) -------------------------------------- */
 
 /* Obs lane of feature k of lead token tok (0..4), or -1 past the token's width

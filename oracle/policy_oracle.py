@@ -316,6 +316,25 @@ def make_actions(B: int, cfg: PolicyConfig, seed: int):
 # ----------------------------------------------------------------------------
 # Forward
 # ----------------------------------------------------------------------------
+def make_upstream(B: int, cfg: PolicyConfig, seed: int):
+    """Upstream gradients of a PPO-like loss for the gradient parity tests: seeded, of the size a
+    mean-reduced loss hands back (1 / B per env)."""
+    g = torch.Generator().manual_seed(seed)
+    return {"logprob": torch.randn(B, generator=g) / B, "entropy": 0.1 * torch.randn(B, generator=g) / B,
+            "value": torch.randn(B, generator=g) / B,
+            "value_logits": 0.2 * torch.randn(B, cfg.value_bins, generator=g) / B}
+
+
+def grad_stats(name: str, g):
+    """[norm, four fixed random projections] of a gradient tensor, float64; the projection vectors are
+    seeded by the parameter's name, so they are the same wherever this runs."""
+    seed = sum((i + 1) * ord(ch) for i, ch in enumerate(name)) % (2 ** 31)
+    gen = torch.Generator().manual_seed(seed)
+    g = g.detach().double().reshape(-1).cpu()
+    r = torch.randn(4, g.numel(), generator=gen, dtype=torch.float64)
+    return torch.cat([g.norm().reshape(1), r @ g])
+
+
 def _lin(sd, name, x):
     return F.linear(x, sd[name + ".weight"], sd[name + ".bias"])
 

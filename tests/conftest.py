@@ -41,3 +41,12 @@ def native():
         build_library()
     from beatsaberrl_b200 import _native
     return _native
+
+
+@pytest.fixture(autouse=True)
+def _inference_mode_by_default():
+    """The reference's callers run the rollout / evaluation forwards under torch.no_grad(); the tests do the
+    same unless they ask for gradients explicitly (with torch.enable_grad())."""
+    import torch
+    with torch.no_grad():
+        yield

@@ -37,6 +37,10 @@ CASES = [
 ]
 
 
+# cases that also get parameter gradients (name -> batch of the gradient run)
+GRAD_CASES = {"tiny_plain": 48, "tiny_geo_mixed": 40, "cfg1": 64}
+
+
 def case_config(cfg_name, geo, hg, opts=None):
     cfg = po.named_config(cfg_name)
     cfg.note_geo = geo
@@ -88,6 +92,34 @@ def main():
             [[float(m.state_dict()[k].double().sum()), float(m.state_dict()[k].double().abs().sum())]
              for k in names])
         out[f"{name}/param_names"] = np.array(names)
+    # gradients of every parameter for the PPO-recompute call, from the reference's own autograd (fp32, CPU)
+    grads = {}
+    for name, cfg_name, geo, hg, xav, seed, jit, B, padded, oseed, opts in CASES:
+        if name not in GRAD_CASES:
+            continue
+        cfg = case_config(cfg_name, geo, hg, opts)
+        torch.manual_seed(seed)
+        m = rp.NotePolicy(**cfg.ref_kwargs()).train()
+        if jit > 0:
+            sd = po.build_state_dict(cfg, seed, xavier=xav, ln_jitter=jit)
+            m.load_state_dict({k: sd[k] for k in m.state_dict()})
+        Bg = GRAD_CASES[name]
+        obs = po.make_obs(Bg, oseed + 100, padded=padded)
+        act = po.make_actions(Bg, cfg, oseed + 101)
+        up = po.make_upstream(Bg, cfg, oseed + 102)
+        with torch.enable_grad():
+            _, lp, ent, val = m.get_action_and_value(obs, act)
+            loss = (up["logprob"] * lp).sum() + (up["entropy"] * ent).sum() + (up["value"] * val).sum() \
+                + (up["value_logits"] * m._value_logits).sum()
+            loss.backward()
+        for k, prm in m.named_parameters():
+            g = prm.grad if prm.grad is not None else torch.zeros_like(prm)
+            # norm and four fixed random projections of every gradient (po.grad_stats): enough to pin the
+            # oracle's autograd to the reference's without storing megabytes of gradients
+            grads[f"{name}/stat/{k}"] = po.grad_stats(k, g).numpy()
+        grads[f"{name}/loss"] = np.array([float(loss)])
+    np.savez_compressed(HERE / "policy_grads_golden.npz", **grads)
+    print("wrote", HERE / "policy_grads_golden.npz", sum(v.nbytes for v in grads.values()), "bytes raw")
     # lane tables straight from the reference module
     out["lanes/saber_l"] = np.array(rp._SABER_L_IDX)
     out["lanes/saber_r"] = np.array(rp._SABER_R_IDX)
