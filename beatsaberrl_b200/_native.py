@@ -34,6 +34,13 @@ class Config(C.Structure):
                 ("value_residual", C.c_int32), ("trunk_v2", C.c_int32)]
 
 
+class GConfig(C.Structure):
+    """Mirror of ``bsrl_gconfig`` (include/bsrl.h): the single-body-token layout."""
+    _fields_ = [("embed", C.c_int32), ("n_heads", C.c_int32), ("n_blocks", C.c_int32), ("ffn_mult", C.c_int32),
+                ("n_obj", C.c_int32), ("n_gears", C.c_int32), ("body_dim", C.c_int32), ("obj_dim", C.c_int32),
+                ("eps", C.c_float)]
+
+
 def make_config(embed, n_heads, n_blocks, ffn_mult, trunk_dim, trunk_hidden, value_bins, note_geo,
                 head_gears, z_asinh=8.0, value_vmax=6.0, eps=1e-5, emb_ln=False, final_ln=False,
                 game_flux=False, value_residual=False, trunk_v2=False) -> Config:
@@ -90,6 +97,17 @@ _sig = {
                                      _P, C.c_int32, _P]),
     "bsrl_linear_bwd_scratch_bytes": (C.c_int64, [C.c_int64, C.c_int32, C.c_int32]),
     "bsrl_linear_bwd": (C.c_int, [_P, _P, _P, C.c_int64, C.c_int32, C.c_int32, _P, _P, _P, C.c_int32, _P, C.c_int64, _P]),
+    "bsrl_g_config_validate": (C.c_int, [C.POINTER(GConfig)]),
+    "bsrl_g_obs_dim": (C.c_int32, [C.POINTER(GConfig)]),
+    "bsrl_g_mac_per_env": (C.c_int64, [C.POINTER(GConfig)]),
+    "bsrl_g_param_count": (C.c_int32, [C.POINTER(GConfig)]),
+    "bsrl_g_param_desc": (C.c_int, [C.POINTER(GConfig), C.c_int32, C.c_char_p, C.c_int32, C.POINTER(C.c_int64),
+                                    C.POINTER(C.c_int64)]),
+    "bsrl_g_weights_bytes": (C.c_int64, [C.POINTER(GConfig)]),
+    "bsrl_g_pack_weights": (C.c_int, [C.POINTER(GConfig), C.POINTER(_P), C.c_int32, _P, C.c_int64, _P]),
+    "bsrl_g_workspace_bytes": (C.c_int64, [C.POINTER(GConfig), C.c_int64]),
+    "bsrl_g_forward": (C.c_int, [C.POINTER(GConfig), _P, _P, C.c_int64, _P, C.c_int32, _P, _P, _P, _P, _P, _P,
+                                 C.c_int64, _P]),
     "bsrl_fixed_scratch_bytes": (C.c_int64, []),
     "bsrl_forward_fixed": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, _P, _P]),
     "bsrl_forward_act": (C.c_int, [_CFG, _P, _P, C.c_int32, C.c_int64, _P, C.c_int32, _P, _P, _P, _P, _P, _P,

@@ -71,6 +71,7 @@ int timed(cudaStream_t st, double flops, double bytes, Fn&& fn) {
 std::atomic<int> g_engine{0};
 thread_local int g_call_engine = 0;   // the engine of the forward running on this thread
 void use_process_engine() { g_call_engine = g_engine.load(std::memory_order_relaxed); }
+int process_engine() { return g_engine.load(std::memory_order_relaxed); }
 int linear(const LinearArgs& p, cudaStream_t st) {
   return timed(st, 2.0 * p.M * p.N * p.K, linear_bytes(p), [&] {
     if (g_call_engine == 0 && p.M >= 128 && linear_tc5_ok(p)) return linear_tc5(p, st);

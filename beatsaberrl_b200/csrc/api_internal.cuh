@@ -63,6 +63,7 @@ void head_shape(const bsrl_config& cfg, const Layout& l, HeadTailArgs& t);
 
 // makes the calling thread's launch wrappers follow the process-wide engine choice (bsrl_set_engine)
 void use_process_engine();
+int process_engine();
 
 // stage-labelled launch wrappers (timed when the calling thread has the profiler on)
 int linear(const LinearArgs& p, cudaStream_t st);

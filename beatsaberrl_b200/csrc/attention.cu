@@ -1,11 +1,12 @@
-// Masked multi-head self-attention over the 29 tokens of one environment.
+// Masked multi-head self-attention over the tokens of one environment (29 in the reference's layout;
+// any count up to 96 for the single-body-token layouts of 17 / 33 / 65 tokens).
 //
-// One warp owns one (env, head) pair: it stages that head's q, k, v slices (29 x head_dim
-// fp16 each) in its private shared-memory tile, computes the 32 x 32 score tile with
+// One warp owns one (env, head) pair: it stages that head's q, k, v slices (tokens x head_dim
+// fp16 each) in its private shared-memory tile, computes a 16-row strip of the score matrix with
 // m16n8k16 MMAs, runs the softmax in fp32 on the accumulator fragments (row statistics by
 // quad shuffles) and feeds the probabilities straight back as the A operand of the P V MMAs.
 // Scores never leave registers.  The additive key bias (0 or -16384) makes masked keys'
-// probabilities exactly 0; the three pad keys (29..31) are forced to -inf.
+// probabilities exactly 0; the pad keys (up to the next multiple of 32) are forced to -inf.
 //
 // Reference: attn29_fwd_kernel (python/beat_arena_env/csrc/small_attn.cu:228-332) and the
 // fp32 arithmetic it is checked against, softmax(q k^T / sqrt(dh) + bias) v
@@ -15,15 +16,15 @@
 
 namespace bsrl {
 namespace {
-constexpr int kWarps = 8;
-constexpr int kRows = 32;  // 29 tokens padded to two 16-row MMA tiles / four 8-key tiles
-
-template <int DH>
-__global__ void __launch_bounds__(kWarps * 32) attn29_kernel(const __half* __restrict__ qkv, int ld,
-                                                            const float* __restrict__ key_bias,
-                                                            int64_t n_pairs, int d, int n_heads,
-                                                            int q_first, int n_q,
-                                                            __half* __restrict__ out, int ldo) {
+// KG: groups of 32 keys (tokens padded to 32 KG rows: two 16-row MMA tiles / four 8-key tiles per group);
+// WARPS: warps per block, fewer where the per-warp tile is large
+template <int DH, int KG, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) attn29_kernel(const __half* __restrict__ qkv, int ld,
+                                                           const float* __restrict__ key_bias,
+                                                           int64_t n_pairs, int tokens, int d, int n_heads,
+                                                           int q_first, int n_q,
+                                                           __half* __restrict__ out, int ldo) {
+  constexpr int kWarps = WARPS, kRows = 32 * KG, NT = 4 * KG;   // NT: 8-key tiles
   constexpr int LDS = DH + 8;          // padded row (halfs): ldmatrix rows land in distinct banks
   constexpr int CH = DH / 8;           // 16-byte chunks per row
   extern __shared__ __align__(16) uint8_t smem[];
@@ -40,7 +41,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn29_kernel(const __half* __res
        pair += (int64_t)gridDim.x * kWarps) {
     const int64_t env = pair / n_heads;
     const int head = static_cast<int>(pair % n_heads);
-    const __half* base = qkv + env * kT * (int64_t)ld + head * DH;
+    const __half* base = qkv + env * tokens * (int64_t)ld + head * DH;
     __syncwarp();
     // stage q (query rows), k, v; rows past the live range are zero
     for (int c = lane; c < kRows * CH; c += 32) {
@@ -48,7 +49,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn29_kernel(const __half* __res
       uint4 zq = make_uint4(0, 0, 0, 0), zk = zq, zv = zq;
       if (row < n_q)
         zq = *reinterpret_cast<const uint4*>(base + (int64_t)(q_first + row) * ld + ch * 8);
-      if (row < kT) {
+      if (row < tokens) {
         const __half* r = base + (int64_t)row * ld + ch * 8;
         zk = *reinterpret_cast<const uint4*>(r + d);
         zv = *reinterpret_cast<const uint4*>(r + 2 * d);
@@ -58,20 +59,20 @@ __global__ void __launch_bounds__(kWarps * 32) attn29_kernel(const __half* __res
       *reinterpret_cast<uint4*>(sv + row * LDS + ch * 8) = zv;
     }
     // key bias of the 8 key columns this lane sees: keys nt*8 + tig*2 + {0,1}
-    float kb[4][2];
+    float kb[NT][2];
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         int key = nt * 8 + tig * 2 + e;
-        kb[nt][e] = key < kT ? key_bias[env * kT + key] : -INFINITY;
+        kb[nt][e] = key < tokens ? key_bias[env * tokens + key] : -INFINITY;
       }
     __syncwarp();
 
     for (int mt = 0; mt < m_tiles; ++mt) {
-      float s[4][4];
+      float s[NT][4];
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
 #pragma unroll
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn29_kernel(const __half* __res
         uint32_t a[4];
         ldmatrix_x4(a, sq_u + ((mt * 16 + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8) * 2);
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
+        for (int j = 0; j < 2 * KG; ++j) {
           uint32_t b[4];
           int row = j * 16 + (lane & 7) + ((lane >> 4) << 3);
           ldmatrix_x4(b, sk_u + (row * LDS + ks * 16 + ((lane >> 3) & 1) * 8) * 2);
@@ -90,7 +91,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn29_kernel(const __half* __res
       // softmax over keys for rows g (e = 0,1) and g + 8 (e = 2,3)
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           s[nt][e] = s[nt][e] * scale + kb[nt][e & 1];
@@ -103,7 +104,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn29_kernel(const __half* __res
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       }
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           s[nt][e] = expf(s[nt][e] - mx[e >> 1]);
@@ -116,9 +117,9 @@ __global__ void __launch_bounds__(kWarps * 32) attn29_kernel(const __half* __res
         sum[r] = 1.f / sum[r];
       }
       // P (normalised, fp16) as the A operand of P V
-      uint32_t pa[2][4];
+      uint32_t pa[2 * KG][4];
 #pragma unroll
-      for (int ks = 0; ks < 2; ++ks) {
+      for (int ks = 0; ks < 2 * KG; ++ks) {
         pa[ks][0] = pack_half2(s[2 * ks][0] * sum[0], s[2 * ks][1] * sum[0]);
         pa[ks][1] = pack_half2(s[2 * ks][2] * sum[1], s[2 * ks][3] * sum[1]);
         pa[ks][2] = pack_half2(s[2 * ks + 1][0] * sum[0], s[2 * ks + 1][1] * sum[0]);
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn29_kernel(const __half* __res
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
 #pragma unroll
-      for (int ks = 0; ks < 2; ++ks) {
+      for (int ks = 0; ks < 2 * KG; ++ks) {
 #pragma unroll
         for (int j = 0; j < DH / 16; ++j) {
           uint32_t b[4];
@@ -154,34 +155,51 @@ __global__ void __launch_bounds__(kWarps * 32) attn29_kernel(const __half* __res
   }
 }
 
-template <int DH>
-int launch(const __half* qkv, int ld, const float* key_bias, int64_t n_envs, int d, int n_heads,
+template <int DH, int KG>
+int launch(const __half* qkv, int ld, const float* key_bias, int64_t n_envs, int tokens, int d, int n_heads,
            int q_first, int n_q, __half* out, int ldo, cudaStream_t stream) {
-  constexpr int smem = kWarps * 3 * kRows * (DH + 8) * 2;
+  constexpr int kWarps = KG == 1 ? 8 : 4;
+  constexpr int smem = kWarps * 3 * (32 * KG) * (DH + 8) * 2;
   static DeviceOnce once;
   int rc = once.run("attn29_kernel set-up", [] {
-    return cudaFuncSetAttribute(attn29_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    return cudaFuncSetAttribute(attn29_kernel<DH, KG, kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   });
   if (rc != BSRL_OK) return rc;
   int64_t pairs = n_envs * n_heads;
   int64_t blocks = (pairs + kWarps - 1) / kWarps;
   int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  attn29_kernel<DH><<<static_cast<unsigned>(blocks), kWarps * 32, smem, stream>>>(
-      qkv, ld, key_bias, pairs, d, n_heads, q_first, n_q, out, ldo);
+  attn29_kernel<DH, KG, kWarps><<<static_cast<unsigned>(blocks), kWarps * 32, smem, stream>>>(
+      qkv, ld, key_bias, pairs, tokens, d, n_heads, q_first, n_q, out, ldo);
   BSRL_LAUNCH_OK("attn29_kernel");
   return BSRL_OK;
+}
+template <int DH>
+int launch_kg(const __half* qkv, int ld, const float* key_bias, int64_t n_envs, int tokens, int d, int n_heads,
+              int q_first, int n_q, __half* out, int ldo, cudaStream_t stream) {
+  if (tokens <= 32) return launch<DH, 1>(qkv, ld, key_bias, n_envs, tokens, d, n_heads, q_first, n_q, out, ldo, stream);
+  if (tokens <= 64) return launch<DH, 2>(qkv, ld, key_bias, n_envs, tokens, d, n_heads, q_first, n_q, out, ldo, stream);
+  return launch<DH, 3>(qkv, ld, key_bias, n_envs, tokens, d, n_heads, q_first, n_q, out, ldo, stream);
 }
 }  // namespace
 
 int attention29(const __half* qkv, int ld_qkv, const float* key_bias, int64_t n_envs, int d,
                 int n_heads, int q_first, int n_q, __half* out, int ldo, cudaStream_t stream) {
+  return attention_tokens(qkv, ld_qkv, key_bias, n_envs, kT, d, n_heads, q_first, n_q, out, ldo, stream);
+}
+
+int attention_tokens(const __half* qkv, int ld_qkv, const float* key_bias, int64_t n_envs, int tokens, int d,
+                     int n_heads, int q_first, int n_q, __half* out, int ldo, cudaStream_t stream) {
   if (!qkv || !key_bias || !out) {
     set_error("attention: NULL operand");
     return BSRL_ERR_NULL;
   }
+  if (tokens < 1 || tokens > 96) {
+    set_error("attention: %d tokens per env unsupported (1..96)", tokens);
+    return BSRL_ERR_UNSUPPORTED;
+  }
   if (n_envs < 0 || n_heads <= 0 || d % n_heads != 0 || q_first < 0 || n_q < 1 ||
-      q_first + n_q > kT || ld_qkv < 3 * d || ldo < d) {
+      q_first + n_q > tokens || ld_qkv < 3 * d || ldo < d) {
     set_error("attention: bad shape d=%d heads=%d q=[%d,%d)", d, n_heads, q_first, q_first + n_q);
     return BSRL_ERR_SHAPE;
   }
@@ -191,9 +209,9 @@ int attention29(const __half* qkv, int ld_qkv, const float* key_bias, int64_t n_
   }
   if (n_envs == 0) return BSRL_OK;
   const int dh = d / n_heads;
-  if (dh == 32) return launch<32>(qkv, ld_qkv, key_bias, n_envs, d, n_heads, q_first, n_q, out, ldo, stream);
-  if (dh == 48) return launch<48>(qkv, ld_qkv, key_bias, n_envs, d, n_heads, q_first, n_q, out, ldo, stream);
-  if (dh == 64) return launch<64>(qkv, ld_qkv, key_bias, n_envs, d, n_heads, q_first, n_q, out, ldo, stream);
+  if (dh == 32) return launch_kg<32>(qkv, ld_qkv, key_bias, n_envs, tokens, d, n_heads, q_first, n_q, out, ldo, stream);
+  if (dh == 48) return launch_kg<48>(qkv, ld_qkv, key_bias, n_envs, tokens, d, n_heads, q_first, n_q, out, ldo, stream);
+  if (dh == 64) return launch_kg<64>(qkv, ld_qkv, key_bias, n_envs, tokens, d, n_heads, q_first, n_q, out, ldo, stream);
   set_error("attention: head_dim %d unsupported (32, 48 or 64)", dh);
   return BSRL_ERR_UNSUPPORTED;
 }

@@ -127,6 +127,9 @@ __device__ __forceinline__ void store_h32(uint8_t* chunks, int row, int col, con
   }
 }
 
+// GELU: the FFN activation is the exact GELU instead of ReLU (a compile-time variant: the hidden-chunk
+// epilogue sits on the chunk loop's critical path)
+template <bool GELU>
 __global__ void __launch_bounds__(THREADS, 1)
 block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_constant__ CUtensorMap tm_wo,
                   const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w2,
@@ -550,10 +553,15 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
 #pragma unroll
           for (int jj = 0; jj < 8; ++jj) {
             const float4 b0 = P_b0[((j * HC + grp * 64 + c) >> 2) + jj];
-            hp[(c >> 1) + 2 * jj] = pack_half2(fmaxf(__uint_as_float(r[4 * jj]) + b0.x, 0.f),
-                                               fmaxf(__uint_as_float(r[4 * jj + 1]) + b0.y, 0.f));
-            hp[(c >> 1) + 2 * jj + 1] = pack_half2(fmaxf(__uint_as_float(r[4 * jj + 2]) + b0.z, 0.f),
-                                                   fmaxf(__uint_as_float(r[4 * jj + 3]) + b0.w, 0.f));
+            const float a0 = __uint_as_float(r[4 * jj]) + b0.x, a1 = __uint_as_float(r[4 * jj + 1]) + b0.y;
+            const float a2 = __uint_as_float(r[4 * jj + 2]) + b0.z, a3 = __uint_as_float(r[4 * jj + 3]) + b0.w;
+            if (GELU) {
+              hp[(c >> 1) + 2 * jj] = pack_half2(gelu_exact(a0), gelu_exact(a1));
+              hp[(c >> 1) + 2 * jj + 1] = pack_half2(gelu_exact(a2), gelu_exact(a3));
+            } else {
+              hp[(c >> 1) + 2 * jj] = pack_half2(fmaxf(a0, 0.f), fmaxf(a1, 0.f));
+              hp[(c >> 1) + 2 * jj + 1] = pack_half2(fmaxf(a2, 0.f), fmaxf(a3, 0.f));
+            }
           }
         }
         // this half of sH is free once the previous chunk's FFN-down MMAs on it have retired
@@ -722,7 +730,9 @@ int block_tail(const BlockTailArgs& a, cudaStream_t stream) {
     if (a.out16[o] && !make_tmap_rows64(&tm_o[o], a.out16[o], 2, a.M, a.d, a.ld16[o], 32)) return BSRL_ERR_CUDA;
   static DeviceOnce once;
   int rc = once.run("block_tail_kernel set-up", [] {
-    return cudaFuncSetAttribute(block_tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(block_tail_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(block_tail_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   });
   if (rc != BSRL_OK) return rc;
   TailParams p;
@@ -737,7 +747,8 @@ int block_tail(const BlockTailArgs& a, cudaStream_t stream) {
   p.x_tma = x_tma ? 1 : 0;
   p.status = status;
   int grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
-  block_tail_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_att, tm_wo, tm_w0, tm_w2, tm_x, tm_xo, tm_o[0], tm_o[1], p);
+  if (a.gelu) block_tail_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(tm_att, tm_wo, tm_w0, tm_w2, tm_x, tm_xo, tm_o[0], tm_o[1], p);
+  else block_tail_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(tm_att, tm_wo, tm_w0, tm_w2, tm_x, tm_xo, tm_o[0], tm_o[1], p);
   BSRL_LAUNCH_OK("block_tail_kernel");
   return BSRL_OK;
 }

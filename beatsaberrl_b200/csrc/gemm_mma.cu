@@ -123,9 +123,12 @@ __global__ void __launch_bounds__(THREADS) linear_mma_kernel(LinearArgs p) {
           v0 += p.bias[col];
           v1 += p.bias[col + 1];
         }
-        if (p.relu) {
+        if (p.relu == 1) {
           v0 = fmaxf(v0, 0.f);
           v1 = fmaxf(v1, 0.f);
+        } else if (p.relu == 2) {
+          v0 = gelu_exact(v0);
+          v1 = gelu_exact(v1);
         }
         if (rrow) {
           float2 r = *reinterpret_cast<const float2*>(rrow + col);

@@ -230,9 +230,12 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               v[j] += bv.x; v[j + 1] += bv.y; v[j + 2] += bv.z; v[j + 3] += bv.w;
             }
           }
-          if (p.relu) {
+          if (p.relu == 1) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+          } else if (p.relu == 2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_exact(v[j]);
           }
           if (tma_c && s32 == 0) {   // the previous block's TMA store has read the staging buffer
             if (lane == 0) bulk_wait_read<0>();

@@ -115,8 +115,17 @@ __global__ void __launch_bounds__(256) head_tail_kernel(HeadTailArgs p) {
         if (p.entropy) p.entropy[env] = ent;
       }
     }
-    // value = softmax(bins) . centres
     const float* vr = p.vraw + env * p.ld_v;
+    if (p.bins == 1) {       // a scalar value head: the one "bin" is the value itself
+      if (lane == 0) {
+        const float v = vr[0];
+        p.value[env] = v;
+        if (p.value_logits) p.value_logits[env] = v;
+        if (p.value_buf) p.value_buf[env] = v * (p.ret_sigma ? *p.ret_sigma : 1.f) + (p.ret_mu ? *p.ret_mu : 0.f);
+      }
+      continue;
+    }
+    // value = softmax(bins) . centres
     float mx = -INFINITY;
     for (int i = lane; i < p.bins; i += 32) mx = fmaxf(mx, vr[i]);
     mx = warp_max(mx);
@@ -148,7 +157,7 @@ int head_tail(const HeadTailArgs& a, cudaStream_t stream) {
     set_error("head_tail: NULL operand");
     return BSRL_ERR_NULL;
   }
-  if (a.k_max < 3 || a.k_max > 7 || a.bins < 2 || a.n_envs < 0) {
+  if (a.k_max < 3 || a.k_max > 7 || a.bins < 1 || a.n_envs < 0) {
     set_error("head_tail: bad shape k_max=%d bins=%d", a.k_max, a.bins);
     return BSRL_ERR_SHAPE;
   }

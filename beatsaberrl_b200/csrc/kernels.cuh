@@ -19,7 +19,7 @@ struct LinearArgs {
   int ldc;
   RowMap cmap;
   int out_f32;
-  int relu;
+  int relu;            // activation: 0 none, 1 ReLU, 2 exact GELU
   int64_t M;
   int N, K;
   // Split-K (weight gradients: few output tiles, a very long K): the K range is cut into k_splits
@@ -57,6 +57,7 @@ struct BlockTailArgs {
   int64_t ld16[2];
   const float* g16[2];
   const float* b16[2];
+  int gelu;            // 1: the FFN activation is the exact GELU instead of ReLU
 };
 bool block_tail_ok(const BlockTailArgs& a);
 int block_tail(const BlockTailArgs& a, cudaStream_t stream);
@@ -132,6 +133,9 @@ struct EncoderArgs {
 bool encoder_fused_ok(const EncoderArgs& a);
 int encoder_fused(const EncoderArgs& a, cudaStream_t stream);
 
+// Masked MHA over the `tokens` keys of each env (1..96); attention29 is the 29-token case.
+int attention_tokens(const __half* qkv, int ld_qkv, const float* key_bias, int64_t n_envs, int tokens, int d,
+                     int n_heads, int q_first, int n_q, __half* out, int ldo, cudaStream_t stream);
 // Masked MHA over the 29 keys of each env.
 int attention29(const __half* qkv, int ld_qkv, const float* key_bias, int64_t n_envs, int d,
                 int n_heads, int q_first, int n_q, __half* out, int ldo, cudaStream_t stream);

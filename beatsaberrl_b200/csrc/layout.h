@@ -66,6 +66,12 @@ struct CopySlot {
   bool half;
 };
 
+// scatter (and optionally AdamW-update) a list of masters into an arena (optim.cu)
+int multi_pack_slots(const std::vector<ParamSlot>& slots, const std::vector<CopySlot>& copies, float* const* params,
+                     const float* const* grads, float* const* exp_avg, float* const* exp_avg_sq, const float* lr,
+                     const float* wd, float beta1, float beta2, float eps, int step, const float* inv_scale,
+                     const float* found_inf, void* arena, cudaStream_t stream);
+
 int validate_config(const bsrl_config* c);
 Layout make_layout(const bsrl_config& c);
 std::vector<ParamSlot> make_param_slots(const bsrl_config& c, const Layout& l);

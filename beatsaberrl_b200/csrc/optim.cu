@@ -86,6 +86,14 @@ int multi_pack(const bsrl_config& cfg, const Layout& l, float* const* params, co
                cudaStream_t stream) {
   const std::vector<ParamSlot> slots = make_param_slots(cfg, l);
   const std::vector<CopySlot> copies = make_copy_slots(cfg, l, slots);
+  return multi_pack_slots(slots, copies, params, grads, exp_avg, exp_avg_sq, lr, wd, beta1, beta2, eps, step, inv_scale,
+                          found_inf, arena, stream);
+}
+
+int multi_pack_slots(const std::vector<ParamSlot>& slots, const std::vector<CopySlot>& copies, float* const* params,
+                     const float* const* grads, float* const* exp_avg, float* const* exp_avg_sq, const float* lr,
+                     const float* wd, float beta1, float beta2, float eps, int step, const float* inv_scale,
+                     const float* found_inf, void* arena, cudaStream_t stream) {
   Table t;
   memset(&t, 0, sizeof(t));
   t.beta1 = beta1; t.beta2 = beta2; t.eps = eps;

@@ -256,6 +256,41 @@ int bsrl_linear_bwd(const void* g_f16, const void* x_f16, const void* w_f16, int
                     float* g_weight, float* g_bias, void* g_x, int32_t g_x_f32, void* scratch, int64_t scratch_bytes,
                     void* stream);
 
+/* --- the single-body-token layout ---------------------------------------------------- *
+ * A second front / back end around the same transformer core, for policies laid out as one body token
+ * plus n_obj object tokens (T = 1 + n_obj, e.g. 17 / 33 / 65):
+ *   obs (n_envs, body_dim + n_obj * obj_dim + n_obj) f32 = body | objects | per-object live flag (0 / 1)
+ *   token 0 = Linear(body_dim, embed)(body);  token 1 + j = Linear(obj_dim, embed)(object j)
+ *   n_blocks pre-LN blocks with an exact-GELU FFN, absent objects masked as keys, the last block on the
+ *   body row only;  heads Linear(embed, 29 * n_gears) -> logits (n_envs, 29, n_gears);  value Linear(embed, 1)
+ * The reference has no such tokenizer or readout (python/policy.py:174-275, :940-952, :1107-1138, :1346-1403
+ * are fixed at 29 tokens, 2-layer ReLU encoders, a SimBa trunk and a distributional critic); its blocks are
+ * the reference's Block (python/policy.py:524-715) with the FFN activation swapped, which is what this
+ * layout's parity oracle composes.  Parameter names: body_enc, obj_enc, blocks.i.{ln_attn, q_proj, k_proj,
+ * v_proj, out_proj, ln_ffn, ffn.0, ffn.2}, heads, value. */
+typedef struct bsrl_gconfig {
+  int32_t embed, n_heads, n_blocks, ffn_mult;
+  int32_t n_obj;       /* object tokens (1..95) */
+  int32_t n_gears;     /* logits per action head (3..7) */
+  int32_t body_dim;    /* e.g. 340 */
+  int32_t obj_dim;     /* e.g. 16 (<= 64) */
+  float eps;           /* LayerNorm epsilon */
+} bsrl_gconfig;
+int bsrl_g_config_validate(const bsrl_gconfig* cfg);
+int32_t bsrl_g_obs_dim(const bsrl_gconfig* cfg);
+int64_t bsrl_g_mac_per_env(const bsrl_gconfig* cfg);
+int32_t bsrl_g_param_count(const bsrl_gconfig* cfg);
+int bsrl_g_param_desc(const bsrl_gconfig* cfg, int32_t i, char* name, int32_t name_cap, int64_t* rows, int64_t* cols);
+int64_t bsrl_g_weights_bytes(const bsrl_gconfig* cfg);
+int bsrl_g_pack_weights(const bsrl_gconfig* cfg, const float* const* params, int32_t n_params, void* arena,
+                        int64_t arena_bytes, void* stream);
+int64_t bsrl_g_workspace_bytes(const bsrl_gconfig* cfg, int64_t n_envs);
+/* Forward; with actions (n_envs, 29) u8 / i32 / i64 also the summed log-prob, entropy and per-head entropy
+ * from the fused head kernel.  logits, logprob, entropy, ent_head may be NULL (logits or logprob must be given). */
+int bsrl_g_forward(const bsrl_gconfig* cfg, const void* arena, const float* obs, int64_t n_envs, const void* actions,
+                   int32_t act_dtype, float* logits, float* logprob, float* entropy, float* ent_head, float* value,
+                   void* workspace, int64_t workspace_bytes, void* stream);
+
 /* --- single stages (unit tests and profiling) -------------------------------------- */
 
 /* Obs lane of feature k of lead token tok (0..4), or -1 past the token's width
