@@ -105,6 +105,29 @@ def run(args):
             best = min(best, (time.perf_counter() - t0) / args.iters)
         return best
 
+    if args.update:
+        # forward in grad mode + backward of a PPO-like loss to every parameter: the reference's fp16 update stream
+        # (its autograd.Functions and backward kernels), protocol of python/bench_policy_update.py
+        gen = torch.Generator().manual_seed(seed + 1)
+        act = torch.randint(0, gears, (envs, 29), generator=gen).to(torch.uint8).cuda()
+        wl, we, wv = (torch.randn(envs, generator=gen) / envs).cuda(), (0.1 * torch.randn(envs, generator=gen) / envs).cuda(), \
+            (torch.randn(envs, generator=gen) / envs).cuda()
+        wvl = (0.2 * torch.randn(envs, pol.value_bins, generator=gen) / envs).cuda()
+        pol.train()
+        obs16 = obs.half()
+
+        def update():
+            _, lp, ent, val = pol.get_action_and_value(obs16, act)
+            loss = (wl * lp.float()).sum() + (we * ent.float()).sum() + (wv * val.float()).sum() + (wvl * pol._value_logits.float()).sum()
+            (loss * 1024.0).backward()
+            for p_ in pol.parameters():
+                p_.grad = None
+        t = bench(update)
+        return {"workload": args.workload, "envs": envs, "gpu": torch.cuda.get_device_name(0), "mode": "update (grad-mode forward + backward)",
+                "ms_per_step": t * 1e3, "env_updates_s": envs / t, "fused_ffn_mode": pol.fused_ffn,
+                "ln_kernel": "jit" if fused_ln._load() is not None else "torch fallback",
+                "gemm_attn_kernels": "jit" if fl._load() is not None else "torch fallback",
+                "protocol": f"best of {args.reps} x {args.iters} updates after {args.warmup} warm-ups, fp16 obs, loss scale 1024"}
     # The reference calls torch's scaled_dot_product_attention where its own 29-token kernel does not
     # engage; if the cuDNN backend refuses the shape (seen at 65,536 envs x 8 heads), fall back to torch's
     # other SDPA backends -- a torch setting, the reference's code is untouched.
@@ -143,6 +166,7 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--update", action="store_true", help="time the grad-mode forward + backward instead of the forward")
     ap.add_argument("--fused-ffn", default="", help="the reference's fused_ffn mode (off/on/up16/up16dn16)")
     args = ap.parse_args()
     try:

@@ -15,12 +15,12 @@
 namespace bsrl {
 namespace {
 
-constexpr int kMaxVec = 8;   // float4 per lane: rows up to 1024 wide
+constexpr int kMaxVecAll = 8;   // float4 per lane: rows up to 1024 wide
 
 // dx = rstd (gy g - mean(gy g) - xhat mean(gy g xhat)); gx_out = (gres ? gres : 0) + dx;
 // ggamma += sum_rows gy xhat, gbeta += sum_rows gy.  One warp per row; per-block partial sums of the
 // parameter gradients in shared memory, then one atomic per column per block.
-template <bool GY_F32>
+template <bool GY_F32, int kMaxVec>
 __global__ void __launch_bounds__(256) ln_bwd_kernel(const float* __restrict__ x, int64_t ldx, RowMap xmap,
                                                      const float* __restrict__ gamma, float eps, const void* __restrict__ gy,
                                                      int64_t ldgy, const float* gres, float* gx_out, int64_t ldg, RowMap gmap,
@@ -176,10 +176,49 @@ __global__ void __launch_bounds__(256) add_rows_kernel(const float* __restrict__
   }
 }
 
-// out (cols, ldo) = in (rows, ldi)^T, fp16, 64 x 64 tiles through shared memory; rows [rows, rows_pad) of
-// the input read as zero, so the padded K range of the following GEMM contributes nothing
+// out (cols, ldo) = in (rows, ldi)^T, fp16, 64 x 64 tiles through shared memory, 16-byte accesses on both
+// sides; rows [rows, rows_pad) of the input read as zero, so the padded K range of the following GEMM
+// contributes nothing.  With colsum, the column sums of the input (a Linear's bias gradient, when the input is
+// dL/dy) are accumulated on the way: per-tile partial sums, one atomic per column and tile.
+// Requires cols % 8 == 0, ldi % 8 == 0, ldo % 8 == 0 and 16-byte aligned bases.
 __global__ void __launch_bounds__(256) transpose16_kernel(const __half* __restrict__ in, int64_t ldi, RowMap imap, int64_t rows,
-                                                          int cols, __half* __restrict__ out, int64_t ldo, int64_t rows_pad) {
+                                                          int cols, __half* __restrict__ out, int64_t ldo, int64_t rows_pad,
+                                                          float* __restrict__ colsum) {
+  __shared__ __align__(16) __half tile[64][72];      // 144-byte rows: column reads of 8 rows hit 8 bank groups
+  const int64_t r0 = (int64_t)blockIdx.x * 64;
+  const int c0 = blockIdx.y * 64;
+  const int t = threadIdx.x;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {                      // 64 rows x 8 chunks of 8 columns
+    const int r = (t >> 3) + 32 * i, ch = t & 7;
+    const int64_t row = r0 + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < rows && c0 + ch * 8 < cols) v = *reinterpret_cast<const uint4*>(in + imap(row) * ldi + c0 + ch * 8);
+    *reinterpret_cast<uint4*>(&tile[r][ch * 8]) = v;
+  }
+  __syncthreads();
+  if (colsum && t < 64 && c0 + t < cols) {
+    float sum = 0.f;
+#pragma unroll 8
+    for (int r = 0; r < 64; ++r) sum += __half2float(tile[r][t]);
+    atomicAdd(&colsum[c0 + t], sum);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {                      // 64 output rows (input columns) x 8 chunks of 8 input rows
+    const int c = (t >> 3) + 32 * i, ch = t & 7;
+    if (c0 + c < cols && r0 + ch * 8 < rows_pad) {
+      __half v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = tile[ch * 8 + k][c];
+      *reinterpret_cast<uint4*>(out + (int64_t)(c0 + c) * ldo + r0 + ch * 8) = *reinterpret_cast<const uint4*>(v);
+    }
+  }
+}
+
+// small-shape fallback of the transpose (any cols / alignment), element-wise
+__global__ void __launch_bounds__(256) transpose16_slow_kernel(const __half* __restrict__ in, int64_t ldi, RowMap imap, int64_t rows,
+                                                               int cols, __half* __restrict__ out, int64_t ldo, int64_t rows_pad,
+                                                               float* __restrict__ colsum) {
   __shared__ __half tile[64][66];
   const int64_t r0 = (int64_t)blockIdx.x * 64;
   const int c0 = blockIdx.y * 64;
@@ -189,6 +228,11 @@ __global__ void __launch_bounds__(256) transpose16_kernel(const __half* __restri
     tile[r][c] = (row < rows && c0 + c < cols) ? in[imap(row) * ldi + c0 + c] : __float2half_rn(0.f);
   }
   __syncthreads();
+  if (colsum && threadIdx.x < 64 && c0 + threadIdx.x < cols) {
+    float sum = 0.f;
+    for (int r = 0; r < 64; ++r) sum += __half2float(tile[r][threadIdx.x]);
+    atomicAdd(&colsum[c0 + threadIdx.x], sum);
+  }
   for (int i = threadIdx.x; i < 64 * 64; i += 256) {
     const int c = i >> 6, r = i & 63;
     if (c0 + c < cols && r0 + r < rows_pad) out[(int64_t)(c0 + c) * ldo + r0 + r] = tile[r][c];
@@ -291,18 +335,22 @@ int layernorm_bwd(const float* x, int64_t ldx, RowMap xmap, const float* gamma, 
     set_error("layernorm_bwd: NULL operand");
     return BSRL_ERR_NULL;
   }
-  if (d % 4 != 0 || d > 128 * kMaxVec || (ldx % 4) || (ldg % 4) || (ldgy % 4)) {
+  if (d % 4 != 0 || d > 128 * kMaxVecAll || (ldx % 4) || (ldg % 4) || (ldgy % 4)) {
     set_error("layernorm_bwd: d = %d unsupported (d %% 4 == 0, d <= 1024, aligned pitches)", d);
     return BSRL_ERR_SHAPE;
   }
   if (rows == 0) return BSRL_OK;
   const int blocks = (int)grid_for(rows, 8 * 4);
-  if (gy_f32)
-    ln_bwd_kernel<true><<<blocks, 256, 2 * d * sizeof(float), stream>>>(x, ldx, xmap, gamma, eps, gy, ldgy, gres, gx_out, ldg,
-                                                                       gmap, ggamma, gbeta, rows, d);
-  else
-    ln_bwd_kernel<false><<<blocks, 256, 2 * d * sizeof(float), stream>>>(x, ldx, xmap, gamma, eps, gy, ldgy, gres, gx_out, ldg,
-                                                                        gmap, ggamma, gbeta, rows, d);
+  const size_t smem = 2 * d * sizeof(float);
+#define BSRL_LN_BWD(F32, NV) \
+  ln_bwd_kernel<F32, NV><<<blocks, 256, smem, stream>>>(x, ldx, xmap, gamma, eps, gy, ldgy, gres, gx_out, ldg, gmap, ggamma, gbeta, rows, d)
+  const int nv = (d + 127) / 128;          // float4 per lane actually needed: fewer registers, more rows in flight
+  if (gy_f32) {
+    if (nv <= 2) BSRL_LN_BWD(true, 2); else if (nv <= 4) BSRL_LN_BWD(true, 4); else BSRL_LN_BWD(true, 8);
+  } else {
+    if (nv <= 2) BSRL_LN_BWD(false, 2); else if (nv <= 4) BSRL_LN_BWD(false, 4); else BSRL_LN_BWD(false, 8);
+  }
+#undef BSRL_LN_BWD
   BSRL_LAUNCH_OK("ln_bwd_kernel");
   return BSRL_OK;
 }
@@ -340,14 +388,17 @@ int add_rows32(const float* src, int64_t lds, float* dst, int64_t ldd, RowMap dm
 }
 
 int transpose16(const __half* in, int64_t ldi, RowMap imap, int64_t rows, int cols, __half* out, int64_t ldo,
-                int64_t rows_pad, cudaStream_t stream) {
+                int64_t rows_pad, cudaStream_t stream, float* colsum) {
   if (rows_pad == 0 || cols == 0) return BSRL_OK;
   const int64_t bx = (rows_pad + 63) / 64;
   if (bx > 0x7fffffff) {
     set_error("transpose16: too many rows");
     return BSRL_ERR_SHAPE;
   }
-  transpose16_kernel<<<dim3((unsigned)bx, (cols + 63) / 64), 256, 0, stream>>>(in, ldi, imap, rows, cols, out, ldo, rows_pad);
+  const dim3 grid((unsigned)bx, (cols + 63) / 64);
+  const bool fast = cols % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && rows_pad % 8 == 0 && aligned16(in) && aligned16(out);
+  if (fast) transpose16_kernel<<<grid, 256, 0, stream>>>(in, ldi, imap, rows, cols, out, ldo, rows_pad, colsum);
+  else transpose16_slow_kernel<<<grid, 256, 0, stream>>>(in, ldi, imap, rows, cols, out, ldo, rows_pad, colsum);
   BSRL_LAUNCH_OK("transpose16_kernel");
   return BSRL_OK;
 }

@@ -142,7 +142,7 @@ Layout make_layout(const bsrl_config& c) {
   l.D = c.trunk_dim;
   l.Hh = c.trunk_hidden;
   l.bins = c.value_bins;
-  l.bins_pad = (int)round_up(c.value_bins, 8);
+  l.bins_pad = (int)round_up(c.value_bins, 16);      // multiples of 16: the packed GEMMs stay on the tcgen05 kernel
   l.note_in = kNoteFeat + (c.note_geo ? kGeoFeat : 0);
   l.note_k = note_k(c.note_geo != 0);
   l.k_max = 0;
@@ -152,7 +152,7 @@ Layout make_layout(const bsrl_config& c) {
     l.n_head_cols += c.head_gears[j];
     if (c.head_gears[j] > l.k_max) l.k_max = c.head_gears[j];
   }
-  l.head_cols_pad = (int)round_up(l.n_head_cols, 8);
+  l.head_cols_pad = (int)round_up(l.n_head_cols, 16);
   const int d = l.d;
   Carver cv;
   auto enc = [&](int in, int kpad) {

@@ -100,7 +100,7 @@ GLayout make_glayout(const bsrl_gconfig& c) {
   l.body_k = (int)round_up(c.body_dim, kBodyPadTo);
   l.obj_k = 64;
   l.n_cols = kActHeads * c.n_gears + 1;
-  l.cols_pad = (int)round_up(l.n_cols, 8);
+  l.cols_pad = (int)round_up(l.n_cols, 16);
   l.obs_dim = c.body_dim + c.n_obj * c.obj_dim + c.n_obj;
   Carve cv;
   const int d = l.d;

@@ -17,6 +17,7 @@
 // caller's loss scale; the residual-stream gradient, LayerNorm arithmetic and parameter gradients are fp32.
 #include <string.h>
 
+#include <initializer_list>
 #include <map>
 #include <string>
 
@@ -33,7 +34,7 @@ int cast_rows16(const float* in, int64_t ldi, RowMap imap, float scale, __half* 
 int add_rows32(const float* src, int64_t lds, float* dst, int64_t ldd, RowMap dmap, int64_t rows, int n, int accumulate,
                cudaStream_t stream);
 int transpose16(const __half* in, int64_t ldi, RowMap imap, int64_t rows, int cols, __half* out, int64_t ldo,
-                int64_t rows_pad, cudaStream_t stream);
+                int64_t rows_pad, cudaStream_t stream, float* colsum = nullptr);
 int head_tail_bwd(const HeadTailArgs& a, const float* g_logprob, const float* g_entropy, const float* g_value,
                   const float* g_vlogits, const float* g_logits, float scale, __half* g_raw, int ldg_raw, __half* g_vraw,
                   int ldg_v, cudaStream_t stream);
@@ -104,6 +105,7 @@ struct BwdLayout {
   int64_t h16, qkv16, att16, x1, h2, hid, gx, g32, gA, gB, tA, tX, wT;
   // readout-side rows (B of them)
   int64_t xt, u16, r16, xt2, z16, hv16, attc16, m1, m2, gz32, graw16, gvraw16, gsmall32, gsmall16, scratch_w;
+  int64_t bias_scratch, heads_scratch;
   int64_t bytes;
   int64_t Rpad;
   int wmax, ld_graw, ld_gv;
@@ -154,6 +156,8 @@ BwdLayout make_bwd(const Layout& l, int64_t B) {
   w.gsmall32 = cv.take(B * (int64_t)wide * 4);
   w.gsmall16 = cv.take(B * (int64_t)wide * 2);
   w.scratch_w = cv.take((int64_t)d * 64 * 4);
+  w.bias_scratch = cv.take((int64_t)wide * 4);
+  w.heads_scratch = cv.take((int64_t)l.head_cols_pad * D * 4);
   w.bytes = cv.off;
   return w;
 }
@@ -187,7 +191,20 @@ struct Bwd {
     return linear(a, st);
   }
   // transposed copies for the weight-gradient products: rows of `m` (M of them, through map) become columns
-  int to_tA(const __half* m, int64_t ld, RowMap map, int64_t M, int N) { return transpose16(m, ld, map, M, N, S<__half>(w.tA), pad64(M), pad64(M), st); }
+  int to_tA(const __half* m, int64_t ld, RowMap map, int64_t M, int N, float* colsum = nullptr) {   // colsum: bias gradient on the way
+    return transpose16(m, ld, map, M, N, S<__half>(w.tA), pad64(M), pad64(M), st, colsum);
+  }
+  // transposed copy of a gradient matrix whose column ranges are the bias gradients of several parameters
+  // (stacked q|k|v, the packed heads): the sums land in a scratch vector and are copied out slice by slice
+  struct BiasSlice { float* dst; int col0, n; };
+  int to_tA_slices(const __half* g, int64_t ld, int64_t M, int N, std::initializer_list<BiasSlice> slices) {
+    float* scratch = S<float>(w.bias_scratch);
+    BSRL_CUDA_OK(cudaMemsetAsync(scratch, 0, (size_t)N * 4, st));
+    BSRL_TRY(to_tA(g, ld, identity_map(), M, N, scratch));
+    for (const BiasSlice& b : slices)
+      if (b.dst) BSRL_CUDA_OK(cudaMemcpyAsync(b.dst, scratch + b.col0, (size_t)b.n * 4, cudaMemcpyDeviceToDevice, st));
+    return BSRL_OK;
+  }
   int to_tX(const __half* m, int64_t ld, RowMap map, int64_t M, int K) { return transpose16(m, ld, map, M, K, S<__half>(w.tX), pad64(M), pad64(M), st); }
   // gW (n, K) f32 (+)= tA[row0 : row0 + n, :] . tX^T, both (., pad64(M)); gW must be zero on entry
   int wgrad_t(int row0, int n, int K, int64_t M, float* gW, int ldgw) {
@@ -205,11 +222,9 @@ struct Bwd {
   }
   // one Linear: gW += g^T x, gb += colsum(g); x through xmap
   int wgrad(const __half* g, int64_t ldg, int64_t M, int N, const __half* x, int64_t ldx, RowMap xmap, int K, const std::string& name) {
-    BSRL_TRY(to_tA(g, ldg, identity_map(), M, N));
+    BSRL_TRY(to_tA(g, ldg, identity_map(), M, N, G(name + ".bias")));
     BSRL_TRY(to_tX(x, ldx, xmap, M, K));
-    BSRL_TRY(wgrad_t(0, N, K, M, G(name + ".weight"), K));
-    if (float* gb = G(name + ".bias")) BSRL_TRY(colsum16(g, ldg, M, N, gb, st));
-    return BSRL_OK;
+    return wgrad_t(0, N, K, M, G(name + ".weight"), K);
   }
   int cast16(const float* in, int64_t ldi, RowMap map, __half* out, int64_t ldo, int64_t rows, int n) {
     return cast_rows16(in, ldi, map, 1.f, out, ldo, rows, n, st);
@@ -310,10 +325,9 @@ struct Bwd {
     BSRL_TRY(linear(linear_args(m1, D, c.W(l.critic_m1), D, c.Bv(l.critic_m1), m2, D, 0, 1, B, D, D), st));
 
     // ---- critic MLP
-    BSRL_TRY(to_tA(gvraw, w.ld_gv, ident, B, l.bins));
+    BSRL_TRY(to_tA_slices(gvraw, w.ld_gv, B, l.bins_pad, {{G("critic_mlp.4.bias"), 0, l.bins}}));
     BSRL_TRY(to_tX(m2, D, ident, B, D));
     BSRL_TRY(wgrad_t(0, l.bins, D, B, G("critic_mlp.4.weight"), D));
-    BSRL_TRY(colsum16(gvraw, w.ld_gv, B, l.bins, G("critic_mlp.4.bias"), st));
     BSRL_TRY(dgrad(gvraw, w.ld_gv, B, c.W(l.critic_m2), l.critic_m2.pitch, l.bins, D, gs16, D, false));
     BSRL_TRY(relu_mask16(gs16, D, m2, D, B, D, st));
     BSRL_TRY(wgrad(gs16, D, B, D, m1, D, ident, D, "critic_mlp.2"));
@@ -328,11 +342,9 @@ struct Bwd {
     __half* gq_c = gs16;                                                                          // (B, d)
     BSRL_TRY(attention29_bwd(qkv, 3 * d, sv.key_bias, B, d, l.H, 2, 1, gA, d, gq_c, d, gB, 2 * d, gB + d, 2 * d, st));
     BSRL_TRY(to_tX(hv, d, ident, R, d));
-    BSRL_TRY(to_tA(gB, 2 * d, ident, R, 2 * d));
+    BSRL_TRY(to_tA_slices(gB, 2 * d, R, 2 * d, {{G("critic_k.bias"), 0, d}, {G("critic_v.bias"), d, d}}));
     BSRL_TRY(wgrad_t(0, d, d, R, G("critic_k.weight"), d));
     BSRL_TRY(wgrad_t(d, d, d, R, G("critic_v.weight"), d));
-    BSRL_TRY(colsum16(gB, 2 * d, R, d, G("critic_k.bias"), st));
-    BSRL_TRY(colsum16(gB + d, 2 * d, R, d, G("critic_v.bias"), st));
     BSRL_TRY(wgrad(gq_c, d, B, d, hv, d, torso_rows, d, "critic_q"));
     BSRL_TRY(dgrad(gB, 2 * d, R, c.W(l.critic_kv), l.critic_kv.pitch, 2 * d, d, g32, d, true));    // g_hv from k, v
     BSRL_TRY(dgrad(gq_c, d, B, c.W(l.critic_q), l.critic_q.pitch, d, d, gs32, d, true));           // ... and from q, torso rows
@@ -340,12 +352,22 @@ struct Bwd {
     BSRL_TRY(ln_bwd(x_last, d, ident, l.critic_ln, "critic_ln", g32, true, d, nullptr, gx, d, ident, R, d));   // gx = critic's share
 
     // ---- action heads and trunk
-    BSRL_TRY(to_tA(graw, w.ld_graw, ident, B, l.n_head_cols));
-    BSRL_TRY(to_tX(z16 + d, ldz, ident, B, D));
-    for (int j = 0; j < kActHeads; ++j) {
-      const std::string hn = "heads." + std::to_string(j);
-      BSRL_TRY(wgrad_t(l.head_first[j], c.cfg->head_gears[j], D, B, G(hn + ".weight"), D));
-      BSRL_TRY(colsum16(graw + l.head_first[j], w.ld_graw, B, c.cfg->head_gears[j], G(hn + ".bias"), st));
+    {   // all 29 heads as ONE stacked product into a scratch matrix, then row slices to each head's gradient
+      float* hw = S<float>(w.heads_scratch);
+      float* hb = S<float>(w.bias_scratch);
+      BSRL_CUDA_OK(cudaMemsetAsync(hw, 0, (size_t)l.head_cols_pad * D * 4, st));
+      BSRL_CUDA_OK(cudaMemsetAsync(hb, 0, (size_t)l.head_cols_pad * 4, st));
+      BSRL_TRY(to_tA(graw, w.ld_graw, ident, B, l.head_cols_pad, hb));
+      BSRL_TRY(to_tX(z16 + d, ldz, ident, B, D));
+      BSRL_TRY(wgrad_t(0, l.head_cols_pad, D, B, hw, D));
+      for (int j = 0; j < kActHeads; ++j) {
+        const std::string hn = "heads." + std::to_string(j);
+        const int k = c.cfg->head_gears[j];
+        if (float* gw = G(hn + ".weight"))
+          BSRL_CUDA_OK(cudaMemcpyAsync(gw, hw + (int64_t)l.head_first[j] * D, (size_t)k * D * 4, cudaMemcpyDeviceToDevice, st));
+        if (float* gb = G(hn + ".bias"))
+          BSRL_CUDA_OK(cudaMemcpyAsync(gb, hb + l.head_first[j], (size_t)k * 4, cudaMemcpyDeviceToDevice, st));
+      }
     }
     BSRL_TRY(dgrad(graw, w.ld_graw, B, c.W(l.heads), l.heads.pitch, l.n_head_cols, D, gs32, D, true));   // g_h from the heads
     BSRL_TRY(add_rows32(gz32 + d, ldz, gs32, D, ident, B, D, 1, st));                                     // + the critic's
@@ -382,11 +404,9 @@ struct Bwd {
       __half* gq = gs16;                               // (Rl, d)
       BSRL_TRY(attention29_bwd(qkv, 3 * d, sv.key_bias, B, d, l.H, 0, kLead, gA, d, gq, d, gB, 2 * d, gB + d, 2 * d, st));
       BSRL_TRY(to_tX(h16, d, ident, R, d));
-      BSRL_TRY(to_tA(gB, 2 * d, ident, R, 2 * d));
+      BSRL_TRY(to_tA_slices(gB, 2 * d, R, 2 * d, {{G(p + ".k_proj.bias"), 0, d}, {G(p + ".v_proj.bias"), d, d}}));
       BSRL_TRY(wgrad_t(0, d, d, R, G(p + ".k_proj.weight"), d));
       BSRL_TRY(wgrad_t(d, d, d, R, G(p + ".v_proj.weight"), d));
-      BSRL_TRY(colsum16(gB, 2 * d, R, d, G(p + ".k_proj.bias"), st));
-      BSRL_TRY(colsum16(gB + d, 2 * d, R, d, G(p + ".v_proj.bias"), st));
       BSRL_TRY(wgrad(gq, d, Rl, d, h16, d, lead_rows, d, p + ".q_proj"));
       BSRL_TRY(dgrad(gB, 2 * d, R, c.W(b.qkv, d), b.qkv.pitch, 2 * d, d, g32, d, true));           // g_h from k, v
       float* gq32 = S<float>(w.x1) + 2 * Rl * d;        // (Rl, d) f32
@@ -408,12 +428,10 @@ struct Bwd {
       BSRL_TRY(tail_bwd(i, R, gx, gx, x1, h2, hid, att, gA));                                       // gx: g(x_{i+1}) -> g(x1)
       BSRL_TRY(attention29_bwd(qkv, 3 * d, sv.key_bias, B, d, l.H, 0, kT, gA, d, gB, 3 * d, gB + d, 3 * d, gB + 2 * d, 3 * d, st));
       BSRL_TRY(to_tX(h16, d, ident, R, d));
-      BSRL_TRY(to_tA(gB, 3 * d, ident, R, 3 * d));
+      BSRL_TRY(to_tA_slices(gB, 3 * d, R, 3 * d, {{G(p + ".q_proj.bias"), 0, d}, {G(p + ".k_proj.bias"), d, d},
+                                                 {G(p + ".v_proj.bias"), 2 * d, d}}));
       const char* names[3] = {".q_proj", ".k_proj", ".v_proj"};
-      for (int s = 0; s < 3; ++s) {
-        BSRL_TRY(wgrad_t(s * d, d, d, R, G(p + names[s] + ".weight"), d));
-        BSRL_TRY(colsum16(gB + s * d, 3 * d, R, d, G(p + names[s] + ".bias"), st));
-      }
+      for (int s = 0; s < 3; ++s) BSRL_TRY(wgrad_t(s * d, d, d, R, G(p + names[s] + ".weight"), d));
       BSRL_TRY(dgrad(gB, 3 * d, R, c.W(b.qkv), b.qkv.pitch, 3 * d, d, g32, d, true));
       BSRL_TRY(ln_bwd(x_in, d, ident, b.ln_attn, p + ".ln_attn", g32, true, d, gx, gx, d, ident, R, d));     // gx: g(x_i)
     }
@@ -435,12 +453,11 @@ struct Bwd {
       // first layer: the K-padded (d, 64) product goes to a scratch matrix, its first `in` columns are the gradient
       float* sw = S<float>(w.scratch_w);
       BSRL_CUDA_OK(cudaMemsetAsync(sw, 0, (size_t)d * 64 * 4, st));
-      BSRL_TRY(to_tA(gA, d, ident, e.rows, d));
+      BSRL_TRY(to_tA(gA, d, ident, e.rows, d, G(std::string(e.name) + ".0.bias")));
       BSRL_TRY(to_tX(feat, 64, ident, e.rows, 64));
       BSRL_TRY(wgrad_t(0, d, 64, e.rows, sw, 64));
       if (float* gw = G(std::string(e.name) + ".0.weight"))
         BSRL_CUDA_OK(cudaMemcpy2DAsync(gw, (size_t)e.in * 4, sw, 64 * 4, (size_t)e.in * 4, d, cudaMemcpyDeviceToDevice, st));
-      BSRL_TRY(colsum16(gA, d, e.rows, d, G(std::string(e.name) + ".0.bias"), st));
     }
     return BSRL_OK;
   }
@@ -532,14 +549,14 @@ int bsrl_linear_bwd(const void* g_f16, const void* x_f16, const void* w_f16, int
   __half* wT = at<__half>(scratch, round_up((int64_t)n * mp * 2, 256) + round_up((int64_t)k * mp * 2, 256));
   const __half* g = static_cast<const __half*>(g_f16);
   if (g_weight) {     // g_weight (n, k) += g^T x as a split-K product of the transposed operands; zero it first
-    BSRL_TRY(transpose16(g, n, identity_map(), m, n, tA, mp, mp, st));
+    BSRL_TRY(transpose16(g, n, identity_map(), m, n, tA, mp, mp, st, g_bias));    // bias gradient on the way
     BSRL_TRY(transpose16(static_cast<const __half*>(x_f16), k, identity_map(), m, k, tX, mp, mp, st));
     LinearArgs a = linear_args(tA, (int)mp, tX, (int)mp, nullptr, g_weight, k, 1, 0, n, k, (int)mp);
     const int64_t tiles = ((n + 127) / 128) * ((k + 255) / 256);
     a.k_splits = (int)(sm_count() / tiles) < 1 ? 1 : (int)(sm_count() / tiles);
     BSRL_TRY(linear(a, st));
   }
-  if (g_bias) BSRL_TRY(colsum16(g, n, m, n, g_bias, st));
+  if (g_bias && !g_weight) BSRL_TRY(colsum16(g, n, m, n, g_bias, st));
   if (g_x) {          // g_x (m, k) = g w
     if (!w_f16) {
       set_error("linear_bwd: the input gradient needs the weight");

@@ -42,6 +42,14 @@ WORKLOADS = {
     # the reference's production shape (d 192, 6 blocks, 4 heads of 48, trunk 384, note-geo; python/train_batch.py:521-525)
     "recipe": ("recipe", 32768, 5, False, False, 5),
 }
+# the same BASELINE configurations in the single-body-token layout (T = 1 + n_obj tokens, GELU FFN, body-token
+# readout; no counterpart in the reference): name -> (oracle config, envs per GPU, weight seed, xavier, padded, obs seed)
+BODY_WORKLOADS = {
+    "g_cfg1": ("cfg1", 1024, 0, False, False, 0),
+    "g_cfg2": ("cfg2", 65536, 1, True, False, 1),
+    "g_cfg3": ("cfg2", 131072, 1, True, True, 2),
+    "g_cfg4": ("cfg4", 32768, 3, False, False, 3),
+}
 
 
 def read_peaks():
@@ -155,14 +163,17 @@ def describe(cfg):
             f"trunk={cfg.trunk_dim} T=29 lead=5 gears={cfg.n_gears}")
 
 
-def reference_gpu_leg(workload, timeout_s=420):
+def reference_gpu_leg(workload, timeout_s=420, update_envs=0):
     """The reference's own fp16 GPU stream on this GPU, in a process of its own (none of this library's
     kernels loaded there): ``baseline/ref_gpu_bench.py`` on the tree ``baseline/setup_ref.py`` staged."""
     script = ROOT / "baseline" / "ref_gpu_bench.py"
     if not (ROOT / "baseline" / "_ref" / "python" / "policy.py").exists():
         return {"unavailable": "baseline/_ref is not staged on this machine"}
     try:
-        r = subprocess.run([sys.executable, str(script), "--workload", workload], capture_output=True, text=True,
+        cmd = [sys.executable, str(script), "--workload", workload]
+        if update_envs:
+            cmd += ["--update", "--envs", str(update_envs)]
+        r = subprocess.run(cmd, capture_output=True, text=True,
                            timeout=timeout_s, env=dict(os.environ, PYTHONDONTWRITEBYTECODE="1"))
     except subprocess.TimeoutExpired:
         return {"unavailable": f"reference GPU stream did not finish within {timeout_s} s"}
@@ -320,6 +331,34 @@ def run_ours(args, rank, world, local_rank):
                      "outputs": "logprob, entropy, per-head entropy, value"}
         del obs5, act5
 
+    # ---- the PPO update's recompute with gradients: forward in grad mode + backward to every parameter, on a
+    # 16,384-env minibatch (python/train_batch.py:2669-2741; the reference's bench_policy_update.py protocol) ----
+    update = None
+    if args.workload == "cfg2" and not args.envs and not args.no_recompute:
+        mb = 16384
+        obs_u = po.make_obs(mb, oseed + 1000 * rank + 11).to(dev)
+        act_u = po.make_actions(mb, cfg, 5 + rank).to(torch.uint8).to(dev)
+        w_u = {k: v.to(dev) for k, v in po.make_upstream(mb, cfg, 6 + rank).items()}
+
+        def update_step():
+            with torch.enable_grad():
+                _, lp, ent, val = policy.get_action_and_value(obs_u, act_u)
+                loss = (w_u["logprob"] * lp).sum() + (w_u["entropy"] * ent).sum() + (w_u["value"] * val).sum() \
+                    + (w_u["value_logits"] * policy._value_logits).sum()
+                loss.backward()
+            for p_ in policy.parameters():
+                p_.grad = None
+        for _ in range(3):
+            update_step()
+        ms_u = timed_ms(update_step, max(3, args.steps // 2))
+        n_u = max(3, args.steps // 2)
+        update = {"workload": f"cfg2 model, {mb}-env minibatch: get_action_and_value(obs, uint8 actions) in grad mode + "
+                              "backward to every parameter",
+                  "value": world * mb * n_u / (ms_u * 1e-3), "unit": "env-updates/s", "ms_per_step": ms_u / n_u,
+                  "envs_per_gpu": mb, "flops_per_env": 6 * po.mac_per_env(cfg),
+                  "tflops": 6.0 * po.mac_per_env(cfg) * mb * n_u / (ms_u * 1e-3) / 1e12}
+        del obs_u, act_u
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -366,7 +405,10 @@ def run_ours(args, rank, world, local_rank):
         if not args.no_ref_gpu:
             del policy, obs
             torch.cuda.empty_cache()
-            reference_gpu = reference_gpu_leg(args.workload if args.workload in ("cfg1", "cfg2", "cfg4", "recipe") else "cfg2")
+            ref_wl = args.workload if args.workload in ("cfg1", "cfg2", "cfg4", "recipe") else "cfg2"
+            reference_gpu = reference_gpu_leg(ref_wl)
+            if update and "unavailable" not in reference_gpu:
+                reference_gpu["update"] = reference_gpu_leg(ref_wl, update_envs=16384)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -387,6 +429,8 @@ def run_ours(args, rank, world, local_rank):
     }
     if recompute:
         line["cfg5_recompute"] = recompute
+    if update:
+        line["ppo_update"] = update
     if reference_gpu is not None:
         line["reference_gpu"] = reference_gpu
     print(json.dumps(line), flush=True)
@@ -403,6 +447,70 @@ def read_traffic_ratios():
         return json.loads(p.read_text())
     except (OSError, ValueError):
         return {}
+
+
+def run_body(args, rank, world, local_rank):
+    """The single-body-token layout: device-resident forward_stacked, graph replays; one JSON line."""
+    import torch.distributed as dist
+    from beatsaberrl_b200.body_policy import BodyObjectPolicy
+    from oracle import body_policy_oracle as bo
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    name, envs, wseed, xavier, padded, oseed = BODY_WORKLOADS[args.workload]
+    envs = args.envs or envs
+    cfg = bo.named_config(name)
+    sd = bo.build_state_dict(cfg, wseed, xavier=xavier)
+    policy = BodyObjectPolicy(**cfg.kwargs())
+    policy.load_state_dict(sd)
+    policy = policy.to(dev)
+    policy.flatten_fp16()
+    obs = bo.make_obs(envs, cfg, oseed + 1000 * rank, padded=padded).to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        policy.forward_stacked(obs)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        policy.forward_stacked(obs)
+    for _ in range(3):
+        graph.replay()
+    sampler = ClockSampler(local_rank)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        peaks = read_peaks()
+        mac = bo.mac_per_env(cfg)
+        value = world * envs * args.steps / (ms * 1e-3)
+        tfl = 2.0 * mac * (value / world) / 1e12
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: single-body-token layout d={cfg.embed} L={cfg.n_blocks} H={cfg.n_heads} "
+                                   f"ffn={cfg.ffn_mult * cfg.embed} GELU T={cfg.tokens} gears={cfg.n_gears}, {envs} envs per GPU",
+                       "timing": "CUDA-graph replays of one captured forward", "mac_per_env": mac},
+            "forward_tflops": tfl, "forward_frac_of_burst": tfl / peaks["tflops_burst"], "clocks": clocks}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_kernel(args):
@@ -437,6 +545,50 @@ def run_kernel(args):
         nbytes = envs * 29 * d * 4
         run = lambda: nat.check(nat.lib.bsrl_qkv_attention(h.data_ptr(), w.data_ptr(), bias.data_ptr(), kb.data_ptr(),
                                                            envs, d, d // 32, 0, 29, out.data_ptr(), st))
+    elif args.kernel == "layernorm":
+        x = rnd(rows, d)
+        lg, lb = torch.ones(d).cuda(), torch.zeros(d).cuda()
+        y = torch.empty(rows, d, dtype=torch.float16, device="cuda")
+        flops, nbytes = 8.0 * rows * d, rows * d * 6
+        run = lambda: nat.check(nat.lib.bsrl_layernorm(x.data_ptr(), lg.data_ptr(), lb.data_ptr(), 1e-5, rows, d, y.data_ptr(), d, st))
+    elif args.kernel == "attention":
+        envs = rows // 29
+        qkv = rnd(envs * 29, 3 * d).half()
+        kb = torch.zeros(envs, 29).cuda()
+        out = torch.empty(envs * 29, d, dtype=torch.float16, device="cuda")
+        flops, nbytes = 4.0 * envs * 29 * 29 * d, envs * 29 * d * 8
+        run = lambda: nat.check(nat.lib.bsrl_attention(qkv.data_ptr(), kb.data_ptr(), envs, d, d // 32, 0, 29, out.data_ptr(), st))
+    elif args.kernel in ("embed", "head_tail"):
+        import ctypes as C
+        from beatsaberrl_b200.policy import NotePolicy
+        from oracle import policy_oracle as po
+        cfg = po.named_config("cfg2")
+        pol = NotePolicy(**cfg.ref_kwargs()).cuda()
+        pol.flatten_fp16()
+        envs = rows // 29
+        c = pol._cfg
+        if args.kernel == "embed":      # tokenizer gather + fused encoders (x only)
+            obs = po.make_obs(envs, 1).cuda()
+            x = torch.empty(envs * 29, d, device="cuda")
+            kbias = torch.empty(envs, 29, device="cuda")
+            n_ws = nat.lib.bsrl_workspace_bytes(C.byref(c), envs)
+            ws = torch.empty(n_ws, dtype=torch.uint8, device="cuda")
+            flops = 2.0 * envs * 29 * d * (64 + d)
+            nbytes = envs * (630 * 4 + 29 * 128 * 2 + 29 * d * 4)
+            run = lambda: nat.check(nat.lib.bsrl_embed(C.byref(c), pol._arena.data_ptr(), obs.data_ptr(), nat.F32, envs, x.data_ptr(),
+                                                       kbias.data_ptr(), ws.data_ptr(), n_ws, st))
+        else:
+            pad, bpad = C.c_int32(), C.c_int32()
+            nat.check(nat.lib.bsrl_head_layout(C.byref(c), C.byref(pad), C.byref(bpad), None))
+            raw, vraw = rnd(envs, pad.value), rnd(envs, bpad.value)
+            act = po.make_actions(envs, cfg, 4).to(torch.int32).cuda()
+            outs = [torch.empty(envs, 29, cfg.k_max, device="cuda"), torch.empty(envs, device="cuda"), torch.empty(envs, device="cuda"),
+                    torch.empty(envs, 29, device="cuda"), torch.empty(envs, device="cuda")]
+            flops = 60.0 * envs * 29 * cfg.k_max
+            nbytes = envs * 4 * (pad.value + bpad.value + 29 * cfg.k_max + 29 + 3)
+            run = lambda: nat.check(nat.lib.bsrl_head_tail(C.byref(c), raw.data_ptr(), vraw.data_ptr(), envs, act.data_ptr(), nat.I32,
+                                                           outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), outs[3].data_ptr(),
+                                                           outs[4].data_ptr(), st))
     else:
         n, k = args.cols or 3 * d, d
         a, w, bias = rnd(rows, k).half(), rnd(n, k, scale=k ** -0.5).half(), rnd(n)
@@ -466,13 +618,13 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + sorted(BODY_WORKLOADS))
     ap.add_argument("--envs", type=int, default=0, help="envs per GPU (default: the workload's)")
     ap.add_argument("--cpu-sample", type=int, default=0, help="envs in the CPU sample")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--no-recompute", action="store_true", help="skip the cfg5 PPO-recompute sub-record")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip the reference's GPU stream (1-GPU runs)")
-    ap.add_argument("--kernel", default="", choices=("", "block_tail", "attn_block", "linear"),
+    ap.add_argument("--kernel", default="", choices=("", "block_tail", "attn_block", "linear", "layernorm", "attention", "embed", "head_tail"),
                     help="time one kernel alone on --rows token rows instead of the whole forward")
     ap.add_argument("--rows", type=int, default=237568)
     ap.add_argument("--embed", type=int, default=256)
@@ -482,6 +634,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
+        if args.workload in BODY_WORKLOADS:
+            raise SystemExit("--impl reference: the single-body-token layout has no counterpart in the reference")
         run_reference(args, rank, world)
         return
     if not torch.cuda.is_available():
@@ -489,6 +643,9 @@ def main():
     with torch.no_grad():          # the rollout / evaluation forward, as the reference's callers run it
         if args.kernel:
             run_kernel(args)
+            return
+        if args.workload in BODY_WORKLOADS:
+            run_body(args, rank, world, local_rank)
             return
         run_ours(args, rank, world, local_rank)
 
