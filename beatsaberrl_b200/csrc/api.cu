@@ -74,10 +74,17 @@ void use_process_engine() { g_call_engine = g_engine.load(std::memory_order_rela
 int process_engine() { return g_engine.load(std::memory_order_relaxed); }
 int linear(const LinearArgs& p, cudaStream_t st) {
   return timed(st, 2.0 * p.M * p.N * p.K, linear_bytes(p), [&] {
+    if (p.a_mn || p.w_mn) {      // operands with the contraction index as rows: the tcgen05 engine only
+      if (g_call_engine == 0 && linear_tc5_ok(p)) return linear_tc5(p, st);
+      set_error("linear: row-contraction operands need the tcgen05 engine and M, N multiples of 64 (m=%lld n=%d k=%d)",
+                (long long)p.M, p.N, p.K);
+      return (int)BSRL_ERR_UNSUPPORTED;
+    }
     if (g_call_engine == 0 && p.M >= 128 && linear_tc5_ok(p)) return linear_tc5(p, st);
     return linear_mma(p, st);
   });
 }
+bool linear_rows_ok(const LinearArgs& p) { return g_call_engine == 0 && linear_tc5_ok(p); }
 int layernorm(const float* x, int64_t ldx, RowMap xmap, const float* g, const float* b, float eps,
               int64_t rows, int d, __half* y, int64_t ldy, cudaStream_t st) {
   int keep = g_stage;

@@ -67,6 +67,8 @@ int process_engine();
 
 // stage-labelled launch wrappers (timed when the calling thread has the profiler on)
 int linear(const LinearArgs& p, cudaStream_t st);
+// a product with row-contraction operands (a_mn / w_mn) can run as asked (engine and shape)
+bool linear_rows_ok(const LinearArgs& p);
 int layernorm(const float* x, int64_t ldx, RowMap xmap, const float* g, const float* b, float eps, int64_t rows, int d,
               __half* y, int64_t ldy, cudaStream_t st);
 int attention(const __half* qkv, int ld, const float* kb, int64_t B, int d, int H, int q0, int nq, __half* out, int ldo,

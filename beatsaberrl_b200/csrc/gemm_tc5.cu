@@ -60,7 +60,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   uint8_t* staging = smem_raw + (tiles_base - raw) + STAGES * STAGE_BYTES;
   Shared* sh = reinterpret_cast<Shared*>(staging + EPI_WARPS * STG_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int k_blocks = p.K / BK;
+  const int k_blocks = (p.K + BK - 1) / BK;
   const int splits = p.k_splits > 1 ? p.k_splits : 1;
   const int kps = (k_blocks + splits - 1) / splits;          // k-blocks per split
   const int64_t n_tile_work = (int64_t)m_tiles * n_tiles;
@@ -107,8 +107,10 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           const uint32_t bar = smem_u32(&sh->full[s]);
           mbar_expect_tx(bar, STAGE_BYTES);
           const uint32_t dst = tiles_base + s * STAGE_BYTES;
-          tma_load_2d(dst, &tm_a, kb * BK, m0, bar);
-          tma_load_2d(dst + A_BYTES, &tm_w, kb * BK, n0, bar);
+          if (p.a_mn) tma_load_3d(dst, &tm_a, 0, kb * BK, m0 / 64, bar);
+          else tma_load_2d(dst, &tm_a, kb * BK, m0, bar);
+          if (p.w_mn) tma_load_3d(dst + A_BYTES, &tm_w, 0, kb * BK, n0 / 64, bar);
+          else tma_load_2d(dst + A_BYTES, &tm_w, kb * BK, n0, bar);
         }
       }
       // the loads still in flight must land before this CTA may exit (also when a wait above
@@ -133,7 +135,10 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const int n0 = (int)(t % n_tiles) * BN;
         int n_cols = p.N - n0;
         if (n_cols > BN) n_cols = BN;
-        const uint32_t idesc = idesc_f16(BM, n_cols);
+        const uint32_t idesc = idesc_f16(BM, n_cols, p.a_mn, p.w_mn);
+        // 16-byte units a K step of 16 advances an operand's start address by: 32 bytes along a K-major row,
+        // two 8-row groups of an MN-major tile
+        const uint32_t a_step = p.a_mn ? 128u : 2u, w_step = p.w_mn ? 128u : 2u;
         const int buf = tile_i & 1;
         const uint32_t acc_ph = (tile_i >> 1) & 1;
         if (!mbar_wait(smem_u32(&sh->tmem_empty[buf]), acc_ph ^ 1, abort)) { give_up(sh, status, 3); ok = false; break; }
@@ -145,11 +150,11 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           if (!mbar_wait(smem_u32(&sh->full[s]), ph, abort)) { give_up(sh, status, 4); ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = tiles_base + s * STAGE_BYTES;
-          const uint64_t a_desc = smem_desc_sw128(a_addr);
-          const uint64_t w_desc = smem_desc_sw128(a_addr + A_BYTES);
+          const uint64_t a_desc = p.a_mn ? smem_desc_mn_sw128(a_addr, BK * 128) : smem_desc_sw128(a_addr);
+          const uint64_t w_desc = p.w_mn ? smem_desc_mn_sw128(a_addr + A_BYTES, BK * 128) : smem_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)   // +32 bytes (2 x 16-byte units) per K step of 16
-            mma_f16_ss(d_tmem, a_desc + 2 * k, w_desc + 2 * k, idesc, (kb != kb0 || k) ? 1u : 0u);
+          for (int k = 0; k < BK / 16; ++k)
+            mma_f16_ss(d_tmem, a_desc + a_step * k, w_desc + w_step * k, idesc, (kb != kb0 || k) ? 1u : 0u);
           tc_commit(smem_u32(&sh->empty[s]));
         }
         if (ok) tc_commit(smem_u32(&sh->tmem_full[buf]));
@@ -404,9 +409,37 @@ bool make_tmap_env3d(CUtensorMap* map, const void* base, int64_t n_envs, int tok
   return true;
 }
 
+// (k_rows, cols) fp16 row-major matrix seen as {64 columns, k rows, cols / 64 blocks}: one load of a
+// {64, box_k, box_blocks} box brings box_blocks tiles of box_k x 128 bytes, each with the 128-byte swizzle
+static bool make_tmap_mn(CUtensorMap* map, const void* base, int64_t k_rows, int64_t cols, int64_t ld_elems, int box_k,
+                         int box_blocks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return false;
+  }
+  cuuint64_t dims[3] = {64, (cuuint64_t)k_rows, (cuuint64_t)(cols / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld_elems * 2, 128};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_k, (cuuint32_t)box_blocks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed (%d) for a (%lld x %lld) fp16 matrix read in 64-column blocks, ld %lld", (int)r,
+              (long long)k_rows, (long long)cols, (long long)ld_elems);
+    return false;
+  }
+  return true;
+}
+
 bool linear_tc5_ok(const LinearArgs& p) {
   if (!p.A || !p.W || !p.C || p.M < 1) return false;
-  if (p.K % BK != 0 || p.N % 16 != 0 || p.N < 16) return false;
+  if (p.N % 16 != 0 || p.N < 16 || p.K < 1) return false;
+  if (!p.a_mn && !p.w_mn && p.K % BK != 0) return false;
+  if (p.K % 8 != 0) return false;                                // columns past K of a K-major operand read as zero
+  if (p.a_mn && (p.M % 64 != 0 || p.lda < p.M)) return false;
+  if (p.w_mn && (p.N % 64 != 0 || p.ldw < p.N)) return false;
   if (p.amap.group != 0x7fffffff || p.amap.first != 0) return false;      // TMA reads A rows in order
   if (!aligned16(p.A) || !aligned16(p.W) || !aligned16(p.C) || (p.lda % 8) || (p.ldw % 8)) return false;
   if (p.ldc % (p.out_f32 ? 4 : 8)) return false;
@@ -419,7 +452,7 @@ bool linear_tc5_ok(const LinearArgs& p) {
 int linear_tc5(const LinearArgs& p_in, cudaStream_t stream) {
   LinearArgs p = p_in;
   if (p.k_splits > 1) {   // no piece may be empty: an empty piece would add an unwritten accumulator
-    const int k_blocks = p.K / BK;
+    const int k_blocks = (p.K + BK - 1) / BK;
     if (p.k_splits > k_blocks) p.k_splits = k_blocks;
     if (p.k_splits > 1) {
       const int kps = (k_blocks + p.k_splits - 1) / p.k_splits;
@@ -433,8 +466,10 @@ int linear_tc5(const LinearArgs& p_in, cudaStream_t stream) {
   int* status = device_status_ptr();
   if (!status) return BSRL_ERR_CUDA;
   CUtensorMap tm_a, tm_w;
-  if (!make_tmap_f16(&tm_a, p.A, p.M, p.K, p.lda, BM)) return BSRL_ERR_CUDA;
-  if (!make_tmap_f16(&tm_w, p.W, p.N, p.K, p.ldw, BN)) return BSRL_ERR_CUDA;
+  if (p.a_mn ? !make_tmap_mn(&tm_a, p.A, p.K, p.M, p.lda, BK, BM / 64) : !make_tmap_f16(&tm_a, p.A, p.M, p.K, p.lda, BM))
+    return BSRL_ERR_CUDA;
+  if (p.w_mn ? !make_tmap_mn(&tm_w, p.W, p.K, p.N, p.ldw, BK, BN / 64) : !make_tmap_f16(&tm_w, p.W, p.N, p.K, p.ldw, BN))
+    return BSRL_ERR_CUDA;
   // dense output rows without a residual leave as TMA stores of the epilogue's 32 x 128-byte staging blocks
   const bool tma_c = !p.R && p.k_splits <= 1 && p.cmap.group == 0x7fffffff && p.cmap.stride == 0 && p.cmap.first == 0 &&
                      p.M <= 0x7fffff00;

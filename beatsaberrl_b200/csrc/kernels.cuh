@@ -26,6 +26,12 @@ struct LinearArgs {
   // pieces that run as separate work items and ADD their partial products into the fp32 output with
   // atomics (the caller zeroes C first; bias goes in with the first piece).  0 or 1 = off.
   int k_splits = 0;
+  // Operands stored with the contraction index as ROWS (tcgen05 engine only): a_mn = A is a (K, M)
+  // row-major matrix with pitch lda, w_mn = W is a (K, N) row-major matrix with pitch ldw.  The tiles
+  // are fetched as 64-column blocks and handed to the tensor cores as MN-major operands, so weight
+  // gradients (g^T x: the contraction runs over token rows) and input gradients (g W) need no
+  // transposed copies.  M % 64 == 0 (a_mn), N % 64 == 0 (w_mn); K is free (rows past K read as zero).
+  int a_mn = 0, w_mn = 0;
 };
 LinearArgs linear_args(const __half* A, int lda, const __half* W, int ldw, const float* bias,
                        void* C, int ldc, int out_f32, int relu, int64_t M, int N, int K);

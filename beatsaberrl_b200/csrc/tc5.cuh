@@ -198,9 +198,24 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
-// Instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128, N = n (n % 16 == 0)
-__host__ __device__ inline uint32_t idesc_f16(int m, int n) {
-  return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+// Descriptor of an MN-major operand tile: the contraction index runs over 128-byte ROWS of 64 fp16
+// along M (or N), 128-byte swizzle, as a TMA load of a {64 columns, k rows, blocks} box writes it:
+// 8-row groups (8 steps of the contraction index) are 1024 bytes apart, the next 64-column block of
+// M / N starts block_bytes further on.  A 16-step K slice advances the start address by 2048 bytes.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t smem_addr, uint32_t block_bytes) {
+  uint64_t d = (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((block_bytes >> 4) & 0x3FFF) << 16;   // leading byte offset: between 64-column blocks
+  d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset: between 8-row groups
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor: f16 x f16 -> f32, M = 128, N = n (n % 16 == 0); both operands K-major
+// unless a_mn / b_mn say that operand is MN-major
+__host__ __device__ inline uint32_t idesc_f16(int m, int n, int a_mn = 0, int b_mn = 0) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(a_mn ? 1 : 0) << 15) | ((uint32_t)(b_mn ? 1 : 0) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // byte offset of element (row, col) inside a [rows][64 fp16] 128-byte-swizzled tile

@@ -182,20 +182,38 @@ struct Bwd {
   template <typename T>
   T* S(int64_t off) const { return at<T>(ws, off); }
 
-  // out (M, K) = g (M, N) . W, W = rows [0, N) of a (N, K) fp16 matrix with pitch ldw; g has pad64(N) columns
+  // out (M, K) = g (M, N) . W, W = rows [0, N) of a (N, K) fp16 matrix with pitch ldw; g has pad64(N) columns.
+  // The contraction runs over W's ROWS: the tensor cores take W as it lies (an MN-major operand); only shapes
+  // that mode does not cover go through a transposed copy.
   int dgrad(const __half* g, int64_t ldg, int64_t M, const __half* W, int ldw, int N, int K, void* out, int64_t ldo, bool out_f32) {
+    LinearArgs r = linear_args(g, (int)ldg, W, ldw, nullptr, out, (int)ldo, out_f32 ? 1 : 0, 0, M, K, N);
+    r.w_mn = 1;
+    if (linear_rows_ok(r)) return linear(r, st);
     const int Np = (int)pad64(N);
     __half* wT = S<__half>(w.wT);
     BSRL_TRY(transpose16(W, ldw, identity_map(), N, K, wT, Np, Np, st));
     LinearArgs a = linear_args(g, (int)ldg, wT, Np, nullptr, out, (int)ldo, out_f32 ? 1 : 0, 0, M, K, Np);
     return linear(a, st);
   }
-  // transposed copies for the weight-gradient products: rows of `m` (M of them, through map) become columns
+  // Operands of the weight-gradient products gW = g^T x (the contraction runs over the M token rows).  to_tA /
+  // to_tX only NAME the two matrices (and take the bias gradient, the column sums of g); wgrad_t hands them
+  // to the tensor cores as they lie (MN-major operands) where the shape allows, and otherwise makes the
+  // transposed copies (tA, tX: rows of the matrix become columns, M padded to 64) on first use.
+  struct Operand { const __half* m = nullptr; int64_t ld = 0; RowMap map{0x7fffffff, 0, 0}; int64_t M = 0; int n = 0; bool copied = false; };
+  Operand opA, opX;
+  static bool is_identity(const RowMap& m) { return m.group == 0x7fffffff && m.stride == 0 && m.first == 0; }
   int to_tA(const __half* m, int64_t ld, RowMap map, int64_t M, int N, float* colsum = nullptr) {   // colsum: bias gradient on the way
-    return transpose16(m, ld, map, M, N, S<__half>(w.tA), pad64(M), pad64(M), st, colsum);
+    opA = Operand{m, ld, map, M, N, false};
+    if (colsum && is_identity(map)) return colsum16(m, ld, M, N, colsum, st);
+    if (colsum) return copy_tA(colsum);
+    return BSRL_OK;
   }
-  // transposed copy of a gradient matrix whose column ranges are the bias gradients of several parameters
-  // (stacked q|k|v, the packed heads): the sums land in a scratch vector and are copied out slice by slice
+  int copy_tA(float* colsum = nullptr) {
+    opA.copied = true;
+    return transpose16(opA.m, opA.ld, opA.map, opA.M, opA.n, S<__half>(w.tA), pad64(opA.M), pad64(opA.M), st, colsum);
+  }
+  // gradient matrix whose column ranges are the bias gradients of several parameters (stacked q|k|v, the packed
+  // heads): the sums land in a scratch vector and are copied out slice by slice
   struct BiasSlice { float* dst; int col0, n; };
   int to_tA_slices(const __half* g, int64_t ld, int64_t M, int N, std::initializer_list<BiasSlice> slices) {
     float* scratch = S<float>(w.bias_scratch);
@@ -205,19 +223,33 @@ struct Bwd {
       if (b.dst) BSRL_CUDA_OK(cudaMemcpyAsync(b.dst, scratch + b.col0, (size_t)b.n * 4, cudaMemcpyDeviceToDevice, st));
     return BSRL_OK;
   }
-  int to_tX(const __half* m, int64_t ld, RowMap map, int64_t M, int K) { return transpose16(m, ld, map, M, K, S<__half>(w.tX), pad64(M), pad64(M), st); }
-  // gW (n, K) f32 (+)= tA[row0 : row0 + n, :] . tX^T, both (., pad64(M)); gW must be zero on entry
+  int to_tX(const __half* m, int64_t ld, RowMap map, int64_t M, int K) {
+    opX = Operand{m, ld, map, M, K, false};
+    return BSRL_OK;
+  }
+  // gW (n, K) f32 (+)= g[:, row0 : row0 + n]^T . x; gW must be zero on entry
   int wgrad_t(int row0, int n, int K, int64_t M, float* gW, int ldgw) {
     if (!gW) return BSRL_OK;
     const int64_t Mp = pad64(M);
-    LinearArgs a = linear_args(S<__half>(w.tA) + (int64_t)row0 * Mp, (int)Mp, S<__half>(w.tX), (int)Mp, nullptr, gW, ldgw, 1, 0, n, K, (int)Mp);
-    int64_t tiles = ((n + 127) / 128) * ((K + 255) / 256);
-    int splits = (int)(sm_count() / (tiles > 0 ? tiles : 1));
-    a.k_splits = splits < 1 ? 1 : splits;
     if (Mp > 0x7fffffff) {
       set_error("backward: too many rows for one weight-gradient product");
       return BSRL_ERR_SHAPE;
     }
+    int64_t tiles = ((n + 127) / 128) * ((K + 255) / 256);
+    int splits = (int)(sm_count() / (tiles > 0 ? tiles : 1));
+    if (is_identity(opA.map) && is_identity(opX.map) && !opA.copied && !opX.copied) {
+      LinearArgs r = linear_args(opA.m + row0, (int)opA.ld, opX.m, (int)opX.ld, nullptr, gW, ldgw, 1, 0, n, K, (int)M);
+      r.a_mn = r.w_mn = 1;
+      r.k_splits = splits < 1 ? 1 : splits;
+      if (linear_rows_ok(r)) return linear(r, st);
+    }
+    if (!opA.copied) BSRL_TRY(copy_tA());
+    if (!opX.copied) {
+      opX.copied = true;
+      BSRL_TRY(transpose16(opX.m, opX.ld, opX.map, opX.M, opX.n, S<__half>(w.tX), Mp, Mp, st));
+    }
+    LinearArgs a = linear_args(S<__half>(w.tA) + (int64_t)row0 * Mp, (int)Mp, S<__half>(w.tX), (int)Mp, nullptr, gW, ldgw, 1, 0, n, K, (int)Mp);
+    a.k_splits = splits < 1 ? 1 : splits;
     return linear(a, st);
   }
   // one Linear: gW += g^T x, gb += colsum(g); x through xmap
@@ -548,13 +580,22 @@ int bsrl_linear_bwd(const void* g_f16, const void* x_f16, const void* w_f16, int
   __half* tX = at<__half>(scratch, round_up((int64_t)n * mp * 2, 256));
   __half* wT = at<__half>(scratch, round_up((int64_t)n * mp * 2, 256) + round_up((int64_t)k * mp * 2, 256));
   const __half* g = static_cast<const __half*>(g_f16);
-  if (g_weight) {     // g_weight (n, k) += g^T x as a split-K product of the transposed operands; zero it first
-    BSRL_TRY(transpose16(g, n, identity_map(), m, n, tA, mp, mp, st, g_bias));    // bias gradient on the way
-    BSRL_TRY(transpose16(static_cast<const __half*>(x_f16), k, identity_map(), m, k, tX, mp, mp, st));
-    LinearArgs a = linear_args(tA, (int)mp, tX, (int)mp, nullptr, g_weight, k, 1, 0, n, k, (int)mp);
+  if (g_weight) {     // g_weight (n, k) += g^T x as a split-K product over the m rows; the caller zeroes it first
     const int64_t tiles = ((n + 127) / 128) * ((k + 255) / 256);
-    a.k_splits = (int)(sm_count() / tiles) < 1 ? 1 : (int)(sm_count() / tiles);
-    BSRL_TRY(linear(a, st));
+    const int splits = (int)(sm_count() / tiles) < 1 ? 1 : (int)(sm_count() / tiles);
+    LinearArgs r = linear_args(g, n, static_cast<const __half*>(x_f16), k, nullptr, g_weight, k, 1, 0, n, k, (int)m);
+    r.a_mn = r.w_mn = 1;                       // both operands as they lie: the contraction index is their row
+    r.k_splits = splits;
+    if (linear_rows_ok(r)) {
+      if (g_bias) BSRL_TRY(colsum16(g, n, m, n, g_bias, st));
+      BSRL_TRY(linear(r, st));
+    } else {                                   // transposed copies, bias gradient on the way
+      BSRL_TRY(transpose16(g, n, identity_map(), m, n, tA, mp, mp, st, g_bias));
+      BSRL_TRY(transpose16(static_cast<const __half*>(x_f16), k, identity_map(), m, k, tX, mp, mp, st));
+      LinearArgs a = linear_args(tA, (int)mp, tX, (int)mp, nullptr, g_weight, k, 1, 0, n, k, (int)mp);
+      a.k_splits = splits;
+      BSRL_TRY(linear(a, st));
+    }
   }
   if (g_bias && !g_weight) BSRL_TRY(colsum16(g, n, m, n, g_bias, st));
   if (g_x) {          // g_x (m, k) = g w
@@ -562,8 +603,14 @@ int bsrl_linear_bwd(const void* g_f16, const void* x_f16, const void* w_f16, int
       set_error("linear_bwd: the input gradient needs the weight");
       return BSRL_ERR_NULL;
     }
-    BSRL_TRY(transpose16(static_cast<const __half*>(w_f16), k, identity_map(), n, k, wT, n, n, st));
-    BSRL_TRY(linear(linear_args(g, n, wT, n, nullptr, g_x, k, g_x_f32 ? 1 : 0, 0, m, k, n), st));
+    LinearArgs r = linear_args(g, n, static_cast<const __half*>(w_f16), k, nullptr, g_x, k, g_x_f32 ? 1 : 0, 0, m, k, n);
+    r.w_mn = 1;
+    if (linear_rows_ok(r)) {
+      BSRL_TRY(linear(r, st));
+    } else {
+      BSRL_TRY(transpose16(static_cast<const __half*>(w_f16), k, identity_map(), n, k, wT, n, n, st));
+      BSRL_TRY(linear(linear_args(g, n, wT, n, nullptr, g_x, k, g_x_f32 ? 1 : 0, 0, m, k, n), st));
+    }
   }
   return BSRL_OK;
 }

@@ -197,10 +197,14 @@ def test_head_tail_bwd_stage(native, case, B):
     assert float(gb[:, cfg.value_bins:].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("m,n,k", [(40, 64, 64), (1000, 128, 256), (5000, 1024, 256), (3333, 256, 1024), (129, 768, 256)])
-def test_linear_bwd_stage(native, m, n, k):
-    """Weight gradient (split-K tcgen05 product of transposed operands), bias gradient and input gradient of one
-    Linear against fp32 matmuls on the same fp16 operands."""
+@pytest.mark.parametrize("engine", [0, 1])
+@pytest.mark.parametrize("m,n,k", [(40, 64, 64), (1000, 128, 256), (5000, 1024, 256), (3333, 256, 1024), (129, 768, 256),
+                                   (2048, 192, 192), (7777, 576, 192)])
+def test_linear_bwd_stage(native, m, n, k, engine):
+    """Weight gradient (split-K tcgen05 product over the token rows), bias gradient and input gradient of one Linear
+    against fp32 matmuls on the same fp16 operands.  Engine 0 hands the operands to the tensor cores as they lie
+    (the contraction index is their row: MN-major tiles); engine 1 is the warp-MMA engine on transposed copies."""
+    native.lib.bsrl_set_engine(engine)
     g = torch.Generator().manual_seed(m + n + k)
     gy = (torch.randn(m, n, generator=g) * 0.5).half()
     x = torch.randn(m, k, generator=g).half()
@@ -212,6 +216,7 @@ def test_linear_bwd_stage(native, m, n, k):
     gyd, xd, wd = gy.cuda(), x.cuda(), w.cuda()
     native.check(native.lib.bsrl_linear_bwd(gyd.data_ptr(), xd.data_ptr(), wd.data_ptr(), m, n, k, gw.data_ptr(), gb.data_ptr(),
                                             gx.data_ptr(), 1, scratch.data_ptr(), nbytes, _st()))
+    native.lib.bsrl_set_engine(0)
     native.check(native.lib.bsrl_device_status())
     torch.testing.assert_close(gw.cpu(), gy.float().t() @ x.float(), atol=2e-3 * m ** 0.5, rtol=2e-3)
     torch.testing.assert_close(gb.cpu(), gy.float().sum(0), atol=1e-3 * m ** 0.5, rtol=1e-3)
