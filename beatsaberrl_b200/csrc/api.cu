@@ -74,7 +74,7 @@ void use_process_engine() { g_call_engine = g_engine.load(std::memory_order_rela
 int process_engine() { return g_engine.load(std::memory_order_relaxed); }
 int linear(const LinearArgs& p, cudaStream_t st) {
   return timed(st, 2.0 * p.M * p.N * p.K, linear_bytes(p), [&] {
-    if (p.a_mn || p.w_mn) {      // operands with the contraction index as rows: the tcgen05 engine only
+    if (p.a_mn || p.w_mn || p.mask) {      // row-contraction operands and the epilogue mask: the tcgen05 engine only
       if (g_call_engine == 0 && linear_tc5_ok(p)) return linear_tc5(p, st);
       set_error("linear: row-contraction operands need the tcgen05 engine and M, N multiples of 64 (m=%lld n=%d k=%d)",
                 (long long)p.M, p.N, p.K);

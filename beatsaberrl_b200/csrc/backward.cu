@@ -17,13 +17,14 @@ namespace {
 
 constexpr int kMaxVecAll = 8;   // float4 per lane: rows up to 1024 wide
 
-// dx = rstd (gy g - mean(gy g) - xhat mean(gy g xhat)); gx_out = (gres ? gres : 0) + dx;
+// dx = rstd (gy g - mean(gy g) - xhat mean(gy g xhat)); gx_out = (gres ? gres : 0) + dx; gx16 = fp16(gx_out) if asked;
 // ggamma += sum_rows gy xhat, gbeta += sum_rows gy.  One warp per row; per-block partial sums of the
 // parameter gradients in shared memory, then one atomic per column per block.
 template <bool GY_F32, int kMaxVec>
 __global__ void __launch_bounds__(256) ln_bwd_kernel(const float* __restrict__ x, int64_t ldx, RowMap xmap,
                                                      const float* __restrict__ gamma, float eps, const void* __restrict__ gy,
                                                      int64_t ldgy, const float* gres, float* gx_out, int64_t ldg, RowMap gmap,
+                                                     __half* __restrict__ gx16, int64_t ldg16,
                                                      float* __restrict__ ggamma, float* __restrict__ gbeta, int64_t rows, int d) {
   extern __shared__ float s_part[];                  // [2][d]
   for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) s_part[i] = 0.f;
@@ -91,6 +92,8 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(const float* __restrict__ x
           o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
         }
         reinterpret_cast<float4*>(gx_out + go)[c] = o;
+        if (gx16)      // the same gradient as the fp16 operand of the products that follow (dense rows)
+          reinterpret_cast<uint2*>(gx16 + row * ldg16)[c] = make_uint2(pack_half2(o.x, o.y), pack_half2(o.z, o.w));
       }
     }
   }
@@ -378,12 +381,12 @@ int64_t grid_for(int64_t work_items, int per_block) {
 
 int layernorm_bwd(const float* x, int64_t ldx, RowMap xmap, const float* gamma, float eps, const void* gy, int gy_f32,
                   int64_t ldgy, const float* gres, float* gx_out, int64_t ldg, RowMap gmap, float* ggamma, float* gbeta,
-                  int64_t rows, int d, cudaStream_t stream) {
+                  int64_t rows, int d, cudaStream_t stream, __half* gx16, int64_t ldg16) {
   if (!x || !gamma || !gy || !gx_out) {
     set_error("layernorm_bwd: NULL operand");
     return BSRL_ERR_NULL;
   }
-  if (d % 4 != 0 || d > 128 * kMaxVecAll || (ldx % 4) || (ldg % 4) || (ldgy % 4)) {
+  if (d % 4 != 0 || d > 128 * kMaxVecAll || (ldx % 4) || (ldg % 4) || (ldgy % 4) || (gx16 && (ldg16 % 4))) {
     set_error("layernorm_bwd: d = %d unsupported (d %% 4 == 0, d <= 1024, aligned pitches)", d);
     return BSRL_ERR_SHAPE;
   }
@@ -391,7 +394,7 @@ int layernorm_bwd(const float* x, int64_t ldx, RowMap xmap, const float* gamma, 
   const int blocks = (int)grid_for(rows, 8 * 4);
   const size_t smem = 2 * d * sizeof(float);
 #define BSRL_LN_BWD(F32, NV) \
-  ln_bwd_kernel<F32, NV><<<blocks, 256, smem, stream>>>(x, ldx, xmap, gamma, eps, gy, ldgy, gres, gx_out, ldg, gmap, ggamma, gbeta, rows, d)
+  ln_bwd_kernel<F32, NV><<<blocks, 256, smem, stream>>>(x, ldx, xmap, gamma, eps, gy, ldgy, gres, gx_out, ldg, gmap, gx16, ldg16, ggamma, gbeta, rows, d)
   const int nv = (d + 127) / 128;          // float4 per lane actually needed: fewer registers, more rows in flight
   if (gy_f32) {
     if (nv <= 2) BSRL_LN_BWD(true, 2); else if (nv <= 4) BSRL_LN_BWD(true, 4); else BSRL_LN_BWD(true, 8);

@@ -221,6 +221,15 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         // ---- phase 1: own row, 32 columns at a time -> bias / ReLU -> staging
         for (int s32 = 0; s32 < cw; s32 += 32) {
           if (col + s32 >= p.N) break;
+          uint4 mk[4];                                   // this row's 32 mask entries, requested ahead of the accumulator
+          const int64_t mrow = m0 + q * 32 + lane;
+          const bool masked = p.mask != nullptr && mrow < p.M;
+          if (masked) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              mk[j] = col + s32 + 8 * j < p.N ? *reinterpret_cast<const uint4*>(p.mask + mrow * p.ldm + col + s32 + 8 * j)
+                                              : make_uint4(0, 0, 0, 0);
+          }
           tmem_ld32(tbase + c + s32, r);
           tmem_wait_ld();
           float v[32];
@@ -241,6 +250,15 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           } else if (p.relu == 2) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = gelu_exact(v[j]);
+          }
+          if (masked) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __half* mh = reinterpret_cast<const __half*>(&mk[j]);
+#pragma unroll
+              for (int t = 0; t < 8; ++t)
+                if (!(__half2float(mh[t]) > 0.f)) v[8 * j + t] = 0.f;
+            }
           }
           if (tma_c && s32 == 0) {   // the previous block's TMA store has read the staging buffer
             if (lane == 0) bulk_wait_read<0>();
@@ -445,7 +463,8 @@ bool linear_tc5_ok(const LinearArgs& p) {
   if (p.ldc % (p.out_f32 ? 4 : 8)) return false;
   if (p.bias && !aligned16(p.bias)) return false;
   if (p.R && (!aligned16(p.R) || (p.ldr % 4))) return false;
-  if (p.k_splits > 1 && (!p.out_f32 || p.relu || p.R)) return false;   // split-K adds raw fp32 partial products
+  if (p.k_splits > 1 && (!p.out_f32 || p.relu || p.R || p.mask)) return false;   // split-K adds raw fp32 partial products
+  if (p.mask && (!aligned16(p.mask) || (p.ldm % 8) || p.cmap.group != 0x7fffffff || p.cmap.first != 0)) return false;
   return true;
 }
 

@@ -32,6 +32,10 @@ struct LinearArgs {
   // gradients (g^T x: the contraction runs over token rows) and input gradients (g W) need no
   // transposed copies.  M % 64 == 0 (a_mn), N % 64 == 0 (w_mn); K is free (rows past K read as zero).
   int a_mn = 0, w_mn = 0;
+  // ReLU backward in the epilogue (tcgen05 engine): entries of C whose counterpart in `mask` (fp16, M rows of
+  // pitch ldm, dense rows) is not positive are written as zero.
+  const __half* mask = nullptr;
+  int ldm = 0;
 };
 LinearArgs linear_args(const __half* A, int lda, const __half* W, int ldw, const float* bias,
                        void* C, int ldc, int out_f32, int relu, int64_t M, int N, int K);

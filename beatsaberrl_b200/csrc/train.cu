@@ -26,7 +26,7 @@
 namespace bsrl {
 int layernorm_bwd(const float* x, int64_t ldx, RowMap xmap, const float* gamma, float eps, const void* gy, int gy_f32,
                   int64_t ldgy, const float* gres, float* gx_out, int64_t ldg, RowMap gmap, float* ggamma, float* gbeta,
-                  int64_t rows, int d, cudaStream_t stream);
+                  int64_t rows, int d, cudaStream_t stream, __half* gx16 = nullptr, int64_t ldg16 = 0);
 int colsum16(const __half* in, int64_t ld, int64_t rows, int n, float* out, cudaStream_t stream);
 int relu_mask16(__half* g, int64_t ldg, const __half* act, int64_t lda, int64_t rows, int n, cudaStream_t stream);
 int cast_rows16(const float* in, int64_t ldi, RowMap imap, float scale, __half* out, int64_t ldo, int64_t rows, int n,
@@ -102,7 +102,7 @@ inline int64_t pad64(int64_t n) { return round_up(n, 64); }
 
 // ---- scratch of the backward
 struct BwdLayout {
-  int64_t h16, qkv16, att16, x1, h2, hid, gx, g32, gA, gB, tA, tX, wT;
+  int64_t h16, qkv16, att16, x1, h2, hid, gx, gx16, g32, gA, gB, tA, tX, wT;
   // readout-side rows (B of them)
   int64_t xt, u16, r16, xt2, z16, hv16, attc16, m1, m2, gz32, graw16, gvraw16, gsmall32, gsmall16, scratch_w;
   int64_t bias_scratch, heads_scratch;
@@ -129,6 +129,7 @@ BwdLayout make_bwd(const Layout& l, int64_t B) {
   w.h2 = cv.take(R * d * 2);
   w.hid = cv.take(R * (int64_t)F * 2);
   w.gx = cv.take(R * d * 4);
+  w.gx16 = cv.take(R * d * 2);     // fp16 copy of the stream gradient, written by the LayerNorm backward that produces it
   w.g32 = cv.take(R * d * 4);
   w.gA = cv.take(R * (int64_t)wide * 2);
   w.gB = cv.take(R * 3 * d * 2);
@@ -185,15 +186,28 @@ struct Bwd {
   // out (M, K) = g (M, N) . W, W = rows [0, N) of a (N, K) fp16 matrix with pitch ldw; g has pad64(N) columns.
   // The contraction runs over W's ROWS: the tensor cores take W as it lies (an MN-major operand); only shapes
   // that mode does not cover go through a transposed copy.
-  int dgrad(const __half* g, int64_t ldg, int64_t M, const __half* W, int ldw, int N, int K, void* out, int64_t ldo, bool out_f32) {
+  // With relu_of (the fp16 output of the ReLU this gradient flows back through, same shape as out), entries
+  // whose activation was not positive come out as zero.
+  int dgrad(const __half* g, int64_t ldg, int64_t M, const __half* W, int ldw, int N, int K, void* out, int64_t ldo, bool out_f32,
+            const __half* relu_of = nullptr, int64_t ld_relu = 0) {
     LinearArgs r = linear_args(g, (int)ldg, W, ldw, nullptr, out, (int)ldo, out_f32 ? 1 : 0, 0, M, K, N);
     r.w_mn = 1;
+    r.mask = relu_of;
+    r.ldm = (int)ld_relu;
     if (linear_rows_ok(r)) return linear(r, st);
     const int Np = (int)pad64(N);
     __half* wT = S<__half>(w.wT);
     BSRL_TRY(transpose16(W, ldw, identity_map(), N, K, wT, Np, Np, st));
     LinearArgs a = linear_args(g, (int)ldg, wT, Np, nullptr, out, (int)ldo, out_f32 ? 1 : 0, 0, M, K, Np);
-    return linear(a, st);
+    BSRL_TRY(linear(a, st));
+    if (relu_of) {
+      if (out_f32) {
+        set_error("backward: the ReLU mask applies to fp16 gradients");
+        return BSRL_ERR_UNSUPPORTED;
+      }
+      return relu_mask16(static_cast<__half*>(out), ldo, relu_of, ld_relu, M, K, st);
+    }
+    return BSRL_OK;
   }
   // Operands of the weight-gradient products gW = g^T x (the contraction runs over the M token rows).  to_tA /
   // to_tX only NAME the two matrices (and take the bias gradient, the column sums of g); wgrad_t hands them
@@ -262,29 +276,32 @@ struct Bwd {
     return cast_rows16(in, ldi, map, 1.f, out, ldo, rows, n, st);
   }
   int ln_bwd(const float* x, int64_t ldx, RowMap xmap, const Norm& n, const std::string& name, const void* gy, bool gy_f32,
-             int64_t ldgy, const float* gres, float* gx_out, int64_t ldg, RowMap gmap, int64_t rows, int width) {
+             int64_t ldgy, const float* gres, float* gx_out, int64_t ldg, RowMap gmap, int64_t rows, int width,
+             __half* gx16 = nullptr) {
     return layernorm_bwd(x, ldx, xmap, c.G(n), c.cfg->eps, gy, gy_f32 ? 1 : 0, ldgy, gres, gx_out, ldg, gmap, G(name + ".weight"),
-                         G(name + ".bias"), rows, width, st);
+                         G(name + ".bias"), rows, width, st, gx16, width);
   }
 
   // FFN + out-projection half of a block on M rows, given the gradient g_out (fp32) of the block's output:
   // leaves the gradient of x1 (the stream after the attention residual) in g_x1 and the fp16 gradient of the
   // attention output in gatt16.  x1 / h2 / hid / att are the recomputed activations of those M rows.
+  // g_out16: the same gradient already as fp16 (M, d) rows, or nullptr.
   int tail_bwd(int i, int64_t M, const float* g_out, float* g_x1, const float* x1, const __half* h2, const __half* hid,
-               const __half* att, __half* gatt16) {
+               const __half* att, __half* gatt16, const __half* g_out16 = nullptr) {
     const BlockW& b = l.blocks[i];
     const std::string p = "blocks." + std::to_string(i);
     __half* gA = S<__half>(w.gA);
     __half* gB = S<__half>(w.gB);
     float* g32 = S<float>(w.g32);
-    BSRL_TRY(cast16(g_out, d, identity_map(), gB, d, M, d));                                    // g_out as a GEMM operand
-    BSRL_TRY(wgrad(gB, d, M, d, hid, F, identity_map(), F, p + ".ffn.2"));
-    BSRL_TRY(dgrad(gB, d, M, c.W(b.down), b.down.pitch, d, F, gA, F, false));                   // g_hid
-    BSRL_TRY(relu_mask16(gA, F, hid, F, M, F, st));
+    if (!g_out16) {                                                                             // g_out as a GEMM operand
+      BSRL_TRY(cast16(g_out, d, identity_map(), gB, d, M, d));
+      g_out16 = gB;
+    }
+    BSRL_TRY(wgrad(g_out16, d, M, d, hid, F, identity_map(), F, p + ".ffn.2"));
+    BSRL_TRY(dgrad(g_out16, d, M, c.W(b.down), b.down.pitch, d, F, gA, F, false, hid, F));      // g_hid, through the ReLU
     BSRL_TRY(wgrad(gA, F, M, F, h2, d, identity_map(), d, p + ".ffn.0"));
     BSRL_TRY(dgrad(gA, F, M, c.W(b.up), b.up.pitch, F, d, g32, d, true));                        // g_h2
-    BSRL_TRY(ln_bwd(x1, d, identity_map(), b.ln_ffn, p + ".ln_ffn", g32, true, d, g_out, g_x1, d, identity_map(), M, d));
-    BSRL_TRY(cast16(g_x1, d, identity_map(), gB, d, M, d));
+    BSRL_TRY(ln_bwd(x1, d, identity_map(), b.ln_ffn, p + ".ln_ffn", g32, true, d, g_out, g_x1, d, identity_map(), M, d, gB));
     BSRL_TRY(wgrad(gB, d, M, d, att, d, identity_map(), d, p + ".out_proj"));
     BSRL_TRY(dgrad(gB, d, M, c.W(b.out), b.out.pitch, d, d, gatt16, d, false));
     return BSRL_OK;
@@ -449,6 +466,8 @@ struct Bwd {
     }
 
     // ---- blocks L-2 .. 0, all rows
+    __half* gx16 = S<__half>(w.gx16);
+    const __half* gx16_live = nullptr;     // fp16 copy of gx, once a LayerNorm backward of this loop has written it
     for (int i = l.L - 2; i >= 0; --i) {
       const BlockW& b = l.blocks[i];
       const std::string p = "blocks." + std::to_string(i);
@@ -457,7 +476,7 @@ struct Bwd {
       BSRL_TRY(linear(linear_args(h16, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, R, 3 * d, d), st));
       BSRL_TRY(attention(qkv, 3 * d, sv.key_bias, B, d, l.H, 0, kT, att, d, st));
       BSRL_TRY(tail_fwd(i, R, x_in, ident, att, x1, h2, hid));
-      BSRL_TRY(tail_bwd(i, R, gx, gx, x1, h2, hid, att, gA));                                       // gx: g(x_{i+1}) -> g(x1)
+      BSRL_TRY(tail_bwd(i, R, gx, gx, x1, h2, hid, att, gA, gx16_live));                            // gx: g(x_{i+1}) -> g(x1)
       BSRL_TRY(attention29_bwd(qkv, 3 * d, sv.key_bias, B, d, l.H, 0, kT, gA, d, gB, 3 * d, gB + d, 3 * d, gB + 2 * d, 3 * d, st));
       BSRL_TRY(to_tX(h16, d, ident, R, d));
       BSRL_TRY(to_tA_slices(gB, 3 * d, R, 3 * d, {{G(p + ".q_proj.bias"), 0, d}, {G(p + ".k_proj.bias"), d, d},
@@ -465,7 +484,8 @@ struct Bwd {
       const char* names[3] = {".q_proj", ".k_proj", ".v_proj"};
       for (int s = 0; s < 3; ++s) BSRL_TRY(wgrad_t(s * d, d, d, R, G(p + names[s] + ".weight"), d));
       BSRL_TRY(dgrad(gB, 3 * d, R, c.W(b.qkv), b.qkv.pitch, 3 * d, d, g32, d, true));
-      BSRL_TRY(ln_bwd(x_in, d, ident, b.ln_attn, p + ".ln_attn", g32, true, d, gx, gx, d, ident, R, d));     // gx: g(x_i)
+      BSRL_TRY(ln_bwd(x_in, d, ident, b.ln_attn, p + ".ln_attn", g32, true, d, gx, gx, d, ident, R, d, gx16));   // gx: g(x_i)
+      gx16_live = gx16;
     }
 
     // ---- token encoders (no gradient flows to the observation)
@@ -480,8 +500,7 @@ struct Bwd {
       BSRL_TRY(linear(linear_args(feat, 64, c.W(e.e->l0), e.e->l0.pitch, c.Bv(e.e->l0), hid, d, 0, 1, e.rows, d, 64), st));   // hidden
       BSRL_TRY(cast16(gx, d, rows, gB, d, e.rows, d));                                               // g of this encoder's tokens
       BSRL_TRY(wgrad(gB, d, e.rows, d, hid, d, ident, d, std::string(e.name) + ".2"));
-      BSRL_TRY(dgrad(gB, d, e.rows, c.W(e.e->l1), e.e->l1.pitch, d, d, gA, d, false));
-      BSRL_TRY(relu_mask16(gA, d, hid, d, e.rows, d, st));
+      BSRL_TRY(dgrad(gB, d, e.rows, c.W(e.e->l1), e.e->l1.pitch, d, d, gA, d, false, hid, d));       // through the hidden ReLU
       // first layer: the K-padded (d, 64) product goes to a scratch matrix, its first `in` columns are the gradient
       float* sw = S<float>(w.scratch_w);
       BSRL_CUDA_OK(cudaMemsetAsync(sw, 0, (size_t)d * 64 * 4, st));
