@@ -7,6 +7,7 @@
 #include <string.h>
 
 #include <atomic>
+#include <functional>
 #include <vector>
 
 #include "api_internal.cuh"
@@ -21,8 +22,6 @@ namespace fwd {
 // Optional CUDA-event timing of every launch of a forward, grouped by stage.  Off by default
 // (a captured graph must not contain it); the benchmark switches it on to time the dominant
 // kernel live, on the stream the kernels run on.
-enum Stage { kStGather = 0, kStEncoder, kStEncoderFused, kStLayerNorm, kStQkv, kStAttention, kStOutProj, kStFfnUp,
-             kStFfnDown, kStBlockTail, kStAttnBlock, kStTrunk, kStCritic, kStHeadTail, kStCount };
 const char* const kStageNames[kStCount] = {"embed_gather", "encoder_gemm", "encoder_fused", "layernorm", "qkv_gemm",
                                            "attention", "out_proj_gemm", "ffn_up_gemm", "ffn_down_gemm", "block_tail", "attn_block",
                                            "trunk", "critic", "head_tail"};
@@ -103,6 +102,9 @@ int attention(const __half* qkv, int ld, const float* kb, int64_t B, int d, int 
   g_stage = keep;
   return rc;
 }
+
+void set_stage(int stage) { g_stage = stage; }
+int timed_call(cudaStream_t st, double flops, double bytes, const std::function<int()>& fn) { return timed(st, flops, bytes, fn); }
 
 int fused_tail(const BlockTailArgs& a, cudaStream_t st) {
   int keep = g_stage;
@@ -978,6 +980,12 @@ int bsrl_attention(const void* qkv_f16, const float* key_bias, int64_t n_envs, i
                    int32_t q_first, int32_t n_q, void* out_f16, void* stream) {
   return attention29(static_cast<const __half*>(qkv_f16), 3 * d, key_bias, n_envs, d, n_heads, q_first, n_q,
                      static_cast<__half*>(out_f16), d, as_stream(stream));
+}
+
+int bsrl_attention_tokens(const void* qkv_f16, const float* key_bias, int64_t n_envs, int32_t tokens, int32_t d, int32_t n_heads,
+                          int32_t q_first, int32_t n_q, void* out_f16, void* stream) {
+  return attention_tokens(static_cast<const __half*>(qkv_f16), 3 * d, key_bias, n_envs, tokens, d, n_heads, q_first, n_q,
+                          static_cast<__half*>(out_f16), d, as_stream(stream));
 }
 
 }  // extern "C"

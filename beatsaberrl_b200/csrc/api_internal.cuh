@@ -2,6 +2,7 @@
 // training entry points (train.cu): the per-call context, byte-offset helpers and the stage-labelled
 // wrappers of the GEMM / LayerNorm / attention launchers.
 #pragma once
+#include <functional>
 #include "kernels.cuh"
 #include "layout.h"
 
@@ -64,6 +65,13 @@ void head_shape(const bsrl_config& cfg, const Layout& l, HeadTailArgs& t);
 // makes the calling thread's launch wrappers follow the process-wide engine choice (bsrl_set_engine)
 void use_process_engine();
 int process_engine();
+
+// stage labels of the optional per-launch profiler (names in api.cu, same order)
+enum Stage { kStGather = 0, kStEncoder, kStEncoderFused, kStLayerNorm, kStQkv, kStAttention, kStOutProj, kStFfnUp,
+             kStFfnDown, kStBlockTail, kStAttnBlock, kStTrunk, kStCritic, kStHeadTail, kStCount };
+void set_stage(int stage);            // label of the launches that follow on this thread
+int timed_call(cudaStream_t st, double flops, double bytes, const std::function<int()>& fn);
+int fused_tail(const BlockTailArgs& a, cudaStream_t st);
 
 // stage-labelled launch wrappers (timed when the calling thread has the profiler on)
 int linear(const LinearArgs& p, cudaStream_t st);

@@ -229,14 +229,17 @@ int g_forward(const GCtx& c, const float* obs, const HeadTailArgs& tail_in) {
   __half* f_obj = at<__half>(c.ws, w.f_obj);
   const RowMap ident = identity_map(), body_rows{1, T, 0}, obj_rows{l.n_obj, T, 1};
 
-  {
+  set_stage(kStGather);
+  BSRL_TRY(timed_call(st, 0.0, (double)B * (l.obs_dim * 4 + (l.body_k + l.n_obj * l.obj_k) * 2 + T * 4), [&]() -> int {
     int64_t blocks = (B + 7) / 8;
     const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
     embed_g_kernel<<<(unsigned)blocks, 256, 0, st>>>(obs, B, l.obs_dim, l.body_dim, l.body_k, l.n_obj, l.obj_dim, f_body, f_obj,
                                                      key_bias);
     BSRL_LAUNCH_OK("embed_g_kernel");
-  }
+    return BSRL_OK;
+  }));
+  set_stage(kStEncoder);
   {
     LinearArgs a = linear_args(f_body, l.body_k, c.W(l.body), l.body.pitch, c.Bv(l.body), x, d, 1, 0, B, d, l.body_k);
     a.cmap = body_rows;
@@ -259,26 +262,35 @@ int g_forward(const GCtx& c, const float* obs, const HeadTailArgs& tail_in) {
     a.gelu = 1;
     return a;
   };
+  auto attend = [&](int n_q) -> int {        // masked attention of n_q query rows per env over its T tokens
+    set_stage(kStAttention);
+    return timed_call(st, 4.0 * B * n_q * T * d, (double)B * (T * 2 * d + n_q * d * 2) * 2 + (double)B * T * 4,
+                      [&]() -> int { return attention_tokens(qkv, 3 * d, key_bias, B, T, d, l.H, 0, n_q, att, d, st); });
+  };
   bool have_h = false;
   for (int i = 0; i + 1 < l.L; ++i) {
     const BlockW& b = l.blocks[i];
     if (!have_h) BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, st));
+    set_stage(kStQkv);
     BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, R, 3 * d, d), st));
-    BSRL_TRY(attention_tokens(qkv, 3 * d, key_bias, B, T, d, l.H, 0, T, att, d, st));
+    BSRL_TRY(attend(T));
     if (c.fused) {
       BlockTailArgs a = tail_args(b, R);
       a.x_out = x;
       const BlockW& nb = l.blocks[i + 1];
       a.out16[0] = h; a.ld16[0] = d; a.g16[0] = c.G(nb.ln_attn); a.b16[0] = c.Be(nb.ln_attn);
-      BSRL_TRY(block_tail(a, st));
+      BSRL_TRY(fused_tail(a, st));
       have_h = true;
       continue;
     }
+    set_stage(kStOutProj);
     LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x, d, 1, 0, R, d, d);
     po.R = x; po.ldr = d;
     BSRL_TRY(linear(po, st));
     BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, R, d, h, d, st));
+    set_stage(kStFfnUp);
     BSRL_TRY(linear(linear_args(h, d, c.W(b.up), d, c.Bv(b.up), hid, F, 0, 2, R, F, d), st));
+    set_stage(kStFfnDown);
     LinearArgs pd = linear_args(hid, F, c.W(b.down), F, c.Bv(b.down), x, d, 1, 0, R, d, F);
     pd.R = x; pd.ldr = d;
     BSRL_TRY(linear(pd, st));
@@ -290,17 +302,19 @@ int g_forward(const GCtx& c, const float* obs, const HeadTailArgs& tail_in) {
   {
     const BlockW& b = l.blocks[l.L - 1];
     if (!have_h) BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, st));
+    set_stage(kStQkv);
     BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv, d), d, c.Bv(b.qkv, d), qkv + d, 3 * d, 0, 0, R, 2 * d, d), st));
     LinearArgs pq = linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, B, d, d);
     pq.amap = body_rows; pq.cmap = body_rows;
     BSRL_TRY(linear(pq, st));
-    BSRL_TRY(attention_tokens(qkv, 3 * d, key_bias, B, T, d, l.H, 0, 1, att, d, st));
+    BSRL_TRY(attend(1));
     if (c.fused) {
       BlockTailArgs a = tail_args(b, B);
       a.xmap = body_rows;
       a.out16[0] = lead16; a.ld16[0] = d;
-      BSRL_TRY(block_tail(a, st));
+      BSRL_TRY(fused_tail(a, st));
     } else {
+      set_stage(kStOutProj);
       LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x_lead, d, 1, 0, B, d, d);
       po.R = x; po.ldr = d; po.rmap = body_rows;
       BSRL_TRY(linear(po, st));
@@ -312,6 +326,7 @@ int g_forward(const GCtx& c, const float* obs, const HeadTailArgs& tail_in) {
     }
   }
   float* raw = at<float>(c.ws, w.raw);
+  set_stage(kStTrunk);
   BSRL_TRY(linear(linear_args(lead16, d, c.W(l.heads), d, c.Bv(l.heads), raw, l.cols_pad, 1, 0, B, l.cols_pad, d), st));
   HeadTailArgs t = tail_in;
   t.raw = raw; t.ld_raw = l.cols_pad;
@@ -322,7 +337,8 @@ int g_forward(const GCtx& c, const float* obs, const HeadTailArgs& tail_in) {
     t.first[j] = j * l.K;
   }
   t.n_envs = B;
-  return head_tail(t, st);
+  set_stage(kStHeadTail);
+  return timed_call(st, 0.0, (double)B * (l.cols_pad * 4 + 64), [&]() -> int { return head_tail(t, st); });
 }
 
 int make_gctx(GCtx& c, const bsrl_gconfig* cfg, const void* arena, int64_t n_envs, void* ws, int64_t ws_bytes, void* stream) {

@@ -496,6 +496,15 @@ def run_body(args, rank, world, local_rank):
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    stages, stage_steps = {}, 3
+    if rank == 0:      # separate eager pass with the library's per-launch events: where the time goes
+        from beatsaberrl_b200 import _native as nat
+        nat.check(nat.lib.bsrl_profile_enable(1))
+        for _ in range(stage_steps):
+            policy.forward_stacked(obs)
+        torch.cuda.synchronize()
+        stages = nat.profile_read()
+        nat.check(nat.lib.bsrl_profile_enable(0))
     if rank == 0:
         peaks = read_peaks()
         mac = bo.mac_per_env(cfg)
@@ -508,7 +517,8 @@ def run_body(args, rank, world, local_rank):
             "config": {"workload": f"{args.workload}: single-body-token layout d={cfg.embed} L={cfg.n_blocks} H={cfg.n_heads} "
                                    f"ffn={cfg.ffn_mult * cfg.embed} GELU T={cfg.tokens} gears={cfg.n_gears}, {envs} envs per GPU",
                        "timing": "CUDA-graph replays of one captured forward", "mac_per_env": mac},
-            "forward_tflops": tfl, "forward_frac_of_burst": tfl / peaks["tflops_burst"], "clocks": clocks}), flush=True)
+            "forward_tflops": tfl, "forward_frac_of_burst": tfl / peaks["tflops_burst"],
+            "stage_ms_per_step": {k: round(v["ms"] / stage_steps, 4) for k, v in stages.items()}, "clocks": clocks}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

@@ -322,6 +322,11 @@ int bsrl_linear(const void* a_f16, const void* w_f16, const float* bias, const f
  * reference arithmetic python/policy.py:686-690). */
 int bsrl_attention(const void* qkv_f16, const float* key_bias, int64_t n_envs, int32_t d,
                    int32_t n_heads, int32_t q_first, int32_t n_q, void* out_f16, void* stream);
+/* The same over `tokens` (1..96) token rows per env: qkv (n_envs*tokens, 3d), key_bias (n_envs, tokens).
+ * With 17 / 33 / 65 tokens (one body token + 16 / 32 / 64 object tokens), all rows or the first row only,
+ * the object tokens fill whole tensor-core tiles and the body token is folded in beside them. */
+int bsrl_attention_tokens(const void* qkv_f16, const float* key_bias, int64_t n_envs, int32_t tokens, int32_t d,
+                          int32_t n_heads, int32_t q_first, int32_t n_q, void* out_f16, void* stream);
 
 /* Fused packed projection + attention of one block (head_dim 32 with an even head count, or head_dim
  * 48; embed <= 256), one tcgen05 kernel:

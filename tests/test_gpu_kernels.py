@@ -90,6 +90,36 @@ def test_attention(native, B, d, H, q_first, n_q):
     assert torch.equal(o1[live_q], o2[live_q])
 
 
+@pytest.mark.parametrize("T,d,H,q_first,n_q", [(17, 128, 4, 0, 17), (17, 128, 4, 0, 1), (33, 256, 8, 0, 33), (33, 256, 8, 0, 1),
+                                                 (65, 512, 8, 0, 65), (65, 512, 8, 0, 1), (65, 256, 8, 0, 65),
+                                                 (33, 128, 2, 0, 33), (33, 256, 8, 1, 32), (40, 256, 8, 0, 40), (33, 192, 4, 0, 33)])
+def test_attention_tokens(native, T, d, H, q_first, n_q):
+    """Token counts of the single-body-token layouts (the body token beside whole MMA tiles of object tokens) and a
+    few shapes that take the padded kernel; masked keys carry exactly zero weight."""
+    B = 37
+    g = torch.Generator().manual_seed(T + d + n_q)
+    qkv = torch.randn(B, T, 3 * d, generator=g).half()
+    n_live = torch.randint(0, T, (B,), generator=g)
+    n_live[0], n_live[1] = 0, T - 1
+    bias = torch.zeros(B, T)
+    bias[:, 1:] = ((torch.arange(T - 1)[None, :] < n_live[:, None]).float() - 1.0) * 16384.0
+    out = torch.empty(B * n_q, d, dtype=torch.float16, device="cuda")
+    qkv_d, bias_d = qkv.cuda(), bias.cuda()
+    native.check(native.lib.bsrl_attention_tokens(qkv_d.data_ptr(), bias_d.data_ptr(), B, T, d, H, q_first, n_q,
+                                                  out.data_ptr(), _stream()))
+    q, k, v = qkv.float().split(d, -1)
+    ref = po.attention(q[:, q_first:q_first + n_q], k, v, bias, H)
+    torch.testing.assert_close(out.float().cpu().view(B, n_q, d), ref, atol=4e-3, rtol=2e-3)
+    junk = qkv.clone()
+    dead = bias < 0
+    junk[..., d:][dead] = 77.0
+    out2 = torch.empty_like(out)
+    junk_d = junk.cuda()
+    native.check(native.lib.bsrl_attention_tokens(junk_d.data_ptr(), bias_d.data_ptr(), B, T, d, H, q_first, n_q,
+                                                  out2.data_ptr(), _stream()))
+    assert torch.equal(out.cpu(), out2.cpu())
+
+
 @pytest.mark.parametrize("case", ["tiny_plain", "tiny_geo_mixed"])
 @pytest.mark.parametrize("obs_f16", [False, True])
 def test_embed(native, case, obs_f16):
