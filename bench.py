@@ -568,6 +568,45 @@ def run_kernel(args):
         out = torch.empty(envs * 29, d, dtype=torch.float16, device="cuda")
         flops, nbytes = 4.0 * envs * 29 * 29 * d, envs * 29 * d * 8
         run = lambda: nat.check(nat.lib.bsrl_attention(qkv.data_ptr(), kb.data_ptr(), envs, d, d // 32, 0, 29, out.data_ptr(), st))
+    elif args.kernel == "attention_tokens":      # the single-body-token layout's attention: 33 tokens per env
+        T = 33
+        envs = rows // T
+        qkv = rnd(envs * T, 3 * d).half()
+        kb = torch.zeros(envs, T).cuda()
+        out = torch.empty(envs * T, d, dtype=torch.float16, device="cuda")
+        flops, nbytes = 4.0 * envs * T * T * d, envs * T * d * 8
+        run = lambda: nat.check(nat.lib.bsrl_attention_tokens(qkv.data_ptr(), kb.data_ptr(), envs, T, d, d // 32, 0, T, out.data_ptr(), st))
+    elif args.kernel == "wgrad":      # weight gradient of one Linear: g^T x over the token rows (split-K, MN-major operands)
+        n, k = args.cols or 4 * d, d
+        gy, x = rnd(rows, n, scale=0.5).half(), rnd(rows, k).half()
+        gw = torch.zeros(n, k, device="cuda")
+        n_s = nat.lib.bsrl_linear_bwd_scratch_bytes(rows, n, k)
+        scratch = torch.empty(n_s, dtype=torch.uint8, device="cuda")
+        flops, nbytes = 2.0 * rows * n * k, rows * (n + k) * 2 + n * k * 4
+        run = lambda: nat.check(nat.lib.bsrl_linear_bwd(gy.data_ptr(), x.data_ptr(), None, rows, n, k, gw.data_ptr(), None, None, 0,
+                                                        scratch.data_ptr(), n_s, st))
+    elif args.kernel == "update":     # one PPO update step (grad-mode forward + backward) on rows / 29 envs of the cfg2 model
+        from beatsaberrl_b200.policy import NotePolicy
+        from oracle import policy_oracle as po
+        cfg = po.named_config("cfg2")
+        pol = NotePolicy(**cfg.ref_kwargs())
+        pol.load_state_dict(po.build_state_dict(cfg, 1, xavier=True))
+        pol = pol.cuda()
+        pol.flatten_fp16()
+        envs = rows // 29
+        obs = po.make_obs(envs, 3).cuda()
+        act = po.make_actions(envs, cfg, 5).to(torch.uint8).cuda()
+        up = {k_: v.cuda() for k_, v in po.make_upstream(envs, cfg, 6).items()}
+        flops, nbytes = 6.0 * po.mac_per_env(cfg) * envs, 0.0
+
+        def run():
+            with torch.enable_grad():
+                _, lp, ent, val = pol.get_action_and_value(obs, act)
+                loss = (up["logprob"] * lp).sum() + (up["entropy"] * ent).sum() + (up["value"] * val).sum() \
+                    + (up["value_logits"] * pol._value_logits).sum()
+                loss.backward()
+            for p_ in pol.parameters():
+                p_.grad = None
     elif args.kernel in ("embed", "head_tail"):
         import ctypes as C
         from beatsaberrl_b200.policy import NotePolicy
@@ -634,7 +673,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--no-recompute", action="store_true", help="skip the cfg5 PPO-recompute sub-record")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip the reference's GPU stream (1-GPU runs)")
-    ap.add_argument("--kernel", default="", choices=("", "block_tail", "attn_block", "linear", "layernorm", "attention", "embed", "head_tail"),
+    ap.add_argument("--kernel", default="", choices=("", "block_tail", "attn_block", "linear", "layernorm", "attention", "embed", "head_tail",
+                                                   "attention_tokens", "wgrad", "update"),
                     help="time one kernel alone on --rows token rows instead of the whole forward")
     ap.add_argument("--rows", type=int, default=237568)
     ap.add_argument("--embed", type=int, default=256)
