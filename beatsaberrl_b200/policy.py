@@ -168,10 +168,10 @@ class NotePolicy(nn.Module):
         assert encoder == "transformer", f"unknown encoder: {encoder}"
         assert n_gears in (3, 5, 7), f"n_gears must be 3/5/7, got {n_gears}"
         assert value_bins > 1, f"value_bins must be > 1, got {value_bins}"
-        # options of the reference that change the forward and are not built here
-        if fp16_accum != "off":     # the one option of the reference's forward that is not built
-            raise NotImplementedError("NotePolicy option fp16_accum is not built in this library "
-                                      "(accumulation is always fp32)")
+        # fp16_accum ("fwd" / "all") is a PERMISSION in the reference: it lets cuBLAS accumulate its fp16 GEMMs in
+        # fp16 where that is faster (python/fp16_linear.py:84-131).  The tensor cores used here accumulate fp16
+        # products in fp32 at full rate, so the mode is accepted, recorded in `arch` like the reference does, and
+        # changes nothing: results stay at least as close to the fp32 forward as the reference's own.
         if head_gears is None:
             head_gears = (n_gears,) * N_ACTION_HEADS
         head_gears = tuple(int(k) for k in head_gears)

@@ -112,8 +112,10 @@ def test_policy_facade_host_side(native):
     assert m.mac_per_env() == po.mac_per_env(cfg)
     with pytest.raises(RuntimeError):   # no CPU path
         m.forward_stacked(torch.zeros(2, 630))
-    with pytest.raises(NotImplementedError):
-        NotePolicy(fp16_accum="all")
+    acc = NotePolicy(fp16_accum="all")      # a permission for cuBLAS in the reference: accepted, recorded, fp32 accumulation kept
+    assert acc.arch["fp16_accum"] == "all" and acc.fp16_accum == "all"
+    with pytest.raises(ValueError):
+        NotePolicy(fp16_accum="sometimes")
     with pytest.raises(ValueError):
         NotePolicy(trunk_arch="mlp")
     with pytest.raises(ValueError):
