@@ -119,9 +119,10 @@ int fused_tail(const BlockTailArgs& a, cudaStream_t st) {
 int fused_attn(const AttnBlockArgs& a, cudaStream_t st) {
   int keep = g_stage;
   g_stage = kStAttnBlock;
-  const double rows = (double)a.n_envs * kT;
-  double fl = 2.0 * rows * 3.0 * a.d * a.d + 4.0 * a.n_envs * a.n_q * kT * a.d;
-  double by = rows * a.d * 2 + (double)a.n_envs * a.n_q * a.d * 2 + (double)a.n_envs * kT * 4;
+  const int tokens = a.body ? a.tokens : kT;
+  const double rows = (double)a.n_envs * tokens;
+  double fl = 2.0 * rows * 3.0 * a.d * a.d + 4.0 * a.n_envs * a.n_q * tokens * a.d;
+  double by = rows * a.d * 2 + (double)a.n_envs * a.n_q * a.d * 2 + (double)a.n_envs * tokens * 4;
   int rc = timed(st, fl, by, [&] { return attn_block(a, st); });
   g_stage = keep;
   return rc;
@@ -973,6 +974,19 @@ int bsrl_qkv_attention(const void* h_f16, const void* w_grouped_f16, const float
   a.wg = static_cast<const __half*>(w_grouped_f16); a.bg = b_grouped;
   a.key_bias = key_bias; a.q_first = q_first; a.n_q = n_q;
   a.out = static_cast<__half*>(out_f16); a.ldo = d;
+  return attn_block(a, as_stream(stream));
+}
+
+int bsrl_qkv_attention_body(const void* h_f16, const void* w_grouped_f16, const float* b_grouped, const void* qkv0_f16,
+                            const float* key_bias, int64_t n_envs, int32_t d, int32_t n_heads, int32_t n_q, void* out_f16,
+                            void* stream) {
+  AttnBlockArgs a;
+  a.d = d; a.n_heads = n_heads; a.n_envs = n_envs;
+  a.h = static_cast<const __half*>(h_f16); a.ldh = d;
+  a.wg = static_cast<const __half*>(w_grouped_f16); a.bg = b_grouped;
+  a.key_bias = key_bias; a.q_first = 0; a.n_q = n_q;
+  a.out = static_cast<__half*>(out_f16); a.ldo = d;
+  a.body = 1; a.tokens = 33; a.qkv0 = static_cast<const __half*>(qkv0_f16);
   return attn_block(a, as_stream(stream));
 }
 

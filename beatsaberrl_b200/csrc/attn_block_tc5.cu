@@ -47,7 +47,8 @@ struct Shape {
   static constexpr int LDQ = NG * 2 + 16;        // row pitch of the q|k|v tile: 400 / 304 bytes, ldmatrix conflict-free
   static constexpr int SQ_BYTES = BM * LDQ;
   static constexpr int SO_BYTES = BM * 128;      // attention output of one group: 128 rows x 128 B, 128-byte swizzle
-  static constexpr int SMEM_BYTES = 4 * CHUNK_BYTES + STAGES * STAGE_BYTES + SO_BYTES + SQ_BYTES + 768 * 4 + 1024 + 256;
+  static constexpr int SB_BYTES = EPT * 2 * 3 * 64;   // body-token mode: q0 | k0 | v0 (64 B each) per env and head of the group
+  static constexpr int SMEM_BYTES = 4 * CHUNK_BYTES + STAGES * STAGE_BYTES + SO_BYTES + SQ_BYTES + 768 * 4 + SB_BYTES + 1024 + 256;
   static_assert(NG % 16 == 0 && NG <= 256 && STAGE_BYTES % 1024 == 0, "group width");
 };
 constexpr int KERNEL_ID = 3;
@@ -71,6 +72,11 @@ struct Params {
   const __half* v0;
   const float* vres;
   int out_tma;             // the group's output leaves as one TMA store from shared memory (all 29 query rows, two heads of 32)
+  // single-body-token layout (BODY kernels): envs of `tokens` = 33 rows; rows 1..32 (the object tokens) are the env's
+  // 32 tile rows, row 0 (the body token) comes projected from qkv0 (n_envs, 3d: q | k | v in the plain column
+  // order) and is folded in beside the MMA tiles; body_only: only the body token's output row is wanted
+  int tokens, tok0, body_only;
+  const __half* qkv0;
   int* status;
 };
 
@@ -95,9 +101,13 @@ __device__ __forceinline__ float rcp_approx(float x) {
 // The MT 16-row query tiles are processed side by side: two independent dependency chains per warp
 // (the kernel is latency-bound here) and each K / V fragment is fetched once for both.
 // OB: bytes per row of the staged group output (128: two heads of 32, swizzled; 96: one head of 48, dense)
-template <int MT, int DH, int LDQ, int OB>
+// BODY: one more key outside the tile (the body token): x_lane = q_row . k_0 for row `lane` (raw), kb0 its
+// base-2 key bias, v0 its DH values (shared memory, generic pointer); its score joins each row's softmax and its
+// probability times v_0 starts the row's output.
+template <int MT, int DH, int LDQ, int OB, bool BODY = false>
 __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t sv, const float (&kb)[4][2],
-                                            int n_q, __half* out_env, int ldo, int lane, uint8_t* so, int so_row0, int so_piece0) {
+                                            int n_q, __half* out_env, int ldo, int lane, uint8_t* so, int so_row0, int so_piece0,
+                                            float x_lane = 0.f, float kb0 = 0.f, const __half* v0 = nullptr) {
   const int g = lane >> 2, tig = lane & 3;
   const float scale = rsqrtf((float)DH) * 1.4426950408889634f;   // 1/sqrt(dh) * log2(e)
   float s[MT][4][4];
@@ -126,9 +136,17 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
     }
   }
   uint32_t pa[MT][2][4];
+  float p0[MT][2];                    // BODY: the body key's probability for rows g and g + 8 of each query tile
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
     float mx[2] = {-INFINITY, -INFINITY};
+    if (BODY) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        p0[mt][r] = fmaf(__shfl_sync(0xffffffffu, x_lane, mt * 16 + g + r * 8), scale, kb0);
+        mx[r] = p0[mt][r];
+      }
+    }
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
@@ -153,7 +171,13 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
     for (int r = 0; r < 2; ++r) {
       sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
       sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
-      sum[r] = rcp_approx(sum[r]);
+      if (BODY) {
+        p0[mt][r] = ex2_approx(p0[mt][r] - mx[r]);
+        sum[r] = rcp_approx(sum[r] + p0[mt][r]);
+        p0[mt][r] *= sum[r];
+      } else {
+        sum[r] = rcp_approx(sum[r]);
+      }
     }
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
@@ -165,11 +189,17 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
   }
   float o[MT][DH / 8][4];
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
+  for (int nt = 0; nt < DH / 8; ++nt) {
+    float2 v = make_float2(0.f, 0.f);
+    if (BODY) v = __half22float2(*reinterpret_cast<const __half2*>(v0 + nt * 8 + tig * 2));
 #pragma unroll
-    for (int nt = 0; nt < DH / 8; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) o[mt][nt][e] = 0.f;
+    for (int mt = 0; mt < MT; ++mt) {
+      o[mt][nt][0] = BODY ? p0[mt][0] * v.x : 0.f;
+      o[mt][nt][1] = BODY ? p0[mt][0] * v.y : 0.f;
+      o[mt][nt][2] = BODY ? p0[mt][1] * v.x : 0.f;
+      o[mt][nt][3] = BODY ? p0[mt][1] * v.y : 0.f;
+    }
+  }
 #pragma unroll
   for (int ks = 0; ks < 2; ++ks) {
 #pragma unroll
@@ -208,7 +238,8 @@ __device__ __forceinline__ void attend_pair(uint32_t sq, uint32_t sk, uint32_t s
 }
 
 // VRES: the value-residual code of the drain is compiled in (it costs ~14 % of the kernel even when idle)
-template <int DH, int G, bool VRES>
+// BODY: the single-body-token layout (Params::tokens and below); DH = 32, G = 2 only
+template <int DH, int G, bool VRES, bool BODY = false>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_w,
                   const __grid_constant__ CUtensorMap tm_o, Params p) {
@@ -222,7 +253,11 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
   uint8_t* sO_g = gen + 4 * CHUNK_BYTES + STAGES * STAGE_BYTES;
   uint8_t* sQ_g = sO_g + S::SO_BYTES;
   float* s_bias = reinterpret_cast<float*>(sQ_g + SQ_BYTES);
-  Shared* sh = reinterpret_cast<Shared*>(sQ_g + SQ_BYTES + 768 * 4);
+  uint8_t* sB_g = sQ_g + SQ_BYTES + 768 * 4;
+  Shared* sh = reinterpret_cast<Shared*>(sB_g + S::SB_BYTES);
+  static_assert(!BODY || (DH == 32 && G == 2 && !VRES), "body-token mode: two heads of 32 per group");
+  constexpr int NKEYS = BODY ? EROWS : kT;            // live keys of an env inside the tile
+  const int T = BODY ? p.tokens : kT;                 // token rows per env in memory
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int d = p.d, KB = d >> 6, n_groups = d / GD;
   volatile int* abort = &sh->abort;
@@ -279,7 +314,7 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
           if (!mbar_wait(smem_u32(&sh->a_free[kb]), (tile_i & 1) ^ 1, abort)) { give_up(sh, p.status, 2); ok = false; break; }
           const uint32_t bar = smem_u32(&sh->a_full[kb]);
           mbar_expect_tx(bar, CHUNK_BYTES);
-          tma_load_3d(sA + kb * CHUNK_BYTES, &tm_h, 64 * kb, 0, t * EPT, bar);
+          tma_load_3d(sA + kb * CHUNK_BYTES, &tm_h, 64 * kb, BODY ? p.tok0 : 0, t * EPT, bar);
           ok = w_stage(0, kb);
         }
         for (int g = 1; g < n_groups && ok; ++g)
@@ -359,10 +394,20 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int key = nt * 8 + (lane & 3) * 2 + e;
-          kb[nt][e] = (key < kT && env < p.n_envs) ? p.key_bias[env * kT + key] * 1.4426950408889634f : -INFINITY;
+          kb[nt][e] = (key < NKEYS && env < p.n_envs) ? p.key_bias[env * T + (BODY ? p.tok0 : 0) + key] * 1.4426950408889634f : -INFINITY;
         }
+      // body-token mode: the body key's bias, and this lane's object key's (lane = key in the body row's softmax)
+      float kb0 = 0.f, kbl = 0.f;
+      if (BODY && env < p.n_envs) {
+        kb0 = p.key_bias[env * T] * 1.4426950408889634f;
+        kbl = p.key_bias[env * T + 1 + lane] * 1.4426950408889634f;
+      }
       for (int g = 0; g < n_groups && ok; ++g, ++gi) {
         const int buf = gi & 1;
+        // body token's q0 | k0 | v0 of this warp's head: lanes 0..11 fetch one 16-byte piece each, long before use
+        uint4 b0v = make_uint4(0, 0, 0, 0);
+        if (BODY && lane < 12 && env < p.n_envs)
+          b0v = *reinterpret_cast<const uint4*>(p.qkv0 + env * 3 * (int64_t)d + (lane >> 2) * d + (g * G + hh) * DH + (lane & 3) * 8);
         // A failed wait must not leave other workers stuck at the CTA-level barriers below: the
         // warp keeps going (on garbage) and everyone leaves together once one thread has sampled
         // the abort flag ahead of a barrier.
@@ -419,6 +464,7 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
             put16(r, u);
           }
         }
+        if (BODY && lane < 12) *reinterpret_cast<uint4*>(sB_g + ((env_l * 2 + hh) * 3 + (lane >> 2)) * 64 + (lane & 3) * 16) = b0v;
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[buf]));     // the TMEM buffer may be refilled
@@ -438,15 +484,60 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
           __half* out_pair = p.out + (env * p.n_q + mt_own * 16) * (int64_t)p.ldo + (g * G + hh) * DH;
           const int n_q = p.n_q - mt_own * 16;      // query rows left from this warp's first one
           uint8_t* so_tile = p.out_tma ? sO_g : nullptr;
-          if (G == 2 && n_q > 16) attend_pair<2, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * EROWS + mt_own * 16, hh * (DH / 8));
-          else if (n_q > 0) attend_pair<1, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * EROWS + mt_own * 16, hh * (DH / 8));
+          if constexpr (BODY) {
+            // ---- the body token beside the tile (one warp = one head of the env's group)
+            const uint8_t* rows_g = sQ_g + (env_l * EROWS) * LDQ;
+            const uint8_t* sb = sB_g + (env_l * 2 + hh) * 192;           // q0 at +0, k0 at +64, v0 at +128
+            const float scale = rsqrtf((float)DH) * 1.4426950408889634f;
+            float x_lane = 0.f, sc = 0.f, s00 = 0.f;
+#pragma unroll
+            for (int ch = 0; ch < DH / 8; ++ch) {
+              const uint4 q0v = *reinterpret_cast<const uint4*>(sb + ch * 16);
+              const uint4 k0v = *reinterpret_cast<const uint4*>(sb + 64 + ch * 16);
+              const uint4 qv = *reinterpret_cast<const uint4*>(rows_g + lane * LDQ + (hh * DH) * 2 + ch * 16);
+              const uint4 kv = *reinterpret_cast<const uint4*>(rows_g + lane * LDQ + (GD + hh * DH) * 2 + ch * 16);
+              const __half2* q0h = reinterpret_cast<const __half2*>(&q0v);
+              const __half2* k0h = reinterpret_cast<const __half2*>(&k0v);
+              const __half2* qh = reinterpret_cast<const __half2*>(&qv);
+              const __half2* kh = reinterpret_cast<const __half2*>(&kv);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 a0 = __half22float2(q0h[e]), b0 = __half22float2(k0h[e]);
+                const float2 a = __half22float2(qh[e]), b = __half22float2(kh[e]);
+                x_lane = fmaf(a.x, b0.x, fmaf(a.y, b0.y, x_lane));       // object row `lane` against the body key
+                sc = fmaf(a0.x, b.x, fmaf(a0.y, b.y, sc));               // body row against object key `lane`
+                s00 = fmaf(a0.x, b0.x, fmaf(a0.y, b0.y, s00));           // body row against the body key
+              }
+            }
+            {   // the body token's own output row: softmax over the 32 object keys (one per lane) and the body key
+              sc = fmaf(sc, scale, kbl);
+              s00 = fmaf(s00, scale, kb0);
+              const float mx = fmaxf(warp_max(sc), s00);
+              const float pj = ex2_approx(sc - mx), p00 = ex2_approx(s00 - mx);
+              const float inv = rcp_approx(warp_sum(pj) + p00);
+              const __half* v0h = reinterpret_cast<const __half*>(sb + 128);
+              const uint8_t* vcol = rows_g + (2 * GD + hh * DH) * 2 + lane * 2;      // column `lane` of the head's v rows
+              float acc = p00 * __half2float(v0h[lane]);
+#pragma unroll 8
+              for (int j = 0; j < EROWS; ++j)
+                acc = fmaf(__shfl_sync(0xffffffffu, pj, j), __half2float(*reinterpret_cast<const __half*>(vcol + j * LDQ)), acc);
+              __half* orow = p.out + (env * (p.body_only ? 1 : T)) * (int64_t)p.ldo + (g * G + hh) * DH;
+              orow[lane] = __float2half_rn(acc * inv);
+            }
+            if (!p.body_only)
+              attend_pair<2, DH, LDQ, GD * 2, true>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile,
+                                                    env_l * EROWS, hh * (DH / 8), x_lane, kb0, reinterpret_cast<const __half*>(sb + 128));
+          } else {
+            if (G == 2 && n_q > 16) attend_pair<2, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * EROWS + mt_own * 16, hh * (DH / 8));
+            else if (n_q > 0) attend_pair<1, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * EROWS + mt_own * 16, hh * (DH / 8));
+          }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh->attn_done[buf]));
         if (p.out_tma) fence_proxy_async_smem();                         // this thread's sO writes -> the TMA engine
         pair_sync();                                                     // the env's rows may be overwritten
         if (p.out_tma && half == 0 && lane == 0 && env < p.n_envs) {     // token rows 29..31 of the box are clipped
-          tma_store_3d(&tm_o, g * GD, 0, (int)env, sO + (uint32_t)(q * EROWS) * (uint32_t)(GD * 2));
+          tma_store_3d(&tm_o, g * GD, BODY ? p.tok0 : 0, (int)env, sO + (uint32_t)(q * EROWS) * (uint32_t)(GD * 2));
           bulk_commit();
         }
       }
@@ -469,8 +560,12 @@ bool attn_block_ok(const AttnBlockArgs& a) {
   const int dh = a.d / a.n_heads;
   if (!((dh == 32 && a.n_heads % 2 == 0) || dh == 48)) return false;
   if (a.n_envs < 1 || a.n_envs > 0x7fffffffLL / (BM * 2)) return false;
-  if (a.q_first < 0 || a.n_q < 1 || a.q_first + a.n_q > kT) return false;
   if (!aligned16(a.h) || !aligned16(a.wg) || !aligned16(a.bg) || !aligned16(a.out) || (a.ldh % 8) || (a.ldo % 8)) return false;
+  if (a.body) {      // one body token + 32 object tokens per env; all rows out, or the body row only
+    if (dh != 32 || a.tokens != EROWS + 1 || !a.qkv0 || !aligned16(a.qkv0) || a.v_out || a.v0) return false;
+    return a.q_first == 0 && (a.n_q == a.tokens || a.n_q == 1);
+  }
+  if (a.q_first < 0 || a.n_q < 1 || a.q_first + a.n_q > kT) return false;
   return true;
 }
 
@@ -480,40 +575,47 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
     return BSRL_ERR_NULL;
   }
   if (!attn_block_ok(a)) {
-    set_error("attn_block: shape d=%d heads=%d does not fit the fused kernel (head_dim 32 or 48, d <= 256)", a.d, a.n_heads);
+    set_error("attn_block: shape d=%d heads=%d tokens=%d does not fit the fused kernel (head_dim 32 or 48, d <= 256; body-token "
+              "layout: head_dim 32, 33 tokens)", a.d, a.n_heads, a.body ? a.tokens : kT);
     return BSRL_ERR_UNSUPPORTED;
   }
   int* status = device_status_ptr();
   if (!status) return BSRL_ERR_CUDA;
   const int dh = a.d / a.n_heads;
+  const int T = a.body ? a.tokens : kT;
   CUtensorMap tm_h, tm_w;
-  if (!make_tmap_env3d(&tm_h, a.h, a.n_envs, kT, a.d, a.ldh, 64, EROWS, EPT)) return BSRL_ERR_CUDA;
+  if (!make_tmap_env3d(&tm_h, a.h, a.n_envs, T, a.d, a.ldh, 64, EROWS, EPT)) return BSRL_ERR_CUDA;
   if (!make_tmap_f16(&tm_w, a.wg, 3 * a.d, a.d, a.d, dh == 32 ? Shape<32, 2>::NG : Shape<48, 1>::NG)) return BSRL_ERR_CUDA;
-  // all 29 query rows: an env's output for a group is 29 contiguous rows x 128 (two heads of 32) or 96 bytes (one of 48) = one TMA store
-  const bool out_tma = a.q_first == 0 && a.n_q == kT;
+  // all query rows: an env's output for a group is contiguous rows x 128 (two heads of 32) or 96 bytes (one of 48) = one TMA store
+  const bool out_tma = a.q_first == 0 && a.n_q == T;
   CUtensorMap tm_o = tm_h;
-  if (out_tma && !make_tmap_env3d(&tm_o, a.out, a.n_envs, kT, a.d, a.ldo, dh == 32 ? 64 : 48, EROWS, 1)) return BSRL_ERR_CUDA;
+  if (out_tma && !make_tmap_env3d(&tm_o, a.out, a.n_envs, T, a.d, a.ldo, dh == 32 ? 64 : 48, EROWS, 1)) return BSRL_ERR_CUDA;
   static DeviceOnce once;
   int rc = once.run("attn_block_kernel set-up", [] {
     const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
     cudaError_t e = cudaFuncSetAttribute(attn_block_kernel<32, 2, false>, at, Shape<32, 2>::SMEM_BYTES);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_block_kernel<32, 2, true>, at, Shape<32, 2>::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_block_kernel<32, 2, false, true>, at, Shape<32, 2>::SMEM_BYTES);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_block_kernel<48, 1, false>, at, Shape<48, 1>::SMEM_BYTES);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_block_kernel<48, 1, true>, at, Shape<48, 1>::SMEM_BYTES);
     return e;
   });
   if (rc != BSRL_OK) return rc;
   Params p;
-  p.d = a.d; p.n_heads = a.n_heads; p.q_first = a.q_first; p.n_q = a.n_q;
+  p.d = a.d; p.n_heads = a.n_heads;
+  p.q_first = a.body ? 0 : a.q_first;
+  p.n_q = a.body ? EROWS : a.n_q;                 // body-token layout: the tile's query rows are the 32 object tokens
   p.n_envs = a.n_envs;
   p.n_tiles = (int)((a.n_envs + EPT - 1) / EPT);
   p.bias = a.bg; p.key_bias = a.key_bias; p.out = a.out; p.ldo = a.ldo;
   p.v_out = a.v_out; p.v0 = a.v0; p.vres = a.vres;
   p.out_tma = out_tma ? 1 : 0;
+  p.tokens = T; p.tok0 = a.body ? 1 : 0; p.body_only = (a.body && a.n_q == 1) ? 1 : 0; p.qkv0 = a.qkv0;
   p.status = status;
   const int grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
   const bool vres = a.v_out || a.v0;
-  if (dh == 32 && !vres) attn_block_kernel<32, 2, false><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
+  if (a.body) attn_block_kernel<32, 2, false, true><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
+  else if (dh == 32 && !vres) attn_block_kernel<32, 2, false><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
   else if (dh == 32) attn_block_kernel<32, 2, true><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
   else if (!vres) attn_block_kernel<48, 1, false><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
   else attn_block_kernel<48, 1, true><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);

@@ -89,6 +89,12 @@ struct AttnBlockArgs {
   __half* v_out = nullptr;
   const __half* v0 = nullptr;
   const float* vres = nullptr;
+  // Single-body-token layout: envs of `tokens` = 33 rows in h / key_bias / out; the 32 object tokens (rows 1..32)
+  // are the env's tile, the body token (row 0) is folded in from qkv0 (n_envs, 3d) f16 = its q | k | v in the
+  // plain column order (a small projection the caller runs first).  n_q = tokens: out (n_envs*tokens, ldo);
+  // n_q = 1: the body row only, out (n_envs, ldo).
+  int body = 0, tokens = 29;
+  const __half* qkv0 = nullptr;
 };
 // v columns of a packed projection: copy out (v_out) and / or mix with v0 in place (value residual)
 int vres_mix(__half* v, int ld, int64_t rows, int d, __half* v_out, const __half* v0, const float* vres,

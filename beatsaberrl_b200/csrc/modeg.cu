@@ -92,6 +92,10 @@ int validate_g(const bsrl_gconfig* c) {
   return BSRL_OK;
 }
 
+// The fused projection + attention kernel covers 33 tokens (one body token + 32 object tokens = one 32-row tile
+// slot per env), head_dim 32 with an even head count, d <= 256.
+bool g_attn_shape(const GLayout& l) { return l.T == 33 && l.d <= 256 && l.d % 64 == 0 && l.d / l.H == 32 && l.H % 2 == 0; }
+
 GLayout make_glayout(const bsrl_gconfig& c) {
   GLayout l;
   l.d = c.embed; l.H = c.n_heads; l.L = c.n_blocks; l.F = c.ffn_mult * c.embed;
@@ -115,6 +119,7 @@ GLayout make_glayout(const bsrl_gconfig& c) {
     b.ln_ffn = carve_norm(cv, d);
     b.up = carve_mat(cv, l.F, d, d, l.F);
     b.down = carve_mat(cv, d, l.F, l.F, d);
+    if (g_attn_shape(l)) b.qkv_g = carve_mat(cv, 3 * d, d, d, 3 * d);   // rows regrouped per pair of heads
   }
   l.heads = carve_mat(cv, l.n_cols, d, d, l.cols_pad);
   l.bytes = cv.off;
@@ -151,7 +156,33 @@ std::vector<ParamSlot> g_slots(const GLayout& l) {
   return s;
 }
 
-GWorkspace make_gws(const GLayout& l, int64_t B, bool tail_fused) {
+// second destinations of q / k / v rows: the per-head-pair regrouped copy the fused attention kernel reads
+std::vector<CopySlot> g_copy_slots(const GLayout& l, const std::vector<ParamSlot>& params) {
+  std::vector<CopySlot> out;
+  if (!g_attn_shape(l)) return out;
+  auto find = [&](const std::string& name) {
+    for (size_t i = 0; i < params.size(); ++i)
+      if (params[i].name == name) return (int)i;
+    return -1;
+  };
+  const int d = l.d, gd = 64, n_groups = d / gd;
+  for (int i = 0; i < l.L; ++i) {
+    const std::string p = "blocks." + std::to_string(i);
+    const std::string names[3] = {p + ".q_proj", p + ".k_proj", p + ".v_proj"};
+    const Mat& m = l.blocks[i].qkv_g;
+    for (int sct = 0; sct < 3; ++sct) {
+      const int pw = find(names[sct] + ".weight"), pb = find(names[sct] + ".bias");
+      for (int g = 0; g < n_groups; ++g) {
+        const int64_t row = (int64_t)g * 3 * gd + sct * gd;
+        out.push_back({pw, (int64_t)g * gd, gd, d, m.w + row * m.pitch * 2, m.pitch, true});
+        out.push_back({pb, (int64_t)g * gd, gd, 1, m.b + row * 4, 0, false});
+      }
+    }
+  }
+  return out;
+}
+
+GWorkspace make_gws(const GLayout& l, int64_t B, bool tail_fused, bool attn_fused) {
   GWorkspace w;
   Carve cv;
   const int64_t R = B * l.T;
@@ -161,7 +192,7 @@ GWorkspace make_gws(const GLayout& l, int64_t B, bool tail_fused) {
   w.f_obj = cv.take(B * (int64_t)l.n_obj * l.obj_k * 2);
   w.x = cv.take(R * d * 4);
   w.h = cv.take(R * d * 2);
-  w.qkv = cv.take(R * 3 * d * 2);
+  w.qkv = cv.take((attn_fused ? B : R) * 3 * d * 2);    // fused attention: only the body rows' projection
   w.att = cv.take(R * d * 2);
   w.hid = tail_fused ? -1 : cv.take(R * (int64_t)l.F * 2);
   w.x_lead = cv.take(B * d * 4);
@@ -172,6 +203,7 @@ GWorkspace make_gws(const GLayout& l, int64_t B, bool tail_fused) {
   return w;
 }
 
+bool g_attn_fused(const GLayout& l, int engine) { return engine == 0 && g_attn_shape(l); }
 bool g_tail_fused(const GLayout& l, int engine) {
   return engine == 0 && l.d % 64 == 0 && l.d <= 256 && l.F % 256 == 0 && l.F >= 256 && l.F <= 1024;
 }
@@ -204,7 +236,7 @@ struct GCtx {
   const void* arena;
   void* ws;
   int64_t B;
-  bool fused;
+  bool fused, attn_fused;
   cudaStream_t st;
   const __half* W(const Mat& m, int row0 = 0) const { return at<__half>(arena, m.w) + (int64_t)row0 * m.pitch; }
   const float* Bv(const Mat& m, int row0 = 0) const { return at<float>(arena, m.b) + row0; }
@@ -262,6 +294,21 @@ int g_forward(const GCtx& c, const float* obs, const HeadTailArgs& tail_in) {
     a.gelu = 1;
     return a;
   };
+  // q|k|v projection + attention of block b for n_q = T (all rows) or 1 (the body row) query rows per env
+  auto project_attend = [&](const BlockW& b, int n_q) -> int {
+    // the body rows' own projection (B x 3d), then one kernel for the object rows' projection and all the attention
+    set_stage(kStQkv);
+    // (the body rows of h are every T-th row: a dense matrix of pitch T d)
+    BSRL_TRY(linear(linear_args(h, T * d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, B, 3 * d, d), st));
+    AttnBlockArgs a;
+    a.d = d; a.n_heads = l.H; a.n_envs = B;
+    a.h = h; a.ldh = d;
+    a.wg = c.W(b.qkv_g); a.bg = c.Bv(b.qkv_g);
+    a.key_bias = key_bias; a.q_first = 0; a.n_q = n_q;
+    a.out = att; a.ldo = d;
+    a.body = 1; a.tokens = T; a.qkv0 = qkv;
+    return fused_attn(a, st);
+  };
   auto attend = [&](int n_q) -> int {        // masked attention of n_q query rows per env over its T tokens
     set_stage(kStAttention);
     return timed_call(st, 4.0 * B * n_q * T * d, (double)B * (T * 2 * d + n_q * d * 2) * 2 + (double)B * T * 4,
@@ -271,9 +318,13 @@ int g_forward(const GCtx& c, const float* obs, const HeadTailArgs& tail_in) {
   for (int i = 0; i + 1 < l.L; ++i) {
     const BlockW& b = l.blocks[i];
     if (!have_h) BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, st));
-    set_stage(kStQkv);
-    BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, R, 3 * d, d), st));
-    BSRL_TRY(attend(T));
+    if (c.attn_fused) {
+      BSRL_TRY(project_attend(b, T));
+    } else {
+      set_stage(kStQkv);
+      BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, R, 3 * d, d), st));
+      BSRL_TRY(attend(T));
+    }
     if (c.fused) {
       BlockTailArgs a = tail_args(b, R);
       a.x_out = x;
@@ -302,12 +353,16 @@ int g_forward(const GCtx& c, const float* obs, const HeadTailArgs& tail_in) {
   {
     const BlockW& b = l.blocks[l.L - 1];
     if (!have_h) BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h, d, st));
-    set_stage(kStQkv);
-    BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv, d), d, c.Bv(b.qkv, d), qkv + d, 3 * d, 0, 0, R, 2 * d, d), st));
-    LinearArgs pq = linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, B, d, d);
-    pq.amap = body_rows; pq.cmap = body_rows;
-    BSRL_TRY(linear(pq, st));
-    BSRL_TRY(attend(1));
+    if (c.attn_fused) {
+      BSRL_TRY(project_attend(b, 1));
+    } else {
+      set_stage(kStQkv);
+      BSRL_TRY(linear(linear_args(h, d, c.W(b.qkv, d), d, c.Bv(b.qkv, d), qkv + d, 3 * d, 0, 0, R, 2 * d, d), st));
+      LinearArgs pq = linear_args(h, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, B, d, d);
+      pq.amap = body_rows; pq.cmap = body_rows;
+      BSRL_TRY(linear(pq, st));
+      BSRL_TRY(attend(1));
+    }
     if (c.fused) {
       BlockTailArgs a = tail_args(b, B);
       a.xmap = body_rows;
@@ -359,7 +414,8 @@ int make_gctx(GCtx& c, const bsrl_gconfig* cfg, const void* arena, int64_t n_env
   c.cfg = cfg;
   c.l = make_glayout(*cfg);
   c.fused = g_tail_fused(c.l, process_engine());
-  c.w = make_gws(c.l, n_envs, c.fused);
+  c.attn_fused = g_attn_fused(c.l, process_engine());
+  c.w = make_gws(c.l, n_envs, c.fused, c.attn_fused);
   if (ws_bytes < c.w.bytes) {
     set_error("g_forward: workspace %lld bytes < required %lld", (long long)ws_bytes, (long long)c.w.bytes);
     return BSRL_ERR_WORKSPACE;
@@ -443,14 +499,14 @@ int bsrl_g_pack_weights(const bsrl_gconfig* cfg, const float* const* params, int
     }
   cudaStream_t st = as_stream(stream);
   BSRL_CUDA_OK(cudaMemsetAsync(arena, 0, l.bytes, st));
-  return multi_pack_slots(s, {}, const_cast<float* const*>(params), nullptr, nullptr, nullptr, nullptr, nullptr, 0.f, 0.f, 0.f, 0,
+  return multi_pack_slots(s, g_copy_slots(l, s), const_cast<float* const*>(params), nullptr, nullptr, nullptr, nullptr, nullptr, 0.f, 0.f, 0.f, 0,
                           nullptr, nullptr, arena, st);
 }
 
 int64_t bsrl_g_workspace_bytes(const bsrl_gconfig* cfg, int64_t n_envs) {
   if (validate_g(cfg) != BSRL_OK || n_envs < 0) return -1;
   const GLayout l = make_glayout(*cfg);
-  return make_gws(l, n_envs, g_tail_fused(l, process_engine())).bytes;
+  return make_gws(l, n_envs, g_tail_fused(l, process_engine()), g_attn_fused(l, process_engine())).bytes;
 }
 
 int bsrl_g_forward(const bsrl_gconfig* cfg, const void* arena, const float* obs, int64_t n_envs, const void* actions,

@@ -339,6 +339,13 @@ int bsrl_attention_tokens(const void* qkv_f16, const float* key_bias, int64_t n_
 int bsrl_qkv_attention(const void* h_f16, const void* w_grouped_f16, const float* b_grouped,
                        const float* key_bias, int64_t n_envs, int32_t d, int32_t n_heads, int32_t q_first,
                        int32_t n_q, void* out_f16, void* stream);
+/* The same for the single-body-token layout with 33 tokens per env (one body token + 32 object tokens): h
+ * (n_envs*33, d), key_bias (n_envs, 33); qkv0 (n_envs, 3d) f16 = the body rows' own projection [q | k | v] in the
+ * plain column order (bsrl_linear on every 33rd row of h).  n_q = 33: out (n_envs*33, d); n_q = 1: the body row
+ * only, out (n_envs, d).  head_dim 32, even head count, d <= 256.  No counterpart kernel in the reference. */
+int bsrl_qkv_attention_body(const void* h_f16, const void* w_grouped_f16, const float* b_grouped, const void* qkv0_f16,
+                            const float* key_bias, int64_t n_envs, int32_t d, int32_t n_heads, int32_t n_q,
+                            void* out_f16, void* stream);
 
 /* Fused tail of one transformer block on a (m, d) token stream, one tcgen05 kernel:
  *   x1 = x + att Wo^T + bo;  xo = x1 + relu(LN(x1; ln_g, ln_b) W0^T + b0) W2^T + b2

@@ -37,6 +37,7 @@ def test_golden_vectors(golden, name):
 @pytest.mark.parametrize("name,geo,xavier,seed,B,padded", [
     ("cfg1", False, False, 0, 1024, False),      # the CPU-reference configuration, whole
     ("cfg2", False, True, 1, 2048, False),       # single-GPU rollout model, Xavier seed 1
+    ("cfg2", False, True, 1, 16384, False),      # the same on 16,384 envs: the argmax gate on 475 K head decisions
     ("cfg2", False, True, 1, 1536, True),        # padded objects: masked attention path
     ("recipe", True, False, 5, 512, True),       # the reference's production shape (head_dim 48, geo)
     ("cfg4", False, False, 3, 256, False),       # wide policy, 7 gears

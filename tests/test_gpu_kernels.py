@@ -215,6 +215,38 @@ def test_qkv_attention(native, B, d, H, q_first, n_q):
     torch.testing.assert_close(out.float().cpu().view(B, n_q, d), ref, atol=5e-3, rtol=3e-3)
 
 
+@pytest.mark.parametrize("B,d,H,n_q", [(4, 64, 2, 33), (37, 128, 4, 33), (601, 256, 8, 33), (601, 256, 8, 1), (5, 128, 4, 1)])
+def test_qkv_attention_body(native, B, d, H, n_q):
+    """Fused projection + attention for 33-token envs (one body token + 32 object tokens): the object tokens are
+    the kernel's tile rows, the body token is folded in from its own small projection.  Against torch fp32 on the
+    same fp16 operands; masked object tokens carry exactly zero weight."""
+    T = 33
+    g = torch.Generator().manual_seed(B + d + n_q)
+    h = torch.randn(B * T, d, generator=g).half()
+    w = (torch.randn(3 * d, d, generator=g) / d ** 0.5).half()
+    bias = torch.randn(3 * d, generator=g) * 0.2
+    n_live = torch.randint(0, T, (B,), generator=g)
+    n_live[0] = 0
+    kb = torch.zeros(B, T)
+    kb[:, 1:] = ((torch.arange(T - 1)[None, :] < n_live[:, None]).float() - 1.0) * 16384.0
+    idx = []
+    for grp in range(d // 64):
+        for sct in range(3):
+            idx += list(range(sct * d + grp * 64, sct * d + grp * 64 + 64))
+    idx = torch.tensor(idx)
+    wg, bg = w[idx].contiguous().cuda(), bias[idx].contiguous().cuda()
+    qkv_ref = (h.float() @ w.float().t() + bias).half()
+    qkv0 = qkv_ref.view(B, T, 3 * d)[:, 0].contiguous().cuda()          # the body rows' own projection
+    out = torch.full((B * n_q, d), float("nan"), dtype=torch.float16, device="cuda")
+    h_d, kb_d = h.cuda(), kb.cuda()
+    native.check(native.lib.bsrl_qkv_attention_body(h_d.data_ptr(), wg.data_ptr(), bg.data_ptr(), qkv0.data_ptr(), kb_d.data_ptr(),
+                                                    B, d, H, n_q, out.data_ptr(), _stream()))
+    native.check(native.lib.bsrl_device_status())
+    q, k, v = qkv_ref.float().view(B, T, 3 * d).split(d, -1)
+    ref = po.attention(q[:, :n_q], k, v, kb, H)
+    torch.testing.assert_close(out.float().cpu().view(B, n_q, d), ref, atol=5e-3, rtol=3e-3)
+
+
 def _native_cfg(native, cfg):
     return native.make_config(cfg.embed, cfg.n_heads, cfg.n_blocks, cfg.ffn_mult, cfg.trunk_dim,
                               cfg.trunk_hidden, cfg.value_bins, cfg.note_geo, cfg.head_gears,
