@@ -102,6 +102,25 @@ def test_cfg2_shape_gradients_and_frozen_parameters():
     _check_grads(m, ref, "cfg2-2blocks", "wide")
 
 
+def test_recipe_shape_gradients():
+    """The reference's production shape (d = 192, four heads of 48, note geometry features), two blocks: the
+    head_dim-48 attention backward and 192 / 384 / 768-wide weight gradients against the gradient oracle."""
+    cfg = make_cfg("recipe", True)
+    cfg.n_blocks = 2
+    cfg.__post_init__()
+    sd = po.build_state_dict(cfg, 5)
+    B = 80
+    obs, act, up = po.make_obs(B, 12, padded=True), po.make_actions(B, cfg, 13), po.make_upstream(B, cfg, 14)
+    ref, ref_loss = oracle_grads(cfg, sd, obs, act, up)
+    m = cuda_policy(cfg, sd)
+    with torch.enable_grad():
+        loss = _loss(m, obs.cuda(), act.cuda(), up)
+        loss.backward()
+    assert abs(float(loss) - ref_loss) <= 2e-2 * max(abs(ref_loss), 1e-3)
+    m.check_device()
+    _check_grads(m, ref, "recipe-2blocks", "wide")
+
+
 # ---- single stages: every backward kernel against torch autograd on identical inputs (no ReLU sign can
 # flip here, so the tolerances are those of fp16 operands with fp32 accumulation)
 import ctypes as C
