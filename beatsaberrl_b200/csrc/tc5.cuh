@@ -1,5 +1,5 @@
 // Blackwell (sm_100a) primitives used by the tcgen05 kernels: mbarrier with bounded waits,
-// TMA tile loads (no cluster multicast anywhere), TMEM allocation, tcgen05.mma / ld / commit,
+// TMA tile loads (each CTA fetches its own tiles; no kernel here uses clusters), TMEM allocation, tcgen05.mma / ld / commit,
 // shared-memory and instruction descriptors.
 #pragma once
 #include <cuda.h>
