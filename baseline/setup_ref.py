@@ -76,7 +76,7 @@ def build() -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("BSRL_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("BSRL_REFERENCE", str(Path(__file__).resolve().parents[2] / "reference")))
     ap.add_argument("--no-build", action="store_true")
     args = ap.parse_args()
     stage(Path(args.reference))

@@ -9,7 +9,8 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 os.environ.setdefault("PYTHONDONTWRITEBYTECODE", "1")
 
-REFERENCE = Path(os.environ.get("BSRL_REFERENCE", "/root/reference"))
+# the reference checkout, where there is one: $BSRL_REFERENCE, else a `reference` directory beside this repository
+REFERENCE = Path(os.environ.get("BSRL_REFERENCE", str(ROOT.parent / "reference")))
 
 
 def pytest_configure(config):
@@ -37,6 +38,9 @@ def native():
     """The ctypes binding; builds the library first if it is missing."""
     lib = ROOT / "beatsaberrl_b200" / "_lib" / "libbsrl.so"
     if not lib.exists():
+        import shutil
+        if shutil.which("nvcc") is None and not Path("/usr/local/cuda/bin/nvcc").exists():
+            pytest.skip("libbsrl.so is not built and there is no nvcc to build it with")
         from beatsaberrl_b200.build import build_library
         build_library()
     from beatsaberrl_b200 import _native

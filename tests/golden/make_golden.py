@@ -1,6 +1,7 @@
 """Generates tests/golden/policy_golden.npz from the REFERENCE implementation.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run in a container that has the reference checkout (default: $BSRL_REFERENCE, else a `reference` directory
+beside this repository):
 
     python tests/golden/make_golden.py [/path/to/reference]
 
@@ -52,7 +53,7 @@ def case_config(cfg_name, geo, hg, opts=None):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BSRL_REFERENCE", str(Path(__file__).resolve().parents[3] / "reference"))
     sys.dont_write_bytecode = True
     sys.path.insert(0, os.path.join(ref, "python"))
     import policy as rp  # the reference module

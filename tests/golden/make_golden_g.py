@@ -32,7 +32,7 @@ CASES = [  # name, config, weight seed, xavier, ln_jitter, B, padded, obs seed
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BSRL_REFERENCE", str(Path(__file__).resolve().parents[3] / "reference"))
     sys.dont_write_bytecode = True
     sys.path.insert(0, os.path.join(ref, "python"))
     import policy as rp  # the reference module
