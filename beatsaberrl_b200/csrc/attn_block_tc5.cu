@@ -38,18 +38,26 @@ constexpr int CHUNK_BYTES = BM * 128;   // 16 KB: 128 rows x 64 k-columns
 constexpr int WORKERS = 8;
 constexpr int THREADS = (2 + WORKERS) * 32;
 // Head group of G heads of width DH: 3 G DH projection columns per group -- (32, 2): 192, two heads;
-// (48, 1): 144, one head (the reference's production shape, 4 heads of 48).
+// (48, 1): 144, one head (the reference's production shape, 4 heads of 48); (64, 1): 192, one head (the wide policy).
 template <int DH_, int G_>
 struct Shape {
   static constexpr int DH = DH_, G = G_, GD = G * DH, NG = 3 * GD;
-  static constexpr int STAGES = DH == 32 ? 3 : 4;
-  static constexpr int STAGE_BYTES = NG * 128;   // NG weight rows x 64 k-columns (24 KB / 18 KB)
+  // STREAM (head_dim 64, d up to 512): the h tile does not stay resident (128 rows x 512 x 2 B = 128 KB); its
+  // 64-column chunks travel through the ring beside the weight chunks, once per head group (from L2 after the first)
+  static constexpr bool STREAM = DH == 64;
+  static constexpr int STAGES = DH == 48 ? 4 : 3;
+  static constexpr int W_BYTES = NG * 128;       // NG weight rows x 64 k-columns (24 KB / 18 KB)
+  static constexpr int STAGE_BYTES = W_BYTES + (STREAM ? CHUNK_BYTES : 0);
+  static constexpr int A_BYTES = STREAM ? 0 : 4 * CHUNK_BYTES;
+  static constexpr int MAX_D = STREAM ? 512 : 256;
   static constexpr int LDQ = NG * 2 + 16;        // row pitch of the q|k|v tile: 400 / 304 bytes, ldmatrix conflict-free
   static constexpr int SQ_BYTES = BM * LDQ;
   static constexpr int SO_BYTES = BM * 128;      // attention output of one group: 128 rows x 128 B, 128-byte swizzle
+  static constexpr int BIAS_BYTES = 3 * MAX_D * 4;
   static constexpr int SB_BYTES = EPT * 2 * 3 * 64;   // body-token mode: q0 | k0 | v0 (64 B each) per env and head of the group
-  static constexpr int SMEM_BYTES = 4 * CHUNK_BYTES + STAGES * STAGE_BYTES + SO_BYTES + SQ_BYTES + 768 * 4 + SB_BYTES + 1024 + 256;
-  static_assert(NG % 16 == 0 && NG <= 256 && STAGE_BYTES % 1024 == 0, "group width");
+  static constexpr int SMEM_BYTES = A_BYTES + STAGES * STAGE_BYTES + SO_BYTES + SQ_BYTES + BIAS_BYTES + SB_BYTES + 1024 + 256;
+  static_assert(NG % 16 == 0 && NG <= 256 && STAGE_BYTES % 1024 == 0 && W_BYTES % 1024 == 0, "group width");
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 };
 constexpr int KERNEL_ID = 3;
 
@@ -249,11 +257,12 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw);
-  const uint32_t sA = base, ring = base + 4 * CHUNK_BYTES, sO = ring + STAGES * STAGE_BYTES, sQ = sO + S::SO_BYTES;
-  uint8_t* sO_g = gen + 4 * CHUNK_BYTES + STAGES * STAGE_BYTES;
+  constexpr bool STREAM = S::STREAM;
+  const uint32_t sA = base, ring = base + S::A_BYTES, sO = ring + STAGES * STAGE_BYTES, sQ = sO + S::SO_BYTES;
+  uint8_t* sO_g = gen + S::A_BYTES + STAGES * STAGE_BYTES;
   uint8_t* sQ_g = sO_g + S::SO_BYTES;
   float* s_bias = reinterpret_cast<float*>(sQ_g + SQ_BYTES);
-  uint8_t* sB_g = sQ_g + SQ_BYTES + 768 * 4;
+  uint8_t* sB_g = sQ_g + SQ_BYTES + S::BIAS_BYTES;
   Shared* sh = reinterpret_cast<Shared*>(sB_g + S::SB_BYTES);
   static_assert(!BODY || (DH == 32 && G == 2 && !VRES), "body-token mode: two heads of 32 per group");
   constexpr int NKEYS = BODY ? EROWS : kT;            // live keys of an env inside the tile
@@ -298,27 +307,33 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
-      auto w_stage = [&](int g, int kb) -> bool {
+      auto w_stage = [&](int g, int kb, int t) -> bool {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
         if (!mbar_wait(smem_u32(&sh->w_empty[s]), ph ^ 1, abort)) { give_up(sh, p.status, 1); return false; }
         const uint32_t bar = smem_u32(&sh->w_full[s]);
         mbar_expect_tx(bar, STAGE_BYTES);
         tma_load_2d(ring + s * STAGE_BYTES, &tm_w, 64 * kb, NG * g, bar);
+        if (STREAM) tma_load_3d(ring + s * STAGE_BYTES + S::W_BYTES, &tm_h, 64 * kb, BODY ? p.tok0 : 0, t * EPT, bar);
         ++it;
         return true;
       };
       for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_i) {
+        if (STREAM) {
+          for (int g = 0; g < n_groups && ok; ++g)
+            for (int kb = 0; kb < KB && ok; ++kb) ok = w_stage(g, kb, t);
+          continue;
+        }
         for (int kb = 0; kb < KB && ok; ++kb) {
           // chunk kb of the h tile is free once the previous tile's last group has used it
           if (!mbar_wait(smem_u32(&sh->a_free[kb]), (tile_i & 1) ^ 1, abort)) { give_up(sh, p.status, 2); ok = false; break; }
           const uint32_t bar = smem_u32(&sh->a_full[kb]);
           mbar_expect_tx(bar, CHUNK_BYTES);
           tma_load_3d(sA + kb * CHUNK_BYTES, &tm_h, 64 * kb, BODY ? p.tok0 : 0, t * EPT, bar);
-          ok = w_stage(0, kb);
+          ok = w_stage(0, kb, t);
         }
         for (int g = 1; g < n_groups && ok; ++g)
-          for (int kb = 0; kb < KB && ok; ++kb) ok = w_stage(g, kb);
+          for (int kb = 0; kb < KB && ok; ++kb) ok = w_stage(g, kb, t);
       }
       // loads in flight must land before the CTA exits (bounded, ignoring abort)
       for (uint32_t j = it > STAGES ? it - STAGES : 0; j < it; ++j) {
@@ -326,7 +341,7 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
         while (!mbar_try_wait(smem_u32(&sh->w_full[j % STAGES]), (j / STAGES) & 1) && ++spins < kSpinLimit) {}
         if (spins >= kSpinLimit) give_up(sh, p.status, 3);
       }
-      if (tile_i > 0)
+      if (!STREAM && tile_i > 0)
         for (int kb = 0; kb < KB; ++kb) {
           uint32_t spins = 0;
           while (!mbar_try_wait(smem_u32(&sh->a_full[kb]), (tile_i - 1) & 1) && ++spins < kSpinLimit) {}
@@ -351,15 +366,16 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * 256;
           for (int kb = 0; kb < KB; ++kb, ++it) {
-            if (g == 0 && !mbar_wait(smem_u32(&sh->a_full[kb]), tile_i & 1, abort)) { give_up(sh, p.status, 6); ok = false; break; }
+            if (!STREAM && g == 0 && !mbar_wait(smem_u32(&sh->a_full[kb]), tile_i & 1, abort)) { give_up(sh, p.status, 6); ok = false; break; }
             const int s = it % STAGES;
             if (!mbar_wait(smem_u32(&sh->w_full[s]), (it / STAGES) & 1, abort)) { give_up(sh, p.status, 7); ok = false; break; }
             tc_fence_after();
-            const uint64_t ad = smem_desc_sw128(sA + kb * CHUNK_BYTES), wd = smem_desc_sw128(ring + s * STAGE_BYTES);
+            const uint64_t ad = smem_desc_sw128(STREAM ? ring + s * STAGE_BYTES + S::W_BYTES : sA + kb * CHUNK_BYTES);
+            const uint64_t wd = smem_desc_sw128(ring + s * STAGE_BYTES);
 #pragma unroll
             for (int k = 0; k < 4; ++k) mma_f16_ss(d_tmem, ad + 2 * k, wd + 2 * k, idesc, (kb | k) != 0);
             tc_commit(smem_u32(&sh->w_empty[s]));
-            if (g == n_groups - 1) tc_commit(smem_u32(&sh->a_free[kb]));
+            if (!STREAM && g == n_groups - 1) tc_commit(smem_u32(&sh->a_free[kb]));
           }
           if (ok) tc_commit(smem_u32(&sh->acc_full[buf]));
         }
@@ -556,9 +572,10 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
 }  // namespace
 
 bool attn_block_ok(const AttnBlockArgs& a) {
-  if (a.d % 64 != 0 || a.d < 64 || a.d > 256 || a.n_heads < 1 || a.d % a.n_heads != 0) return false;
+  if (a.d % 64 != 0 || a.d < 64 || a.n_heads < 1 || a.d % a.n_heads != 0) return false;
   const int dh = a.d / a.n_heads;
-  if (!((dh == 32 && a.n_heads % 2 == 0) || dh == 48)) return false;
+  if (!((dh == 32 && a.n_heads % 2 == 0) || dh == 48 || dh == 64)) return false;
+  if (a.d > (dh == 64 ? Shape<64, 1>::MAX_D : Shape<32, 2>::MAX_D)) return false;
   if (a.n_envs < 1 || a.n_envs > 0x7fffffffLL / (BM * 2)) return false;
   if (!aligned16(a.h) || !aligned16(a.wg) || !aligned16(a.bg) || !aligned16(a.out) || (a.ldh % 8) || (a.ldo % 8)) return false;
   if (a.body) {      // one body token + 32 object tokens per env; all rows out, or the body row only
@@ -575,8 +592,8 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
     return BSRL_ERR_NULL;
   }
   if (!attn_block_ok(a)) {
-    set_error("attn_block: shape d=%d heads=%d tokens=%d does not fit the fused kernel (head_dim 32 or 48, d <= 256; body-token "
-              "layout: head_dim 32, 33 tokens)", a.d, a.n_heads, a.body ? a.tokens : kT);
+    set_error("attn_block: shape d=%d heads=%d tokens=%d does not fit the fused kernel (head_dim 32 or 48 with d <= 256, head_dim "
+              "64 with d <= 512; body-token layout: head_dim 32, 33 tokens)", a.d, a.n_heads, a.body ? a.tokens : kT);
     return BSRL_ERR_UNSUPPORTED;
   }
   int* status = device_status_ptr();
@@ -585,11 +602,11 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
   const int T = a.body ? a.tokens : kT;
   CUtensorMap tm_h, tm_w;
   if (!make_tmap_env3d(&tm_h, a.h, a.n_envs, T, a.d, a.ldh, 64, EROWS, EPT)) return BSRL_ERR_CUDA;
-  if (!make_tmap_f16(&tm_w, a.wg, 3 * a.d, a.d, a.d, dh == 32 ? Shape<32, 2>::NG : Shape<48, 1>::NG)) return BSRL_ERR_CUDA;
+  if (!make_tmap_f16(&tm_w, a.wg, 3 * a.d, a.d, a.d, dh == 48 ? Shape<48, 1>::NG : Shape<32, 2>::NG)) return BSRL_ERR_CUDA;
   // all query rows: an env's output for a group is contiguous rows x 128 (two heads of 32) or 96 bytes (one of 48) = one TMA store
   const bool out_tma = a.q_first == 0 && a.n_q == T;
   CUtensorMap tm_o = tm_h;
-  if (out_tma && !make_tmap_env3d(&tm_o, a.out, a.n_envs, T, a.d, a.ldo, dh == 32 ? 64 : 48, EROWS, 1)) return BSRL_ERR_CUDA;
+  if (out_tma && !make_tmap_env3d(&tm_o, a.out, a.n_envs, T, a.d, a.ldo, dh == 48 ? 48 : 64, EROWS, 1)) return BSRL_ERR_CUDA;
   static DeviceOnce once;
   int rc = once.run("attn_block_kernel set-up", [] {
     const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
@@ -598,6 +615,8 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_block_kernel<32, 2, false, true>, at, Shape<32, 2>::SMEM_BYTES);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_block_kernel<48, 1, false>, at, Shape<48, 1>::SMEM_BYTES);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_block_kernel<48, 1, true>, at, Shape<48, 1>::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_block_kernel<64, 1, false>, at, Shape<64, 1>::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_block_kernel<64, 1, true>, at, Shape<64, 1>::SMEM_BYTES);
     return e;
   });
   if (rc != BSRL_OK) return rc;
@@ -617,8 +636,10 @@ int attn_block(const AttnBlockArgs& a, cudaStream_t stream) {
   if (a.body) attn_block_kernel<32, 2, false, true><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
   else if (dh == 32 && !vres) attn_block_kernel<32, 2, false><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
   else if (dh == 32) attn_block_kernel<32, 2, true><<<grid, THREADS, Shape<32, 2>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
-  else if (!vres) attn_block_kernel<48, 1, false><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
-  else attn_block_kernel<48, 1, true><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
+  else if (dh == 48 && !vres) attn_block_kernel<48, 1, false><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
+  else if (dh == 48) attn_block_kernel<48, 1, true><<<grid, THREADS, Shape<48, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
+  else if (!vres) attn_block_kernel<64, 1, false><<<grid, THREADS, Shape<64, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
+  else attn_block_kernel<64, 1, true><<<grid, THREADS, Shape<64, 1>::SMEM_BYTES, stream>>>(tm_h, tm_w, tm_o, p);
   BSRL_LAUNCH_OK("attn_block_kernel");
   return BSRL_OK;
 }

@@ -203,9 +203,10 @@ Layout make_layout(const bsrl_config& c) {
   // fused QKV+attention kernel: head_dim 32, two heads per group (192 output columns per group), or
   // head_dim 48, one head per group (144 columns)
   l.attn_G = 0;
-  if (d % 64 == 0 && d <= 256 && d % l.H == 0) {
-    if (d / l.H == 32 && l.H % 2 == 0) l.attn_G = 2;
-    else if (d / l.H == 48) l.attn_G = 1;
+  if (d % 64 == 0 && d % l.H == 0) {
+    if (d <= 256 && d / l.H == 32 && l.H % 2 == 0) l.attn_G = 2;
+    else if (d <= 256 && d / l.H == 48) l.attn_G = 1;
+    else if (d <= 512 && d / l.H == 64) l.attn_G = 1;      // the h tile streams through the ring
   }
   l.bytes = cv.off;
   return l;
@@ -309,7 +310,7 @@ std::vector<CopySlot> make_copy_slots(const bsrl_config& c, const Layout& l, con
 Paths plan_paths(const Layout& l, int engine) {
   Paths p;
   const bool widths = engine == 0 && l.d % 64 == 0 && l.d >= 64 && l.d <= 256;
-  p.attn_fused = widths && l.attn_G > 0;
+  p.attn_fused = engine == 0 && l.attn_G > 0;
   p.tail_fused = widths && l.F % 256 == 0 && l.F >= 256 && l.F <= 1024;
   p.enc_fused = widths && !l.emb_ln.width && l.note_k == 64;
   return p;

@@ -186,7 +186,10 @@ def test_block_tail(native, m, d, f, ln_out):
                                                (50, 128, 4, 0, 5), (33, 256, 8, 2, 1), (3000, 256, 8, 0, 29),
                                                # head_dim 48 (one head per group): the production shape
                                                (5, 192, 4, 0, 29), (1001, 192, 4, 0, 29), (70, 192, 4, 0, 5),
-                                               (9, 192, 4, 2, 1)])
+                                               (9, 192, 4, 2, 1),
+                                               # head_dim 64 (one head per group, the h tile streamed): the wide policy
+                                               (3, 64, 1, 0, 29), (50, 512, 8, 0, 29), (1001, 512, 8, 0, 29), (70, 512, 8, 0, 5),
+                                               (9, 512, 8, 2, 1), (33, 256, 4, 0, 29)])
 def test_qkv_attention(native, B, d, H, q_first, n_q):
     """Fused projection + attention kernel against torch fp32 on the same fp16 operands."""
     g = torch.Generator().manual_seed(B + d + n_q)
