@@ -116,6 +116,24 @@ int fused_tail(const BlockTailArgs& a, cudaStream_t st) {
   return rc;
 }
 
+// out-projection + residual + LayerNorm as one kernel where it pays (rows wider than the fused block tail takes, K =
+// d: the kernel is HBM-bound and saves the LayerNorm pass), else as the GEMM and the LayerNorm kernel
+int out_proj_ln(const LinearLnArgs& a, cudaStream_t st) {
+  int keep = g_stage;
+  g_stage = kStOutProj;
+  int rc;
+  if (g_call_engine == 0 && a.N > 256 && a.M >= 128 && linear_ln_ok(a)) {
+    rc = timed(st, 2.0 * a.M * a.N * a.K, (double)a.M * (a.K * 2 + a.N * 10.0), [&] { return linear_ln(a, st); });
+  } else {
+    LinearArgs po = linear_args(a.A, a.lda, a.W, a.ldw, a.bias, a.x_out, (int)a.ldx, 1, 0, a.M, a.N, a.K);
+    po.R = a.R; po.ldr = (int)a.ldr;
+    rc = linear(po, st);
+    if (rc == BSRL_OK) rc = layernorm(a.x_out, a.ldx, identity_map(), a.gamma, a.beta, a.eps, a.M, a.N, a.h, a.ldh, st);
+  }
+  g_stage = keep;
+  return rc;
+}
+
 int fused_attn(const AttnBlockArgs& a, cudaStream_t st) {
   int keep = g_stage;
   g_stage = kStAttnBlock;
@@ -336,12 +354,11 @@ int run_forward(const Ctx& c, const void* obs, int obs_dtype, const HeadTailArgs
       x = x_next;
       continue;
     }
-    LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x_next, d, 1, 0, R, d, d);
-    po.R = x; po.ldr = d;
-    g_stage = kStOutProj;
-    BSRL_TRY(linear(po, c.st));
+    {
+      LinearLnArgs po{att, d, c.W(b.out), d, c.Bv(b.out), x, d, x_next, d, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, h, d, R, d, d};
+      BSRL_TRY(out_proj_ln(po, c.st));
+    }
     x = x_next;
-    BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, R, d, h, d, c.st));
     g_stage = kStFfnUp;
     BSRL_TRY(linear(linear_args(h, d, c.W(b.up), d, c.Bv(b.up), hid, F, 0, 1, R, F, d), c.st));
     LinearArgs pd = linear_args(hid, F, c.W(b.down), F, c.Bv(b.down), x, d, 1, 0, R, d, F);
@@ -975,6 +992,13 @@ int bsrl_qkv_attention(const void* h_f16, const void* w_grouped_f16, const float
   a.key_bias = key_bias; a.q_first = q_first; a.n_q = n_q;
   a.out = static_cast<__half*>(out_f16); a.ldo = d;
   return attn_block(a, as_stream(stream));
+}
+
+int bsrl_linear_ln(const void* a_f16, const void* w_f16, const float* bias, const float* residual, const float* gamma,
+                   const float* beta, float eps, int64_t m, int32_t n, int32_t k, float* x_out, void* h_f16, void* stream) {
+  LinearLnArgs a{static_cast<const __half*>(a_f16), k, static_cast<const __half*>(w_f16), k, bias, residual, n, x_out, n,
+                 gamma, beta, eps, static_cast<__half*>(h_f16), n, m, n, k};
+  return linear_ln(a, as_stream(stream));
 }
 
 int bsrl_qkv_attention_body(const void* h_f16, const void* w_grouped_f16, const float* b_grouped, const void* qkv0_f16,

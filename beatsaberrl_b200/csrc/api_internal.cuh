@@ -73,6 +73,7 @@ void set_stage(int stage);            // label of the launches that follow on th
 int timed_call(cudaStream_t st, double flops, double bytes, const std::function<int()>& fn);
 int fused_tail(const BlockTailArgs& a, cudaStream_t st);
 int fused_attn(const AttnBlockArgs& a, cudaStream_t st);
+int out_proj_ln(const LinearLnArgs& a, cudaStream_t st);
 
 // stage-labelled launch wrappers (timed when the calling thread has the profiler on)
 int linear(const LinearArgs& p, cudaStream_t st);

@@ -44,6 +44,30 @@ int linear_mma(const LinearArgs& p, cudaStream_t stream);   // warp-MMA engine
 int linear_tc5(const LinearArgs& p, cudaStream_t stream);   // tcgen05 / TMEM engine
 bool linear_tc5_ok(const LinearArgs& p);                     // shape fits the tcgen05 engine
 
+// Projection + residual + LayerNorm in one kernel (gemm_ln_tc5.cu): x_out = R + A W^T + bias (fp32), h =
+// LayerNorm(x_out) (fp16).  N a multiple of 64 up to 512 (of 128 above 256), K a multiple of 64.  R and x_out
+// may be the same buffer.
+struct LinearLnArgs {
+  const __half* A;
+  int lda;
+  const __half* W;      // (N, K)
+  int ldw;
+  const float* bias;    // (N) or nullptr
+  const float* R;       // (M, ldr) f32
+  int64_t ldr;
+  float* x_out;         // (M, ldx) f32
+  int64_t ldx;
+  const float* gamma;   // LayerNorm weight / bias (N)
+  const float* beta;
+  float eps;
+  __half* h;            // (M, ldh) f16
+  int64_t ldh;
+  int64_t M;
+  int N, K;
+};
+bool linear_ln_ok(const LinearLnArgs& a);
+int linear_ln(const LinearLnArgs& a, cudaStream_t stream);
+
 // Fused block tail (out-projection + residual + LayerNorm + FFN + residual + output LayerNorms).
 struct BlockTailArgs {
   int d, F;

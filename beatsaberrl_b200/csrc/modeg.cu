@@ -334,11 +334,10 @@ int g_forward(const GCtx& c, const float* obs, const HeadTailArgs& tail_in) {
       have_h = true;
       continue;
     }
-    set_stage(kStOutProj);
-    LinearArgs po = linear_args(att, d, c.W(b.out), d, c.Bv(b.out), x, d, 1, 0, R, d, d);
-    po.R = x; po.ldr = d;
-    BSRL_TRY(linear(po, st));
-    BSRL_TRY(layernorm(x, d, ident, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, R, d, h, d, st));
+    {
+      LinearLnArgs po{att, d, c.W(b.out), d, c.Bv(b.out), x, d, x, d, c.G(b.ln_ffn), c.Be(b.ln_ffn), eps, h, d, R, d, d};
+      BSRL_TRY(out_proj_ln(po, st));
+    }
     set_stage(kStFfnUp);
     BSRL_TRY(linear(linear_args(h, d, c.W(b.up), d, c.Bv(b.up), hid, F, 0, 2, R, F, d), st));
     set_stage(kStFfnDown);

@@ -316,6 +316,13 @@ int bsrl_linear(const void* a_f16, const void* w_f16, const float* bias, const f
                 void* out, int32_t out_f32, int32_t relu, int64_t m, int32_t n, int32_t k,
                 int32_t engine, void* stream);
 
+/* x_out = residual + a @ w^T + bias (fp32) and h = LayerNorm(x_out; gamma, beta, eps) (fp16) in one tcgen05
+ * kernel: a (m, k) f16, w (n, k) f16, residual / x_out (m, n) f32 (may be the same buffer), h (m, n) f16.
+ * n a multiple of 64 up to 512 (of 128 above 256), k a multiple of 64.  (out_proj + ln_ffn.forward_add,
+ * python/policy.py:655-668, for rows wider than the fused block tail takes.) */
+int bsrl_linear_ln(const void* a_f16, const void* w_f16, const float* bias, const float* residual, const float* gamma,
+                   const float* beta, float eps, int64_t m, int32_t n, int32_t k, float* x_out, void* h_f16, void* stream);
+
 /* Masked multi-head attention over 29 keys: qkv (n_envs*29, 3d) f16 packed [q|k|v],
  * key_bias (n_envs, 29) f32, queries = token rows [q_first, q_first + n_q) of each env
  * -> out (n_envs*n_q, d) f16 (attn29_fwd, python/beat_arena_env/csrc/small_attn.cu:515-536;

@@ -250,6 +250,29 @@ def test_qkv_attention_body(native, B, d, H, n_q):
     torch.testing.assert_close(out.float().cpu().view(B, n_q, d), ref, atol=5e-3, rtol=3e-3)
 
 
+@pytest.mark.parametrize("m,n,k,in_place", [(128, 512, 512, False), (1000, 512, 512, True), (4099, 512, 256, False), (300, 256, 256, False),
+                                            (77, 384, 128, True), (20000, 512, 512, True), (513, 64, 64, False)])
+def test_linear_ln(native, m, n, k, in_place):
+    """Projection + residual + LayerNorm kernel against fp32 torch on the same fp16 operands."""
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).half()
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).half()
+    bias = torch.randn(n, generator=g) * 0.3
+    res = torch.randn(m, n, generator=g) * 2.0 + 0.5
+    gamma, beta = 1.0 + 0.2 * torch.randn(n, generator=g), 0.1 * torch.randn(n, generator=g)
+    ref_x = res + a.float() @ w.float().t() + bias
+    ref_h = torch.nn.functional.layer_norm(ref_x, (n,), gamma, beta, 1e-5)
+    res_d = res.cuda()
+    x_out = res_d if in_place else torch.full((m, n), float("nan"), device="cuda")
+    h = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+    a_d, w_d, b_d, g_d, be_d = a.cuda(), w.cuda(), bias.cuda(), gamma.cuda(), beta.cuda()
+    native.check(native.lib.bsrl_linear_ln(a_d.data_ptr(), w_d.data_ptr(), b_d.data_ptr(), res_d.data_ptr(), g_d.data_ptr(),
+                                           be_d.data_ptr(), 1e-5, m, n, k, x_out.data_ptr(), h.data_ptr(), _stream()))
+    native.check(native.lib.bsrl_device_status())
+    torch.testing.assert_close(x_out.cpu(), ref_x, atol=2e-3, rtol=1e-3)
+    torch.testing.assert_close(h.float().cpu(), ref_h, atol=4e-3, rtol=2e-3)
+
+
 def _native_cfg(native, cfg):
     return native.make_config(cfg.embed, cfg.n_heads, cfg.n_blocks, cfg.ffn_mult, cfg.trunk_dim,
                               cfg.trunk_hidden, cfg.value_bins, cfg.note_geo, cfg.head_gears,
