@@ -42,6 +42,19 @@ int attention29_bwd(const __half* qkv, int ld_qkv, const float* key_bias, int64_
                     int n_q, const __half* g_out, int ldgo, __half* gq, int ldq, __half* gk, int ldk, __half* gv, int ldv,
                     cudaStream_t stream);
 
+int vres_mix(__half* v, int ld, int64_t rows, int d, __half* v_out, const __half* v0, const float* vres, cudaStream_t stream);
+int vres_bwd(__half* g, int64_t ldg, const __half* v_own, const __half* v0, const float* ab, float* g_v0, float* g_a, float* g_b,
+             int64_t rows, int d, cudaStream_t stream);
+int add_f32_into_f16(__half* g, int64_t ldg, const float* acc, int64_t rows, int d, cudaStream_t stream);
+int simba2_rows(int mode, const float* in, float* x, const float* vec, float c_alpha, int64_t rows, int d, __half* out16, int64_t ld16,
+                cudaStream_t stream);
+int scale_relu_rows(const float* in, const float* s, int64_t rows, int n, __half* out16, cudaStream_t stream);
+int simba2_out_bwd(const float* x0, const float* t2, const float* alpha, float c_alpha, const float* g_h, float* g_x0, __half* g_t2,
+                   float* g_alpha, int64_t rows, int d, cudaStream_t stream);
+int simba2_in_bwd(const float* t0, const float* s, const float* g_a, const float* g_b, __half* g_t0, float* g_s, int64_t rows, int d,
+                  cudaStream_t stream);
+int scale_relu_bwd(__half* g, const float* t, const float* s, float* g_s, int64_t rows, int n, cudaStream_t stream);
+
 namespace {
 using namespace fwd;
 
@@ -83,10 +96,6 @@ TrainPtrs save_ptrs(const SaveLayout& s, const Layout& l, void* save) {
 }
 
 int train_supported(const bsrl_config* cfg, const Layout& l) {
-  if (cfg->emb_ln || cfg->final_ln || cfg->value_residual || cfg->trunk_v2) {
-    set_error("training entry points: emb_ln / final_ln / value_residual / trunk_v2 have no backward here yet");
-    return BSRL_ERR_UNSUPPORTED;
-  }
   if (l.L > kMaxBlocks) {
     set_error("training entry points: at most %d blocks", kMaxBlocks);
     return BSRL_ERR_UNSUPPORTED;
@@ -106,6 +115,8 @@ struct BwdLayout {
   // readout-side rows (B of them)
   int64_t xt, u16, r16, xt2, z16, hv16, attc16, m1, m2, gz32, graw16, gvraw16, gsmall32, gsmall16, scratch_w;
   int64_t bias_scratch, heads_scratch;
+  int64_t v0, vown, gv0;        // value residual: block 0's values, a block's own values, fp32 gradient of block 0's values
+  int64_t t1_32, t2_32;         // SimBaV2 trunk: fc1 and fc2 outputs (fp32)
   int64_t bytes;
   int64_t Rpad;
   int wmax, ld_graw, ld_gv;
@@ -159,6 +170,16 @@ BwdLayout make_bwd(const Layout& l, int64_t B) {
   w.scratch_w = cv.take((int64_t)d * 64 * 4);
   w.bias_scratch = cv.take((int64_t)wide * 4);
   w.heads_scratch = cv.take((int64_t)l.head_cols_pad * D * 4);
+  w.v0 = w.vown = w.gv0 = w.t1_32 = w.t2_32 = -1;
+  if (l.value_residual && l.L > 1) {
+    w.v0 = cv.take(R * d * 2);
+    w.vown = cv.take(R * d * 2);
+    w.gv0 = cv.take(R * d * 4);
+  }
+  if (l.trunk_v2) {
+    w.t1_32 = cv.take(B * (int64_t)l.Hh * 4);
+    w.t2_32 = cv.take(B * D * 4);
+  }
   w.bytes = cv.off;
   return w;
 }
@@ -353,14 +374,24 @@ struct Bwd {
 
     // ---- recompute the readout side: trunk and critic activations
     BSRL_TRY(linear(linear_args(sv.lead16, kLead * d, c.W(l.trunk_proj), kLead * d, c.Bv(l.trunk_proj), xt, D, 1, 0, B, D, kLead * d), st));
-    BSRL_TRY(layernorm(xt, D, ident, c.G(l.trunk_ln1), c.Be(l.trunk_ln1), eps, B, D, u16, D, st));
-    BSRL_TRY(linear(linear_args(u16, D, c.W(l.trunk_fc1), D, c.Bv(l.trunk_fc1), r16, Hh, 0, 1, B, Hh, D), st));
-    {
+    const float c_alpha = 0.5f * sqrtf((float)D);      // SimBaV2: alpha = trunk_alpha * c_alpha
+    float* t1_32 = l.trunk_v2 ? S<float>(w.t1_32) : nullptr;
+    float* t2_32 = l.trunk_v2 ? S<float>(w.t2_32) : nullptr;
+    if (l.trunk_v2) {
+      // xt = t0 = W_in z; xt2 = x0 = l2n(t0 s_in); t1 = W1 x0; r = relu(t1 s_1); t2 = W2 r; h = sqrt(D) l2n(x0 + a (l2n(t2) - x0))
+      BSRL_TRY(simba2_rows(0, xt, xt2, at<float>(c.arena, l.v2_s_in), 0.f, B, D, u16, D, st));
+      BSRL_TRY(linear(linear_args(u16, D, c.W(l.trunk_fc1), D, c.Bv(l.trunk_fc1), t1_32, Hh, 1, 0, B, Hh, D), st));
+      BSRL_TRY(scale_relu_rows(t1_32, at<float>(c.arena, l.v2_s_1), B, Hh, r16, st));
+      BSRL_TRY(linear(linear_args(r16, Hh, c.W(l.trunk_fc2), Hh, c.Bv(l.trunk_fc2), t2_32, D, 1, 0, B, D, Hh), st));
+      BSRL_TRY(simba2_rows(1, t2_32, xt2, at<float>(c.arena, l.v2_alpha), c_alpha, B, D, z16 + d, ldz, st));
+    } else {
+      BSRL_TRY(layernorm(xt, D, ident, c.G(l.trunk_ln1), c.Be(l.trunk_ln1), eps, B, D, u16, D, st));
+      BSRL_TRY(linear(linear_args(u16, D, c.W(l.trunk_fc1), D, c.Bv(l.trunk_fc1), r16, Hh, 0, 1, B, Hh, D), st));
       LinearArgs p2 = linear_args(r16, Hh, c.W(l.trunk_fc2), Hh, c.Bv(l.trunk_fc2), xt2, D, 1, 0, B, D, Hh);
       p2.R = xt; p2.ldr = D;
       BSRL_TRY(linear(p2, st));
+      BSRL_TRY(layernorm(xt2, D, ident, c.G(l.trunk_ln2), c.Be(l.trunk_ln2), eps, B, D, z16 + d, ldz, st));
     }
-    BSRL_TRY(layernorm(xt2, D, ident, c.G(l.trunk_ln2), c.Be(l.trunk_ln2), eps, B, D, z16 + d, ldz, st));
     BSRL_TRY(layernorm(x_last, d, ident, c.G(l.critic_ln), c.Be(l.critic_ln), eps, R, d, hv, d, st));
     BSRL_TRY(linear(linear_args(hv, d, c.W(l.critic_kv), d, c.Bv(l.critic_kv), qkv + d, 3 * d, 0, 0, R, 2 * d, d), st));
     {
@@ -421,18 +452,55 @@ struct Bwd {
     BSRL_TRY(dgrad(graw, w.ld_graw, B, c.W(l.heads), l.heads.pitch, l.n_head_cols, D, gs32, D, true));   // g_h from the heads
     BSRL_TRY(add_rows32(gz32 + d, ldz, gs32, D, ident, B, D, 1, st));                                     // + the critic's
     float* g_xt2 = gz32;                               // (B, D) f32, reuses the head of g_z (g_a was consumed above)
-    BSRL_TRY(ln_bwd(xt2, D, ident, l.trunk_ln2, "trunk_ln2", gs32, true, D, nullptr, g_xt2, D, ident, B, D));
-    BSRL_TRY(cast16(g_xt2, D, ident, gs16, D, B, D));
-    BSRL_TRY(wgrad(gs16, D, B, D, r16, Hh, ident, Hh, "trunk_fc2"));
-    BSRL_TRY(dgrad(gs16, D, B, c.W(l.trunk_fc2), l.trunk_fc2.pitch, D, Hh, gA, Hh, false));
-    BSRL_TRY(relu_mask16(gA, Hh, r16, Hh, B, Hh, st));
-    BSRL_TRY(wgrad(gA, Hh, B, Hh, u16, D, ident, D, "trunk_fc1"));
-    BSRL_TRY(dgrad(gA, Hh, B, c.W(l.trunk_fc1), l.trunk_fc1.pitch, Hh, D, gs32, D, true));
-    BSRL_TRY(ln_bwd(xt, D, ident, l.trunk_ln1, "trunk_ln1", gs32, true, D, g_xt2, g_xt2, D, ident, B, D));   // g_xt
-    BSRL_TRY(cast16(g_xt2, D, ident, gs16, D, B, D));
-    BSRL_TRY(wgrad(gs16, D, B, D, sv.lead16, kLead * d, ident, kLead * d, "trunk_proj"));
+    if (l.trunk_v2) {
+      // out side: g_x0 (its direct share) -> g_xt2, g_t2 -> gs16, g_alpha; then W2, the scaled ReLU, W1; in side
+      BSRL_TRY(simba2_out_bwd(xt2, t2_32, at<float>(c.arena, l.v2_alpha), c_alpha, gs32, g_xt2, gs16, G("trunk_alpha"), B, D, st));
+      BSRL_TRY(wgrad(gs16, D, B, D, r16, Hh, ident, Hh, "trunk_w2"));
+      BSRL_TRY(dgrad(gs16, D, B, c.W(l.trunk_fc2), l.trunk_fc2.pitch, D, Hh, gA, Hh, false));
+      BSRL_TRY(scale_relu_bwd(gA, t1_32, at<float>(c.arena, l.v2_s_1), G("trunk_s_1"), B, Hh, st));
+      BSRL_TRY(wgrad(gA, Hh, B, Hh, u16, D, ident, D, "trunk_w1"));
+      BSRL_TRY(dgrad(gA, Hh, B, c.W(l.trunk_fc1), l.trunk_fc1.pitch, Hh, D, gs32, D, true));       // g_x0 through W1
+      BSRL_TRY(simba2_in_bwd(xt, at<float>(c.arena, l.v2_s_in), g_xt2, gs32, gs16, G("trunk_s_in"), B, D, st));
+      BSRL_TRY(wgrad(gs16, D, B, D, sv.lead16, kLead * d, ident, kLead * d, "trunk_in"));
+    } else {
+      BSRL_TRY(ln_bwd(xt2, D, ident, l.trunk_ln2, "trunk_ln2", gs32, true, D, nullptr, g_xt2, D, ident, B, D));
+      BSRL_TRY(cast16(g_xt2, D, ident, gs16, D, B, D));
+      BSRL_TRY(wgrad(gs16, D, B, D, r16, Hh, ident, Hh, "trunk_fc2"));
+      BSRL_TRY(dgrad(gs16, D, B, c.W(l.trunk_fc2), l.trunk_fc2.pitch, D, Hh, gA, Hh, false));
+      BSRL_TRY(relu_mask16(gA, Hh, r16, Hh, B, Hh, st));
+      BSRL_TRY(wgrad(gA, Hh, B, Hh, u16, D, ident, D, "trunk_fc1"));
+      BSRL_TRY(dgrad(gA, Hh, B, c.W(l.trunk_fc1), l.trunk_fc1.pitch, Hh, D, gs32, D, true));
+      BSRL_TRY(ln_bwd(xt, D, ident, l.trunk_ln1, "trunk_ln1", gs32, true, D, g_xt2, g_xt2, D, ident, B, D));   // g_xt
+      BSRL_TRY(cast16(g_xt2, D, ident, gs16, D, B, D));
+      BSRL_TRY(wgrad(gs16, D, B, D, sv.lead16, kLead * d, ident, kLead * d, "trunk_proj"));
+    }
     float* g_lead = gs32;                              // (B, 5 d) = (5 B, d) lead rows
     BSRL_TRY(dgrad(gs16, D, B, c.W(l.trunk_proj), l.trunk_proj.pitch, D, kLead * d, g_lead, kLead * d, true));
+
+    // ---- value residual: block 0's values (every later block mixes them in) and the fp32 gradient that flows back to them
+    const bool vres = l.value_residual && l.L > 1;
+    __half* v0 = vres ? S<__half>(w.v0) : nullptr;
+    __half* vown = vres ? S<__half>(w.vown) : nullptr;
+    float* gv0 = vres ? S<float>(w.gv0) : nullptr;
+    if (vres) {
+      const BlockW& b0 = l.blocks[0];
+      BSRL_TRY(layernorm(sv.x[0], d, ident, c.G(b0.ln_attn), c.Be(b0.ln_attn), eps, R, d, h16, d, st));
+      BSRL_TRY(linear(linear_args(h16, d, c.W(b0.qkv, 2 * d), d, c.Bv(b0.qkv, 2 * d), v0, d, 0, 0, R, d, d), st));
+      BSRL_CUDA_OK(cudaMemsetAsync(gv0, 0, (size_t)R * d * 4, st));
+    }
+    // after the projection of block i > 0: keep the block's own values, mix block 0's in (the forward's arithmetic)
+    auto mix_values = [&](int i, __half* vcols, int ld) -> int {
+      if (!vres || i == 0) return BSRL_OK;
+      return vres_mix(vcols, ld, R, d, vown, v0, at<float>(c.arena, l.blocks[i].vres), st);
+    };
+    // after the attention backward of block i: the gradient of the mixed values becomes that of the block's own values
+    // (i > 0; block 0's share collects in gv0), or block 0's own gradient takes the collected share in
+    auto unmix_grads = [&](int i, __half* gvcols, int64_t ld) -> int {
+      if (!vres) return BSRL_OK;
+      if (i == 0) return add_f32_into_f16(gvcols, ld, gv0, R, d, st);
+      const std::string pn = "blocks." + std::to_string(i);
+      return vres_bwd(gvcols, ld, vown, v0, at<float>(c.arena, l.blocks[i].vres), gv0, G(pn + ".vres_a"), G(pn + ".vres_b"), R, d, st);
+    };
 
     // ---- last block, on the lead rows
     {
@@ -446,12 +514,23 @@ struct Bwd {
         pq.amap = lead_rows; pq.cmap = lead_rows;
         BSRL_TRY(linear(pq, st));
       }
+      BSRL_TRY(mix_values(i, qkv + 2 * d, 3 * d));
       BSRL_TRY(attention(qkv, 3 * d, sv.key_bias, B, d, l.H, 0, kLead, att, d, st));
       BSRL_TRY(tail_fwd(i, Rl, x_last, lead_rows, att, x1, h2, hid));
       float* g_x1 = x1 + Rl * d;                       // (Rl, d) f32: the unused upper part of the x1 buffer
+      if (c.cfg->final_ln) {
+        // the readout is final_ln of the block's output rows: recompute them (x2 = x1 + hid W2^T + b2) and take the
+        // readout gradient back through the LayerNorm, in place
+        float* x2 = x1 + 3 * Rl * d;
+        LinearArgs pd = linear_args(hid, F, c.W(b.down), F, c.Bv(b.down), x2, d, 1, 0, Rl, d, F);
+        pd.R = x1; pd.ldr = d;
+        BSRL_TRY(linear(pd, st));
+        BSRL_TRY(ln_bwd(x2, d, ident, l.final_ln, "final_ln", g_lead, true, d, nullptr, g_lead, d, ident, Rl, d));
+      }
       BSRL_TRY(tail_bwd(i, Rl, g_lead, g_x1, x1, h2, hid, att, gA));       // gA: fp16 gradient of the attention output
       __half* gq = gs16;                               // (Rl, d)
       BSRL_TRY(attention29_bwd(qkv, 3 * d, sv.key_bias, B, d, l.H, 0, kLead, gA, d, gq, d, gB, 2 * d, gB + d, 2 * d, st));
+      BSRL_TRY(unmix_grads(i, gB + d, 2 * d));
       BSRL_TRY(to_tX(h16, d, ident, R, d));
       BSRL_TRY(to_tA_slices(gB, 2 * d, R, 2 * d, {{G(p + ".k_proj.bias"), 0, d}, {G(p + ".v_proj.bias"), d, d}}));
       BSRL_TRY(wgrad_t(0, d, d, R, G(p + ".k_proj.weight"), d));
@@ -474,10 +553,12 @@ struct Bwd {
       const float* x_in = sv.x[i];
       BSRL_TRY(layernorm(x_in, d, ident, c.G(b.ln_attn), c.Be(b.ln_attn), eps, R, d, h16, d, st));
       BSRL_TRY(linear(linear_args(h16, d, c.W(b.qkv), d, c.Bv(b.qkv), qkv, 3 * d, 0, 0, R, 3 * d, d), st));
+      BSRL_TRY(mix_values(i, qkv + 2 * d, 3 * d));
       BSRL_TRY(attention(qkv, 3 * d, sv.key_bias, B, d, l.H, 0, kT, att, d, st));
       BSRL_TRY(tail_fwd(i, R, x_in, ident, att, x1, h2, hid));
       BSRL_TRY(tail_bwd(i, R, gx, gx, x1, h2, hid, att, gA, gx16_live));                            // gx: g(x_{i+1}) -> g(x1)
       BSRL_TRY(attention29_bwd(qkv, 3 * d, sv.key_bias, B, d, l.H, 0, kT, gA, d, gB, 3 * d, gB + d, 3 * d, gB + 2 * d, 3 * d, st));
+      BSRL_TRY(unmix_grads(i, gB + 2 * d, 3 * d));
       BSRL_TRY(to_tX(h16, d, ident, R, d));
       BSRL_TRY(to_tA_slices(gB, 3 * d, R, 3 * d, {{G(p + ".q_proj.bias"), 0, d}, {G(p + ".k_proj.bias"), d, d},
                                                  {G(p + ".v_proj.bias"), 2 * d, d}}));
@@ -499,6 +580,13 @@ struct Bwd {
       const RowMap rows{e.group, kT, e.first};
       BSRL_TRY(linear(linear_args(feat, 64, c.W(e.e->l0), e.e->l0.pitch, c.Bv(e.e->l0), hid, d, 0, 1, e.rows, d, 64), st));   // hidden
       BSRL_TRY(cast16(gx, d, rows, gB, d, e.rows, d));                                               // g of this encoder's tokens
+      if (c.cfg->emb_ln) {
+        // tokens = emb_ln(encoder output): recompute the encoder's output rows (fp32) and take g back through the
+        // LayerNorm; the fp16 copy of the result lands in gB again
+        float* pre = x1;                                  // (e.rows, d) f32: the block scratch is free by now
+        BSRL_TRY(linear(linear_args(hid, d, c.W(e.e->l1), e.e->l1.pitch, c.Bv(e.e->l1), pre, d, 1, 0, e.rows, d, d), st));
+        BSRL_TRY(ln_bwd(pre, d, ident, l.emb_ln, "emb_ln", gB, false, d, nullptr, g32, d, ident, e.rows, d, gB));
+      }
       BSRL_TRY(wgrad(gB, d, e.rows, d, hid, d, ident, d, std::string(e.name) + ".2"));
       BSRL_TRY(dgrad(gB, d, e.rows, c.W(e.e->l1), e.e->l1.pitch, d, d, gA, d, false, hid, d));       // through the hidden ReLU
       // first layer: the K-padded (d, 64) product goes to a scratch matrix, its first `in` columns are the gradient

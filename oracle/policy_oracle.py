@@ -325,6 +325,14 @@ def make_upstream(B: int, cfg: PolicyConfig, seed: int):
             "value_logits": 0.2 * torch.randn(B, cfg.value_bins, generator=g) / B}
 
 
+def frozen_params(cfg) -> tuple:
+    """Parameters the reference keeps out of training: the SimBaV2 trunk's three biases are created zero with
+    requires_grad False (python/policy.py:1003-1009), so their gradient is None there."""
+    if cfg.trunk_arch == "simbav2":
+        return ("trunk_in.bias", "trunk_w1.bias", "trunk_w2.bias")
+    return ()
+
+
 def grad_stats(name: str, g):
     """[norm, four fixed random projections] of a gradient tensor, float64; the projection vectors are
     seeded by the parameter's name, so they are the same wherever this runs."""

@@ -39,7 +39,7 @@ CASES = [
 
 
 # cases that also get parameter gradients (name -> batch of the gradient run)
-GRAD_CASES = {"tiny_plain": 48, "tiny_geo_mixed": 40, "cfg1": 64}
+GRAD_CASES = {"tiny_plain": 48, "tiny_geo_mixed": 40, "cfg1": 64, "tiny_options": 44, "tiny_vres": 36, "tiny_simbav2": 52}
 
 
 def case_config(cfg_name, geo, hg, opts=None):

@@ -7,7 +7,8 @@ import torch
 
 from helpers import ROOT, golden_case, po
 
-GRAD_CASES = {"tiny_plain": (48, 21), "tiny_geo_mixed": (40, 22), "cfg1": (64, 0)}   # batch, obs seed of the case
+GRAD_CASES = {"tiny_plain": (48, 21), "tiny_geo_mixed": (40, 22), "cfg1": (64, 0),           # batch, obs seed of the case
+              "tiny_options": (44, 23), "tiny_vres": (36, 24), "tiny_simbav2": (52, 25)}
 
 
 def oracle_grads(cfg, sd, obs, act, up):
@@ -19,7 +20,8 @@ def oracle_grads(cfg, sd, obs, act, up):
         loss = (up["logprob"] * lp).sum() + (up["entropy"] * ent).sum() + (up["value"] * value).sum() \
             + (up["value_logits"] * keep["value_logits"]).sum()
         loss.backward()
-    return {k: (v.grad if v.grad is not None else torch.zeros_like(v)) for k, v in sd_g.items()}, float(loss)
+    frozen = po.frozen_params(cfg)          # no gradient in the reference (requires_grad False)
+    return {k: (v.grad if v.grad is not None and k not in frozen else torch.zeros_like(v)) for k, v in sd_g.items()}, float(loss)
 
 
 def grad_inputs(name):
