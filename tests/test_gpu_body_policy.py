@@ -99,3 +99,41 @@ def test_in_place_weight_refresh():
     l1, _ = m.forward_stacked(obs)
     assert m._arena.data_ptr() == ptr
     torch.testing.assert_close(l1, 2 * l0, atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("B", [1, 5, 131, 700])
+def test_fused_attention_path_batch_invariance_and_masking(B):
+    """33 tokens, head_dim 32: the fused projection + attention kernel.  An env's result does not depend on its
+    position or on the batch size (bit for bit), and absent objects' lanes cannot leak."""
+    cfg = bo.named_config("cfg2")
+    sd = bo.build_state_dict(cfg, 7, xavier=True)
+    m = cuda_body_policy(cfg, sd)
+    obs = bo.make_obs(700, cfg, 11, padded=True)
+    full_l, full_v = m.forward_stacked(obs.cuda())
+    l, v = m.forward_stacked(obs[:B].cuda())
+    assert torch.equal(l, full_l[:B]) and torch.equal(v, full_v[:B])
+    junk = obs[:B].clone()
+    live = junk[:, -cfg.n_obj:]
+    objs = junk[:, cfg.body_dim: cfg.body_dim + cfg.n_obj * cfg.obj_dim].view(B, cfg.n_obj, cfg.obj_dim)
+    objs += (1.0 - live)[:, :, None] * 29.0
+    l2, v2 = m.forward_stacked(junk.cuda())
+    torch.testing.assert_close(l2, l, atol=1e-5, rtol=0)
+    torch.testing.assert_close(v2, v, atol=1e-5, rtol=0)
+
+
+def test_full_size_properties():
+    """65,536 envs of the 33-token configuration: finite outputs, rows re-ordered -> outputs re-ordered bit for bit,
+    and a sample of 512 envs spread over the batch within the gates of the oracle."""
+    cfg = bo.named_config("cfg2")
+    sd = bo.build_state_dict(cfg, 1, xavier=True)
+    m = cuda_body_policy(cfg, sd)
+    B = 65536
+    obs = bo.make_obs(B, cfg, 3, padded=True).cuda()
+    logits, value = m.forward_stacked(obs)
+    assert torch.isfinite(logits).all() and torch.isfinite(value).all()
+    perm = torch.randperm(B, device="cuda", generator=torch.Generator(device="cuda").manual_seed(0))
+    l2, v2 = m.forward_stacked(obs[perm].contiguous())
+    assert torch.equal(l2, logits[perm]) and torch.equal(v2, value[perm])
+    idx = torch.arange(0, B, 128, device="cuda")
+    ref_l, ref_v = bo.forward(sd, cfg, obs[idx].cpu())
+    assert_parity(logits[idx], value[idx], ref_l, ref_v, argmax_min=0.998)
