@@ -138,6 +138,7 @@ _sig = {
                                   C.c_int32, _P, _P, _P, _P, _P]),
     "bsrl_qkv_attention": (C.c_int, [_P, _P, _P, _P, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
     "bsrl_attention": (C.c_int, [_P, _P, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
+    "bsrl_apply_updates_pack": (C.c_int, [_CFG, C.POINTER(_P), C.POINTER(_P), C.c_int32, _P, _P, C.c_int64, _P]),
     "bsrl_linear_ln": (C.c_int, [_P, _P, _P, _P, _P, _P, C.c_float, C.c_int64, C.c_int32, C.c_int32, _P, _P, _P]),
     "bsrl_qkv_attention_body": (C.c_int, [_P, _P, _P, _P, _P, C.c_int64, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
     "bsrl_attention_tokens": (C.c_int, [_P, _P, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P]),

@@ -613,6 +613,33 @@ int bsrl_adam_step_pack(const bsrl_config* cfg, float* const* params, const floa
                     found_inf, arena, as_stream(stream));
 }
 
+int bsrl_apply_updates_pack(const bsrl_config* cfg, float* const* params, const float* const* updates, int32_t n_params,
+                            const float* found_inf, void* arena, int64_t arena_bytes, void* stream) {
+  BSRL_TRY(validate_config(cfg));
+  Layout l = make_layout(*cfg);
+  const int32_t want = (int32_t)make_param_slots(*cfg, l).size();
+  if (!params || !updates || !arena) {
+    set_error("apply_updates_pack: NULL argument");
+    return BSRL_ERR_NULL;
+  }
+  if (n_params != want) {
+    set_error("apply_updates_pack: %d parameters given, %d expected", n_params, want);
+    return BSRL_ERR_SHAPE;
+  }
+  if (arena_bytes < l.bytes || (reinterpret_cast<uintptr_t>(arena) & 255)) {
+    set_error("apply_updates_pack: arena too small (%lld < %lld) or not 256-byte aligned", (long long)arena_bytes, (long long)l.bytes);
+    return BSRL_ERR_WORKSPACE;
+  }
+  for (int32_t i = 0; i < n_params; ++i)
+    if (!params[i]) {
+      set_error("apply_updates_pack: parameter %d is NULL", i);
+      return BSRL_ERR_NULL;
+    }
+  // step 0 + gradients given = additive mode of the pack kernel
+  return multi_pack(*cfg, l, params, updates, nullptr, nullptr, nullptr, nullptr, 0.f, 0.f, 1.f, 0, nullptr, found_inf, arena,
+                    as_stream(stream));
+}
+
 int64_t bsrl_workspace_bytes(const bsrl_config* cfg, int64_t n_envs) {
   if (validate_config(cfg) != BSRL_OK) return -1;
   if (n_envs < 0) return -1;

@@ -13,7 +13,10 @@
 //   g' = g * inv_scale;  p *= 1 - lr wd;  m = b1 m + (1 - b1) g';  v = b2 v + (1 - b2) g'^2
 //   p -= (lr / (1 - b1^t)) m / (sqrt(v) / sqrt(1 - b2^t) + eps)        (torch.optim.AdamW)
 //
-// so the fp16 arena is produced by the optimizer kernel itself and no separate refresh pass runs.
+// so the fp16 arena is produced by the optimizer kernel itself and no separate refresh pass runs.  In additive
+// mode (step = 0 with gradients given) the "gradient" is a finished update and the step is p += u: the last
+// stage of an optimizer whose direction is computed elsewhere (the Muon half of the reference's hybrid optimizer
+// orthogonalises its momentum with a chain of small matrix products first, python/train_batch.py:818-931).
 #include "kernels.cuh"
 #include "layout.h"
 
@@ -44,6 +47,7 @@ struct Table {
   float beta1, beta2, eps, bc1, rsqrt_bc2;   // bias corrections 1 - b1^t and 1 / sqrt(1 - b2^t)
   const float* inv_scale;                    // device scalar multiplying every gradient, or nullptr
   const float* found_inf;                    // device scalar: non-zero = skip every update (scatter still runs)
+  int additive;                              // the gradients are finished updates: p += g
 };
 
 __device__ __forceinline__ void put(uint8_t* arena, int64_t dst, int pitch, int half, int r, int c, int cols, float val) {
@@ -60,7 +64,10 @@ __global__ void __launch_bounds__(256) multi_pack_kernel(const __grid_constant__
   const float step = s.lr / t.bc1, decay = 1.f - s.lr * s.wd;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     float p = s.p[i];
-    if (update) {
+    if (update && t.additive) {
+      p += s.g[i];
+      s.p[i] = p;
+    } else if (update) {
       const float g = s.g[i] * inv_scale;
       const float m = t.beta1 * s.m[i] + (1.f - t.beta1) * g;
       const float v = t.beta2 * s.v[i] + (1.f - t.beta2) * g * g;
@@ -101,6 +108,7 @@ int multi_pack_slots(const std::vector<ParamSlot>& slots, const std::vector<Copy
   t.rsqrt_bc2 = step > 0 ? 1.f / sqrtf(1.f - powf(beta2, (float)step)) : 1.f;
   t.inv_scale = inv_scale;
   t.found_inf = found_inf;
+  t.additive = (step == 0 && grads != nullptr) ? 1 : 0;
   int n_copy = 0;
   int64_t max_elems = 0;
   auto flush = [&]() -> int {
@@ -133,7 +141,7 @@ int multi_pack_slots(const std::vector<ParamSlot>& slots, const std::vector<Copy
     s.g = grads ? grads[i] : nullptr;
     s.m = (s.g && exp_avg) ? exp_avg[i] : nullptr;
     s.v = (s.g && exp_avg_sq) ? exp_avg_sq[i] : nullptr;
-    if (s.g && (!s.m || !s.v)) {
+    if (s.g && !t.additive && (!s.m || !s.v)) {
       set_error("adam_step_pack: parameter %s has a gradient but no optimizer state", ps.name.c_str());
       return BSRL_ERR_NULL;
     }

@@ -122,6 +122,13 @@ int bsrl_adam_step_pack(const bsrl_config* cfg, float* const* params, const floa
                         const float* inv_scale, const float* found_inf, void* arena, int64_t arena_bytes,
                         void* stream);
 
+/* The last stage of an optimizer whose update direction is computed by the caller (the Muon half of the reference's
+ * hybrid optimizer, python/train_batch.py:854-931: momentum, Newton-Schulz orthogonalisation, scale): params[i] +=
+ * updates[i] (fp32, in place; NULL = untouched) and every parameter's places in the arena are rewritten in the same
+ * kernel, as in bsrl_adam_step_pack.  found_inf (device float, may be NULL): non-zero skips the updates. */
+int bsrl_apply_updates_pack(const bsrl_config* cfg, float* const* params, const float* const* updates, int32_t n_params,
+                            const float* found_inf, void* arena, int64_t arena_bytes, void* stream);
+
 /* --- forward -------------------------------------------------------------------- */
 int64_t bsrl_workspace_bytes(const bsrl_config* cfg, int64_t n_envs);
 

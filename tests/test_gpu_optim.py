@@ -111,3 +111,61 @@ def test_update_loop_learns_and_matches_a_torch_trained_twin():
     before = m._arena.clone()
     m.refresh_fp16_caches()
     assert torch.equal(before, m._arena)
+
+
+def test_packed_muon_matches_a_per_matrix_implementation_and_a_repack():
+    """The Muon half: Nesterov momentum -> five Newton-Schulz steps -> RMS-matched scale -> step, against a plain
+    per-matrix fp32 implementation of the same recipe; the arena it leaves equals a full repack; AdamW with
+    ``exclude`` leaves Muon's parameters alone."""
+    import math
+    from beatsaberrl_b200.optim import MUON_NS_COEFS, PackedAdamW, PackedMuon, muon_param_names
+    cfg, sd = golden_case("tiny_plain")
+    m = cuda_policy(cfg, sd)
+    m.flatten_fp16()
+    names = muon_param_names(m)
+    assert "blocks.0.ffn.0.weight" in names and "trunk_fc1.weight" in names and "critic_mlp.0.weight" in names
+    assert not any(n.startswith(("heads.", "note_mlp", "saber_mlp")) or n.endswith(".bias") for n in names)
+    assert f"critic_mlp.{len(m.critic_mlp) - 1}.weight" not in names
+    assert "note_mlp.2.weight" in muon_param_names(m, enc_hidden=True)
+    muon = PackedMuon(m, names, lr=0.02, momentum=0.9)
+    adam = PackedAdamW(m, lr=1e-3, exclude=names)
+    named = dict(m.named_parameters())
+    ref = {n: named[n].detach().clone() for n in names}
+    bufs = {n: torch.zeros_like(ref[n]) for n in names}
+    others = {n: p.detach().clone() for n, p in named.items() if n not in names}
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for step in range(2):
+        for n, p in named.items():
+            p.grad = torch.randn(p.shape, generator=g, device="cuda") * 0.05
+        for n in names:                                  # the recipe, one matrix at a time
+            gr = named[n].grad
+            bufs[n] = 0.9 * bufs[n] + gr
+            u = gr + 0.9 * bufs[n]
+            tall = u.shape[0] > u.shape[1]
+            x = u.t() if tall else u
+            x = x / (x.norm() + 1e-7)
+            for a, b, c in MUON_NS_COEFS:
+                s = x @ x.t()
+                x = a * x + (b * s + c * (s @ s)) @ x
+            x = x.t() if tall else x
+            ref[n] = ref[n] - 0.02 * 0.2 * math.sqrt(max(u.shape)) * x
+        muon.step()
+        for n in names:
+            torch.testing.assert_close(named[n], ref[n], atol=2e-6, rtol=2e-5, msg=lambda s, n=n: f"{n}: {s}")
+        for n, before in others.items():                 # not Muon's: untouched by its step
+            assert torch.equal(named[n], before), n
+    arena = m._arena.clone()
+    m.refresh_fp16_caches()
+    assert torch.equal(arena, m._arena)
+    # the Adam half ignores Muon's parameters and moves the rest
+    snap = {n: p.detach().clone() for n, p in named.items()}
+    adam.step()
+    assert all(torch.equal(named[n], snap[n]) for n in names)
+    assert any(not torch.equal(named[n], snap[n]) for n in others)
+    arena = m._arena.clone()
+    m.refresh_fp16_caches()
+    assert torch.equal(arena, m._arena)
+    sd2 = muon.state_dict()
+    muon2 = PackedMuon(m, names)
+    muon2.load_state_dict(sd2)
+    assert torch.equal(muon2.bufs[0], muon.bufs[0])
