@@ -553,8 +553,18 @@ def run_kernel(args):
         out = torch.empty(envs * 29, d, dtype=torch.float16, device="cuda")
         flops = 2.0 * envs * 29 * 3 * d * d + 4.0 * envs * 29 * 29 * d
         nbytes = envs * 29 * d * 4
+        heads = args.heads or d // 32                       # random weights: the per-group row order does not matter here
         run = lambda: nat.check(nat.lib.bsrl_qkv_attention(h.data_ptr(), w.data_ptr(), bias.data_ptr(), kb.data_ptr(),
-                                                           envs, d, d // 32, 0, 29, out.data_ptr(), st))
+                                                           envs, d, heads, 0, 29, out.data_ptr(), st))
+    elif args.kernel == "linear_ln":      # out-projection + residual + LayerNorm for rows wider than the fused block tail
+        n = k = d
+        a, w, bias = rnd(rows, k).half(), rnd(n, k, scale=k ** -0.5).half(), rnd(n, scale=0.1)
+        res = rnd(rows, n)
+        lg, lb = torch.ones(n).cuda(), torch.zeros(n).cuda()
+        h = torch.empty(rows, n, dtype=torch.float16, device="cuda")
+        flops, nbytes = 2.0 * rows * n * k, rows * (k * 2 + n * 10)
+        run = lambda: nat.check(nat.lib.bsrl_linear_ln(a.data_ptr(), w.data_ptr(), bias.data_ptr(), res.data_ptr(), lg.data_ptr(),
+                                                       lb.data_ptr(), 1e-5, rows, n, k, res.data_ptr(), h.data_ptr(), st))
     elif args.kernel == "layernorm":
         x = rnd(rows, d)
         lg, lb = torch.ones(d).cuda(), torch.zeros(d).cuda()
@@ -674,10 +684,11 @@ def main():
     ap.add_argument("--no-recompute", action="store_true", help="skip the cfg5 PPO-recompute sub-record")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip the reference's GPU stream (1-GPU runs)")
     ap.add_argument("--kernel", default="", choices=("", "block_tail", "attn_block", "linear", "layernorm", "attention", "embed", "head_tail",
-                                                   "attention_tokens", "wgrad", "update"),
+                                                   "attention_tokens", "wgrad", "update", "linear_ln"),
                     help="time one kernel alone on --rows token rows instead of the whole forward")
     ap.add_argument("--rows", type=int, default=237568)
     ap.add_argument("--embed", type=int, default=256)
+    ap.add_argument("--heads", type=int, default=0, help="heads of --kernel attn_block (default embed / 32)")
     ap.add_argument("--cols", type=int, default=0, help="output columns of --kernel linear (default 3 * embed)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
