@@ -123,6 +123,26 @@ def test_recipe_shape_gradients():
     _check_grads(m, ref, "recipe-2blocks", "wide")
 
 
+def test_wide_policy_shape_gradients():
+    """The wide policy's widths (d = 512, eight heads of 64, 7 gears), two blocks: the streamed fused attention and the
+    projection + LayerNorm kernel going forward, head_dim-64 attention backward and 512 / 2048-wide weight gradients
+    coming back, against the gradient oracle."""
+    cfg = make_cfg("cfg4")
+    cfg.n_blocks = 2
+    cfg.__post_init__()
+    sd = po.build_state_dict(cfg, 3)
+    B = 72
+    obs, act, up = po.make_obs(B, 15, padded=True), po.make_actions(B, cfg, 16), po.make_upstream(B, cfg, 17)
+    ref, ref_loss = oracle_grads(cfg, sd, obs, act, up)
+    m = cuda_policy(cfg, sd)
+    with torch.enable_grad():
+        loss = _loss(m, obs.cuda(), act.cuda(), up)
+        loss.backward()
+    assert abs(float(loss) - ref_loss) <= 2e-2 * max(abs(ref_loss), 1e-3)
+    m.check_device()
+    _check_grads(m, ref, "cfg4-2blocks", "wide")
+
+
 # ---- single stages: every backward kernel against torch autograd on identical inputs (no ReLU sign can
 # flip here, so the tolerances are those of fp16 operands with fp32 accumulation)
 import ctypes as C
