@@ -39,8 +39,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn29_kernel(const __half* __rest
 
   for (int64_t pair = (int64_t)blockIdx.x * kWarps + warp; pair < n_pairs;
        pair += (int64_t)gridDim.x * kWarps) {
-    const int64_t env = pair / n_heads;
-    const int head = static_cast<int>(pair % n_heads);
+    int head;
+    const int64_t env = div_index(pair, n_heads, &head);
     const __half* base = qkv + env * tokens * (int64_t)ld + head * DH;
     __syncwarp();
     // stage q (query rows), k, v; rows past the live range are zero
@@ -187,8 +187,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_body_kernel(const __half* __r
   const bool all_rows = n_q == T;
 
   for (int64_t pair = (int64_t)blockIdx.x * WARPS + warp; pair < n_pairs; pair += (int64_t)gridDim.x * WARPS) {
-    const int64_t env = pair / n_heads;
-    const int head = static_cast<int>(pair % n_heads);
+    int head;
+    const int64_t env = div_index(pair, n_heads, &head);
     const __half* base = qkv + env * T * (int64_t)ld + head * DH;
     __syncwarp();
     for (int c = lane; c < NOBJ * CH; c += 32) {
@@ -509,8 +509,9 @@ __global__ void vres_mix_kernel(__half* __restrict__ v, int ld, int64_t rows, in
   const int per_row = d >> 3;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * per_row;
        i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / per_row;
-    const int c = (int)(i % per_row) * 8;
+    int piece;
+    const int64_t row = div_index(i, per_row, &piece);
+    const int c = piece * 8;
     uint4 w = *reinterpret_cast<const uint4*>(v + row * ld + c);
     if (v_out) *reinterpret_cast<uint4*>(v_out + row * d + c) = w;
     if (v0) {

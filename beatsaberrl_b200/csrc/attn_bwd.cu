@@ -46,8 +46,8 @@ __global__ void __launch_bounds__(kWarps * 32) attn_bwd_kernel(const __half* __r
   const int g = lane >> 2, tig = lane & 3;
   const int64_t warps = (int64_t)gridDim.x * kWarps;
   for (int64_t pair = (int64_t)blockIdx.x * kWarps + warp; pair < n_pairs; pair += warps) {
-    const int64_t env = pair / n_heads;
-    const int head = (int)(pair % n_heads);
+    int head;
+    const int64_t env = div_index(pair, n_heads, &head);
     const __half* base = qkv + env * kT * (int64_t)ld + head * DH;
     __syncwarp();
     // stage q, dO (query rows) and k, v (key rows); rows past the live range are zero

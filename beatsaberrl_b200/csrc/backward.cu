@@ -180,8 +180,9 @@ __global__ void __launch_bounds__(256) relu_mask_kernel(__half* __restrict__ g, 
   const int nv = n >> 3;
   const int64_t total = rows * nv;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / nv;
-    const int c = (int)(i % nv) * 8;
+    int piece;
+    const int64_t r = div_index(i, nv, &piece);
+    const int c = piece * 8;
     uint4 gv = *reinterpret_cast<const uint4*>(g + r * ldg + c);
     const uint4 av = *reinterpret_cast<const uint4*>(act + r * lda + c);
     __half* gh = reinterpret_cast<__half*>(&gv);
@@ -199,8 +200,9 @@ __global__ void __launch_bounds__(256) cast_rows16_kernel(const float* __restric
   const int nv = n >> 2;
   const int64_t total = rows * nv;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / nv;
-    const int c = (int)(i % nv) * 4;
+    int piece;
+    const int64_t r = div_index(i, nv, &piece);
+    const int c = piece * 4;
     const float4 v = *reinterpret_cast<const float4*>(in + imap(r) * ldi + c);
     uint2 o;
     o.x = pack_half2(v.x * scale, v.y * scale);
@@ -215,8 +217,9 @@ __global__ void __launch_bounds__(256) add_rows_kernel(const float* __restrict__
   const int nv = n >> 2;
   const int64_t total = rows * nv;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / nv;
-    const int c = (int)(i % nv) * 4;
+    int piece;
+    const int64_t r = div_index(i, nv, &piece);
+    const int c = piece * 4;
     float4 v = *reinterpret_cast<const float4*>(src + r * lds + c);
     float4* o = reinterpret_cast<float4*>(dst + dmap(r) * ldd + c);
     if (accumulate) {

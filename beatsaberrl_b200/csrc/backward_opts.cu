@@ -27,8 +27,9 @@ __global__ void __launch_bounds__(256) vres_bwd_kernel(__half* __restrict__ g, i
   const int per_row = d >> 3;
   float sa = 0.f, sb = 0.f;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * per_row; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / per_row;
-    const int c = (int)(i % per_row) * 8;
+    int piece;
+    const int64_t row = div_index(i, per_row, &piece);
+    const int c = piece * 8;
     uint4 gv = *reinterpret_cast<const uint4*>(g + row * ldg + c);
     const uint4 ov = *reinterpret_cast<const uint4*>(v_own + row * d + c);
     const uint4 zv = *reinterpret_cast<const uint4*>(v0 + row * d + c);
@@ -76,8 +77,9 @@ __global__ void __launch_bounds__(256) add_f32_into_f16_kernel(__half* __restric
                                                                int64_t rows, int d) {
   const int per_row = d >> 2;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * per_row; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / per_row;
-    const int c = (int)(i % per_row) * 4;
+    int piece;
+    const int64_t row = div_index(i, per_row, &piece);
+    const int c = piece * 4;
     const float4 a = *reinterpret_cast<const float4*>(acc + row * d + c);
     uint2 gv = *reinterpret_cast<const uint2*>(g + row * ldg + c);
     const float2 g0 = __half22float2(*reinterpret_cast<const __half2*>(&gv.x)), g1 = __half22float2(*reinterpret_cast<const __half2*>(&gv.y));

@@ -273,7 +273,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         for (int r = lane; r < BM; r += 32) {
           const int64_t row = (int64_t)tn * BM + r;
           if (row < p.M) {
-            const float* xr = p.x + p.xmap(row) * p.ldx;
+            const float* xr = p.x + p.xmap.plain(row) * p.ldx;
             for (int c = 0; c < d; c += 32) prefetch_l2(xr + c);
           }
         }
@@ -406,7 +406,7 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int64_t row = (int64_t)t * BM + q * 32 + i * 8 + sub8;
-        src[i] = row < p.M ? p.x + p.xmap(row) * p.ldx + piece * 4 : nullptr;
+        src[i] = row < p.M ? p.x + p.xmap.plain(row) * p.ldx + piece * 4 : nullptr;
       }
       uint4 nxt[4];
 #pragma unroll

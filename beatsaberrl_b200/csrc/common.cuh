@@ -19,6 +19,20 @@ constexpr int kActHeads = BSRL_N_ACT_HEADS;
 constexpr float kMaskBias = 16384.0f;  // additive key mask magnitude
 constexpr float kMaskedLogit = -1e9f;  // fill of lanes past a head's gear count
 
+// Quotient and remainder of a row or element index (0 <= i) by a small positive divisor.  64-bit integer
+// division is a long software routine on the GPU (~150 cycles per call where a thread needs it before it can do
+// anything else); indices that fit 32 bits -- all of them at the sizes these kernels see -- take the 32-bit
+// unsigned division instead.
+__host__ __device__ __forceinline__ int64_t div_index(int64_t i, int d, int* rem) {
+  if (!((uint64_t)i >> 32)) {
+    const uint32_t q = (uint32_t)i / (uint32_t)d;
+    *rem = (int)((uint32_t)i - q * (uint32_t)d);
+    return (int64_t)q;
+  }
+  *rem = (int)(i % d);
+  return i / d;
+}
+
 // Row remapping of a (rows, ld) matrix: logical row r lives at physical row
 // (r / group) * stride + first + (r % group).  Identity: group = INT_MAX, stride = 0, first = 0.
 struct RowMap {
@@ -26,6 +40,13 @@ struct RowMap {
   int stride;
   int first;
   __host__ __device__ inline int64_t operator()(int64_t r) const {
+    if (r < (int64_t)group) return (int64_t)first + r;      // identity maps and every first group: no division
+    int rem;
+    const int64_t q = div_index(r, group, &rem);
+    return q * (int64_t)stride + first + rem;
+  }
+  // the same map as the plain formula, for cold paths of kernels whose code generation should not move
+  __host__ __device__ inline int64_t plain(int64_t r) const {
     return (r / group) * (int64_t)stride + first + (r % group);
   }
 };

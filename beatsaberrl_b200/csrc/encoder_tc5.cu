@@ -263,8 +263,10 @@ encoder_kernel(const __grid_constant__ Maps m, EncParams p) {
       const int64_t r_tile = (int64_t)(t - (int)pe.tile0) * BM;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const int64_t r = r_tile + q * 32 + i * 4 + sub;
-        orow[i] = r < pe.rows ? ((r / pe.group) * kT + pe.first + (r % pe.group)) * (int64_t)d : -1;
+        const int64_t r = r_tile + q * 32 + i * 4 + sub;      // < 2^31 (checked on the host)
+        int slot;
+        const int64_t env = div_index(r, pe.group, &slot);
+        orow[i] = r < pe.rows ? (env * kT + pe.first + slot) * (int64_t)d : -1;
       }
       // ---- layer 0: relu(acc1 + b0) -> fp16 hidden tile, 64-column chunks signalled as they complete
       if (!mbar_wait_warp(smem_u32(&sh->acc1_full), par, abort)) {

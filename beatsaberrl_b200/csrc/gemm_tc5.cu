@@ -47,6 +47,18 @@ __device__ __forceinline__ void give_up(Shared* sh, int* status, int role) {
   sh->abort = 1;
 }
 
+// work item w = (K split, row tile, column tile), split-major; the tile count fits 31 bits (checked on the host)
+struct WorkItem {
+  int split, mt, nt;
+};
+__device__ __forceinline__ WorkItem work_item(int64_t w, int n_tile_work, int n_tiles) {
+  WorkItem it;
+  int t;
+  it.split = (int)div_index(w, n_tile_work, &t);
+  it.mt = (int)div_index(t, n_tiles, &it.nt);
+  return it;
+}
+
 // HAS_R: a residual is added in the epilogue (its prefetch registers and address arithmetic are compiled
 // out otherwise: they cost the residual-free fp32 epilogue ~15 %).
 template <bool HAS_R>
@@ -97,9 +109,9 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       uint32_t it = 0;
       bool ok = true;
       for (int64_t w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-        const int64_t t = w % n_tile_work;
-        const int kb0 = (int)(w / n_tile_work) * kps, kb1 = min(k_blocks, kb0 + kps);
-        const int m0 = (int)(t / n_tiles) * BM, n0 = (int)(t % n_tiles) * BN;
+        const WorkItem wi = work_item(w, (int)n_tile_work, n_tiles);
+        const int kb0 = wi.split * kps, kb1 = min(k_blocks, kb0 + kps);
+        const int m0 = wi.mt * BM, n0 = wi.nt * BN;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -130,9 +142,9 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
       for (int64_t w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++tile_i) {
-        const int64_t t = w % n_tile_work;
-        const int kb0 = (int)(w / n_tile_work) * kps, kb1 = min(k_blocks, kb0 + kps);
-        const int n0 = (int)(t % n_tiles) * BN;
+        const WorkItem wi = work_item(w, (int)n_tile_work, n_tiles);
+        const int kb0 = wi.split * kps, kb1 = min(k_blocks, kb0 + kps);
+        const int n0 = wi.nt * BN;
         int n_cols = p.N - n0;
         if (n_cols > BN) n_cols = BN;
         const uint32_t idesc = idesc_f16(BM, n_cols, p.a_mn, p.w_mn);
@@ -181,10 +193,10 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     uint32_t tile_i = 0;
     bool ok = true;
     for (int64_t w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++tile_i) {
-      const int64_t t = w % n_tile_work;
+      const WorkItem wi = work_item(w, (int)n_tile_work, n_tiles);
       const bool first_split = w < n_tile_work;              // the piece that carries the bias
-      const int64_t m0 = (t / n_tiles) * BM;
-      const int n0 = (int)(t % n_tiles) * BN;
+      const int64_t m0 = (int64_t)wi.mt * BM;
+      const int n0 = wi.nt * BN;
       const int buf = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
       // output / residual row offsets of the 8 rows this lane writes in the transposed phase

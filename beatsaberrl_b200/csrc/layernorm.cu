@@ -206,7 +206,8 @@ __global__ void scale_relu_kernel(const float* __restrict__ in, const float* __r
   const int per_row = n >> 2;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * per_row;
        i += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(i % per_row);
+    int c;
+    div_index(i, per_row, &c);
     const float4 v = reinterpret_cast<const float4*>(in)[i], sv = reinterpret_cast<const float4*>(s)[c];
     reinterpret_cast<uint2*>(out16)[i] = make_uint2(pack_half2(fmaxf(v.x * sv.x, 0.f), fmaxf(v.y * sv.y, 0.f)),
                                                    pack_half2(fmaxf(v.z * sv.z, 0.f), fmaxf(v.w * sv.w, 0.f)));
