@@ -10,15 +10,18 @@
 // separate LayerNorm pass going through HBM: per token the kernel reads 128 B of features and writes
 // 4d B of x and 2d B of h -- HBM-bound.
 //
-//   warp 0      TMA producer: the feature tile (128 x 64, 128B swizzle) and the weights through a
-//               3-stage ring of (d x 64) tiles: W0, then the d/64 k-blocks of W1 (L2-resident)
-//   warp 1      MMA issuer: acc1 = f W0^T (one k-block, N = d) and acc2 = hid W1^T (d/64 k-blocks), each
-//               k-block of the second GEMM as soon as that 64-column slice of hid is in shared memory
-//   warps 2..9  epilogue, thread = row, two groups of four warps owning half of the columns each:
-//               acc1 -> bias, ReLU, fp16 -> swizzled hid tile; acc2 -> bias -> x and the row statistics,
-//               then a second pass over acc2 for the LayerNorm rows.  Rows leave through a per-warp
-//               transposition buffer as 16-byte stores covering full 128-byte lines of the mapped rows.
-// TMEM: acc1 in columns [0, d), acc2 in [256, 256 + d).  All waits are bounded (tc5.cuh).
+//   warp 0       TMA producer: the feature tile (128 x 64, 128B swizzle) and the weights through a
+//                3-stage ring of (d x 64) tiles: W0, then the d/64 k-blocks of W1 (L2-resident)
+//   warp 1       MMA issuer: acc = f W0^T (one k-block, N = d), then -- once the hidden tile is in shared
+//                memory -- acc = hid W1^T (d/64 k-blocks) over the same TMEM columns
+//   warps 2..5   hidden warps, thread = row: acc -> bias, ReLU, fp16 -> swizzled hid tile
+//   warps 6..13  output warps, thread = row, two groups of four warps owning half of the columns each:
+//                acc -> bias -> x and the row statistics, then a second pass over acc for the LayerNorm
+//                rows.  Rows leave through a per-warp transposition buffer as 16-byte stores covering full
+//                128-byte lines of the mapped rows.
+// TMEM: tile i of a CTA uses columns [256 (i & 1), 256 (i & 1) + d) for both of its accumulators, so the
+// output warps drain tile i while the MMAs and the hidden warps work on tile i + 1: the output phase
+// (HBM stores) is the kernel's period, everything else runs in its shadow.  All waits are bounded (tc5.cuh).
 #include "kernels.cuh"
 #include "tc5.cuh"
 
@@ -31,8 +34,9 @@ constexpr int STAGES = 3, STAGE_BYTES = 32768;
 constexpr int CHUNK_BYTES = BM * 64 * 2;           // one [128 x 64] fp16 swizzled chunk
 constexpr int SA_BYTES = CHUNK_BYTES;              // feature tile
 constexpr int SH_BYTES = 4 * CHUNK_BYTES;          // hidden tile, d <= 256
-constexpr int EPI_WARPS = 8;
-constexpr int THREADS = (2 + EPI_WARPS) * 32;
+constexpr int HID_WARPS = 4, EPI_WARPS = 8;
+constexpr int FIRST_EPI = 2 + HID_WARPS;
+constexpr int THREADS = (2 + HID_WARPS + EPI_WARPS) * 32;
 constexpr int STG_BYTES = 32 * 128;                // per-warp transposition buffer: 32 rows x 128 bytes
 constexpr int PARAM_FLOATS = (2 * 4 + 2) * 256;    // b0[4], b1[4], ln gamma, ln beta
 constexpr int PART_BYTES = 2 * BM * 8;
@@ -42,8 +46,8 @@ constexpr int KERNEL_ID = 4;
 
 struct Shared {
   uint64_t w_full[STAGES], w_empty[STAGES];
-  uint64_t a_full, a_free, acc1_full, acc1_free, acc2_full, acc2_free, mma_done;
-  uint64_t h_ready[4];
+  uint64_t a_full, a_free, h_ready, mma_done;
+  uint64_t acc1_full[2], acc2_full[2], acc_free[2];     // per TMEM half
   uint32_t tmem_base;
   int abort;
 };
@@ -123,17 +127,13 @@ encoder_kernel(const __grid_constant__ Maps m, EncParams p) {
     }
     mbar_init(smem_u32(&sh->a_full), 1);
     mbar_init(smem_u32(&sh->a_free), 1);
-    mbar_init(smem_u32(&sh->acc1_full), 1);
-    mbar_init(smem_u32(&sh->acc1_free), EPI_WARPS);
-    mbar_init(smem_u32(&sh->acc2_full), 1);
-    mbar_init(smem_u32(&sh->acc2_free), EPI_WARPS);
-    mbar_init(smem_u32(&sh->mma_done), 1);
-    // hidden chunk kb is written by the warps of every column group whose half overlaps it
-    for (int kb = 0; kb < 4; ++kb) {
-      const int lo = kb * 64, hi = lo + 64;
-      const int groups = (lo < dh2 ? 1 : 0) + (hi > dh2 ? 1 : 0);
-      mbar_init(smem_u32(&sh->h_ready[kb]), 4 * (groups > 0 ? groups : 1));
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh->acc1_full[b]), 1);
+      mbar_init(smem_u32(&sh->acc2_full[b]), 1);
+      mbar_init(smem_u32(&sh->acc_free[b]), EPI_WARPS);
     }
+    mbar_init(smem_u32(&sh->h_ready), HID_WARPS);
+    mbar_init(smem_u32(&sh->mma_done), 1);
     sh->abort = 0;
     fence_barrier_init();
     tma_prefetch_desc(&m.a);
@@ -205,7 +205,6 @@ encoder_kernel(const __grid_constant__ Maps m, EncParams p) {
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
       const uint32_t idesc = idesc_f16(BM, d);
-      const uint32_t acc1 = tmem_base, acc2 = tmem_base + 256u;
       // one ring stage: four K = 16 MMAs of A chunk x the staged (d x 64) weight tile
       auto kblock = [&](uint32_t a_addr, uint32_t d_tmem, bool acc_first) -> bool {
         const int s = it % STAGES;
@@ -219,65 +218,48 @@ encoder_kernel(const __grid_constant__ Maps m, EncParams p) {
         return true;
       };
       for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_i) {
-        const uint32_t par = tile_i & 1;
+        const uint32_t par = tile_i & 1, b = tile_i & 1, use = (tile_i >> 1) & 1;
+        const uint32_t acc = tmem_base + 256u * b;
         if (!mbar_wait(smem_u32(&sh->a_full), par, abort)) { give_up(sh, p.status, 6); break; }
-        if (!mbar_wait(smem_u32(&sh->acc1_free), par ^ 1, abort)) { give_up(sh, p.status, 7); break; }
+        // this half of TMEM is free once the output warps have drained the tile before last
+        if (!mbar_wait(smem_u32(&sh->acc_free[b]), use ^ 1, abort)) { give_up(sh, p.status, 7); break; }
         tc_fence_after();
-        if (!kblock(sA, acc1, false)) break;
+        if (!kblock(sA, acc, false)) break;
         tc_commit(smem_u32(&sh->a_free));
-        tc_commit(smem_u32(&sh->acc1_full));
-        if (!mbar_wait(smem_u32(&sh->acc2_free), par ^ 1, abort)) { give_up(sh, p.status, 8); break; }
-        for (int kb = 0; kb < KB && ok; ++kb) {
-          if (!mbar_wait(smem_u32(&sh->h_ready[kb]), par, abort)) { give_up(sh, p.status, 9); ok = false; break; }
-          tc_fence_after();
-          ok = kblock(sH + kb * CHUNK_BYTES, acc2, kb != 0);
-        }
-        if (ok) tc_commit(smem_u32(&sh->acc2_full));
+        tc_commit(smem_u32(&sh->acc1_full[b]));
+        // the second GEMM overwrites the first one's accumulator: the hidden warps must have read all of it
+        if (!mbar_wait(smem_u32(&sh->h_ready), par, abort)) { give_up(sh, p.status, 9); break; }
+        tc_fence_after();
+        for (int kb = 0; kb < KB && ok; ++kb) ok = kblock(sH + kb * CHUNK_BYTES, acc, kb != 0);
+        if (ok) tc_commit(smem_u32(&sh->acc2_full[b]));
       }
       tc_commit(smem_u32(&sh->mma_done));
       uint32_t spins = 0;
       while (!mbar_try_wait(smem_u32(&sh->mma_done), 0) && ++spins < kSpinLimit) {}
       if (spins >= kSpinLimit) give_up(sh, p.status, 10);
     }
-  } else {
-    // ------------------------------------------------------------ epilogue warps, thread = row
-    const int grp = (warp - 2) >> 2;
+  } else if (warp < FIRST_EPI) {
+    // ------------------------------------------------------------ hidden warps, thread = row
+    // layer 0: relu(acc + b0) -> the fp16 hidden tile, all d columns of this warp's 32 rows
     const int q = warp & 3;
     const int trow = q * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-    uint8_t* stg = stg_all + (warp - 2) * STG_BYTES;
-    const int sub = lane >> 3, piece = lane & 7;            // transposed phase: row sub + 4 i, 16-byte piece
-    const int c_lo = grp * dh2, c_hi = c_lo + dh2;
     const float4* prm4 = reinterpret_cast<const float4*>(prm);
-    const float4 *P_g = prm4 + 8 * 64, *P_b = prm4 + 9 * 64;
-    const float inv_d = 1.0f / (float)d;
     uint32_t tile_i = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_i) {
-      const uint32_t par = tile_i & 1;
-      const int e = part_of_tile(p, t);
-      const EncPart pe = p.part[e];
-      const float4 *P_b0 = prm4 + e * 64, *P_b1 = prm4 + (4 + e) * 64;
-      // x / h row offsets (elements) of the 8 rows this lane writes in the transposed phase; -1 past the end
-      int64_t orow[8];
-      const int64_t r_tile = (int64_t)(t - (int)pe.tile0) * BM;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int64_t r = r_tile + q * 32 + i * 4 + sub;      // < 2^31 (checked on the host)
-        int slot;
-        const int64_t env = div_index(r, pe.group, &slot);
-        orow[i] = r < pe.rows ? (env * kT + pe.first + slot) * (int64_t)d : -1;
-      }
-      // ---- layer 0: relu(acc1 + b0) -> fp16 hidden tile, 64-column chunks signalled as they complete
-      if (!mbar_wait_warp(smem_u32(&sh->acc1_full), par, abort)) {
+    for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, ++tile_i) {
+      const uint32_t b = tile_i & 1, use = (tile_i >> 1) & 1;
+      const float4* P_b0 = prm4 + part_of_tile(p, t) * 64;
+      // the first GEMM of this tile was issued after the second GEMM of the tile before: its completion also
+      // means that nothing reads the hidden tile any more
+      if (!mbar_wait_warp(smem_u32(&sh->acc1_full[b]), use, abort)) {
         if (lane == 0) give_up(sh, p.status, 11);
         break;
       }
       tc_fence_after();
-      for (int c = c_lo; c < c_hi; c += 32) {
+      for (int c = 0; c < d; c += 32) {
         uint32_t r[32];
         float v[32];
-        tmem_ld32(lane_base + c, r);
+        tmem_ld32(lane_base + 256u * b + c, r);
         tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -288,33 +270,70 @@ encoder_kernel(const __grid_constant__ Maps m, EncParams p) {
           v[4 * j + 3] = fmaxf(__uint_as_float(r[4 * j + 3]) + b0.w, 0.f);
         }
         store_h32(sH_g, trow, c, v);
-        if (((c + 32) & 63) == 0 || c + 32 == c_hi) {       // this thread is done with chunk c / 64
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&sh->h_ready[c >> 6]));
-        }
       }
+      fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sh->acc1_free));
-      // ---- layer 1: tok = acc2 + b1 -> x (fp32), row statistics
-      if (!mbar_wait_warp(smem_u32(&sh->acc2_full), par, abort)) {
+      if (lane == 0) mbar_arrive(smem_u32(&sh->h_ready));
+    }
+  } else {
+    // ------------------------------------------------------------ output warps, thread = row
+    const int ew = warp - FIRST_EPI;
+    const int grp = ew >> 2;
+    const int q = warp & 3;
+    const int trow = q * 32 + lane;
+    const uint32_t lane_q = tmem_base + ((uint32_t)(q * 32) << 16);
+    uint8_t* stg = stg_all + ew * STG_BYTES;
+    const int sub = lane >> 3, piece = lane & 7;            // transposed phase: row sub + 4 i, 16-byte piece
+    const int c_lo = grp * dh2, c_hi = c_lo + dh2;
+    const float4* prm4 = reinterpret_cast<const float4*>(prm);
+    const float4 *P_g = prm4 + 8 * 64, *P_b = prm4 + 9 * 64;
+    const float inv_d = 1.0f / (float)d;
+    uint32_t tile_i = 0;
+    for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, ++tile_i) {
+      const uint32_t b = tile_i & 1, use = (tile_i >> 1) & 1;
+      const uint32_t lane_base = lane_q + 256u * b;
+      const int e = part_of_tile(p, t);
+      const EncPart pe = p.part[e];
+      const float4* P_b1 = prm4 + (4 + e) * 64;
+      // x / h row offsets (elements) of the 8 rows this lane writes in the transposed phase; -1 past the end
+      // (one division per tile, then steps of four rows that jump over the other encoders' slots at an env
+      // boundary: eight 64-bit divisions here cost the epilogue ~2 K cycles per tile)
+      int64_t orow[8];
+      const int64_t r_tile = (int64_t)(t - (int)pe.tile0) * BM;
+      {
+        int slot;
+        const int64_t env = div_index(r_tile + q * 32 + sub, pe.group, &slot);      // rows < 2^31 (checked on the host)
+        int64_t off = (env * kT + pe.first + slot) * (int64_t)d;
+        const int64_t rows_left = pe.rows - (r_tile + q * 32 + sub);
+        const int step4 = 4 * d, jump = (kT - pe.group) * d;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          orow[i] = 4 * i < rows_left ? off : -1;
+          slot += 4;
+          off += step4;
+          while (slot >= pe.group) {
+            slot -= pe.group;
+            off += jump;
+          }
+        }
+      }
+      // ---- layer 1: tok = acc + b1 -> x (fp32), row statistics
+      if (!mbar_wait_warp(smem_u32(&sh->acc2_full[b]), use, abort)) {
         if (lane == 0) give_up(sh, p.status, 12);
         break;
       }
       tc_fence_after();
-      float sum = 0.f, sq = 0.f;
-      for (int c = c_lo; c < c_hi; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + 256u + c, r);
-        tmem_wait_ld();
+      float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f), q4 = s4;      // per-component partial sums: four short chains
+      // 32 accumulator columns -> bias, statistics, fp32 staging block -> 16-byte stores covering full lines
+      auto x_block = [&](const uint32_t (&r)[32], int c) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float4 b1 = P_b1[(c >> 2) + j];
           const float4 v = make_float4(__uint_as_float(r[4 * j]) + b1.x, __uint_as_float(r[4 * j + 1]) + b1.y,
                                        __uint_as_float(r[4 * j + 2]) + b1.z, __uint_as_float(r[4 * j + 3]) + b1.w);
-          sum += (v.x + v.y) + (v.z + v.w);
-          sq = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, sq))));
+          s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
+          q4.x = fmaf(v.x, v.x, q4.x); q4.y = fmaf(v.y, v.y, q4.y); q4.z = fmaf(v.z, v.z, q4.z); q4.w = fmaf(v.w, v.w, q4.w);
           *reinterpret_cast<float4*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
         }
         __syncwarp();
@@ -326,7 +345,14 @@ encoder_kernel(const __grid_constant__ Maps m, EncParams p) {
           *reinterpret_cast<uint4*>(p.x + orow[i] + c + piece * 4) = v;
         }
         __syncwarp();
+      };
+      for (int c = c_lo; c < c_hi; c += 32) {
+        uint32_t r0[32];
+        tmem_ld32(lane_base + c, r0);
+        tmem_wait_ld();
+        x_block(r0, c);
       }
+      const float sum = (s4.x + s4.y) + (s4.z + s4.w), sq = (q4.x + q4.y) + (q4.z + q4.w);
       // ---- block 0's LayerNorm rows (fp16), second pass over the accumulator
       if (p.h) {
         part[grp * BM + trow] = make_float2(sum, sq);
@@ -341,7 +367,7 @@ encoder_kernel(const __grid_constant__ Maps m, EncParams p) {
           for (int s32 = 0; s32 < 64; s32 += 32) {
             if (s32 >= nc) break;
             uint32_t r[32];
-            tmem_ld32(lane_base + 256u + c + s32, r);
+            tmem_ld32(lane_base + c + s32, r);
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {                   // 8 columns -> one 16-byte piece
@@ -374,7 +400,7 @@ encoder_kernel(const __grid_constant__ Maps m, EncParams p) {
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sh->acc2_free));
+      if (lane == 0) mbar_arrive(smem_u32(&sh->acc_free[b]));
     }
   }
 
