@@ -40,6 +40,12 @@ __device__ __forceinline__ float tab(const float* o, int tok, int k) {
   int l = c_lanes.v[tok][k];
   return l >= 0 ? o[l] : (l == -2 ? 1.f : 0.f);
 }
+// the same through a shared-memory copy of the table, for indices that differ between the lanes of a warp
+// (the constant cache serves one address per cycle: 32 lanes with 32 different k take 32 passes)
+__device__ __forceinline__ float tab_s(const float* o, const int16_t (*lanes)[64], int tok, int k) {
+  int l = lanes[tok][k];
+  return l >= 0 ? o[l] : (l == -2 ? 1.f : 0.f);
+}
 
 // 22 geometry lanes of one slot: per hand 7, then per hand 4.  flux: a bar slot (lane 9 > 0.5) is aimed
 // at lanes 12, 13, where it must be crossed (python/policy.py:357-360).
@@ -91,7 +97,12 @@ __global__ void __launch_bounds__(kWarps * 32) embed_gather_kernel(const void* _
                                                                   float z_asinh, EmbedBuffers out) {
   __shared__ float s_obs[kWarps][kObs + 2];
   __shared__ float s_geo[kWarps][kSlots * kGeoFeat];
+  __shared__ int16_t s_lanes[5][64];
+  static_assert(kSaberK == 64 && kTorsoK == 64 && kLegK == 64 && note_k(true) == 64 && note_k(false) == 64,
+                "one lane per feature pair of a 64-wide padded row");
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 5 * 64; i += blockDim.x) s_lanes[i >> 6][i & 63] = c_lanes.v[i >> 6][i & 63];
+  __syncthreads();
   float* o = s_obs[warp];
   float* geo = s_geo[warp];
   for (int64_t env = (int64_t)blockIdx.x * kWarps + warp; env < n_envs;
@@ -114,36 +125,31 @@ __global__ void __launch_bounds__(kWarps * 32) embed_gather_kernel(const void* _
     {
       const int k = lane * 2;
       uint32_t* d;
-      d = reinterpret_cast<uint32_t*>(out.saber + (env * 2 + 0) * out.ks);
-      d[lane] = pack_half2(tab(o, 0, k), tab(o, 0, k + 1));
-      d = reinterpret_cast<uint32_t*>(out.saber + (env * 2 + 1) * out.ks);
-      d[lane] = pack_half2(tab(o, 1, k), tab(o, 1, k + 1));
-      d = reinterpret_cast<uint32_t*>(out.leg + (env * 2 + 0) * out.kl);
-      d[lane] = pack_half2(tab(o, 3, k), tab(o, 3, k + 1));
-      d = reinterpret_cast<uint32_t*>(out.leg + (env * 2 + 1) * out.kl);
-      d[lane] = pack_half2(tab(o, 4, k), tab(o, 4, k + 1));
-      if (lane < out.kt / 2) {
-        d = reinterpret_cast<uint32_t*>(out.torso + env * out.kt);
-        d[lane] = pack_half2(tab(o, 2, k), tab(o, 2, k + 1));
-      }
+      d = reinterpret_cast<uint32_t*>(out.saber + (env * 2 + 0) * kSaberK);
+      d[lane] = pack_half2(tab_s(o, s_lanes, 0, k), tab_s(o, s_lanes, 0, k + 1));
+      d = reinterpret_cast<uint32_t*>(out.saber + (env * 2 + 1) * kSaberK);
+      d[lane] = pack_half2(tab_s(o, s_lanes, 1, k), tab_s(o, s_lanes, 1, k + 1));
+      d = reinterpret_cast<uint32_t*>(out.leg + (env * 2 + 0) * kLegK);
+      d[lane] = pack_half2(tab_s(o, s_lanes, 3, k), tab_s(o, s_lanes, 3, k + 1));
+      d = reinterpret_cast<uint32_t*>(out.leg + (env * 2 + 1) * kLegK);
+      d[lane] = pack_half2(tab_s(o, s_lanes, 4, k), tab_s(o, s_lanes, 4, k + 1));
+      d = reinterpret_cast<uint32_t*>(out.torso + env * kTorsoK);
+      d[lane] = pack_half2(tab_s(o, s_lanes, 2, k), tab_s(o, s_lanes, 2, k + 1));
     }
     __syncwarp();
     // slot rows
     {
-      const int kn = out.kn, kn2 = kn >> 1;
-      uint32_t* d = reinterpret_cast<uint32_t*>(out.note + env * kSlots * kn);
-      for (int i = lane; i < kSlots * kn2; i += 32) {
-        int slot = i / kn2, k = (i % kn2) * 2;
-        float v[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          int kk = k + e;
-          v[e] = kk < kNoteFeat ? o[kOffNotes + slot * kNoteFeat + kk]
-                 : (note_geo && kk < kNoteFeat + kGeoFeat) ? geo[slot * kGeoFeat + kk - kNoteFeat]
-                                                            : 0.f;
-        }
-        d[i] = pack_half2(v[0], v[1]);
-      }
+      // every slot row is 64 features = one lane per pair: obs lanes, then the geometry lanes, then zeros
+      // (the feature counts are even, so a pair never straddles two sources)
+      static_assert(kNoteFeat % 2 == 0 && kGeoFeat % 2 == 0, "feature pairs");
+      uint32_t* d = reinterpret_cast<uint32_t*>(out.note + env * kSlots * 64);
+      const int k = lane * 2;
+      const float* src = k < kNoteFeat ? o + kOffNotes + k
+                         : (note_geo && k < kNoteFeat + kGeoFeat) ? geo + (k - kNoteFeat) : nullptr;
+      const int step = k < kNoteFeat ? kNoteFeat : kGeoFeat;
+#pragma unroll 8
+      for (int slot = 0; slot < kSlots; ++slot)
+        d[slot * 32 + lane] = src ? pack_half2(src[slot * step], src[slot * step + 1]) : 0u;
     }
     if (lane < kT)
       out.key_bias[env * kT + lane] = lane < kLead ? 0.f : (o[kOffMask + lane - kLead] - 1.0f) * kMaskBias;
