@@ -92,7 +92,7 @@ __device__ void slot_geometry(const float* o, int slot, float z_asinh, bool flux
 }
 
 template <bool OBS_F16>
-__global__ void __launch_bounds__(kWarps * 32) embed_gather_kernel(const void* __restrict__ obs_,
+__global__ void __launch_bounds__(kWarps * 32, 4) embed_gather_kernel(const void* __restrict__ obs_,
                                                                   int64_t n_envs, int note_geo,
                                                                   float z_asinh, EmbedBuffers out) {
   __shared__ float s_obs[kWarps][kObs + 2];
