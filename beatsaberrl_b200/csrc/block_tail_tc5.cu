@@ -30,6 +30,8 @@
 //
 // Every wait is bounded (see tc5.cuh); on expiry the status word is set and all roles fall
 // through to the teardown.
+#include <type_traits>
+
 #include "kernels.cuh"
 #include "tc5.cuh"
 
@@ -114,6 +116,25 @@ __device__ __forceinline__ void mma_kblock(uint32_t d_tmem, uint32_t a_addr, uin
     mma_f16_ss(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (acc_first || k) ? 1u : 0u);
   }
 }
+
+// the same four MMAs from ready-made descriptors; `fresh`: the first one overwrites the accumulator
+__device__ __forceinline__ void mma_acc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc)
+      : "memory");
+}
+__device__ __forceinline__ void mma_kblock_desc(uint32_t d_tmem, uint64_t ad, uint64_t bd, uint32_t idesc, bool fresh) {
+  if (fresh) mma_f16_ss(d_tmem, ad, bd, idesc, 0u);
+  else mma_acc(d_tmem, ad, bd, idesc);
+  mma_acc(d_tmem, ad + 2, bd + 2, idesc);
+  mma_acc(d_tmem, ad + 4, bd + 4, idesc);
+  mma_acc(d_tmem, ad + 6, bd + 6, idesc);
+}
+template <int N>
+using StageNo = std::integral_constant<int, N>;
 
 // 32 fp32 values of row `row`, columns [col, col + 32) -> fp16 into a swizzled [128 x 64] chunk set
 __device__ __forceinline__ void store_h32(uint8_t* chunks, int row, int col, const float (&v)[32]) {
@@ -303,6 +324,97 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
         ++it;
         return true;
       };
+      // ---- the widest shape (d = 256, F = 1024: 36 ring stages per tile = 12 whole turns of the ring): every stage's
+      // ring slot and barrier phase are compile-time constants and the operand descriptors are built once.  The
+      // issuing thread is the bottleneck of the chunk loop -- an MMA costs it ~50 cycles, a wait 16, a commit 44 --
+      // and the general loop below spends as much again on index arithmetic and descriptor set-up (chunk loop
+      // replayed without dependencies: 2,960 cycles per chunk with the general loop, 2,280 with this one).
+      if (KB == 4 && NC == 8) {
+        const uint64_t rd0 = smem_desc_sw128(ring), ad0 = smem_desc_sw128(sA), hd0 = smem_desc_sw128(sH);
+        const uint32_t wf0 = smem_u32(&sh->w_full[0]), we0 = smem_u32(&sh->w_empty[0]);
+        constexpr uint64_t kSlot = STAGE_BYTES >> 4, kChunk = CHUNK_BYTES >> 4;   // descriptor address units
+        // wait for ring stage n (tile-relative): slot n % 3, phase (n / 3) & 1
+        auto wait_stage = [&](auto n_) -> bool {
+          constexpr int n = decltype(n_)::value;
+          if (!mbar_wait(wf0 + 8u * (n % 3), (uint32_t)((n / 3) & 1), abort)) { give_up(sh, p.status, 5); return false; }
+          tc_fence_after();
+          return true;
+        };
+        auto release_stage = [&](auto n_) { tc_commit(we0 + 8u * (decltype(n_)::value % 3)); };
+        // FFN-up of one hidden chunk: two stages of two k-blocks each, N = 128
+        auto up = [&](auto n_, uint32_t dst, uint64_t* acc1_bar) -> bool {
+          constexpr int n = decltype(n_)::value;
+          if (!wait_stage(StageNo<n>{})) return false;
+          mma_kblock_desc(dst, ad0, rd0 + kSlot * (n % 3), idesc_h, true);
+          mma_kblock_desc(dst, ad0 + kChunk, rd0 + kSlot * (n % 3) + kChunk, idesc_h, false);
+          release_stage(StageNo<n>{});
+          if (!wait_stage(StageNo<n + 1>{})) return false;
+          mma_kblock_desc(dst, ad0 + 2 * kChunk, rd0 + kSlot * ((n + 1) % 3), idesc_h, false);
+          mma_kblock_desc(dst, ad0 + 3 * kChunk, rd0 + kSlot * ((n + 1) % 3) + kChunk, idesc_h, false);
+          release_stage(StageNo<n + 1>{});
+          tc_commit(smem_u32(acc1_bar));
+          return true;
+        };
+        // FFN-down of one hidden chunk: its two 64-column halves as the epilogue publishes them, N = 256
+        auto down = [&](auto n_, uint32_t xcol, uint32_t hid_par) -> bool {
+          constexpr int n = decltype(n_)::value;
+          if (!mbar_wait(smem_u32(&sh->hid_ready[0]), hid_par, abort)) { give_up(sh, p.status, 9); return false; }
+          if (!wait_stage(StageNo<n>{})) return false;
+          mma_kblock_desc(xcol, hd0, rd0 + kSlot * (n % 3), idesc_d, false);
+          release_stage(StageNo<n>{});
+          tc_commit(smem_u32(&sh->hid_free[0]));
+          if (!mbar_wait(smem_u32(&sh->hid_ready[1]), hid_par, abort)) { give_up(sh, p.status, 9); return false; }
+          if (!wait_stage(StageNo<n + 1>{})) return false;
+          mma_kblock_desc(xcol, hd0 + kChunk, rd0 + kSlot * ((n + 1) % 3), idesc_d, false);
+          release_stage(StageNo<n + 1>{});
+          tc_commit(smem_u32(&sh->hid_free[1]));
+          return true;
+        };
+        for (int t = tile0; t < t_end && ok; t += tstep, ++tile_i) {
+          const uint32_t par = tile_i & 1;
+          const uint32_t xcol = tmem_base + (par ? 256u : 0u);     // region X of this tile
+          const uint32_t acol = tmem_base + (par ? 0u : 256u);     // two hidden-chunk buffers
+          TAIL_WAIT(&sh->a_full, par, 6);
+          TAIL_WAIT(&sh->x_ready, par, 7);
+          tc_fence_after();
+          // x1 = x (pre-stored) + att Wo^T: stages 0..3
+          ok = wait_stage(StageNo<0>{});
+          if (!ok) break;
+          mma_kblock_desc(xcol, ad0, rd0, idesc_d, false);
+          release_stage(StageNo<0>{});
+          ok = wait_stage(StageNo<1>{});
+          if (!ok) break;
+          mma_kblock_desc(xcol, ad0 + kChunk, rd0 + kSlot, idesc_d, false);
+          release_stage(StageNo<1>{});
+          ok = wait_stage(StageNo<2>{});
+          if (!ok) break;
+          mma_kblock_desc(xcol, ad0 + 2 * kChunk, rd0 + 2 * kSlot, idesc_d, false);
+          release_stage(StageNo<2>{});
+          ok = wait_stage(StageNo<3>{});
+          if (!ok) break;
+          mma_kblock_desc(xcol, ad0 + 3 * kChunk, rd0, idesc_d, false);
+          release_stage(StageNo<3>{});
+          commit(&sh->o_done);
+          TAIL_WAIT(&sh->h2_ready, par, 8);
+          tc_fence_after();
+          // hidden chunks 0 and 1: stages 4..7
+          ok = up(StageNo<4>{}, acol, &sh->acc1_full[0]) && up(StageNo<6>{}, acol + HC, &sh->acc1_full[1]);
+          // chunks j = 3 g + {0, 1, 2}: FFN-down of chunk j, then FFN-up of chunk j + 2 (12 stages = 4 turns of the ring
+          // per g: slots and phases repeat); the hidden-chunk barriers complete once per chunk: parity j & 1
+          for (uint32_t g = 0; g < 2 && ok; ++g) {
+            ok = down(StageNo<8>{}, xcol, g & 1) && up(StageNo<10>{}, acol + ((g & 1) ? HC : 0), &sh->acc1_full[g & 1]) &&
+                 down(StageNo<12>{}, xcol, (g & 1) ^ 1) && up(StageNo<14>{}, acol + ((g & 1) ? 0 : HC), &sh->acc1_full[(g & 1) ^ 1]) &&
+                 down(StageNo<16>{}, xcol, g & 1) && up(StageNo<18>{}, acol + ((g & 1) ? HC : 0), &sh->acc1_full[g & 1]);
+          }
+          if (!ok) break;
+          commit(&sh->a_free);                                     // the last reader of h2 (chunk 7's FFN-up) is issued
+          // chunks 6 and 7: FFN-down only, stages 32..35
+          ok = down(StageNo<32>{}, xcol, 0u) && down(StageNo<34>{}, xcol, 1u);
+          if (ok) commit(&sh->x_done);
+          it += 36;
+          n_hid += 8;
+        }
+      } else
       for (int t = tile0; t < t_end && ok; t += tstep, ++tile_i) {
         const uint32_t par = tile_i & 1;
         const uint32_t xcol = tmem_base + (par ? 256u : 0u);     // region X of this tile
