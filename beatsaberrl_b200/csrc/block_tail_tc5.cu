@@ -414,6 +414,84 @@ block_tail_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid_const
           it += 36;
           n_hid += 8;
         }
+      } else if (KB == 3 && NC == 6) {
+        // ---- d = 192, F = 768 (the reference's production width): 27 ring stages per tile = 9 whole turns of the
+        // ring, an odd number: the slots repeat from tile to tile, the phases alternate with the tile's parity
+        const uint64_t rd0 = smem_desc_sw128(ring), ad0 = smem_desc_sw128(sA), hd0 = smem_desc_sw128(sH);
+        const uint32_t wf0 = smem_u32(&sh->w_full[0]), we0 = smem_u32(&sh->w_empty[0]);
+        constexpr uint64_t kSlot = STAGE_BYTES >> 4, kChunk = CHUNK_BYTES >> 4;   // descriptor address units
+        uint32_t flip = 0;                                          // tile parity: phase of stage n is ((n / 3) & 1) ^ flip
+        auto wait_stage = [&](auto n_) -> bool {
+          constexpr int n = decltype(n_)::value;
+          if (!mbar_wait(wf0 + 8u * (n % 3), (uint32_t)((n / 3) & 1) ^ flip, abort)) { give_up(sh, p.status, 5); return false; }
+          tc_fence_after();
+          return true;
+        };
+        auto release_stage = [&](auto n_) { tc_commit(we0 + 8u * (decltype(n_)::value % 3)); };
+        // FFN-up of one hidden chunk: k-blocks 0 and 1 from one stage, k-block 2 from the next, N = 128
+        auto up = [&](auto n_, uint32_t dst, uint64_t* acc1_bar) -> bool {
+          constexpr int n = decltype(n_)::value;
+          if (!wait_stage(StageNo<n>{})) return false;
+          mma_kblock_desc(dst, ad0, rd0 + kSlot * (n % 3), idesc_h, true);
+          mma_kblock_desc(dst, ad0 + kChunk, rd0 + kSlot * (n % 3) + kChunk, idesc_h, false);
+          release_stage(StageNo<n>{});
+          if (!wait_stage(StageNo<n + 1>{})) return false;
+          mma_kblock_desc(dst, ad0 + 2 * kChunk, rd0 + kSlot * ((n + 1) % 3), idesc_h, false);
+          release_stage(StageNo<n + 1>{});
+          tc_commit(smem_u32(acc1_bar));
+          return true;
+        };
+        auto down = [&](auto n_, uint32_t xcol, uint32_t hid_par) -> bool {
+          constexpr int n = decltype(n_)::value;
+          if (!mbar_wait(smem_u32(&sh->hid_ready[0]), hid_par, abort)) { give_up(sh, p.status, 9); return false; }
+          if (!wait_stage(StageNo<n>{})) return false;
+          mma_kblock_desc(xcol, hd0, rd0 + kSlot * (n % 3), idesc_d, false);
+          release_stage(StageNo<n>{});
+          tc_commit(smem_u32(&sh->hid_free[0]));
+          if (!mbar_wait(smem_u32(&sh->hid_ready[1]), hid_par, abort)) { give_up(sh, p.status, 9); return false; }
+          if (!wait_stage(StageNo<n + 1>{})) return false;
+          mma_kblock_desc(xcol, hd0 + kChunk, rd0 + kSlot * ((n + 1) % 3), idesc_d, false);
+          release_stage(StageNo<n + 1>{});
+          tc_commit(smem_u32(&sh->hid_free[1]));
+          return true;
+        };
+        for (int t = tile0; t < t_end && ok; t += tstep, ++tile_i) {
+          const uint32_t par = tile_i & 1;
+          const uint32_t xcol = tmem_base + (par ? 256u : 0u);     // region X of this tile
+          const uint32_t acol = tmem_base + (par ? 0u : 256u);     // two hidden-chunk buffers
+          flip = par;
+          TAIL_WAIT(&sh->a_full, par, 6);
+          TAIL_WAIT(&sh->x_ready, par, 7);
+          tc_fence_after();
+          // x1 = x (pre-stored) + att Wo^T: stages 0..2
+          ok = wait_stage(StageNo<0>{});
+          if (!ok) break;
+          mma_kblock_desc(xcol, ad0, rd0, idesc_d, false);
+          release_stage(StageNo<0>{});
+          ok = wait_stage(StageNo<1>{});
+          if (!ok) break;
+          mma_kblock_desc(xcol, ad0 + kChunk, rd0 + kSlot, idesc_d, false);
+          release_stage(StageNo<1>{});
+          ok = wait_stage(StageNo<2>{});
+          if (!ok) break;
+          mma_kblock_desc(xcol, ad0 + 2 * kChunk, rd0 + 2 * kSlot, idesc_d, false);
+          release_stage(StageNo<2>{});
+          commit(&sh->o_done);
+          TAIL_WAIT(&sh->h2_ready, par, 8);
+          tc_fence_after();
+          // hidden chunks 0 and 1 (stages 3..6), then chunk j's FFN-down and chunk j + 2's FFN-up for j = 0..3
+          // (stages 7..22), then the FFN-down of chunks 4 and 5 (stages 23..26); the hidden-chunk barriers complete
+          // once per chunk, six times per tile: parity j & 1
+          ok = up(StageNo<3>{}, acol, &sh->acc1_full[0]) && up(StageNo<5>{}, acol + HC, &sh->acc1_full[1]) &&
+               down(StageNo<7>{}, xcol, 0u) && up(StageNo<9>{}, acol, &sh->acc1_full[0]) &&
+               down(StageNo<11>{}, xcol, 1u) && up(StageNo<13>{}, acol + HC, &sh->acc1_full[1]) &&
+               down(StageNo<15>{}, xcol, 0u) && up(StageNo<17>{}, acol, &sh->acc1_full[0]) &&
+               down(StageNo<19>{}, xcol, 1u) && up(StageNo<21>{}, acol + HC, &sh->acc1_full[1]);
+          if (!ok) break;
+          commit(&sh->a_free);                                     // the last reader of h2 (chunk 5's FFN-up) is issued
+          ok = down(StageNo<23>{}, xcol, 0u) && down(StageNo<25>{}, xcol, 1u);
+          if (ok) commit(&sh->x_done);
+        }
       } else
       for (int t = tile0; t < t_end && ok; t += tstep, ++tile_i) {
         const uint32_t par = tile_i & 1;
