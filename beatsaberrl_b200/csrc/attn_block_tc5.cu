@@ -418,6 +418,10 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
         kb0 = p.key_bias[env * T] * 1.4426950408889634f;
         kbl = p.key_bias[env * T + 1 + lane] * 1.4426950408889634f;
       }
+      // single-query launches (the critic): lane = key in that row's softmax
+      const bool one_row = !BODY && p.n_q == 1;
+      float kb_row = -INFINITY;
+      if (one_row && lane < NKEYS && env < p.n_envs) kb_row = p.key_bias[env * T + lane] * 1.4426950408889634f;
       for (int g = 0; g < n_groups && ok; ++g, ++gi) {
         const int buf = gi & 1;
         // body token's q0 | k0 | v0 of this warp's head: lanes 0..11 fetch one 16-byte piece each, long before use
@@ -543,6 +547,43 @@ attn_block_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constan
             if (!p.body_only)
               attend_pair<2, DH, LDQ, GD * 2, true>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile,
                                                     env_l * EROWS, hh * (DH / 8), x_lane, kb0, reinterpret_cast<const __half*>(sb + 128));
+          } else if (one_row) {
+            // One query row per env: on the CUDA cores.  A 16-row MMA tile for one row costs the tensor pipe, which
+            // the projection of the next head group shares, 16 warp MMAs of 32 cycles per (env, head); this is ~200
+            // plain instructions (lane = key for the scores, lane = output column for the weighted sum).
+            if (mt_own == 0) {
+              const uint8_t* rows_g = sQ_g + (env_l * EROWS) * LDQ;
+              const uint8_t* qrow = rows_g + p.q_first * LDQ + (hh * DH) * 2;
+              const uint8_t* krow = rows_g + (lane < NKEYS ? lane : 0) * LDQ + (GD + hh * DH) * 2;
+              float sc = 0.f;
+#pragma unroll
+              for (int ch = 0; ch < DH / 8; ++ch) {
+                const uint4 qv = *reinterpret_cast<const uint4*>(qrow + ch * 16);
+                const uint4 kv = *reinterpret_cast<const uint4*>(krow + ch * 16);
+                const __half2* qh = reinterpret_cast<const __half2*>(&qv);
+                const __half2* kh = reinterpret_cast<const __half2*>(&kv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 a = __half22float2(qh[e]), b = __half22float2(kh[e]);
+                  sc = fmaf(a.x, b.x, fmaf(a.y, b.y, sc));
+                }
+              }
+              sc = fmaf(sc, rsqrtf((float)DH) * 1.4426950408889634f, kb_row);      // -inf past the last key
+              const float mx = warp_max(sc);
+              const float pj = ex2_approx(sc - mx);
+              const float inv = rcp_approx(warp_sum(pj));
+              __half* orow = p.out + env * (int64_t)p.ldo + (g * G + hh) * DH;
+#pragma unroll
+              for (int dd = 0; dd < DH; dd += 32) {
+                const int col = dd + lane;
+                const uint8_t* vcol = rows_g + (2 * GD + hh * DH) * 2 + (col < DH ? col : 0) * 2;
+                float acc = 0.f;
+#pragma unroll 8
+                for (int j = 0; j < NKEYS; ++j)
+                  acc = fmaf(__shfl_sync(0xffffffffu, pj, j), __half2float(*reinterpret_cast<const __half*>(vcol + j * LDQ)), acc);
+                if (col < DH) orow[col] = __float2half_rn(acc * inv);
+              }
+            }
           } else {
             if (G == 2 && n_q > 16) attend_pair<2, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * EROWS + mt_own * 16, hh * (DH / 8));
             else if (n_q > 0) attend_pair<1, DH, LDQ, GD * 2>(sq_pair, sk_pair, sv_pair, kb, n_q, out_pair, p.ldo, lane, so_tile, env_l * EROWS + mt_own * 16, hh * (DH / 8));

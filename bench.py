@@ -554,8 +554,9 @@ def run_kernel(args):
         flops = 2.0 * envs * 29 * 3 * d * d + 4.0 * envs * 29 * 29 * d
         nbytes = envs * 29 * d * 4
         heads = args.heads or d // 32                       # random weights: the per-group row order does not matter here
+        n_q = args.nq or 29                                 # 5: the last block's lead rows; 1: the critic's query
         run = lambda: nat.check(nat.lib.bsrl_qkv_attention(h.data_ptr(), w.data_ptr(), bias.data_ptr(), kb.data_ptr(),
-                                                           envs, d, heads, 0, 29, out.data_ptr(), st))
+                                                           envs, d, heads, 0, n_q, out.data_ptr(), st))
     elif args.kernel == "linear_ln":      # out-projection + residual + LayerNorm for rows wider than the fused block tail
         n = k = d
         a, w, bias = rnd(rows, k).half(), rnd(n, k, scale=k ** -0.5).half(), rnd(n, scale=0.1)
@@ -689,6 +690,7 @@ def main():
     ap.add_argument("--rows", type=int, default=237568)
     ap.add_argument("--embed", type=int, default=256)
     ap.add_argument("--heads", type=int, default=0, help="heads of --kernel attn_block (default embed / 32)")
+    ap.add_argument("--nq", type=int, default=0, help="query rows per env of --kernel attn_block (default 29)")
     ap.add_argument("--cols", type=int, default=0, help="output columns of --kernel linear (default 3 * embed)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
