@@ -100,12 +100,13 @@ def test_update_loop_learns_and_matches_a_torch_trained_twin():
         topt.step()
         theirs.append(float(tloss.detach()))
     m.check_device()
-    # the fp32 twin's curve: the same to four digits for the first ten steps, within a few per cent later (rounding
-    # differences grow along a training trajectory), and both end below 55 % of where they started
+    # the fp32 twin's curve: the same to four digits for the first ten steps, within ten per cent later (rounding
+    # differences grow along a training trajectory: 1-3 % by step 30 with the tcgen05 kernels, up to 6 % with the
+    # warp-MMA cross-check engine, whose sums run in another order), and both end below 55 % of where they started
     for a, b in zip(ours[:10], theirs[:10]):
         assert abs(a - b) <= 2e-3 * abs(b), (ours, theirs)
     for a, b in zip(ours, theirs):
-        assert abs(a - b) <= 0.05 * abs(b), (ours, theirs)
+        assert abs(a - b) <= 0.10 * abs(b), (ours, theirs)
     assert ours[-1] < 0.55 * ours[0] and theirs[-1] < 0.55 * theirs[0], (ours, theirs)
     # the fp16 arena the forward reads is the one the optimizer kernel kept in step with the masters
     before = m._arena.clone()
